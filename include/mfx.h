@@ -1,0 +1,115 @@
+/* libmfx — C ABI of the B200 (sm_100a) quantized DiT denoising-step kernels.
+ *
+ * The reference (filipstrand/mflux) has no native boundary of its own: its hot path is a chain of
+ * Python-level MLX calls. Each entry point below replaces one of those calls; the comment above it
+ * names the reference call site (path inside the reference project : line).
+ *
+ * Conventions
+ *  - every pointer is a DEVICE pointer owned by the caller, unless a comment says "host";
+ *  - every call enqueues work on `stream` (a cudaStream_t passed as void*) and returns at once;
+ *  - the return value is 0 (MFX_OK) or a negative mfx_status; nothing throws across this boundary;
+ *  - the library allocates no device memory; shapes and alignments are validated on the host
+ *    before anything is launched;
+ *  - bounded device-side waits report through mfx_poll_device_status() instead of hanging.
+ */
+#ifndef MFX_H_
+#define MFX_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MFX_VERSION 100
+
+typedef enum mfx_status {
+  MFX_OK = 0,
+  MFX_ERR_SHAPE = -1,            /* a size is zero/negative or violates a divisibility rule */
+  MFX_ERR_ALIGN = -2,            /* a pointer or stride is not 16-byte aligned where required */
+  MFX_ERR_UNSUPPORTED_BITS = -3, /* bits not in {4, 8} or group size != 64 */
+  MFX_ERR_DTYPE = -4,            /* dtype code not accepted by this entry point */
+  MFX_ERR_ARCH = -5,             /* current device is not compute capability 10.x */
+  MFX_ERR_CUDA = -6,             /* a CUDA runtime/driver call failed (see mfx_last_cuda_error) */
+  MFX_ERR_NULL = -7,             /* a required pointer is NULL */
+  MFX_ERR_DEVICE_TIMEOUT = -8,   /* a bounded device-side wait gave up (mfx_poll_device_status) */
+  MFX_ERR_TOO_LARGE = -9         /* a size exceeds a documented fixed limit */
+} mfx_status;
+
+typedef enum mfx_dtype { MFX_F32 = 0, MFX_BF16 = 1, MFX_F16 = 2 } mfx_dtype;
+
+/* Quantizer flavour. MFX_QMODE_MLX: the algorithm MLX ships (scale oriented towards the extreme of
+ * larger magnitude and snapped so that 0.0 is exactly representable). MFX_QMODE_DOC: the formula of
+ * MLX's documentation, scale=(max-min)/(2^bits-1), bias=min. */
+typedef enum mfx_qmode { MFX_QMODE_MLX = 0, MFX_QMODE_DOC = 1 } mfx_qmode;
+
+/* Epilogues fused into the quantized matmul (v = acc + bias). */
+typedef enum mfx_epilogue {
+  MFX_EPI_NONE = 0,          /* y = v */
+  MFX_EPI_GELU_ERF = 1,      /* y = gelu(v), erf form        (mlx.nn.gelu) */
+  MFX_EPI_GELU_TANH = 2,     /* y = gelu(v), tanh form       (mlx.nn.gelu_approx) */
+  MFX_EPI_GATE_RESIDUAL = 3, /* y = residual + gate[sample] * v */
+  MFX_EPI_SILU = 4           /* y = v * sigmoid(v) */
+} mfx_epilogue;
+
+int mfx_version(void);
+const char* mfx_status_str(int status);
+/* Text of the last CUDA error this library saw on the calling thread ("" if none). */
+const char* mfx_last_cuda_error(void);
+/* Reads and clears the device status word written by bounded waits. *status_out = 0 when clean,
+ * else a positive code naming the wait that gave up. Synchronises `stream`. */
+int mfx_poll_device_status(int* status_out, void* stream);
+
+/* Replaces mx.quantize(w, group_size=64, bits) as reached through mlx.nn.quantize from
+ * src/mflux/models/common/weights/loading/weight_applier.py:93-103.
+ * w [N, K] row-major (w_dtype) -> wq uint32 [N, K*bits/32], scales/biases [N, K/64] in w_dtype. */
+int mfx_quantize_affine(const void* w, int w_dtype, int64_t N, int64_t K, int bits, int group_size, int qmode,
+                        uint32_t* wq, void* scales, void* biases, void* stream);
+
+/* Replaces mx.dequantize (used when a quantized layer is read back as dense weights, e.g. LoRA baking,
+ * src/mflux/models/common/lora/mapping/lora_saver.py). out [N, K] in out_dtype = q*scale + bias. */
+int mfx_dequantize_affine(const uint32_t* wq, const void* scales, const void* biases, int sb_dtype, int64_t N,
+                          int64_t K, int bits, int group_size, void* out, int out_dtype, void* stream);
+
+/* Replaces mlx.nn.QuantizedLinear.__call__ = mx.quantized_matmul(x, w, scales, biases, transpose=True,
+ * group_size=64, bits) + bias, i.e. every nn.Linear of the transformer blocks, e.g.
+ * src/mflux/models/flux/model/flux_transformer/joint_attention.py:14-21, feed_forward.py:8-9,
+ * single_transformer_block.py:14-15.
+ * y[M, N] = x[M, K] . dequant(wq)^T + bias.  x bf16 with row stride ldx (elements, multiple of 8);
+ * y bf16 or f32 with row stride ldy; bias nullable. K % 64 == 0, N % 8 == 0. */
+int mfx_qlinear(const void* x, int64_t M, int64_t K, int64_t ldx, const uint32_t* wq, const void* scales,
+                const void* biases, int sb_dtype, int64_t N, int bits, int group_size, const void* bias,
+                int bias_dtype, void* y, int y_dtype, int64_t ldy, void* stream);
+
+/* Strided, batched form with fused epilogues. The activations are `batch` samples of `rows` rows:
+ * element (b, r, k) at x + b*x_batch_stride + r*x_row_stride + k; y and residual likewise; gate is
+ * [batch, N] with gate_batch_stride. This lets the joint text+image blocks read/write slices of one
+ * sequence buffer without concatenation copies (joint_attention.py:57-60,75-79) and fuses the gated
+ * residual of joint_transformer_block.py:84-90 / single_transformer_block.py:45,56-57. */
+typedef struct mfx_qlinear_args {
+  const void* x;            /* bf16 */
+  int64_t x_row_stride, x_batch_stride;
+  int64_t rows, batch, K, N;
+  const uint32_t* wq;
+  const void* scales;
+  const void* biases;
+  int sb_dtype, bits, group_size;
+  const void* bias;         /* nullable, [N] */
+  int bias_dtype;
+  int epilogue;             /* mfx_epilogue */
+  const void* gate;         /* [batch, N], required for MFX_EPI_GATE_RESIDUAL */
+  int gate_dtype;
+  int64_t gate_batch_stride;
+  const void* residual;     /* same dtype as y, required for MFX_EPI_GATE_RESIDUAL */
+  int64_t res_row_stride, res_batch_stride;
+  void* y;
+  int y_dtype;              /* MFX_BF16 or MFX_F32 */
+  int64_t y_row_stride, y_batch_stride;
+} mfx_qlinear_args;
+int mfx_qlinear_ex(const mfx_qlinear_args* args /* host */, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MFX_H_ */

@@ -1,0 +1,113 @@
+"""ctypes binding of libmfx.so, the C-ABI library declared in include/mfx.h.
+
+There is no fallback: if the shared library has not been built (python -m mflux_b200.build) every
+operation raises. Status codes are turned into ValueError (caller mistakes: shapes, dtypes,
+alignment) or RuntimeError (device / CUDA failures), mirroring how the reference surfaces MLX
+errors as Python exceptions.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_int, c_int64, c_void_p
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libmfx.so"
+
+# mfx_dtype
+F32, BF16, F16 = 0, 1, 2
+# mfx_qmode
+QMODE_MLX, QMODE_DOC = 0, 1
+# mfx_epilogue
+EPI_NONE, EPI_GELU_ERF, EPI_GELU_TANH, EPI_GATE_RESIDUAL, EPI_SILU = 0, 1, 2, 3, 4
+
+_VALUE_ERRORS = {-1, -2, -3, -4, -7, -9}
+
+
+class QLinearArgs(ctypes.Structure):
+    """struct mfx_qlinear_args (include/mfx.h)."""
+
+    _fields_ = [
+        ("x", c_void_p),
+        ("x_row_stride", c_int64),
+        ("x_batch_stride", c_int64),
+        ("rows", c_int64),
+        ("batch", c_int64),
+        ("K", c_int64),
+        ("N", c_int64),
+        ("wq", c_void_p),
+        ("scales", c_void_p),
+        ("biases", c_void_p),
+        ("sb_dtype", c_int),
+        ("bits", c_int),
+        ("group_size", c_int),
+        ("bias", c_void_p),
+        ("bias_dtype", c_int),
+        ("epilogue", c_int),
+        ("gate", c_void_p),
+        ("gate_dtype", c_int),
+        ("gate_batch_stride", c_int64),
+        ("residual", c_void_p),
+        ("res_row_stride", c_int64),
+        ("res_batch_stride", c_int64),
+        ("y", c_void_p),
+        ("y_dtype", c_int),
+        ("y_row_stride", c_int64),
+        ("y_batch_stride", c_int64),
+    ]
+
+
+# name -> (restype, argtypes); every symbol include/mfx.h declares
+SIGNATURES = {
+    "mfx_version": (c_int, []),
+    "mfx_status_str": (c_char_p, [c_int]),
+    "mfx_last_cuda_error": (c_char_p, []),
+    "mfx_poll_device_status": (c_int, [ctypes.POINTER(c_int), c_void_p]),
+    "mfx_quantize_affine": (
+        c_int,
+        [c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+    ),
+    "mfx_dequantize_affine": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_void_p, c_int, c_void_p],
+    ),
+    "mfx_qlinear": (
+        c_int,
+        [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int,
+         c_void_p, c_int, c_void_p, c_int, c_int64, c_void_p],
+    ),
+    "mfx_qlinear_ex": (c_int, [ctypes.POINTER(QLinearArgs), c_void_p]),
+}
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load libmfx.so once; raise loudly when it is missing."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: the CUDA library has not been built. "
+            "Run `python -m mflux_b200.build` (needs nvcc; no GPU needed to build). There is no CPU fallback."
+        )
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def check(status: int, what: str) -> None:
+    """Raise the Python exception that corresponds to a negative mfx_status."""
+    if status == 0:
+        return
+    lib = load()
+    msg = lib.mfx_status_str(status).decode()
+    detail = lib.mfx_last_cuda_error().decode() if status == -6 else ""
+    text = f"{what}: {msg}" + (f" [{detail}]" if detail else "")
+    if status in _VALUE_ERRORS:
+        raise ValueError(text)
+    raise RuntimeError(text)

@@ -1,0 +1,24 @@
+// Entry points that span several translation units.
+#include "host_util.cuh"
+
+namespace mfx {
+namespace qmm {
+int read_status(int* out, cudaStream_t stream);
+}
+}  // namespace mfx
+
+extern "C" {
+
+int mfx_poll_device_status(int* status_out, void* stream) {
+  if (!status_out) return MFX_ERR_NULL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int v = 0;
+  if (mfx::qmm::read_status(&v, st) != 0) {
+    mfx::set_cuda_error_text("reading the device status word failed");
+    return MFX_ERR_CUDA;
+  }
+  *status_out = v;
+  return v == 0 ? MFX_OK : MFX_ERR_DEVICE_TIMEOUT;
+}
+
+}  // extern "C"

@@ -1,0 +1,599 @@
+// Quantized linear layer  Y[M,N] = X[M,K] . dequant(Wq[N,K])^T + bias  for large M (tensor-core bound).
+//
+// Replaces mlx.nn.QuantizedLinear.__call__ -> mx.quantized_matmul(x, w, scales, biases, transpose=True,
+// group_size=64, bits) for every nn.Linear of the transformer blocks of the reference
+// (e.g. src/mflux/models/flux/model/flux_transformer/joint_attention.py:14-21, feed_forward.py:8-9).
+//
+// One persistent CTA per SM, 512 threads, warp-specialised:
+//   warp 0      TMA producer: X tile [128 x 64] bf16 (128-byte swizzle) and the packed weight tile
+//               [256 rows x 64 codes] per k-block, 64 = one quantization group
+//   warp 1      allocates TMEM, issues tcgen05.mma (M=128, N=256, K=16, fp32 accumulate in TMEM)
+//   warps 4-7   epilogue: tcgen05.ld -> bias / activation / gated residual -> global
+//   warps 8-15  dequantizers: packed codes (smem) -> bf16/f16 via exponent-magic + one fma with the
+//               group's scale and bias -> B operand tile in the 128-byte-swizzled K-major layout
+// Two accumulator stages (2 x 256 TMEM columns) let the epilogue of tile i overlap the main loop of
+// tile i+1. All mbarrier waits are bounded.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "host_util.cuh"
+#include "ptx.cuh"
+
+namespace mfx {
+namespace qmm {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int SD = 3;  // stages of the dequantized-weight ring
+constexpr int NUM_THREADS = 512;
+constexpr int NUM_DQ_WARPS = 8;
+constexpr int FIRST_DQ_WARP = 8;
+constexpr int FIRST_EPI_WARP = 4;
+constexpr int X_TILE_BYTES = BM * BK * 2;   // 16 KiB
+constexpr int WD_TILE_BYTES = BN * BK * 2;  // 32 KiB
+constexpr uint32_t TMEM_COLS = 512;
+
+struct Params {
+  int rows, batch, N, K;
+  int tiles_m_per_sample, tiles_m, tiles_n, total_tiles;
+  const void* scales;
+  const void* biases;
+  int sb_dtype;
+  const void* bias;
+  int bias_dtype;
+  int epilogue;
+  const void* gate;
+  int gate_dtype;
+  int64_t gate_batch_stride;
+  const void* residual;
+  int64_t res_row_stride, res_batch_stride;
+  void* y;
+  int64_t y_row_stride, y_batch_stride;
+};
+
+template <int BITS, int ST>
+struct Smem {
+  static constexpr int WQ_TILE_BYTES = BN * BK * BITS / 8;
+  static constexpr int OFF_X = 0;
+  static constexpr int OFF_WD = OFF_X + ST * X_TILE_BYTES;
+  static constexpr int OFF_WQ = OFF_WD + SD * WD_TILE_BYTES;
+  static constexpr int OFF_VEC = OFF_WQ + ST * WQ_TILE_BYTES;  // bias[2][256] + gate[2][256] floats
+  static constexpr int OFF_BAR = OFF_VEC + 4 * BN * 4;
+  static constexpr int NUM_BARS = 2 * ST + 2 * SD + 4;
+  static constexpr int OFF_TMEM = OFF_BAR + NUM_BARS * 8;
+  static constexpr int TOTAL = OFF_TMEM + 16;
+  static constexpr int DYN_BYTES = TOTAL + 1024;  // slack for manual 1024-byte alignment
+};
+
+__device__ __forceinline__ float load_scalar(const void* p, int dtype, int64_t i) {
+  if (dtype == MFX_F32) return __ldg(static_cast<const float*>(p) + i);
+  if (dtype == MFX_BF16) return __bfloat162float(__ldg(static_cast<const __nv_bfloat16*>(p) + i));
+  return __half2float(__ldg(static_cast<const __half*>(p) + i));
+}
+
+template <uint32_t WF>
+__device__ __forceinline__ uint32_t pack_pair(float v) {
+  if (WF == FMT_BF16) {
+    __nv_bfloat162 h = __float2bfloat162_rn(v);
+    return *reinterpret_cast<uint32_t*>(&h);
+  } else {
+    __half2 h = __float2half2_rn(v);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+}
+
+// d = (a - magic) * s + b on packed 16-bit pairs: the subtraction is exact (small integers),
+// the fma rounds once.
+template <uint32_t WF>
+__device__ __forceinline__ uint32_t sub_fma(uint32_t a, uint32_t magic, uint32_t s, uint32_t b) {
+  uint32_t d;
+  if (WF == FMT_BF16) {
+    asm("{\n\t.reg .b32 t;\n\t"
+        "sub.rn.bf16x2 t, %1, %2;\n\t"
+        "fma.rn.bf16x2 %0, t, %3, %4;\n\t}"
+        : "=r"(d)
+        : "r"(a), "r"(magic), "r"(s), "r"(b));
+  } else {
+    asm("{\n\t.reg .b32 t;\n\t"
+        "sub.rn.f16x2 t, %1, %2;\n\t"
+        "fma.rn.f16x2 %0, t, %3, %4;\n\t}"
+        : "=r"(d)
+        : "r"(a), "r"(magic), "r"(s), "r"(b));
+  }
+  return d;
+}
+
+// 8 four-bit codes (one uint32, element j in bits [4j, 4j+4)) -> 8 values in K order.
+template <uint32_t WF>
+__device__ __forceinline__ uint4 dequant_w4(uint32_t q, uint32_t s2, uint32_t b2) {
+  constexpr uint32_t MAGIC = (WF == FMT_BF16) ? 0x43004300u : 0x64006400u;  // 128.0 | 1024.0: ulp 1
+  const uint32_t t0 = (q & 0x000F000Fu) | MAGIC;          // (e0, e4)
+  const uint32_t t1 = ((q >> 4) & 0x000F000Fu) | MAGIC;   // (e1, e5)
+  const uint32_t t2 = ((q >> 8) & 0x000F000Fu) | MAGIC;   // (e2, e6)
+  const uint32_t t3 = ((q >> 12) & 0x000F000Fu) | MAGIC;  // (e3, e7)
+  uint4 r;
+  r.x = sub_fma<WF>(__byte_perm(t0, t1, 0x5410), MAGIC, s2, b2);  // (e0, e1)
+  r.y = sub_fma<WF>(__byte_perm(t2, t3, 0x5410), MAGIC, s2, b2);  // (e2, e3)
+  r.z = sub_fma<WF>(__byte_perm(t0, t1, 0x7632), MAGIC, s2, b2);  // (e4, e5)
+  r.w = sub_fma<WF>(__byte_perm(t2, t3, 0x7632), MAGIC, s2, b2);  // (e6, e7)
+  return r;
+}
+
+// 4 eight-bit codes (one uint32) -> 4 f16 values in K order (codes up to 255 need f16's 10-bit mantissa).
+__device__ __forceinline__ uint2 dequant_w8_f16(uint32_t q, uint32_t s2, uint32_t b2) {
+  constexpr uint32_t MAGIC = 0x64006400u;
+  uint2 r;
+  r.x = sub_fma<FMT_F16>(__byte_perm(q, MAGIC, 0x5150), MAGIC, s2, b2);  // (e0, e1)
+  r.y = sub_fma<FMT_F16>(__byte_perm(q, MAGIC, 0x5352), MAGIC, s2, b2);  // (e2, e3)
+  return r;
+}
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+__device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f)); }
+__device__ __forceinline__ float gelu_tanh(float v) {
+  const float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
+  return 0.5f * v * (1.0f + tanhf(u));
+}
+__device__ __forceinline__ float silu(float v) { return v / (1.0f + __expf(-v)); }
+
+template <int BITS, uint32_t WF, int ST, typename OUT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, const Params p) {
+  using L = Smem<BITS, ST>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+  const uint32_t x_s = smem_base + L::OFF_X;
+  const uint32_t wd_s = smem_base + L::OFF_WD;
+  const uint32_t wq_s = smem_base + L::OFF_WQ;
+  float* vec_s = reinterpret_cast<float*>(smem_gen + L::OFF_VEC);
+  const uint32_t bar0 = smem_base + L::OFF_BAR;
+  auto t_full = [&](int s) { return bar0 + 8u * s; };
+  auto t_empty = [&](int s) { return bar0 + 8u * (ST + s); };
+  auto d_full = [&](int s) { return bar0 + 8u * (2 * ST + s); };
+  auto d_empty = [&](int s) { return bar0 + 8u * (2 * ST + SD + s); };
+  auto acc_full = [&](int s) { return bar0 + 8u * (2 * ST + 2 * SD + s); };
+  auto acc_empty = [&](int s) { return bar0 + 8u * (2 * ST + 2 * SD + 2 + s); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::OFF_TMEM);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_kb = p.K / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < ST; ++s) {
+      mbar_init(t_full(s), 1);
+      mbar_init(t_empty(s), 1 + NUM_DQ_WARPS);
+    }
+    for (int s = 0; s < SD; ++s) {
+      mbar_init(d_full(s), NUM_DQ_WARPS);
+      mbar_init(d_empty(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(acc_full(s), 1);
+      mbar_init(acc_empty(s), 4);
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_x);
+    tma_prefetch_desc(&tmap_w);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_base + L::OFF_TMEM, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (lane 0 issues)
+    int st = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+      const int tm = tile % p.tiles_m;
+      const int tn = tile / p.tiles_m;
+      const int b = tm / p.tiles_m_per_sample;
+      const int r0 = (tm % p.tiles_m_per_sample) * BM;
+      const int n0 = tn * BN;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait(t_empty(st), ph ^ 1u, DEV_TIMEOUT_TMA_EMPTY)) {
+          ok = false;
+          break;
+        }
+        if (lane == 0) {
+          mbar_arrive_expect_tx(t_full(st), X_TILE_BYTES + L::WQ_TILE_BYTES);
+          tma_load_3d(x_s + st * X_TILE_BYTES, &tmap_x, t_full(st), kb * BK, r0, b);
+          tma_load_2d(wq_s + st * L::WQ_TILE_BYTES, &tmap_w, t_full(st), kb * (BK * BITS / 32), n0);
+        }
+        __syncwarp();
+        if (++st == ST) {
+          st = 0;
+          ph ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    constexpr uint32_t IDESC = make_idesc(FMT_BF16, WF, BM, BN);
+    int st = 0, sd = 0;
+    uint32_t ph_t = 0, ph_d = 0;
+    bool ok = true;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++it) {
+      const int a = it & 1;
+      const uint32_t aph = (it >> 1) & 1;
+      if (!mbar_wait(acc_empty(a), aph ^ 1u, DEV_TIMEOUT_ACC_EMPTY)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + a * BN;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait(t_full(st), ph_t, DEV_TIMEOUT_TMA_FULL) || !mbar_wait(d_full(sd), ph_d, DEV_TIMEOUT_DQ_FULL)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint64_t adesc = smem_desc_sw128(x_s + st * X_TILE_BYTES);
+          const uint64_t bdesc = smem_desc_sw128(wd_s + sd * WD_TILE_BYTES);
+#pragma unroll
+          for (int k4 = 0; k4 < BK / 16; ++k4) {
+            // +32 bytes (>>4 = 2) per 16-element K step inside the 128-byte swizzle atom
+            umma_f16_ss(d_tmem, adesc + 2 * k4, bdesc + 2 * k4, IDESC, (kb | k4) != 0 ? 1u : 0u);
+          }
+          umma_commit(t_empty(st));
+          umma_commit(d_empty(sd));
+          if (kb == num_kb - 1) umma_commit(acc_full(a));
+        }
+        __syncwarp();
+        if (++st == ST) {
+          st = 0;
+          ph_t ^= 1u;
+        }
+        if (++sd == SD) {
+          sd = 0;
+          ph_d ^= 1u;
+        }
+      }
+    }
+  } else if (warp >= FIRST_DQ_WARP) {
+    // ------------------------------------------------------------ dequantizers
+    const int row = (warp - FIRST_DQ_WARP) * 32 + lane;  // row of the 256-row weight tile
+    const int groups = num_kb;                            // scales/biases are [N, K/64]
+    constexpr int ROW_BYTES = BK * BITS / 8;              // packed bytes per row per k-block
+    int st = 0, sd = 0;
+    uint32_t ph_t = 0, ph_d = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+      const int tn = tile / p.tiles_m;
+      const int n = tn * BN + row;
+      const bool valid = n < p.N;
+      const int64_t sb_off = static_cast<int64_t>(valid ? n : 0) * groups;
+      float s_next = valid ? load_scalar(p.scales, p.sb_dtype, sb_off) : 0.f;
+      float b_next = valid ? load_scalar(p.biases, p.sb_dtype, sb_off) : 0.f;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const uint32_t s2 = pack_pair<WF>(s_next);
+        const uint32_t b2 = pack_pair<WF>(b_next);
+        if (kb + 1 < num_kb && valid) {
+          s_next = load_scalar(p.scales, p.sb_dtype, sb_off + kb + 1);
+          b_next = load_scalar(p.biases, p.sb_dtype, sb_off + kb + 1);
+        }
+        if (!mbar_wait(t_full(st), ph_t, DEV_TIMEOUT_TMA_FULL) ||
+            !mbar_wait(d_empty(sd), ph_d ^ 1u, DEV_TIMEOUT_DQ_EMPTY)) {
+          ok = false;
+          break;
+        }
+        const uint32_t src = wq_s + st * L::WQ_TILE_BYTES + row * ROW_BYTES;
+        const uint32_t dst = wd_s + sd * WD_TILE_BYTES + row * 128;
+        const uint32_t sw = static_cast<uint32_t>(row & 7);
+        if (BITS == 4) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint4 pk = ld_shared_v4(src + 16 * h);
+            const uint32_t wds[4] = {pk.x, pk.y, pk.z, pk.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t c = static_cast<uint32_t>(h * 4 + j);
+              st_shared_v4(dst + ((c ^ sw) << 4), dequant_w4<WF>(wds[j], s2, b2));
+            }
+          }
+        } else {
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            const uint4 pk = ld_shared_v4(src + 16 * h);
+            const uint2 lo0 = dequant_w8_f16(pk.x, s2, b2);
+            const uint2 hi0 = dequant_w8_f16(pk.y, s2, b2);
+            const uint2 lo1 = dequant_w8_f16(pk.z, s2, b2);
+            const uint2 hi1 = dequant_w8_f16(pk.w, s2, b2);
+            const uint32_t c0 = static_cast<uint32_t>(2 * h), c1 = c0 + 1;
+            st_shared_v4(dst + ((c0 ^ sw) << 4), make_uint4(lo0.x, lo0.y, hi0.x, hi0.y));
+            st_shared_v4(dst + ((c1 ^ sw) << 4), make_uint4(lo1.x, lo1.y, hi1.x, hi1.y));
+          }
+        }
+        fence_proxy_async_smem();  // make these generic-proxy writes visible to the tensor core
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(d_full(sd));
+          mbar_arrive(t_empty(st));
+        }
+        if (++st == ST) {
+          st = 0;
+          ph_t ^= 1u;
+        }
+        if (++sd == SD) {
+          sd = 0;
+          ph_d ^= 1u;
+        }
+      }
+    }
+  } else if (warp >= FIRST_EPI_WARP) {
+    // ------------------------------------------------------------ epilogue
+    const int q = warp & 3;            // TMEM lane quarter this warp may read
+    const int et = threadIdx.x - FIRST_EPI_WARP * 32;  // 0..127
+    const int row = q * 32 + lane;
+    bool ok = true;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++it) {
+      const int a = it & 1;
+      const uint32_t aph = (it >> 1) & 1;
+      const int tm = tile % p.tiles_m;
+      const int tn = tile / p.tiles_m;
+      const int b = tm / p.tiles_m_per_sample;
+      const int r = (tm % p.tiles_m_per_sample) * BM + row;
+      const int n0 = tn * BN;
+      float* bias_s = vec_s + a * BN;
+      float* gate_s = vec_s + 2 * BN + a * BN;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int c = et + 128 * h;
+        const int n = n0 + c;
+        bias_s[c] = (p.bias != nullptr && n < p.N) ? load_scalar(p.bias, p.bias_dtype, n) : 0.f;
+        if (p.epilogue == MFX_EPI_GATE_RESIDUAL)
+          gate_s[c] = (n < p.N) ? load_scalar(p.gate, p.gate_dtype, b * p.gate_batch_stride + n) : 0.f;
+      }
+      named_bar_sync(1, 128);
+      if (!mbar_wait(acc_full(a), aph, DEV_TIMEOUT_ACC_FULL)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const bool row_ok = r < p.rows;
+      OUT* yrow = static_cast<OUT*>(p.y) + b * p.y_batch_stride + static_cast<int64_t>(r) * p.y_row_stride + n0;
+      const OUT* rrow = nullptr;
+      if (p.epilogue == MFX_EPI_GATE_RESIDUAL)
+        rrow = static_cast<const OUT*>(p.residual) + b * p.res_batch_stride +
+               static_cast<int64_t>(r) * p.res_row_stride + n0;
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + a * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t acc[32];
+        tmem_ld_32x32(t_addr + c * 32, acc);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int g8 = 0; g8 < 4; ++g8) {
+            const int col = c * 32 + g8 * 8;
+            if (n0 + col >= p.N) break;
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(acc[g8 * 8 + j]) + bias_s[col + j];
+            if (p.epilogue == MFX_EPI_GELU_ERF) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = gelu_erf(v[j]);
+            } else if (p.epilogue == MFX_EPI_GELU_TANH) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = gelu_tanh(v[j]);
+            } else if (p.epilogue == MFX_EPI_SILU) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = silu(v[j]);
+            } else if (p.epilogue == MFX_EPI_GATE_RESIDUAL) {
+              float rs[8];
+              if constexpr (sizeof(OUT) == 4) {
+                const float4 r0 = *reinterpret_cast<const float4*>(rrow + col);
+                const float4 r1 = *reinterpret_cast<const float4*>(rrow + col + 4);
+                rs[0] = r0.x; rs[1] = r0.y; rs[2] = r0.z; rs[3] = r0.w;
+                rs[4] = r1.x; rs[5] = r1.y; rs[6] = r1.z; rs[7] = r1.w;
+              } else {
+                const uint4 raw = *reinterpret_cast<const uint4*>(rrow + col);
+                const __nv_bfloat16* hb = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) rs[j] = __bfloat162float(hb[j]);
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = rs[j] + gate_s[col + j] * v[j];
+            }
+            if constexpr (sizeof(OUT) == 4) {
+              *reinterpret_cast<float4*>(yrow + col) = make_float4(v[0], v[1], v[2], v[3]);
+              *reinterpret_cast<float4*>(yrow + col + 4) = make_float4(v[4], v[5], v[6], v[7]);
+            } else {
+              __nv_bfloat162 h[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+              *reinterpret_cast<uint4*>(yrow + col) = *reinterpret_cast<uint4*>(h);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty(a));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+MFX_DEFINE_STATUS_READER(read_status)
+
+template <int BITS, uint32_t WF, int ST, typename OUT>
+int launch(const CUtensorMap& tx, const CUtensorMap& tw, const Params& p, int grid, cudaStream_t st) {
+  using L = Smem<BITS, ST>;
+  auto kern = qmm_kernel<BITS, WF, ST, OUT>;
+  static bool configured = false;  // attribute is per function; set once per process and device reuse is fine
+  static int configured_dev = -1;
+  int dev = 0;
+  MFX_CUDA_TRY(cudaGetDevice(&dev));
+  if (!configured || configured_dev != dev) {
+    MFX_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
+    configured = true;
+    configured_dev = dev;
+  }
+  kern<<<grid, NUM_THREADS, L::DYN_BYTES, st>>>(tx, tw, p);
+  MFX_CUDA_TRY(cudaGetLastError());
+  return MFX_OK;
+}
+
+int sm_count() {
+  static int cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+int run(const mfx_qlinear_args& a, cudaStream_t st) {
+  if (!a.x || !a.wq || !a.scales || !a.biases || !a.y) return MFX_ERR_NULL;
+  if ((a.bits != 4 && a.bits != 8) || a.group_size != 64) return MFX_ERR_UNSUPPORTED_BITS;
+  if (a.rows <= 0 || a.batch <= 0 || a.N <= 0 || a.K <= 0) return MFX_ERR_SHAPE;
+  if (a.K % 64 != 0 || a.N % 8 != 0) return MFX_ERR_SHAPE;
+  if (a.rows > (1 << 30) || a.N > (1 << 30) || a.K > (1 << 30) || a.batch > (1 << 20)) return MFX_ERR_TOO_LARGE;
+  if (!valid_dtype(a.sb_dtype)) return MFX_ERR_DTYPE;
+  if (a.bias && !valid_dtype(a.bias_dtype)) return MFX_ERR_DTYPE;
+  if (a.y_dtype != MFX_BF16 && a.y_dtype != MFX_F32) return MFX_ERR_DTYPE;
+  if (a.epilogue < MFX_EPI_NONE || a.epilogue > MFX_EPI_SILU) return MFX_ERR_SHAPE;
+  if (a.epilogue == MFX_EPI_GATE_RESIDUAL) {
+    if (!a.gate || !a.residual) return MFX_ERR_NULL;
+    if (!valid_dtype(a.gate_dtype)) return MFX_ERR_DTYPE;
+    const size_t es = dtype_size(a.y_dtype);
+    if (!aligned16(a.residual) || (a.res_row_stride * es) % 16 != 0 || (a.res_batch_stride * es) % 16 != 0)
+      return MFX_ERR_ALIGN;
+  }
+  {
+    const size_t es = dtype_size(a.y_dtype);
+    if (!aligned16(a.y) || (a.y_row_stride * es) % 16 != 0 || (a.y_batch_stride * es) % 16 != 0)
+      return MFX_ERR_ALIGN;
+    if (!aligned16(a.x) || (a.x_row_stride * 2) % 16 != 0 || (a.x_batch_stride * 2) % 16 != 0 || !aligned16(a.wq))
+      return MFX_ERR_ALIGN;
+  }
+  if (int rc = check_arch()) return rc;
+
+  CUtensorMap tx, tw;
+  {
+    const uint64_t dims[3] = {static_cast<uint64_t>(a.K), static_cast<uint64_t>(a.rows),
+                              static_cast<uint64_t>(a.batch)};
+    // a single sample may carry a zero batch stride; the tensor map still wants a valid (>0) one
+    const uint64_t bstride = a.batch > 1 ? static_cast<uint64_t>(a.x_batch_stride) * 2
+                                         : static_cast<uint64_t>(a.x_row_stride) * 2 * a.rows;
+    const uint64_t strides[2] = {static_cast<uint64_t>(a.x_row_stride) * 2, bstride};
+    const uint32_t box[3] = {BK, BM, 1};
+    if (int rc = encode_tmap(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a.x, dims, strides, box,
+                             CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  }
+  {
+    const uint64_t words_per_row = static_cast<uint64_t>(a.K) * a.bits / 32;
+    const uint64_t dims[2] = {words_per_row, static_cast<uint64_t>(a.N)};
+    const uint64_t strides[1] = {words_per_row * 4};
+    const uint32_t box[2] = {static_cast<uint32_t>(BK * a.bits / 32), BN};
+    if (int rc = encode_tmap(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, a.wq, dims, strides, box,
+                             CU_TENSOR_MAP_SWIZZLE_NONE))
+      return rc;
+  }
+  Params p;
+  p.rows = static_cast<int>(a.rows);
+  p.batch = static_cast<int>(a.batch);
+  p.N = static_cast<int>(a.N);
+  p.K = static_cast<int>(a.K);
+  p.tiles_m_per_sample = static_cast<int>((a.rows + BM - 1) / BM);
+  p.tiles_m = p.tiles_m_per_sample * p.batch;
+  p.tiles_n = static_cast<int>((a.N + BN - 1) / BN);
+  const int64_t total = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
+  if (total > (1ll << 30)) return MFX_ERR_TOO_LARGE;
+  p.total_tiles = static_cast<int>(total);
+  p.scales = a.scales;
+  p.biases = a.biases;
+  p.sb_dtype = a.sb_dtype;
+  p.bias = a.bias;
+  p.bias_dtype = a.bias_dtype;
+  p.epilogue = a.epilogue;
+  p.gate = a.gate;
+  p.gate_dtype = a.gate_dtype;
+  p.gate_batch_stride = a.gate_batch_stride;
+  p.residual = a.residual;
+  p.res_row_stride = a.res_row_stride;
+  p.res_batch_stride = a.res_batch_stride;
+  p.y = a.y;
+  p.y_row_stride = a.y_row_stride;
+  p.y_batch_stride = a.y_batch_stride;
+  const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
+  const bool f32 = a.y_dtype == MFX_F32;
+  if (a.bits == 4) {
+    return f32 ? launch<4, FMT_BF16, 4, float>(tx, tw, p, grid, st)
+               : launch<4, FMT_BF16, 4, __nv_bfloat16>(tx, tw, p, grid, st);
+  }
+  return f32 ? launch<8, FMT_F16, 3, float>(tx, tw, p, grid, st)
+             : launch<8, FMT_F16, 3, __nv_bfloat16>(tx, tw, p, grid, st);
+}
+
+}  // namespace qmm
+}  // namespace mfx
+
+extern "C" {
+
+int mfx_qlinear_ex(const mfx_qlinear_args* args, void* stream) {
+  if (!args) return MFX_ERR_NULL;
+  return mfx::qmm::run(*args, static_cast<cudaStream_t>(stream));
+}
+
+int mfx_qlinear(const void* x, int64_t M, int64_t K, int64_t ldx, const uint32_t* wq, const void* scales,
+                const void* biases, int sb_dtype, int64_t N, int bits, int group_size, const void* bias,
+                int bias_dtype, void* y, int y_dtype, int64_t ldy, void* stream) {
+  mfx_qlinear_args a;
+  memset(&a, 0, sizeof(a));
+  a.x = x;
+  a.x_row_stride = ldx;
+  a.x_batch_stride = 0;
+  a.rows = M;
+  a.batch = 1;
+  a.K = K;
+  a.N = N;
+  a.wq = wq;
+  a.scales = scales;
+  a.biases = biases;
+  a.sb_dtype = sb_dtype;
+  a.bits = bits;
+  a.group_size = group_size;
+  a.bias = bias;
+  a.bias_dtype = bias_dtype;
+  a.epilogue = MFX_EPI_NONE;
+  a.y = y;
+  a.y_dtype = y_dtype;
+  a.y_row_stride = ldy;
+  a.y_batch_stride = 0;
+  return mfx_qlinear_ex(&a, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,163 @@
+"""GPU parity of the quantized linear layer (tcgen05 kernel) through the C ABI.
+
+Tolerance: rel-L2 <= 1e-2 against the float32 oracle (dequantize, then X @ W^T + b in float32),
+the bound the project brief sets for bf16 layer outputs.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import quant
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+def _case(m, n, k, bits, seed, w_dtype=torch.float32, bias=True):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    w = (torch.randn(n, k, generator=g) * 0.02).to(w_dtype)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    b = (torch.randn(n, generator=g) * 0.02).to(w_dtype) if bias else None
+    return w, x, b
+
+
+def _oracle(w, x, b, bits, w_dtype_name):
+    pq, ps, pb = quant.quantize_affine(w, 64, bits, dtype=w_dtype_name)
+    return pq, ps, pb, quant.qlinear(x, pq, ps, pb, b, 64, bits)
+
+
+def _run(w, x, b, bits, **kw):
+    from mflux_b200 import ops
+
+    wq, s, bi = ops.quantize_affine(w.cuda(), 64, bits)
+    y = ops.qlinear(x.cuda(), wq, s, bi, None if b is None else b.cuda(), bits=bits, **kw)
+    torch.cuda.synchronize()
+    assert ops.poll_device_status() == 0
+    return wq, s, bi, y
+
+
+def test_config1_single_linear(lib_built):
+    """M=4096, N=12288, K=3072, W4 g64, fp32 weights, seed 0."""
+    w, x, b = _case(4096, 12288, 3072, 4, 0)
+    pq, ps, pb, ref = _oracle(w, x, b, 4, "f32")
+    wq, s, bi, y = _run(w, x, b, 4)
+    np.testing.assert_array_equal(wq.cpu().numpy(), pq)
+    assert y.dtype == torch.bfloat16 and y.shape == (4096, 12288)
+    err = quant.rel_l2(y, ref)
+    assert err <= TOL, err
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("nk", [(3072, 3072), (9216, 3072), (3072, 12288)])
+@pytest.mark.parametrize("m", [256, 1024])
+def test_sweep_shapes(lib_built, bits, nk, m):
+    n, k = nk
+    w, x, b = _case(m, n, k, bits, hash((bits, n, k, m)) % (2**31), torch.bfloat16)
+    _, _, _, ref = _oracle(w, x, b, bits, "bf16")
+    _, _, _, y = _run(w, x, b, bits)
+    err = quant.rel_l2(y, ref)
+    assert err <= TOL, err
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("mnk", [(1, 64, 64), (7, 8, 128), (129, 264, 192), (300, 1000, 320), (128, 256, 64),
+                                 (513, 520, 3840)])
+def test_ragged_edges(lib_built, bits, mnk):
+    """Row, column and depth tails: M not a multiple of 128, N not a multiple of 256, one k-block."""
+    m, n, k = mnk
+    w, x, b = _case(m, n, k, bits, 100 + m + n + k, torch.bfloat16)
+    _, _, _, ref = _oracle(w, x, b, bits, "bf16")
+    _, _, _, y = _run(w, x, b, bits)
+    err = quant.rel_l2(y, ref)
+    assert err <= TOL, err
+    # fp32 output leaves only the operand rounding
+    _, _, _, y32 = _run(w, x, b, bits, out_dtype=torch.float32)
+    assert quant.rel_l2(y32, ref) <= TOL
+
+
+def test_no_bias_and_canary(lib_built):
+    """Rows/columns beyond the problem must not be written: output padded with a canary."""
+    from mflux_b200 import ops
+
+    m, n, k = 200, 328, 256
+    w, x, _ = _case(m, n, k, 4, 5, torch.bfloat16, bias=False)
+    wq, s, bi = ops.quantize_affine(w.cuda(), 64, 4)
+    buf = torch.full((m + 64, n + 64), 7.0, dtype=torch.bfloat16, device="cuda")
+    out = buf[:m, :n]
+    ops.qlinear(x.cuda(), wq, s, bi, None, bits=4, out=out)
+    torch.cuda.synchronize()
+    assert (buf[m:] == 7.0).all() and (buf[:, n:] == 7.0).all()
+    ref = quant.qlinear(x, wq.cpu().numpy(), s.float().cpu().numpy(), bi.float().cpu().numpy(), None, 64, 4)
+    assert quant.rel_l2(out, ref) <= TOL
+
+
+def test_batched_strided_views(lib_built):
+    """[batch, rows, K] slices of a larger sequence buffer in, slices of another buffer out."""
+    from mflux_b200 import ops
+
+    bsz, s_all, off, rows, k, n = 3, 640, 128, 500, 256, 512
+    g = torch.Generator(device="cpu").manual_seed(9)
+    w = (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16)
+    seq = torch.randn(bsz, s_all, k, generator=g).to(torch.bfloat16)
+    wq, s, bi = ops.quantize_affine(w.cuda(), 64, 4)
+    seq_d = seq.cuda()
+    out_buf = torch.zeros(bsz, s_all, 2 * n, dtype=torch.bfloat16, device="cuda")
+    ops.qlinear(seq_d[:, off:off + rows], wq, s, bi, None, bits=4, out=out_buf[:, off:off + rows, n:])
+    torch.cuda.synchronize()
+    ref = quant.qlinear(seq[:, off:off + rows], wq.cpu().numpy(), s.float().cpu().numpy(),
+                        bi.float().cpu().numpy(), None, 64, 4)
+    assert quant.rel_l2(out_buf[:, off:off + rows, n:], ref) <= TOL
+    assert (out_buf[:, :off] == 0).all() and (out_buf[:, off + rows:] == 0).all() and (out_buf[..., :n] == 0).all()
+
+
+@pytest.mark.parametrize("epi", ["gelu", "gelu_approx", "silu"])
+def test_activation_epilogues(lib_built, epi):
+    m, n, k = 256, 512, 256
+    w, x, b = _case(m, n, k, 4, 21, torch.bfloat16)
+    _, _, _, ref = _oracle(w, x, b, 4, "bf16")
+    t = torch.from_numpy(ref) * 8  # spread the values over the non-linear range
+    _, _, _, y = _run(w * 8, x, b * 8, 4, epilogue=epi, out_dtype=torch.float32)
+    _, _, _, ref8 = _oracle(w * 8, x, b * 8, 4, "bf16")
+    t = torch.from_numpy(ref8)
+    act = {"gelu": torch.nn.functional.gelu(t), "gelu_approx": torch.nn.functional.gelu(t, approximate="tanh"),
+           "silu": torch.nn.functional.silu(t)}[epi]
+    assert quant.rel_l2(y, act.numpy()) <= TOL
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_gate_residual_epilogue(lib_built, dtype):
+    from mflux_b200 import ops
+
+    bsz, rows, k, n = 2, 300, 256, 512
+    g = torch.Generator(device="cpu").manual_seed(33)
+    w = (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16)
+    bias = (torch.randn(n, generator=g) * 0.02).to(torch.bfloat16)
+    x = torch.randn(bsz, rows, k, generator=g).to(torch.bfloat16)
+    gate = torch.randn(bsz, n, generator=g).to(torch.bfloat16)
+    res = torch.randn(bsz, rows, n, generator=g).to(dtype)
+    wq, s, bi = ops.quantize_affine(w.cuda(), 64, 4)
+    y = ops.qlinear(x.cuda(), wq, s, bi, bias.cuda(), bits=4, epilogue="gate_residual", gate=gate.cuda(),
+                    residual=res.cuda())
+    torch.cuda.synchronize()
+    lin = quant.qlinear(x, wq.cpu().numpy(), s.float().cpu().numpy(), bi.float().cpu().numpy(), bias, 64, 4)
+    ref = res.float().numpy() + gate.float().numpy()[:, None, :] * lin
+    assert y.dtype == dtype
+    assert quant.rel_l2(y, ref) <= TOL
+
+
+def test_deterministic_run_to_run(lib_built):
+    w, x, b = _case(512, 768, 512, 4, 77, torch.bfloat16)
+    _, _, _, y1 = _run(w, x, b, 4)
+    _, _, _, y2 = _run(w, x, b, 4)
+    assert torch.equal(y1, y2)
+
+
+def test_rejects_bad_arguments(lib_built):
+    from mflux_b200 import ops
+
+    w, x, b = _case(64, 64, 128, 4, 1, torch.bfloat16)
+    wq, s, bi = ops.quantize_affine(w.cuda(), 64, 4)
+    with pytest.raises(ValueError):
+        ops.qlinear(x.cuda()[:, :64], wq, s, bi, None, bits=4)  # K mismatch
+    with pytest.raises(RuntimeError):
+        ops.qlinear(x, wq, s, bi, None, bits=4)  # CPU tensor
