@@ -72,21 +72,34 @@ int mfx_quantize_affine(const void* w, int w_dtype, int64_t N, int64_t K, int bi
 int mfx_dequantize_affine(const uint32_t* wq, const void* scales, const void* biases, int sb_dtype, int64_t N,
                           int64_t K, int bits, int group_size, void* out, int out_dtype, void* stream);
 
+/* Kernel-side layout of the per-group scales and biases. The matmul kernel streams them with TMA, one
+ * [N]-long row per 64-wide k-block, so it wants them transposed and paired: packed[g*N + n] =
+ * bf16(scales[n, g]) | bf16(biases[n, g]) << 16, g = 0..K/64-1. No counterpart in the reference (MLX
+ * keeps [N, K/64] arrays); callers that keep weights resident pack once and pass `sb_packed`. */
+size_t mfx_qlinear_workspace_bytes(int64_t N, int64_t K, int group_size); /* = N * (K/64) * 4 */
+int mfx_qlinear_pack_scales(const void* scales, const void* biases, int sb_dtype, int64_t N, int64_t K,
+                            int group_size, uint32_t* packed, void* stream);
+
 /* Replaces mlx.nn.QuantizedLinear.__call__ = mx.quantized_matmul(x, w, scales, biases, transpose=True,
  * group_size=64, bits) + bias, i.e. every nn.Linear of the transformer blocks, e.g.
  * src/mflux/models/flux/model/flux_transformer/joint_attention.py:14-21, feed_forward.py:8-9,
  * single_transformer_block.py:14-15.
  * y[M, N] = x[M, K] . dequant(wq)^T + bias.  x bf16 with row stride ldx (elements, multiple of 8);
- * y bf16 or f32 with row stride ldy; bias nullable. K % 64 == 0, N % 8 == 0. */
+ * y bf16 or f32 with row stride ldy; bias nullable. K % 64 == 0, N % 8 == 0.
+ * workspace: caller-owned scratch of mfx_qlinear_workspace_bytes(N, K, 64) bytes, 16-byte aligned; the
+ * call first packs scales/biases into it (see above), then runs the matmul, both on `stream`. */
 int mfx_qlinear(const void* x, int64_t M, int64_t K, int64_t ldx, const uint32_t* wq, const void* scales,
                 const void* biases, int sb_dtype, int64_t N, int bits, int group_size, const void* bias,
-                int bias_dtype, void* y, int y_dtype, int64_t ldy, void* stream);
+                int bias_dtype, void* y, int y_dtype, int64_t ldy, void* workspace, size_t workspace_bytes,
+                void* stream);
 
 /* Strided, batched form with fused epilogues. The activations are `batch` samples of `rows` rows:
  * element (b, r, k) at x + b*x_batch_stride + r*x_row_stride + k; y and residual likewise; gate is
  * [batch, N] with gate_batch_stride. This lets the joint text+image blocks read/write slices of one
  * sequence buffer without concatenation copies (joint_attention.py:57-60,75-79) and fuses the gated
- * residual of joint_transformer_block.py:84-90 / single_transformer_block.py:45,56-57. */
+ * residual of joint_transformer_block.py:84-90 / single_transformer_block.py:45,56-57.
+ * Scales/biases: either `sb_packed` (from mfx_qlinear_pack_scales; then scales/biases may be NULL) or
+ * scales + biases + a workspace as in mfx_qlinear. */
 typedef struct mfx_qlinear_args {
   const void* x;            /* bf16 */
   int64_t x_row_stride, x_batch_stride;
@@ -95,6 +108,9 @@ typedef struct mfx_qlinear_args {
   const void* scales;
   const void* biases;
   int sb_dtype, bits, group_size;
+  const uint32_t* sb_packed; /* nullable */
+  void* workspace;           /* nullable when sb_packed is given */
+  size_t workspace_bytes;
   const void* bias;         /* nullable, [N] */
   int bias_dtype;
   int epilogue;             /* mfx_epilogue */

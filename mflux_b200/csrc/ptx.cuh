@@ -96,6 +96,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int cod
   return false;
 }
 
+// Same, for waits that are off the critical path (a whole main loop, a ring with several free
+// stages): back off with nanosleep so the polling warp leaves the issue slots to the math warps.
+__device__ __forceinline__ bool mbar_wait_sleep(uint32_t bar, uint32_t parity, int code) {
+  for (uint32_t i = 0; i < MFX_SPIN_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(i < 64 ? 32 : 256);
+  }
+  record_failure(code);
+  return false;
+}
+
 // ---------------------------------------------------------------- proxies / fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

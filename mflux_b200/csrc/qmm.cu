@@ -9,7 +9,7 @@
 //               [256 rows x 64 codes] per k-block, 64 = one quantization group
 //   warp 1      allocates TMEM, issues tcgen05.mma (M=128, N=256, K=16, fp32 accumulate in TMEM)
 //   warps 4-7   epilogue: tcgen05.ld -> bias / activation / gated residual -> global
-//   warps 8-15  dequantizers: packed codes (smem) -> bf16/f16 via exponent-magic + one fma with the
+//   warps 8-15  dequantizers: packed codes (smem) -> bf16 via exponent-magic + one fma with the
 //               group's scale and bias -> B operand tile in the 128-byte-swizzled K-major layout
 // Two accumulator stages (2 x 256 TMEM columns) let the epilogue of tile i overlap the main loop of
 // tile i+1. All mbarrier waits are bounded.
@@ -32,14 +32,12 @@ constexpr int FIRST_DQ_WARP = 8;
 constexpr int FIRST_EPI_WARP = 4;
 constexpr int X_TILE_BYTES = BM * BK * 2;   // 16 KiB
 constexpr int WD_TILE_BYTES = BN * BK * 2;  // 32 KiB
+constexpr int SB_TILE_BYTES = BN * 4;         // one bf16 (scale, bias) pair per weight row
 constexpr uint32_t TMEM_COLS = 512;
 
 struct Params {
   int rows, batch, N, K;
   int tiles_m_per_sample, tiles_m, tiles_n, total_tiles;
-  const void* scales;
-  const void* biases;
-  int sb_dtype;
   const void* bias;
   int bias_dtype;
   int epilogue;
@@ -58,7 +56,8 @@ struct Smem {
   static constexpr int OFF_X = 0;
   static constexpr int OFF_WD = OFF_X + ST * X_TILE_BYTES;
   static constexpr int OFF_WQ = OFF_WD + SD * WD_TILE_BYTES;
-  static constexpr int OFF_VEC = OFF_WQ + ST * WQ_TILE_BYTES;  // bias[2][256] + gate[2][256] floats
+  static constexpr int OFF_SB = OFF_WQ + ST * WQ_TILE_BYTES;   // packed (scale, bias) pairs, 256 x 4 B per stage
+  static constexpr int OFF_VEC = OFF_SB + ST * SB_TILE_BYTES;  // bias[2][256] + gate[2][256] floats
   static constexpr int OFF_BAR = OFF_VEC + 4 * BN * 4;
   static constexpr int NUM_BARS = 2 * ST + 2 * SD + 4;
   static constexpr int OFF_TMEM = OFF_BAR + NUM_BARS * 8;
@@ -70,17 +69,6 @@ __device__ __forceinline__ float load_scalar(const void* p, int dtype, int64_t i
   if (dtype == MFX_F32) return __ldg(static_cast<const float*>(p) + i);
   if (dtype == MFX_BF16) return __bfloat162float(__ldg(static_cast<const __nv_bfloat16*>(p) + i));
   return __half2float(__ldg(static_cast<const __half*>(p) + i));
-}
-
-template <uint32_t WF>
-__device__ __forceinline__ uint32_t pack_pair(float v) {
-  if (WF == FMT_BF16) {
-    __nv_bfloat162 h = __float2bfloat162_rn(v);
-    return *reinterpret_cast<uint32_t*>(&h);
-  } else {
-    __half2 h = __float2half2_rn(v);
-    return *reinterpret_cast<uint32_t*>(&h);
-  }
 }
 
 // d = (a - magic) * s + b on packed 16-bit pairs: the subtraction is exact (small integers),
@@ -120,12 +108,28 @@ __device__ __forceinline__ uint4 dequant_w4(uint32_t q, uint32_t s2, uint32_t b2
   return r;
 }
 
-// 4 eight-bit codes (one uint32) -> 4 f16 values in K order (codes up to 255 need f16's 10-bit mantissa).
-__device__ __forceinline__ uint2 dequant_w8_f16(uint32_t q, uint32_t s2, uint32_t b2) {
-  constexpr uint32_t MAGIC = 0x64006400u;
+// 4 eight-bit codes (one uint32) -> 4 bf16 values in K order. A code (0..255) is rebuilt exactly as
+// 16*hi + lo from its nibbles (each nibble through the exponent-magic), then one fma with scale and bias.
+// (tcgen05.mma kind::f16 wants A and B in the same 16-bit format, so f16 is not an option for B.)
+__device__ __forceinline__ uint32_t w8_pair(uint32_t v, uint32_t s2, uint32_t b2) {
+  constexpr uint32_t MAGIC = 0x43004300u;    // (128.0, 128.0)
+  constexpr uint32_t SIXTEEN = 0x41804180u;  // (16.0, 16.0)
+  const uint32_t lo = (v & 0x000F000Fu) | MAGIC;
+  const uint32_t hi = ((v >> 4) & 0x000F000Fu) | MAGIC;
+  uint32_t d;
+  asm("{\n\t.reg .b32 l, h, q;\n\t"
+      "sub.rn.bf16x2 l, %1, %3;\n\t"
+      "sub.rn.bf16x2 h, %2, %3;\n\t"
+      "fma.rn.bf16x2 q, h, %4, l;\n\t"
+      "fma.rn.bf16x2 %0, q, %5, %6;\n\t}"
+      : "=r"(d)
+      : "r"(lo), "r"(hi), "r"(MAGIC), "r"(SIXTEEN), "r"(s2), "r"(b2));
+  return d;
+}
+__device__ __forceinline__ uint2 dequant_w8(uint32_t q, uint32_t s2, uint32_t b2) {
   uint2 r;
-  r.x = sub_fma<FMT_F16>(__byte_perm(q, MAGIC, 0x5150), MAGIC, s2, b2);  // (e0, e1)
-  r.y = sub_fma<FMT_F16>(__byte_perm(q, MAGIC, 0x5352), MAGIC, s2, b2);  // (e2, e3)
+  r.x = w8_pair(__byte_perm(q, 0u, 0x4140), s2, b2);  // bytes (e0, 0, e1, 0)
+  r.y = w8_pair(__byte_perm(q, 0u, 0x4342), s2, b2);  // bytes (e2, 0, e3, 0)
   return r;
 }
 
@@ -148,7 +152,8 @@ __device__ __forceinline__ float silu(float v) { return v / (1.0f + __expf(-v));
 
 template <int BITS, uint32_t WF, int ST, typename OUT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, const Params p) {
+qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+           const __grid_constant__ CUtensorMap tmap_sb, const Params p) {
   using L = Smem<BITS, ST>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -157,6 +162,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
   const uint32_t x_s = smem_base + L::OFF_X;
   const uint32_t wd_s = smem_base + L::OFF_WD;
   const uint32_t wq_s = smem_base + L::OFF_WQ;
+  const uint32_t sb_s = smem_base + L::OFF_SB;
   float* vec_s = reinterpret_cast<float*>(smem_gen + L::OFF_VEC);
   const uint32_t bar0 = smem_base + L::OFF_BAR;
   auto t_full = [&](int s) { return bar0 + 8u * s; };
@@ -187,6 +193,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     fence_mbar_init();
     tma_prefetch_desc(&tmap_x);
     tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_sb);
   }
   if (warp == 1) {
     tmem_alloc(smem_base + L::OFF_TMEM, TMEM_COLS);
@@ -209,14 +216,15 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
       const int r0 = (tm % p.tiles_m_per_sample) * BM;
       const int n0 = tn * BN;
       for (int kb = 0; kb < num_kb; ++kb) {
-        if (!mbar_wait(t_empty(st), ph ^ 1u, DEV_TIMEOUT_TMA_EMPTY)) {
+        if (!mbar_wait_sleep(t_empty(st), ph ^ 1u, DEV_TIMEOUT_TMA_EMPTY)) {
           ok = false;
           break;
         }
         if (lane == 0) {
-          mbar_arrive_expect_tx(t_full(st), X_TILE_BYTES + L::WQ_TILE_BYTES);
+          mbar_arrive_expect_tx(t_full(st), X_TILE_BYTES + L::WQ_TILE_BYTES + SB_TILE_BYTES);
           tma_load_3d(x_s + st * X_TILE_BYTES, &tmap_x, t_full(st), kb * BK, r0, b);
           tma_load_2d(wq_s + st * L::WQ_TILE_BYTES, &tmap_w, t_full(st), kb * (BK * BITS / 32), n0);
+          tma_load_2d(sb_s + st * SB_TILE_BYTES, &tmap_sb, t_full(st), n0, kb);
         }
         __syncwarp();
         if (++st == ST) {
@@ -273,37 +281,33 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
   } else if (warp >= FIRST_DQ_WARP) {
     // ------------------------------------------------------------ dequantizers
     const int row = (warp - FIRST_DQ_WARP) * 32 + lane;  // row of the 256-row weight tile
-    const int groups = num_kb;                            // scales/biases are [N, K/64]
     constexpr int ROW_BYTES = BK * BITS / 8;              // packed bytes per row per k-block
+    // The packed tile is loaded with the TMA swizzle whose span equals one row (32 B for 4 bits,
+    // 64 B for 8 bits): 16-byte chunk c of row r sits at chunk c ^ ((r*ROW_BYTES >> 7) & mask), which
+    // spreads the per-row reads of a quarter-warp over all banks.
+    constexpr uint32_t RD_MASK = ROW_BYTES / 16 - 1;
+    const uint32_t rd_sw = (static_cast<uint32_t>(row * ROW_BYTES) >> 7) & RD_MASK;
+    const uint32_t sw = static_cast<uint32_t>(row & 7);
     int st = 0, sd = 0;
     uint32_t ph_t = 0, ph_d = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
-      const int tn = tile / p.tiles_m;
-      const int n = tn * BN + row;
-      const bool valid = n < p.N;
-      const int64_t sb_off = static_cast<int64_t>(valid ? n : 0) * groups;
-      float s_next = valid ? load_scalar(p.scales, p.sb_dtype, sb_off) : 0.f;
-      float b_next = valid ? load_scalar(p.biases, p.sb_dtype, sb_off) : 0.f;
       for (int kb = 0; kb < num_kb; ++kb) {
-        const uint32_t s2 = pack_pair<WF>(s_next);
-        const uint32_t b2 = pack_pair<WF>(b_next);
-        if (kb + 1 < num_kb && valid) {
-          s_next = load_scalar(p.scales, p.sb_dtype, sb_off + kb + 1);
-          b_next = load_scalar(p.biases, p.sb_dtype, sb_off + kb + 1);
-        }
         if (!mbar_wait(t_full(st), ph_t, DEV_TIMEOUT_TMA_FULL) ||
             !mbar_wait(d_empty(sd), ph_d ^ 1u, DEV_TIMEOUT_DQ_EMPTY)) {
           ok = false;
           break;
         }
+        uint32_t sbv;
+        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(sbv) : "r"(sb_s + st * SB_TILE_BYTES + row * 4));
+        const uint32_t s2 = __byte_perm(sbv, sbv, 0x1010);  // (scale, scale)
+        const uint32_t b2 = __byte_perm(sbv, sbv, 0x3232);  // (bias, bias)
         const uint32_t src = wq_s + st * L::WQ_TILE_BYTES + row * ROW_BYTES;
         const uint32_t dst = wd_s + sd * WD_TILE_BYTES + row * 128;
-        const uint32_t sw = static_cast<uint32_t>(row & 7);
         if (BITS == 4) {
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            const uint4 pk = ld_shared_v4(src + 16 * h);
+            const uint4 pk = ld_shared_v4(src + ((static_cast<uint32_t>(h) ^ rd_sw) << 4));
             const uint32_t wds[4] = {pk.x, pk.y, pk.z, pk.w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -314,11 +318,11 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         } else {
 #pragma unroll
           for (int h = 0; h < 4; ++h) {
-            const uint4 pk = ld_shared_v4(src + 16 * h);
-            const uint2 lo0 = dequant_w8_f16(pk.x, s2, b2);
-            const uint2 hi0 = dequant_w8_f16(pk.y, s2, b2);
-            const uint2 lo1 = dequant_w8_f16(pk.z, s2, b2);
-            const uint2 hi1 = dequant_w8_f16(pk.w, s2, b2);
+            const uint4 pk = ld_shared_v4(src + ((static_cast<uint32_t>(h) ^ rd_sw) << 4));
+            const uint2 lo0 = dequant_w8(pk.x, s2, b2);
+            const uint2 hi0 = dequant_w8(pk.y, s2, b2);
+            const uint2 lo1 = dequant_w8(pk.z, s2, b2);
+            const uint2 hi1 = dequant_w8(pk.w, s2, b2);
             const uint32_t c0 = static_cast<uint32_t>(2 * h), c1 = c0 + 1;
             st_shared_v4(dst + ((c0 ^ sw) << 4), make_uint4(lo0.x, lo0.y, hi0.x, hi0.y));
             st_shared_v4(dst + ((c1 ^ sw) << 4), make_uint4(lo1.x, lo1.y, hi1.x, hi1.y));
@@ -366,7 +370,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
           gate_s[c] = (n < p.N) ? load_scalar(p.gate, p.gate_dtype, b * p.gate_batch_stride + n) : 0.f;
       }
       named_bar_sync(1, 128);
-      if (!mbar_wait(acc_full(a), aph, DEV_TIMEOUT_ACC_FULL)) {
+      if (!mbar_wait_sleep(acc_full(a), aph, DEV_TIMEOUT_ACC_FULL)) {
         ok = false;
         break;
       }
@@ -445,7 +449,8 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
 MFX_DEFINE_STATUS_READER(read_status)
 
 template <int BITS, uint32_t WF, int ST, typename OUT>
-int launch(const CUtensorMap& tx, const CUtensorMap& tw, const Params& p, int grid, cudaStream_t st) {
+int launch(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tsb, const Params& p, int grid,
+           cudaStream_t st) {
   using L = Smem<BITS, ST>;
   auto kern = qmm_kernel<BITS, WF, ST, OUT>;
   static bool configured = false;  // attribute is per function; set once per process and device reuse is fine
@@ -457,7 +462,7 @@ int launch(const CUtensorMap& tx, const CUtensorMap& tw, const Params& p, int gr
     configured = true;
     configured_dev = dev;
   }
-  kern<<<grid, NUM_THREADS, L::DYN_BYTES, st>>>(tx, tw, p);
+  kern<<<grid, NUM_THREADS, L::DYN_BYTES, st>>>(tx, tw, tsb, p);
   MFX_CUDA_TRY(cudaGetLastError());
   return MFX_OK;
 }
@@ -474,16 +479,66 @@ int sm_count() {
   return cached[dev];
 }
 
+// packed[g * N + n] = bf16(scales[n, g]) | bf16(biases[n, g]) << 16
+__global__ void __launch_bounds__(256) pack_scales_kernel(const void* __restrict__ scales,
+                                                          const void* __restrict__ biases, int sb_dtype, int N,
+                                                          int G, uint32_t* __restrict__ packed) {
+  __shared__ uint32_t tile[32][33];
+  const int n0 = blockIdx.x * 32, g0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int n = n0 + ty + 8 * i, g = g0 + tx;  // reads run along g (contiguous in [N, G])
+    uint32_t v = 0;
+    if (n < N && g < G) {
+      const int64_t idx = static_cast<int64_t>(n) * G + g;
+      const __nv_bfloat16 sv = __float2bfloat16_rn(load_scalar(scales, sb_dtype, idx));
+      const __nv_bfloat16 bv = __float2bfloat16_rn(load_scalar(biases, sb_dtype, idx));
+      v = static_cast<uint32_t>(__bfloat16_as_ushort(sv)) | (static_cast<uint32_t>(__bfloat16_as_ushort(bv)) << 16);
+    }
+    tile[ty + 8 * i][tx] = v;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int g = g0 + ty + 8 * i, n = n0 + tx;  // writes run along n (contiguous in [G, N])
+    if (n < N && g < G) packed[static_cast<int64_t>(g) * N + n] = tile[tx][ty + 8 * i];
+  }
+}
+
+int pack_scales(const void* scales, const void* biases, int sb_dtype, int64_t N, int64_t K, int group_size,
+                uint32_t* packed, cudaStream_t st) {
+  if (!scales || !biases || !packed) return MFX_ERR_NULL;
+  if (group_size != 64) return MFX_ERR_UNSUPPORTED_BITS;
+  if (N <= 0 || K <= 0 || K % 64 != 0) return MFX_ERR_SHAPE;
+  if (N > (1 << 30) || K > (1 << 30)) return MFX_ERR_TOO_LARGE;
+  if (!valid_dtype(sb_dtype)) return MFX_ERR_DTYPE;
+  if (int rc = check_arch()) return rc;
+  const int G = static_cast<int>(K / 64);
+  dim3 grid(static_cast<unsigned>((N + 31) / 32), static_cast<unsigned>((G + 31) / 32));
+  pack_scales_kernel<<<grid, 256, 0, st>>>(scales, biases, sb_dtype, static_cast<int>(N), G, packed);
+  MFX_CUDA_TRY(cudaGetLastError());
+  return MFX_OK;
+}
+
 int run(const mfx_qlinear_args& a, cudaStream_t st) {
-  if (!a.x || !a.wq || !a.scales || !a.biases || !a.y) return MFX_ERR_NULL;
+  if (!a.x || !a.wq || !a.y) return MFX_ERR_NULL;
   if ((a.bits != 4 && a.bits != 8) || a.group_size != 64) return MFX_ERR_UNSUPPORTED_BITS;
   if (a.rows <= 0 || a.batch <= 0 || a.N <= 0 || a.K <= 0) return MFX_ERR_SHAPE;
   if (a.K % 64 != 0 || a.N % 8 != 0) return MFX_ERR_SHAPE;
   if (a.rows > (1 << 30) || a.N > (1 << 30) || a.K > (1 << 30) || a.batch > (1 << 20)) return MFX_ERR_TOO_LARGE;
-  if (!valid_dtype(a.sb_dtype)) return MFX_ERR_DTYPE;
   if (a.bias && !valid_dtype(a.bias_dtype)) return MFX_ERR_DTYPE;
   if (a.y_dtype != MFX_BF16 && a.y_dtype != MFX_F32) return MFX_ERR_DTYPE;
   if (a.epilogue < MFX_EPI_NONE || a.epilogue > MFX_EPI_SILU) return MFX_ERR_SHAPE;
+  const uint32_t* sb_packed = a.sb_packed;
+  if (!sb_packed) {
+    if (!a.scales || !a.biases || !a.workspace) return MFX_ERR_NULL;
+    if (!valid_dtype(a.sb_dtype)) return MFX_ERR_DTYPE;
+    if (a.workspace_bytes < static_cast<size_t>(a.N) * (a.K / 64) * 4) return MFX_ERR_SHAPE;
+    if (!aligned16(a.workspace)) return MFX_ERR_ALIGN;
+  } else if (!aligned16(sb_packed)) {
+    return MFX_ERR_ALIGN;
+  }
   if (a.epilogue == MFX_EPI_GATE_RESIDUAL) {
     if (!a.gate || !a.residual) return MFX_ERR_NULL;
     if (!valid_dtype(a.gate_dtype)) return MFX_ERR_DTYPE;
@@ -499,8 +554,13 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
       return MFX_ERR_ALIGN;
   }
   if (int rc = check_arch()) return rc;
+  if (!sb_packed) {
+    uint32_t* ws = static_cast<uint32_t*>(a.workspace);
+    if (int rc = pack_scales(a.scales, a.biases, a.sb_dtype, a.N, a.K, a.group_size, ws, st)) return rc;
+    sb_packed = ws;
+  }
 
-  CUtensorMap tx, tw;
+  CUtensorMap tx, tw, tsb;
   {
     const uint64_t dims[3] = {static_cast<uint64_t>(a.K), static_cast<uint64_t>(a.rows),
                               static_cast<uint64_t>(a.batch)};
@@ -519,6 +579,14 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
     const uint64_t strides[1] = {words_per_row * 4};
     const uint32_t box[2] = {static_cast<uint32_t>(BK * a.bits / 32), BN};
     if (int rc = encode_tmap(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, a.wq, dims, strides, box,
+                             a.bits == 4 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B))
+      return rc;
+  }
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(a.N), static_cast<uint64_t>(a.K / 64)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(a.N) * 4};
+    const uint32_t box[2] = {BN, 1};
+    if (int rc = encode_tmap(&tsb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, sb_packed, dims, strides, box,
                              CU_TENSOR_MAP_SWIZZLE_NONE))
       return rc;
   }
@@ -533,9 +601,6 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
   const int64_t total = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
   if (total > (1ll << 30)) return MFX_ERR_TOO_LARGE;
   p.total_tiles = static_cast<int>(total);
-  p.scales = a.scales;
-  p.biases = a.biases;
-  p.sb_dtype = a.sb_dtype;
   p.bias = a.bias;
   p.bias_dtype = a.bias_dtype;
   p.epilogue = a.epilogue;
@@ -551,11 +616,11 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
   const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
   const bool f32 = a.y_dtype == MFX_F32;
   if (a.bits == 4) {
-    return f32 ? launch<4, FMT_BF16, 4, float>(tx, tw, p, grid, st)
-               : launch<4, FMT_BF16, 4, __nv_bfloat16>(tx, tw, p, grid, st);
+    return f32 ? launch<4, FMT_BF16, 4, float>(tx, tw, tsb, p, grid, st)
+               : launch<4, FMT_BF16, 4, __nv_bfloat16>(tx, tw, tsb, p, grid, st);
   }
-  return f32 ? launch<8, FMT_F16, 3, float>(tx, tw, p, grid, st)
-             : launch<8, FMT_F16, 3, __nv_bfloat16>(tx, tw, p, grid, st);
+  return f32 ? launch<8, FMT_BF16, 3, float>(tx, tw, tsb, p, grid, st)
+             : launch<8, FMT_BF16, 3, __nv_bfloat16>(tx, tw, tsb, p, grid, st);
 }
 
 }  // namespace qmm
@@ -568,14 +633,25 @@ int mfx_qlinear_ex(const mfx_qlinear_args* args, void* stream) {
   return mfx::qmm::run(*args, static_cast<cudaStream_t>(stream));
 }
 
+size_t mfx_qlinear_workspace_bytes(int64_t N, int64_t K, int group_size) {
+  if (N <= 0 || K <= 0 || group_size != 64 || K % 64 != 0) return 0;
+  return static_cast<size_t>(N) * static_cast<size_t>(K / 64) * 4;
+}
+
+int mfx_qlinear_pack_scales(const void* scales, const void* biases, int sb_dtype, int64_t N, int64_t K,
+                            int group_size, uint32_t* packed, void* stream) {
+  return mfx::qmm::pack_scales(scales, biases, sb_dtype, N, K, group_size, packed,
+                               static_cast<cudaStream_t>(stream));
+}
+
 int mfx_qlinear(const void* x, int64_t M, int64_t K, int64_t ldx, const uint32_t* wq, const void* scales,
                 const void* biases, int sb_dtype, int64_t N, int bits, int group_size, const void* bias,
-                int bias_dtype, void* y, int y_dtype, int64_t ldy, void* stream) {
+                int bias_dtype, void* y, int y_dtype, int64_t ldy, void* workspace, size_t workspace_bytes,
+                void* stream) {
   mfx_qlinear_args a;
   memset(&a, 0, sizeof(a));
   a.x = x;
   a.x_row_stride = ldx;
-  a.x_batch_stride = 0;
   a.rows = M;
   a.batch = 1;
   a.K = K;
@@ -586,13 +662,14 @@ int mfx_qlinear(const void* x, int64_t M, int64_t K, int64_t ldx, const uint32_t
   a.sb_dtype = sb_dtype;
   a.bits = bits;
   a.group_size = group_size;
+  a.workspace = workspace;
+  a.workspace_bytes = workspace_bytes;
   a.bias = bias;
   a.bias_dtype = bias_dtype;
   a.epilogue = MFX_EPI_NONE;
   a.y = y;
   a.y_dtype = y_dtype;
   a.y_row_stride = ldy;
-  a.y_batch_stride = 0;
   return mfx_qlinear_ex(&a, stream);
 }
 

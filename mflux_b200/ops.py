@@ -87,6 +87,19 @@ def dequantize_affine(wq: torch.Tensor, scales: torch.Tensor, biases: torch.Tens
     return out
 
 
+def pack_scales(scales: torch.Tensor, biases: torch.Tensor, group_size: int = 64) -> torch.Tensor:
+    """Kernel-side layout of scales/biases: uint32 [K/64, N], bf16 scale in the low half, bf16 bias in the high."""
+    lib = _lib.load()
+    _cuda(scales, "scales")
+    scales, biases = scales.contiguous(), biases.contiguous()
+    n, g = scales.shape
+    packed = torch.empty((g, n), dtype=torch.uint32, device=scales.device)
+    rc = lib.mfx_qlinear_pack_scales(_ptr(scales), _ptr(biases), _dt(scales), n, g * group_size, group_size,
+                                     _ptr(packed), _stream())
+    _lib.check(rc, "mfx_qlinear_pack_scales")
+    return packed
+
+
 def _rows_view(t: torch.Tensor, name: str):
     """(tensor, rows, batch, row_stride, batch_stride) of a [..., rows, cols] tensor whose last dim is dense."""
     if t.dim() < 2:
@@ -103,12 +116,15 @@ def _rows_view(t: torch.Tensor, name: str):
 def qlinear(x: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor,
             bias: torch.Tensor | None = None, *, bits: int = 4, group_size: int = 64, epilogue: str | None = None,
             gate: torch.Tensor | None = None, residual: torch.Tensor | None = None,
-            out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+            out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
+            sb_packed: torch.Tensor | None = None) -> torch.Tensor:
     """nn.QuantizedLinear.__call__: y[..., N] = x[..., K] . dequant(wq)^T + bias, with optional fused epilogue.
 
     x is [rows, K] or [batch, rows, K] (bf16; row/batch strides may be arbitrary multiples of 8
     elements, the last dim must be dense). `out`, when given, may be a strided view of the same
     leading shape. epilogue "gate_residual" computes residual + gate[batch] * y with gate [batch, N].
+    `sb_packed` is the cached result of pack_scales(scales, biases); without it the scales are packed
+    into a scratch tensor on every call.
     """
     lib = _lib.load()
     _cuda(x, "x")
@@ -122,7 +138,10 @@ def qlinear(x: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, biases: tor
     n = wq.shape[0]
     if wq.shape[1] * 32 // bits != k:
         raise ValueError(f"x has K={k} but the packed weight encodes K={wq.shape[1] * 32 // bits}")
-    wq, scales, biases = wq.contiguous(), scales.contiguous(), biases.contiguous()
+    wq = wq.contiguous()
+    if sb_packed is None:
+        scales, biases = scales.contiguous(), biases.contiguous()
+        workspace = torch.empty((k // group_size, n), dtype=torch.uint32, device=x.device)
     if out is None:
         od = out_dtype or (residual.dtype if residual is not None else torch.bfloat16)
         out = torch.empty((*xv.shape[:-1], n), dtype=od, device=x.device)
@@ -135,8 +154,14 @@ def qlinear(x: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, biases: tor
     a = QLinearArgs()
     a.x, a.x_row_stride, a.x_batch_stride = xv.data_ptr(), x_rs, x_bs
     a.rows, a.batch, a.K, a.N = rows, batch, k, n
-    a.wq, a.scales, a.biases = wq.data_ptr(), scales.data_ptr(), biases.data_ptr()
-    a.sb_dtype, a.bits, a.group_size = _dt(scales), bits, group_size
+    a.wq, a.bits, a.group_size = wq.data_ptr(), bits, group_size
+    if sb_packed is None:
+        a.scales, a.biases, a.sb_dtype = scales.data_ptr(), biases.data_ptr(), _dt(scales)
+        a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel() * 4
+    else:
+        if sb_packed.shape != (k // group_size, n) or not sb_packed.is_contiguous():
+            raise ValueError("sb_packed must be the contiguous [K/64, N] result of pack_scales")
+        a.sb_packed = sb_packed.data_ptr()
     if bias is not None:
         bias = bias.contiguous()
         a.bias, a.bias_dtype = bias.data_ptr(), _dt(bias)

@@ -44,9 +44,14 @@ def test_argument_validation_needs_no_gpu(lib_built):
     a = _lib.QLinearArgs()
     assert lib.mfx_qlinear_ex(a, None) == -7
     assert lib.mfx_qlinear_ex(None, None) == -7
-    a.x = a.wq = a.scales = a.biases = a.y = 1024
+    a.x = a.wq = a.scales = a.biases = a.y = a.workspace = 1024
     a.rows, a.batch, a.K, a.N, a.bits, a.group_size = 128, 1, 96, 64, 4, 64
     assert lib.mfx_qlinear_ex(a, None) == -1  # K % 64
     a.K = 128
     a.bits = 5
     assert lib.mfx_qlinear_ex(a, None) == -3
+    a.bits = 4
+    a.workspace_bytes = 16  # too small for N * K/64 * 4
+    assert lib.mfx_qlinear_ex(a, None) == -1
+    assert lib.mfx_qlinear_workspace_bytes(12288, 3072, 64) == 12288 * 48 * 4
+    assert lib.mfx_qlinear_workspace_bytes(12288, 3000, 64) == 0

@@ -74,10 +74,12 @@ def test_dequantize_bit_exact_and_round_trip(lib_built, bits, sb_dtype):
     w_hat = ops.dequantize_affine(wq, s, b, 64, bits, dtype=torch.float32)
     ref = quant.dequantize_affine(wq.cpu().numpy(), s.float().cpu().numpy(), b.float().cpu().numpy(), 64, bits)
     np.testing.assert_array_equal(w_hat.cpu().numpy(), ref)
-    # idempotence: re-quantizing the dequantized weights reproduces the codes' values
-    wq2, s2, b2 = ops.quantize_affine(w_hat.to(sb_dtype), 64, bits)
-    w_hat2 = ops.dequantize_affine(wq2, s2, b2, 64, bits, dtype=torch.float32)
-    assert quant.rel_l2(w_hat2, w_hat) < (2e-2 if sb_dtype == torch.bfloat16 else 1e-5)
+    # round trip: every value lands within one quantization step of where it started
+    err = (w_hat.cpu() - w.float()).abs().reshape(256, 8, 64).amax(-1)
+    # (scales/biases stored in bf16 move every code by their own rounding error as well)
+    sf, bf = s.float().cpu().abs(), b.float().cpu().abs()
+    slack = 0.0 if sb_dtype == torch.float32 else 2.0 ** -8
+    assert (err <= sf * (1.01 + slack * ((1 << bits) - 1)) + bf * slack + 1e-9).all()
 
 
 def test_quantize_rejects_bad_arguments(lib_built):
