@@ -72,13 +72,17 @@ int mfx_quantize_affine(const void* w, int w_dtype, int64_t N, int64_t K, int bi
 int mfx_dequantize_affine(const uint32_t* wq, const void* scales, const void* biases, int sb_dtype, int64_t N,
                           int64_t K, int bits, int group_size, void* out, int out_dtype, void* stream);
 
-/* Kernel-side layout of the per-group scales and biases. The matmul kernel streams them with TMA, one
- * [N]-long row per 64-wide k-block, so it wants them transposed and paired: packed[g*N + n] =
- * bf16(scales[n, g]) | bf16(biases[n, g]) << 16, g = 0..K/64-1. No counterpart in the reference (MLX
- * keeps [N, K/64] arrays); callers that keep weights resident pack once and pass `sb_packed`. */
-size_t mfx_qlinear_workspace_bytes(int64_t N, int64_t K, int group_size); /* = N * (K/64) * 4 */
-int mfx_qlinear_pack_scales(const void* scales, const void* biases, int sb_dtype, int64_t N, int64_t K,
-                            int group_size, uint32_t* packed, void* stream);
+/* Kernel-side ("prepared") form of one quantized weight. The matmul kernel streams weights and
+ * per-group scale/bias pairs with TMA and dequantizes with the fewest integer instructions when
+ *  (a) the codes of each uint32 are interleaved so that one mask yields two neighbouring values
+ *      (4 bits: nibble order e0,e2,e4,e6,e1,e3,e5,e7; 8 bits: byte order e0,e2,e1,e3), and
+ *  (b) scales and biases are transposed and paired: sb[g*N + n] = bf16(scales[n,g]) | bf16(biases[n,g]) << 16.
+ * The blob is [interleaved codes, N*K*bits/8 bytes, padded to 256][sb, (K/64)*N*4 bytes]. It has no
+ * counterpart in the reference (MLX consumes its own [N, K*bits/32] / [N, K/64] arrays directly); a
+ * caller that keeps weights resident prepares once per weight and passes `prepared` afterwards. */
+size_t mfx_qlinear_prepared_bytes(int64_t N, int64_t K, int bits, int group_size); /* 0 on bad arguments */
+int mfx_qlinear_prepare(const uint32_t* wq, const void* scales, const void* biases, int sb_dtype, int64_t N,
+                        int64_t K, int bits, int group_size, void* prepared, size_t prepared_bytes, void* stream);
 
 /* Replaces mlx.nn.QuantizedLinear.__call__ = mx.quantized_matmul(x, w, scales, biases, transpose=True,
  * group_size=64, bits) + bias, i.e. every nn.Linear of the transformer blocks, e.g.
@@ -86,8 +90,8 @@ int mfx_qlinear_pack_scales(const void* scales, const void* biases, int sb_dtype
  * single_transformer_block.py:14-15.
  * y[M, N] = x[M, K] . dequant(wq)^T + bias.  x bf16 with row stride ldx (elements, multiple of 8);
  * y bf16 or f32 with row stride ldy; bias nullable. K % 64 == 0, N % 8 == 0.
- * workspace: caller-owned scratch of mfx_qlinear_workspace_bytes(N, K, 64) bytes, 16-byte aligned; the
- * call first packs scales/biases into it (see above), then runs the matmul, both on `stream`. */
+ * workspace: caller-owned scratch of mfx_qlinear_prepared_bytes(N, K, bits, 64) bytes, 256-byte aligned;
+ * the call first prepares the weight into it (see above), then runs the matmul, both on `stream`. */
 int mfx_qlinear(const void* x, int64_t M, int64_t K, int64_t ldx, const uint32_t* wq, const void* scales,
                 const void* biases, int sb_dtype, int64_t N, int bits, int group_size, const void* bias,
                 int bias_dtype, void* y, int y_dtype, int64_t ldy, void* workspace, size_t workspace_bytes,
@@ -98,8 +102,8 @@ int mfx_qlinear(const void* x, int64_t M, int64_t K, int64_t ldx, const uint32_t
  * [batch, N] with gate_batch_stride. This lets the joint text+image blocks read/write slices of one
  * sequence buffer without concatenation copies (joint_attention.py:57-60,75-79) and fuses the gated
  * residual of joint_transformer_block.py:84-90 / single_transformer_block.py:45,56-57.
- * Scales/biases: either `sb_packed` (from mfx_qlinear_pack_scales; then scales/biases may be NULL) or
- * scales + biases + a workspace as in mfx_qlinear. */
+ * Weights: either `prepared` (from mfx_qlinear_prepare; then wq/scales/biases may be NULL) or
+ * wq + scales + biases + a workspace as in mfx_qlinear. */
 typedef struct mfx_qlinear_args {
   const void* x;            /* bf16 */
   int64_t x_row_stride, x_batch_stride;
@@ -108,8 +112,8 @@ typedef struct mfx_qlinear_args {
   const void* scales;
   const void* biases;
   int sb_dtype, bits, group_size;
-  const uint32_t* sb_packed; /* nullable */
-  void* workspace;           /* nullable when sb_packed is given */
+  const void* prepared;      /* nullable */
+  void* workspace;           /* nullable when prepared is given */
   size_t workspace_bytes;
   const void* bias;         /* nullable, [N] */
   int bias_dtype;

@@ -40,7 +40,7 @@ class QLinearArgs(ctypes.Structure):
         ("sb_dtype", c_int),
         ("bits", c_int),
         ("group_size", c_int),
-        ("sb_packed", c_void_p),
+        ("prepared", c_void_p),
         ("workspace", c_void_p),
         ("workspace_bytes", ctypes.c_size_t),
         ("bias", c_void_p),
@@ -73,8 +73,11 @@ SIGNATURES = {
         c_int,
         [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_void_p, c_int, c_void_p],
     ),
-    "mfx_qlinear_workspace_bytes": (ctypes.c_size_t, [c_int64, c_int64, c_int]),
-    "mfx_qlinear_pack_scales": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p]),
+    "mfx_qlinear_prepared_bytes": (ctypes.c_size_t, [c_int64, c_int64, c_int, c_int]),
+    "mfx_qlinear_prepare": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_void_p, ctypes.c_size_t, c_void_p],
+    ),
     "mfx_qlinear": (
         c_int,
         [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int,

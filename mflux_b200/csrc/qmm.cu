@@ -92,30 +92,25 @@ __device__ __forceinline__ uint32_t sub_fma(uint32_t a, uint32_t magic, uint32_t
   return d;
 }
 
-// 8 four-bit codes (one uint32, element j in bits [4j, 4j+4)) -> 8 values in K order.
+// 8 four-bit codes of one prepared uint32 (nibble order e0,e2,e4,e6,e1,e3,e5,e7) -> 8 values in K order:
+// nibble j lands in the low half and nibble 4+j in the high half of one masked word.
 template <uint32_t WF>
 __device__ __forceinline__ uint4 dequant_w4(uint32_t q, uint32_t s2, uint32_t b2) {
   constexpr uint32_t MAGIC = (WF == FMT_BF16) ? 0x43004300u : 0x64006400u;  // 128.0 | 1024.0: ulp 1
-  const uint32_t t0 = (q & 0x000F000Fu) | MAGIC;          // (e0, e4)
-  const uint32_t t1 = ((q >> 4) & 0x000F000Fu) | MAGIC;   // (e1, e5)
-  const uint32_t t2 = ((q >> 8) & 0x000F000Fu) | MAGIC;   // (e2, e6)
-  const uint32_t t3 = ((q >> 12) & 0x000F000Fu) | MAGIC;  // (e3, e7)
   uint4 r;
-  r.x = sub_fma<WF>(__byte_perm(t0, t1, 0x5410), MAGIC, s2, b2);  // (e0, e1)
-  r.y = sub_fma<WF>(__byte_perm(t2, t3, 0x5410), MAGIC, s2, b2);  // (e2, e3)
-  r.z = sub_fma<WF>(__byte_perm(t0, t1, 0x7632), MAGIC, s2, b2);  // (e4, e5)
-  r.w = sub_fma<WF>(__byte_perm(t2, t3, 0x7632), MAGIC, s2, b2);  // (e6, e7)
+  r.x = sub_fma<WF>((q & 0x000F000Fu) | MAGIC, MAGIC, s2, b2);          // (e0, e1)
+  r.y = sub_fma<WF>(((q >> 4) & 0x000F000Fu) | MAGIC, MAGIC, s2, b2);   // (e2, e3)
+  r.z = sub_fma<WF>(((q >> 8) & 0x000F000Fu) | MAGIC, MAGIC, s2, b2);   // (e4, e5)
+  r.w = sub_fma<WF>(((q >> 12) & 0x000F000Fu) | MAGIC, MAGIC, s2, b2);  // (e6, e7)
   return r;
 }
 
-// 4 eight-bit codes (one uint32) -> 4 bf16 values in K order. A code (0..255) is rebuilt exactly as
-// 16*hi + lo from its nibbles (each nibble through the exponent-magic), then one fma with scale and bias.
+// Two eight-bit codes -> two bf16 values. A code (0..255) is rebuilt exactly as 16*hi + lo from its
+// nibbles (each through the exponent-magic), then one fma with scale and bias.
 // (tcgen05.mma kind::f16 wants A and B in the same 16-bit format, so f16 is not an option for B.)
-__device__ __forceinline__ uint32_t w8_pair(uint32_t v, uint32_t s2, uint32_t b2) {
+__device__ __forceinline__ uint32_t w8_pair(uint32_t lo, uint32_t hi, uint32_t s2, uint32_t b2) {
   constexpr uint32_t MAGIC = 0x43004300u;    // (128.0, 128.0)
   constexpr uint32_t SIXTEEN = 0x41804180u;  // (16.0, 16.0)
-  const uint32_t lo = (v & 0x000F000Fu) | MAGIC;
-  const uint32_t hi = ((v >> 4) & 0x000F000Fu) | MAGIC;
   uint32_t d;
   asm("{\n\t.reg .b32 l, h, q;\n\t"
       "sub.rn.bf16x2 l, %1, %3;\n\t"
@@ -123,24 +118,15 @@ __device__ __forceinline__ uint32_t w8_pair(uint32_t v, uint32_t s2, uint32_t b2
       "fma.rn.bf16x2 q, h, %4, l;\n\t"
       "fma.rn.bf16x2 %0, q, %5, %6;\n\t}"
       : "=r"(d)
-      : "r"(lo), "r"(hi), "r"(MAGIC), "r"(SIXTEEN), "r"(s2), "r"(b2));
+      : "r"(lo | MAGIC), "r"(hi | MAGIC), "r"(MAGIC), "r"(SIXTEEN), "r"(s2), "r"(b2));
   return d;
 }
+// 4 eight-bit codes of one prepared uint32 (byte order e0,e2,e1,e3) -> 4 values in K order.
 __device__ __forceinline__ uint2 dequant_w8(uint32_t q, uint32_t s2, uint32_t b2) {
   uint2 r;
-  r.x = w8_pair(__byte_perm(q, 0u, 0x4140), s2, b2);  // bytes (e0, 0, e1, 0)
-  r.y = w8_pair(__byte_perm(q, 0u, 0x4342), s2, b2);  // bytes (e2, 0, e3, 0)
+  r.x = w8_pair(q & 0x000F000Fu, (q >> 4) & 0x000F000Fu, s2, b2);           // (e0, e1)
+  r.y = w8_pair((q >> 8) & 0x000F000Fu, (q >> 12) & 0x000F000Fu, s2, b2);  // (e2, e3)
   return r;
-}
-
-__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
-  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
-               : "memory");
-}
-__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-  return v;
 }
 
 __device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f)); }
@@ -282,12 +268,21 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     // ------------------------------------------------------------ dequantizers
     const int row = (warp - FIRST_DQ_WARP) * 32 + lane;  // row of the 256-row weight tile
     constexpr int ROW_BYTES = BK * BITS / 8;              // packed bytes per row per k-block
+    constexpr int RD_CHUNKS = ROW_BYTES / 16;
     // The packed tile is loaded with the TMA swizzle whose span equals one row (32 B for 4 bits,
     // 64 B for 8 bits): 16-byte chunk c of row r sits at chunk c ^ ((r*ROW_BYTES >> 7) & mask), which
-    // spreads the per-row reads of a quarter-warp over all banks.
-    constexpr uint32_t RD_MASK = ROW_BYTES / 16 - 1;
-    const uint32_t rd_sw = (static_cast<uint32_t>(row * ROW_BYTES) >> 7) & RD_MASK;
-    const uint32_t sw = static_cast<uint32_t>(row & 7);
+    // spreads the per-row reads of a quarter-warp over all banks. Offsets are per-thread constants.
+    const uint32_t rd_sw = (static_cast<uint32_t>(row * ROW_BYTES) >> 7) & (RD_CHUNKS - 1);
+    const uint8_t* rd_base = smem_gen + L::OFF_WQ + row * ROW_BYTES;
+    uint32_t rd_off[RD_CHUNKS];
+#pragma unroll
+    for (int h = 0; h < RD_CHUNKS; ++h) rd_off[h] = (static_cast<uint32_t>(h) ^ rd_sw) << 4;
+    // B operand tile: 128-byte rows, 16-byte chunk c of row r at chunk c ^ (r & 7)
+    uint8_t* wr_base = smem_gen + L::OFF_WD + row * 128;
+    uint32_t wr_off[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) wr_off[c] = (static_cast<uint32_t>(c) ^ static_cast<uint32_t>(row & 7)) << 4;
+    const uint32_t* sb_base = reinterpret_cast<const uint32_t*>(smem_gen + L::OFF_SB) + row;
     int st = 0, sd = 0;
     uint32_t ph_t = 0, ph_d = 0;
     bool ok = true;
@@ -298,34 +293,30 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
           ok = false;
           break;
         }
-        uint32_t sbv;
-        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(sbv) : "r"(sb_s + st * SB_TILE_BYTES + row * 4));
+        const uint32_t sbv = sb_base[st * (SB_TILE_BYTES / 4)];
         const uint32_t s2 = __byte_perm(sbv, sbv, 0x1010);  // (scale, scale)
         const uint32_t b2 = __byte_perm(sbv, sbv, 0x3232);  // (bias, bias)
-        const uint32_t src = wq_s + st * L::WQ_TILE_BYTES + row * ROW_BYTES;
-        const uint32_t dst = wd_s + sd * WD_TILE_BYTES + row * 128;
+        const uint8_t* src = rd_base + st * L::WQ_TILE_BYTES;
+        uint8_t* dst = wr_base + sd * WD_TILE_BYTES;
         if (BITS == 4) {
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            const uint4 pk = ld_shared_v4(src + ((static_cast<uint32_t>(h) ^ rd_sw) << 4));
+            const uint4 pk = *reinterpret_cast<const uint4*>(src + rd_off[h]);
             const uint32_t wds[4] = {pk.x, pk.y, pk.z, pk.w};
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint32_t c = static_cast<uint32_t>(h * 4 + j);
-              st_shared_v4(dst + ((c ^ sw) << 4), dequant_w4<WF>(wds[j], s2, b2));
-            }
+            for (int j = 0; j < 4; ++j)
+              *reinterpret_cast<uint4*>(dst + wr_off[h * 4 + j]) = dequant_w4<WF>(wds[j], s2, b2);
           }
         } else {
 #pragma unroll
           for (int h = 0; h < 4; ++h) {
-            const uint4 pk = ld_shared_v4(src + ((static_cast<uint32_t>(h) ^ rd_sw) << 4));
+            const uint4 pk = *reinterpret_cast<const uint4*>(src + rd_off[h]);
             const uint2 lo0 = dequant_w8(pk.x, s2, b2);
             const uint2 hi0 = dequant_w8(pk.y, s2, b2);
             const uint2 lo1 = dequant_w8(pk.z, s2, b2);
             const uint2 hi1 = dequant_w8(pk.w, s2, b2);
-            const uint32_t c0 = static_cast<uint32_t>(2 * h), c1 = c0 + 1;
-            st_shared_v4(dst + ((c0 ^ sw) << 4), make_uint4(lo0.x, lo0.y, hi0.x, hi0.y));
-            st_shared_v4(dst + ((c1 ^ sw) << 4), make_uint4(lo1.x, lo1.y, hi1.x, hi1.y));
+            *reinterpret_cast<uint4*>(dst + wr_off[2 * h]) = make_uint4(lo0.x, lo0.y, hi0.x, hi0.y);
+            *reinterpret_cast<uint4*>(dst + wr_off[2 * h + 1]) = make_uint4(lo1.x, lo1.y, hi1.x, hi1.y);
           }
         }
         fence_proxy_async_smem();  // make these generic-proxy writes visible to the tensor core
@@ -479,7 +470,7 @@ int sm_count() {
   return cached[dev];
 }
 
-// packed[g * N + n] = bf16(scales[n, g]) | bf16(biases[n, g]) << 16
+// sb[g * N + n] = bf16(scales[n, g]) | bf16(biases[n, g]) << 16
 __global__ void __launch_bounds__(256) pack_scales_kernel(const void* __restrict__ scales,
                                                           const void* __restrict__ biases, int sb_dtype, int N,
                                                           int G, uint32_t* __restrict__ packed) {
@@ -506,23 +497,71 @@ __global__ void __launch_bounds__(256) pack_scales_kernel(const void* __restrict
   }
 }
 
-int pack_scales(const void* scales, const void* biases, int sb_dtype, int64_t N, int64_t K, int group_size,
-                uint32_t* packed, cudaStream_t st) {
-  if (!scales || !biases || !packed) return MFX_ERR_NULL;
-  if (group_size != 64) return MFX_ERR_UNSUPPORTED_BITS;
+// Interleave the codes of every uint32: 4 bits -> nibbles e0,e2,e4,e6,e1,e3,e5,e7; 8 bits -> bytes e0,e2,e1,e3.
+template <int BITS>
+__global__ void __launch_bounds__(256) interleave_codes_kernel(const uint4* __restrict__ in, uint4* __restrict__ out,
+                                                               int64_t n_vec) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n_vec) return;
+  const uint4 v = __ldg(in + i);
+  uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t q = w[j];
+    if (BITS == 4) {
+      uint32_t r = 0;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const int pos = (e & 1) ? 4 + (e >> 1) : (e >> 1);
+        r |= ((q >> (4 * e)) & 0xFu) << (4 * pos);
+      }
+      w[j] = r;
+    } else {
+      w[j] = __byte_perm(q, 0u, 0x3120);
+    }
+  }
+  out[i] = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+size_t codes_bytes_padded(int64_t N, int64_t K, int bits) {
+  const size_t raw = static_cast<size_t>(N) * static_cast<size_t>(K) * bits / 8;
+  return (raw + 255) & ~static_cast<size_t>(255);
+}
+
+size_t prepared_bytes(int64_t N, int64_t K, int bits, int group_size) {
+  if (N <= 0 || K <= 0 || group_size != 64 || K % 64 != 0 || (bits != 4 && bits != 8)) return 0;
+  return codes_bytes_padded(N, K, bits) + static_cast<size_t>(N) * static_cast<size_t>(K / 64) * 4;
+}
+
+int prepare(const uint32_t* wq, const void* scales, const void* biases, int sb_dtype, int64_t N, int64_t K,
+            int bits, int group_size, void* prepared, size_t bytes, cudaStream_t st) {
+  if (!wq || !scales || !biases || !prepared) return MFX_ERR_NULL;
+  if ((bits != 4 && bits != 8) || group_size != 64) return MFX_ERR_UNSUPPORTED_BITS;
   if (N <= 0 || K <= 0 || K % 64 != 0) return MFX_ERR_SHAPE;
   if (N > (1 << 30) || K > (1 << 30)) return MFX_ERR_TOO_LARGE;
   if (!valid_dtype(sb_dtype)) return MFX_ERR_DTYPE;
+  if (bytes < prepared_bytes(N, K, bits, group_size)) return MFX_ERR_SHAPE;
+  if (!aligned16(wq) || (reinterpret_cast<uintptr_t>(prepared) & 255u) != 0) return MFX_ERR_ALIGN;
   if (int rc = check_arch()) return rc;
+  const int64_t n_vec = N * K * bits / 8 / 16;  // K % 64 == 0 makes every row a whole number of 16-byte vectors
+  const unsigned blocks = static_cast<unsigned>((n_vec + 255) / 256);
+  if (bits == 4)
+    interleave_codes_kernel<4><<<blocks, 256, 0, st>>>(reinterpret_cast<const uint4*>(wq),
+                                                       static_cast<uint4*>(prepared), n_vec);
+  else
+    interleave_codes_kernel<8><<<blocks, 256, 0, st>>>(reinterpret_cast<const uint4*>(wq),
+                                                       static_cast<uint4*>(prepared), n_vec);
+  MFX_CUDA_TRY(cudaGetLastError());
   const int G = static_cast<int>(K / 64);
+  uint32_t* sb = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(prepared) + codes_bytes_padded(N, K, bits));
   dim3 grid(static_cast<unsigned>((N + 31) / 32), static_cast<unsigned>((G + 31) / 32));
-  pack_scales_kernel<<<grid, 256, 0, st>>>(scales, biases, sb_dtype, static_cast<int>(N), G, packed);
+  pack_scales_kernel<<<grid, 256, 0, st>>>(scales, biases, sb_dtype, static_cast<int>(N), G, sb);
   MFX_CUDA_TRY(cudaGetLastError());
   return MFX_OK;
 }
 
 int run(const mfx_qlinear_args& a, cudaStream_t st) {
-  if (!a.x || !a.wq || !a.y) return MFX_ERR_NULL;
+  if (!a.x || !a.y) return MFX_ERR_NULL;
   if ((a.bits != 4 && a.bits != 8) || a.group_size != 64) return MFX_ERR_UNSUPPORTED_BITS;
   if (a.rows <= 0 || a.batch <= 0 || a.N <= 0 || a.K <= 0) return MFX_ERR_SHAPE;
   if (a.K % 64 != 0 || a.N % 8 != 0) return MFX_ERR_SHAPE;
@@ -530,13 +569,11 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
   if (a.bias && !valid_dtype(a.bias_dtype)) return MFX_ERR_DTYPE;
   if (a.y_dtype != MFX_BF16 && a.y_dtype != MFX_F32) return MFX_ERR_DTYPE;
   if (a.epilogue < MFX_EPI_NONE || a.epilogue > MFX_EPI_SILU) return MFX_ERR_SHAPE;
-  const uint32_t* sb_packed = a.sb_packed;
-  if (!sb_packed) {
-    if (!a.scales || !a.biases || !a.workspace) return MFX_ERR_NULL;
-    if (!valid_dtype(a.sb_dtype)) return MFX_ERR_DTYPE;
-    if (a.workspace_bytes < static_cast<size_t>(a.N) * (a.K / 64) * 4) return MFX_ERR_SHAPE;
-    if (!aligned16(a.workspace)) return MFX_ERR_ALIGN;
-  } else if (!aligned16(sb_packed)) {
+  const void* prepared = a.prepared;
+  if (!prepared) {
+    if (!a.wq || !a.scales || !a.biases || !a.workspace) return MFX_ERR_NULL;
+    if (a.workspace_bytes < prepared_bytes(a.N, a.K, a.bits, a.group_size)) return MFX_ERR_SHAPE;
+  } else if ((reinterpret_cast<uintptr_t>(prepared) & 255u) != 0) {
     return MFX_ERR_ALIGN;
   }
   if (a.epilogue == MFX_EPI_GATE_RESIDUAL) {
@@ -550,15 +587,17 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
     const size_t es = dtype_size(a.y_dtype);
     if (!aligned16(a.y) || (a.y_row_stride * es) % 16 != 0 || (a.y_batch_stride * es) % 16 != 0)
       return MFX_ERR_ALIGN;
-    if (!aligned16(a.x) || (a.x_row_stride * 2) % 16 != 0 || (a.x_batch_stride * 2) % 16 != 0 || !aligned16(a.wq))
-      return MFX_ERR_ALIGN;
+    if (!aligned16(a.x) || (a.x_row_stride * 2) % 16 != 0 || (a.x_batch_stride * 2) % 16 != 0) return MFX_ERR_ALIGN;
   }
   if (int rc = check_arch()) return rc;
-  if (!sb_packed) {
-    uint32_t* ws = static_cast<uint32_t*>(a.workspace);
-    if (int rc = pack_scales(a.scales, a.biases, a.sb_dtype, a.N, a.K, a.group_size, ws, st)) return rc;
-    sb_packed = ws;
+  if (!prepared) {
+    if (int rc = prepare(a.wq, a.scales, a.biases, a.sb_dtype, a.N, a.K, a.bits, a.group_size, a.workspace,
+                         a.workspace_bytes, st))
+      return rc;
+    prepared = a.workspace;
   }
+  const void* codes = prepared;
+  const void* sb_packed = static_cast<const uint8_t*>(prepared) + codes_bytes_padded(a.N, a.K, a.bits);
 
   CUtensorMap tx, tw, tsb;
   {
@@ -578,7 +617,7 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
     const uint64_t dims[2] = {words_per_row, static_cast<uint64_t>(a.N)};
     const uint64_t strides[1] = {words_per_row * 4};
     const uint32_t box[2] = {static_cast<uint32_t>(BK * a.bits / 32), BN};
-    if (int rc = encode_tmap(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, a.wq, dims, strides, box,
+    if (int rc = encode_tmap(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, codes, dims, strides, box,
                              a.bits == 4 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B))
       return rc;
   }
@@ -633,15 +672,14 @@ int mfx_qlinear_ex(const mfx_qlinear_args* args, void* stream) {
   return mfx::qmm::run(*args, static_cast<cudaStream_t>(stream));
 }
 
-size_t mfx_qlinear_workspace_bytes(int64_t N, int64_t K, int group_size) {
-  if (N <= 0 || K <= 0 || group_size != 64 || K % 64 != 0) return 0;
-  return static_cast<size_t>(N) * static_cast<size_t>(K / 64) * 4;
+size_t mfx_qlinear_prepared_bytes(int64_t N, int64_t K, int bits, int group_size) {
+  return mfx::qmm::prepared_bytes(N, K, bits, group_size);
 }
 
-int mfx_qlinear_pack_scales(const void* scales, const void* biases, int sb_dtype, int64_t N, int64_t K,
-                            int group_size, uint32_t* packed, void* stream) {
-  return mfx::qmm::pack_scales(scales, biases, sb_dtype, N, K, group_size, packed,
-                               static_cast<cudaStream_t>(stream));
+int mfx_qlinear_prepare(const uint32_t* wq, const void* scales, const void* biases, int sb_dtype, int64_t N,
+                        int64_t K, int bits, int group_size, void* prepared, size_t prepared_bytes, void* stream) {
+  return mfx::qmm::prepare(wq, scales, biases, sb_dtype, N, K, bits, group_size, prepared, prepared_bytes,
+                           static_cast<cudaStream_t>(stream));
 }
 
 int mfx_qlinear(const void* x, int64_t M, int64_t K, int64_t ldx, const uint32_t* wq, const void* scales,

@@ -87,17 +87,25 @@ def dequantize_affine(wq: torch.Tensor, scales: torch.Tensor, biases: torch.Tens
     return out
 
 
-def pack_scales(scales: torch.Tensor, biases: torch.Tensor, group_size: int = 64) -> torch.Tensor:
-    """Kernel-side layout of scales/biases: uint32 [K/64, N], bf16 scale in the low half, bf16 bias in the high."""
+def prepare_qlinear(wq: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor, bits: int = 4,
+                    group_size: int = 64) -> torch.Tensor:
+    """Kernel-side form of one quantized weight (interleaved codes + transposed bf16 scale/bias pairs).
+
+    Returns an opaque uint8 blob to be passed as `prepared=` to qlinear; build it once per weight.
+    """
     lib = _lib.load()
-    _cuda(scales, "scales")
-    scales, biases = scales.contiguous(), biases.contiguous()
-    n, g = scales.shape
-    packed = torch.empty((g, n), dtype=torch.uint32, device=scales.device)
-    rc = lib.mfx_qlinear_pack_scales(_ptr(scales), _ptr(biases), _dt(scales), n, g * group_size, group_size,
-                                     _ptr(packed), _stream())
-    _lib.check(rc, "mfx_qlinear_pack_scales")
-    return packed
+    _cuda(wq, "wq")
+    wq, scales, biases = wq.contiguous(), scales.contiguous(), biases.contiguous()
+    n = wq.shape[0]
+    k = wq.shape[1] * 32 // bits
+    nbytes = lib.mfx_qlinear_prepared_bytes(n, k, bits, group_size)
+    if nbytes == 0:
+        _lib.check(-3 if (bits not in (4, 8) or group_size != 64) else -1, "prepare_qlinear")
+    blob = torch.empty(nbytes, dtype=torch.uint8, device=wq.device)
+    rc = lib.mfx_qlinear_prepare(_ptr(wq), _ptr(scales), _ptr(biases), _dt(scales), n, k, bits, group_size,
+                                 _ptr(blob), nbytes, _stream())
+    _lib.check(rc, "mfx_qlinear_prepare")
+    return blob
 
 
 def _rows_view(t: torch.Tensor, name: str):
@@ -117,14 +125,14 @@ def qlinear(x: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, biases: tor
             bias: torch.Tensor | None = None, *, bits: int = 4, group_size: int = 64, epilogue: str | None = None,
             gate: torch.Tensor | None = None, residual: torch.Tensor | None = None,
             out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
-            sb_packed: torch.Tensor | None = None) -> torch.Tensor:
+            prepared: torch.Tensor | None = None) -> torch.Tensor:
     """nn.QuantizedLinear.__call__: y[..., N] = x[..., K] . dequant(wq)^T + bias, with optional fused epilogue.
 
     x is [rows, K] or [batch, rows, K] (bf16; row/batch strides may be arbitrary multiples of 8
     elements, the last dim must be dense). `out`, when given, may be a strided view of the same
     leading shape. epilogue "gate_residual" computes residual + gate[batch] * y with gate [batch, N].
-    `sb_packed` is the cached result of pack_scales(scales, biases); without it the scales are packed
-    into a scratch tensor on every call.
+    `prepared` is the cached result of prepare_qlinear(wq, scales, biases); without it the weight is
+    prepared into a scratch tensor on every call.
     """
     lib = _lib.load()
     _cuda(x, "x")
@@ -138,10 +146,10 @@ def qlinear(x: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, biases: tor
     n = wq.shape[0]
     if wq.shape[1] * 32 // bits != k:
         raise ValueError(f"x has K={k} but the packed weight encodes K={wq.shape[1] * 32 // bits}")
-    wq = wq.contiguous()
-    if sb_packed is None:
-        scales, biases = scales.contiguous(), biases.contiguous()
-        workspace = torch.empty((k // group_size, n), dtype=torch.uint32, device=x.device)
+    if prepared is None:
+        wq, scales, biases = wq.contiguous(), scales.contiguous(), biases.contiguous()
+        workspace = torch.empty(lib.mfx_qlinear_prepared_bytes(n, k, bits, group_size), dtype=torch.uint8,
+                                device=x.device)
     if out is None:
         od = out_dtype or (residual.dtype if residual is not None else torch.bfloat16)
         out = torch.empty((*xv.shape[:-1], n), dtype=od, device=x.device)
@@ -154,14 +162,14 @@ def qlinear(x: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, biases: tor
     a = QLinearArgs()
     a.x, a.x_row_stride, a.x_batch_stride = xv.data_ptr(), x_rs, x_bs
     a.rows, a.batch, a.K, a.N = rows, batch, k, n
-    a.wq, a.bits, a.group_size = wq.data_ptr(), bits, group_size
-    if sb_packed is None:
-        a.scales, a.biases, a.sb_dtype = scales.data_ptr(), biases.data_ptr(), _dt(scales)
-        a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel() * 4
+    a.bits, a.group_size = bits, group_size
+    if prepared is None:
+        a.wq, a.scales, a.biases, a.sb_dtype = wq.data_ptr(), scales.data_ptr(), biases.data_ptr(), _dt(scales)
+        a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel()
     else:
-        if sb_packed.shape != (k // group_size, n) or not sb_packed.is_contiguous():
-            raise ValueError("sb_packed must be the contiguous [K/64, N] result of pack_scales")
-        a.sb_packed = sb_packed.data_ptr()
+        if prepared.dtype != torch.uint8 or prepared.numel() != lib.mfx_qlinear_prepared_bytes(n, k, bits, group_size):
+            raise ValueError("prepared must be the blob prepare_qlinear returned for this weight")
+        a.prepared = prepared.data_ptr()
     if bias is not None:
         bias = bias.contiguous()
         a.bias, a.bias_dtype = bias.data_ptr(), _dt(bias)

@@ -51,7 +51,8 @@ def test_argument_validation_needs_no_gpu(lib_built):
     a.bits = 5
     assert lib.mfx_qlinear_ex(a, None) == -3
     a.bits = 4
-    a.workspace_bytes = 16  # too small for N * K/64 * 4
+    a.workspace_bytes = 16  # too small for the prepared form of the weight
     assert lib.mfx_qlinear_ex(a, None) == -1
-    assert lib.mfx_qlinear_workspace_bytes(12288, 3072, 64) == 12288 * 48 * 4
-    assert lib.mfx_qlinear_workspace_bytes(12288, 3000, 64) == 0
+    assert lib.mfx_qlinear_prepared_bytes(12288, 3072, 4, 64) == 12288 * 3072 // 2 + 12288 * 48 * 4
+    assert lib.mfx_qlinear_prepared_bytes(12288, 3000, 4, 64) == 0
+    assert lib.mfx_qlinear_prepared_bytes(10, 64, 4, 64) == 512 + 40  # 320 code bytes padded to 256s + pairs
