@@ -89,7 +89,7 @@ int mfx_qlinear_prepare(const uint32_t* wq, const void* scales, const void* bias
  * src/mflux/models/flux/model/flux_transformer/joint_attention.py:14-21, feed_forward.py:8-9,
  * single_transformer_block.py:14-15.
  * y[M, N] = x[M, K] . dequant(wq)^T + bias.  x bf16 with row stride ldx (elements, multiple of 8);
- * y bf16 or f32 with row stride ldy; bias nullable. K % 64 == 0, N % 4 == 0.
+ * y bf16 or f32 with row stride ldy; bias nullable. K % 64 == 0, N % 8 == 0.
  * workspace: caller-owned scratch of mfx_qlinear_prepared_bytes(N, K, bits, 64) bytes, 256-byte aligned;
  * the call first prepares the weight into it (see above), then runs the matmul, both on `stream`. */
 int mfx_qlinear(const void* x, int64_t M, int64_t K, int64_t ldx, const uint32_t* wq, const void* scales,

@@ -44,7 +44,7 @@ enum : int {
 };
 
 #ifndef MFX_SPIN_LIMIT
-#define MFX_SPIN_LIMIT (1u << 20)  // polls of mbarrier.try_wait (each suspends up to ~10 us): seconds at most
+#define MFX_SPIN_LIMIT (1u << 24)  // polls of mbarrier.try_wait (each may suspend ~1 us): seconds at most
 #endif
 
 __device__ __forceinline__ void record_failure(int code) { atomicCAS(&g_device_status, 0, code); }
@@ -76,15 +76,14 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-// One poll: suspends the thread in hardware until the phase completes or ~10 us pass.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(10000u)
+      : "r"(bar), "r"(parity)
       : "memory");
   return ok != 0;
 }
@@ -97,12 +96,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int cod
   return false;
 }
 
-// Same, for waits that are off the critical path (a whole main loop): back off with nanosleep so
-// the polling warp leaves the issue slots to the math warps.
+// Same, for waits that are off the critical path (a whole main loop, a ring with several free
+// stages): back off with nanosleep so the polling warp leaves the issue slots to the math warps.
 __device__ __forceinline__ bool mbar_wait_sleep(uint32_t bar, uint32_t parity, int code) {
   for (uint32_t i = 0; i < MFX_SPIN_LIMIT; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    __nanosleep(128);
+    __nanosleep(i < 64 ? 32 : 256);
   }
   record_failure(code);
   return false;
@@ -211,17 +210,6 @@ __device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r
       "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
       ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
         "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]),
-        "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]),
-        "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }

@@ -4,43 +4,36 @@
 // group_size=64, bits) for every nn.Linear of the transformer blocks of the reference
 // (e.g. src/mflux/models/flux/model/flux_transformer/joint_attention.py:14-21, feed_forward.py:8-9).
 //
-// The kernel computes the transposed product  D[n, m] = sum_k W^[n, k] X[m, k]  so that the dequantized
-// weights are the A operand of tcgen05.mma and can live in tensor memory: they never touch shared
-// memory, which is the scarce resource (tensor-core operand reads, TMA writes and ld/st share it).
 // One persistent CTA per SM, 512 threads, warp-specialised:
-//   warp 0      TMA producer: per 64-wide k-block (= one quantization group) the X tile [192 x 64] bf16
-//               (128-byte swizzle, the B operand), the packed codes of 128 weight rows and their
-//               (scale, bias) pairs
-//   warp 1      allocates TMEM, issues tcgen05.mma (M=128 weight rows, N=192 activation rows, K=16)
-//   warps 4-7   epilogue: tcgen05.ld (lane = output column n) -> bias / activation / gated residual ->
-//               global; a warp writes 32 consecutive n per activation row
-//   warps 8-15  dequantizers: codes (smem) -> bf16 by exponent-magic + one fma with the group's scale
-//               and bias -> tcgen05.st into the A-operand ring in TMEM (lane = weight row)
-// TMEM columns: 2 accumulator stages of 192 + 4 A-operand stages of 32 = 512. The epilogue of tile i
-// overlaps the main loop of tile i+1. All mbarrier waits are bounded.
+//   warp 0      TMA producer: X tile [128 x 64] bf16 (128-byte swizzle) and the packed weight tile
+//               [256 rows x 64 codes] per k-block, 64 = one quantization group
+//   warp 1      allocates TMEM, issues tcgen05.mma (M=128, N=256, K=16, fp32 accumulate in TMEM)
+//   warps 4-7   epilogue: tcgen05.ld -> bias / activation / gated residual -> global
+//   warps 8-15  dequantizers: packed codes (smem) -> bf16 via exponent-magic + one fma with the
+//               group's scale and bias -> B operand tile in the 128-byte-swizzled K-major layout
+// Two accumulator stages (2 x 256 TMEM columns) let the epilogue of tile i overlap the main loop of
+// tile i+1. All mbarrier waits are bounded.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
-#include <stdlib.h>
 #include "host_util.cuh"
 #include "ptx.cuh"
 
 namespace mfx {
 namespace qmm {
 
-constexpr int BN = 128;   // weight rows (output columns) per tile = MMA M
-constexpr int BM = 192;   // activation rows per tile = MMA N
-constexpr int BK = 64;    // one quantization group
-constexpr int SD = 4;     // stages of the dequantized A-operand ring in TMEM
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int SD = 3;  // stages of the dequantized-weight ring
 constexpr int NUM_THREADS = 512;
 constexpr int NUM_DQ_WARPS = 8;
 constexpr int FIRST_DQ_WARP = 8;
 constexpr int FIRST_EPI_WARP = 4;
-constexpr int X_TILE_BYTES = BM * BK * 2;  // 24 KiB
-constexpr int SB_TILE_BYTES = BN * 4;      // one bf16 (scale, bias) pair per weight row
+constexpr int X_TILE_BYTES = BM * BK * 2;   // 16 KiB
+constexpr int WD_TILE_BYTES = BN * BK * 2;  // 32 KiB
+constexpr int SB_TILE_BYTES = BN * 4;         // one bf16 (scale, bias) pair per weight row
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t TMEM_A_COL0 = 2 * BM;   // A-operand ring starts after the two accumulators
-constexpr uint32_t A_STAGE_COLS = BK / 2;  // 64 bf16 = 32 columns of 32 bits
 
 struct Params {
   int rows, batch, N, K;
@@ -55,16 +48,17 @@ struct Params {
   int64_t res_row_stride, res_batch_stride;
   void* y;
   int64_t y_row_stride, y_batch_stride;
-  int dbg;
 };
 
 template <int BITS, int ST>
 struct Smem {
   static constexpr int WQ_TILE_BYTES = BN * BK * BITS / 8;
   static constexpr int OFF_X = 0;
-  static constexpr int OFF_WQ = OFF_X + ST * X_TILE_BYTES;
-  static constexpr int OFF_SB = OFF_WQ + ST * WQ_TILE_BYTES;
-  static constexpr int OFF_BAR = OFF_SB + ST * SB_TILE_BYTES;
+  static constexpr int OFF_WD = OFF_X + ST * X_TILE_BYTES;
+  static constexpr int OFF_WQ = OFF_WD + SD * WD_TILE_BYTES;
+  static constexpr int OFF_SB = OFF_WQ + ST * WQ_TILE_BYTES;   // packed (scale, bias) pairs, 256 x 4 B per stage
+  static constexpr int OFF_VEC = OFF_SB + ST * SB_TILE_BYTES;  // bias[2][256] + gate[2][256] floats
+  static constexpr int OFF_BAR = OFF_VEC + 4 * BN * 4;
   static constexpr int NUM_BARS = 2 * ST + 2 * SD + 4;
   static constexpr int OFF_TMEM = OFF_BAR + NUM_BARS * 8;
   static constexpr int TOTAL = OFF_TMEM + 16;
@@ -142,17 +136,6 @@ __device__ __forceinline__ float gelu_tanh(float v) {
 }
 __device__ __forceinline__ float silu(float v) { return v / (1.0f + __expf(-v)); }
 
-template <typename OUT>
-__device__ __forceinline__ void store_out(OUT* p, float v) {
-  if constexpr (sizeof(OUT) == 4) *p = v;
-  else *p = __float2bfloat16_rn(v);
-}
-template <typename OUT>
-__device__ __forceinline__ float load_out(const OUT* p) {
-  if constexpr (sizeof(OUT) == 4) return *p;
-  else return __bfloat162float(*p);
-}
-
 template <int BITS, uint32_t WF, int ST, typename OUT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
@@ -163,8 +146,10 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
   const uint32_t x_s = smem_base + L::OFF_X;
+  const uint32_t wd_s = smem_base + L::OFF_WD;
   const uint32_t wq_s = smem_base + L::OFF_WQ;
   const uint32_t sb_s = smem_base + L::OFF_SB;
+  float* vec_s = reinterpret_cast<float*>(smem_gen + L::OFF_VEC);
   const uint32_t bar0 = smem_base + L::OFF_BAR;
   auto t_full = [&](int s) { return bar0 + 8u * s; };
   auto t_empty = [&](int s) { return bar0 + 8u * (ST + s); };
@@ -181,10 +166,10 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
   if (threadIdx.x == 0) {
     for (int s = 0; s < ST; ++s) {
       mbar_init(t_full(s), 1);
-      mbar_init(t_empty(s), 1 + NUM_DQ_WARPS / 2);  // MMA commit (X tile) + the dequantizer warps of one parity
+      mbar_init(t_empty(s), 1 + NUM_DQ_WARPS);
     }
     for (int s = 0; s < SD; ++s) {
-      mbar_init(d_full(s), NUM_DQ_WARPS / 2);
+      mbar_init(d_full(s), NUM_DQ_WARPS);
       mbar_init(d_empty(s), 1);
     }
     for (int s = 0; s < 2; ++s) {
@@ -217,7 +202,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
       const int r0 = (tm % p.tiles_m_per_sample) * BM;
       const int n0 = tn * BN;
       for (int kb = 0; kb < num_kb; ++kb) {
-        if (!mbar_wait(t_empty(st), ph ^ 1u, DEV_TIMEOUT_TMA_EMPTY)) {
+        if (!mbar_wait_sleep(t_empty(st), ph ^ 1u, DEV_TIMEOUT_TMA_EMPTY)) {
           ok = false;
           break;
         }
@@ -236,7 +221,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    constexpr uint32_t IDESC = make_idesc(WF, FMT_BF16, BN, BM);  // M = weight rows, N = activation rows
+    constexpr uint32_t IDESC = make_idesc(FMT_BF16, WF, BM, BN);
     int st = 0, sd = 0;
     uint32_t ph_t = 0, ph_d = 0;
     bool ok = true;
@@ -249,7 +234,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         break;
       }
       tc_fence_after();
-      const uint32_t d_tmem = tmem_base + a * BM;
+      const uint32_t d_tmem = tmem_base + a * BN;
       for (int kb = 0; kb < num_kb; ++kb) {
         if (!mbar_wait(t_full(st), ph_t, DEV_TIMEOUT_TMA_FULL) || !mbar_wait(d_full(sd), ph_d, DEV_TIMEOUT_DQ_FULL)) {
           ok = false;
@@ -257,12 +242,12 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         }
         tc_fence_after();
         if (lane == 0) {
-          const uint32_t a_tmem = tmem_base + TMEM_A_COL0 + sd * A_STAGE_COLS;
-          const uint64_t bdesc = smem_desc_sw128(x_s + st * X_TILE_BYTES);
+          const uint64_t adesc = smem_desc_sw128(x_s + st * X_TILE_BYTES);
+          const uint64_t bdesc = smem_desc_sw128(wd_s + sd * WD_TILE_BYTES);
 #pragma unroll
           for (int k4 = 0; k4 < BK / 16; ++k4) {
-            // A: 16 bf16 = 8 TMEM columns per K step; B: +32 bytes (>>4 = 2) inside the swizzle atom
-            if (!(p.dbg & 4)) umma_f16_ts(d_tmem, a_tmem + 8 * k4, bdesc + 2 * k4, IDESC, (kb | k4) != 0 ? 1u : 0u);
+            // +32 bytes (>>4 = 2) per 16-element K step inside the 128-byte swizzle atom
+            umma_f16_ss(d_tmem, adesc + 2 * k4, bdesc + 2 * k4, IDESC, (kb | k4) != 0 ? 1u : 0u);
           }
           umma_commit(t_empty(st));
           umma_commit(d_empty(sd));
@@ -281,107 +266,80 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     }
   } else if (warp >= FIRST_DQ_WARP) {
     // ------------------------------------------------------------ dequantizers
-    // Two groups of four warps take alternate k-blocks of the k-block stream, so each group has two
-    // MMA k-block times per block; inside a warp the shared-memory loads of its next block are issued
-    // while the tcgen05.st of the current one is in flight.
-    const int q = warp & 3;                       // TMEM lane quarter this warp may write
-    const int par = (warp - FIRST_DQ_WARP) >> 2;  // parity of the k-blocks this warp handles
-    const int row = q * 32 + lane;                // weight row inside the tile = TMEM lane
-    constexpr int ROW_BYTES = BK * BITS / 8;      // packed bytes per row per k-block
-    constexpr int RD_CHUNKS = ROW_BYTES / 16;     // 16-byte chunks per row: 2 (4 bits) or 4 (8 bits)
+    const int row = (warp - FIRST_DQ_WARP) * 32 + lane;  // row of the 256-row weight tile
+    constexpr int ROW_BYTES = BK * BITS / 8;              // packed bytes per row per k-block
+    constexpr int RD_CHUNKS = ROW_BYTES / 16;
     // The packed tile is loaded with the TMA swizzle whose span equals one row (32 B for 4 bits,
-    // 64 B for 8 bits): chunk c of row r sits at chunk c ^ ((r*ROW_BYTES >> 7) & mask), which spreads
-    // the reads of a quarter-warp over all banks. Offsets are per-thread constants.
+    // 64 B for 8 bits): 16-byte chunk c of row r sits at chunk c ^ ((r*ROW_BYTES >> 7) & mask), which
+    // spreads the per-row reads of a quarter-warp over all banks. Offsets are per-thread constants.
     const uint32_t rd_sw = (static_cast<uint32_t>(row * ROW_BYTES) >> 7) & (RD_CHUNKS - 1);
     const uint8_t* rd_base = smem_gen + L::OFF_WQ + row * ROW_BYTES;
     uint32_t rd_off[RD_CHUNKS];
 #pragma unroll
     for (int h = 0; h < RD_CHUNKS; ++h) rd_off[h] = (static_cast<uint32_t>(h) ^ rd_sw) << 4;
+    // B operand tile: 128-byte rows, 16-byte chunk c of row r at chunk c ^ (r & 7)
+    uint8_t* wr_base = smem_gen + L::OFF_WD + row * 128;
+    uint32_t wr_off[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) wr_off[c] = (static_cast<uint32_t>(c) ^ static_cast<uint32_t>(row & 7)) << 4;
     const uint32_t* sb_base = reinterpret_cast<const uint32_t*>(smem_gen + L::OFF_SB) + row;
-    const uint32_t a_tmem0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + TMEM_A_COL0;
-    static_assert(ST % 2 == 0 && SD % 2 == 0, "parity split needs even ring depths");
-
-    const int my_tiles = (p.total_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
-                         static_cast<int>(gridDim.x);
-    const int64_t total_g = static_cast<int64_t>(my_tiles) * num_kb;  // k-blocks this CTA streams
-    int st = par, sd = par;
+    int st = 0, sd = 0;
     uint32_t ph_t = 0, ph_d = 0;
-    uint4 cw[RD_CHUNKS];
-    uint32_t sbv = 0;
     bool ok = true;
-    if (par < total_g) {
-      ok = mbar_wait(t_full(st), ph_t, DEV_TIMEOUT_TMA_FULL);
-      if (ok) {
+    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait(t_full(st), ph_t, DEV_TIMEOUT_TMA_FULL) ||
+            !mbar_wait(d_empty(sd), ph_d ^ 1u, DEV_TIMEOUT_DQ_EMPTY)) {
+          ok = false;
+          break;
+        }
+        const uint32_t sbv = sb_base[st * (SB_TILE_BYTES / 4)];
+        const uint32_t s2 = __byte_perm(sbv, sbv, 0x1010);  // (scale, scale)
+        const uint32_t b2 = __byte_perm(sbv, sbv, 0x3232);  // (bias, bias)
         const uint8_t* src = rd_base + st * L::WQ_TILE_BYTES;
+        uint8_t* dst = wr_base + sd * WD_TILE_BYTES;
+        if (BITS == 4) {
 #pragma unroll
-        for (int h = 0; h < RD_CHUNKS; ++h) cw[h] = *reinterpret_cast<const uint4*>(src + rd_off[h]);
-        sbv = sb_base[st * (SB_TILE_BYTES / 4)];
-      }
-    }
-    for (int64_t g = par; g < total_g && ok; g += 2) {
-      const uint32_t s2 = __byte_perm(sbv, sbv, 0x1010);  // (scale, scale)
-      const uint32_t b2 = __byte_perm(sbv, sbv, 0x3232);  // (bias, bias)
-      uint32_t vals[32];  // the 64 dequantized k-values of this row, packed in pairs
-      if (p.dbg & 2) {
+          for (int h = 0; h < 2; ++h) {
+            const uint4 pk = *reinterpret_cast<const uint4*>(src + rd_off[h]);
+            const uint32_t wds[4] = {pk.x, pk.y, pk.z, pk.w};
 #pragma unroll
-        for (int i = 0; i < 32; ++i) vals[i] = cw[0].x + i;
-      } else
+            for (int j = 0; j < 4; ++j)
+              *reinterpret_cast<uint4*>(dst + wr_off[h * 4 + j]) = dequant_w4<WF>(wds[j], s2, b2);
+          }
+        } else {
 #pragma unroll
-      for (int h = 0; h < RD_CHUNKS; ++h) {
-        const uint32_t wds[4] = {cw[h].x, cw[h].y, cw[h].z, cw[h].w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (BITS == 4) {
-            const uint4 d = dequant_w4<WF>(wds[j], s2, b2);
-            vals[16 * h + 4 * j + 0] = d.x;
-            vals[16 * h + 4 * j + 1] = d.y;
-            vals[16 * h + 4 * j + 2] = d.z;
-            vals[16 * h + 4 * j + 3] = d.w;
-          } else {
-            const uint2 d = dequant_w8(wds[j], s2, b2);
-            vals[8 * h + 2 * j + 0] = d.x;
-            vals[8 * h + 2 * j + 1] = d.y;
+          for (int h = 0; h < 4; ++h) {
+            const uint4 pk = *reinterpret_cast<const uint4*>(src + rd_off[h]);
+            const uint2 lo0 = dequant_w8(pk.x, s2, b2);
+            const uint2 hi0 = dequant_w8(pk.y, s2, b2);
+            const uint2 lo1 = dequant_w8(pk.z, s2, b2);
+            const uint2 hi1 = dequant_w8(pk.w, s2, b2);
+            *reinterpret_cast<uint4*>(dst + wr_off[2 * h]) = make_uint4(lo0.x, lo0.y, hi0.x, hi0.y);
+            *reinterpret_cast<uint4*>(dst + wr_off[2 * h + 1]) = make_uint4(lo1.x, lo1.y, hi1.x, hi1.y);
           }
         }
-      }
-      // the packed codes are in registers: hand the TMA stage back
-      __syncwarp();
-      if (lane == 0) mbar_arrive(t_empty(st));
-      if (!mbar_wait(d_empty(sd), ph_d ^ 1u, DEV_TIMEOUT_DQ_EMPTY)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-      if (!(p.dbg & 8)) tmem_st_32x32(a_tmem0 + sd * A_STAGE_COLS, vals);
-      const int sd_cur = sd;
-      st += 2;
-      if (st >= ST) {
-        st -= ST;
-        ph_t ^= 1u;
-      }
-      sd += 2;
-      if (sd >= SD) {
-        sd -= SD;
-        ph_d ^= 1u;
-      }
-      if (g + 2 < total_g) {  // next block's loads overlap the tensor-memory store
-        if (!mbar_wait(t_full(st), ph_t, DEV_TIMEOUT_TMA_FULL)) {
-          ok = false;
-        } else {
-          const uint8_t* src = rd_base + st * L::WQ_TILE_BYTES;
-#pragma unroll
-          for (int h = 0; h < RD_CHUNKS; ++h) cw[h] = *reinterpret_cast<const uint4*>(src + rd_off[h]);
-          sbv = sb_base[st * (SB_TILE_BYTES / 4)];
+        fence_proxy_async_smem();  // make these generic-proxy writes visible to the tensor core
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(d_full(sd));
+          mbar_arrive(t_empty(st));
+        }
+        if (++st == ST) {
+          st = 0;
+          ph_t ^= 1u;
+        }
+        if (++sd == SD) {
+          sd = 0;
+          ph_d ^= 1u;
         }
       }
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(d_full(sd_cur));
     }
   } else if (warp >= FIRST_EPI_WARP) {
-    // ------------------------------------------------------------ epilogue (lane = output column)
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    // ------------------------------------------------------------ epilogue
+    const int q = warp & 3;            // TMEM lane quarter this warp may read
+    const int et = threadIdx.x - FIRST_EPI_WARP * 32;  // 0..127
+    const int row = q * 32 + lane;
     bool ok = true;
     int it = 0;
     for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++it) {
@@ -390,42 +348,77 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
       const int tm = tile % p.tiles_m;
       const int tn = tile / p.tiles_m;
       const int b = tm / p.tiles_m_per_sample;
-      const int r0 = (tm % p.tiles_m_per_sample) * BM;
-      const int n = tn * BN + q * 32 + lane;
-      const bool n_ok = n < p.N;
-      const float bias_v = (p.bias != nullptr && n_ok) ? load_scalar(p.bias, p.bias_dtype, n) : 0.f;
-      float gate_v = 0.f;
-      if (p.epilogue == MFX_EPI_GATE_RESIDUAL && n_ok)
-        gate_v = load_scalar(p.gate, p.gate_dtype, b * p.gate_batch_stride + n);
-      OUT* ycol = static_cast<OUT*>(p.y) + b * p.y_batch_stride + n;
-      const OUT* rcol = nullptr;
-      if (p.epilogue == MFX_EPI_GATE_RESIDUAL)
-        rcol = static_cast<const OUT*>(p.residual) + b * p.res_batch_stride + n;
+      const int r = (tm % p.tiles_m_per_sample) * BM + row;
+      const int n0 = tn * BN;
+      float* bias_s = vec_s + a * BN;
+      float* gate_s = vec_s + 2 * BN + a * BN;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int c = et + 128 * h;
+        const int n = n0 + c;
+        bias_s[c] = (p.bias != nullptr && n < p.N) ? load_scalar(p.bias, p.bias_dtype, n) : 0.f;
+        if (p.epilogue == MFX_EPI_GATE_RESIDUAL)
+          gate_s[c] = (n < p.N) ? load_scalar(p.gate, p.gate_dtype, b * p.gate_batch_stride + n) : 0.f;
+      }
+      named_bar_sync(1, 128);
       if (!mbar_wait_sleep(acc_full(a), aph, DEV_TIMEOUT_ACC_FULL)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + a * BM;
-      const int rows_here = min(BM, p.rows - r0);  // activation rows of this tile that exist
+      const bool row_ok = r < p.rows;
+      OUT* yrow = static_cast<OUT*>(p.y) + b * p.y_batch_stride + static_cast<int64_t>(r) * p.y_row_stride + n0;
+      const OUT* rrow = nullptr;
+      if (p.epilogue == MFX_EPI_GATE_RESIDUAL)
+        rrow = static_cast<const OUT*>(p.residual) + b * p.res_batch_stride +
+               static_cast<int64_t>(r) * p.res_row_stride + n0;
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + a * BN;
 #pragma unroll 1
-      for (int c = 0; c < BM / 32; ++c) {
-        if (c * 32 >= rows_here) break;  // warp-uniform
+      for (int c = 0; c < BN / 32; ++c) {
         uint32_t acc[32];
         tmem_ld_32x32(t_addr + c * 32, acc);
         tmem_ld_wait();
-        if (n_ok) {
+        if (row_ok) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int r = c * 32 + j;
-            if (r < rows_here) {
-              float v = __uint_as_float(acc[j]) + bias_v;
-              if (p.epilogue == MFX_EPI_GELU_ERF) v = gelu_erf(v);
-              else if (p.epilogue == MFX_EPI_GELU_TANH) v = gelu_tanh(v);
-              else if (p.epilogue == MFX_EPI_SILU) v = silu(v);
-              else if (p.epilogue == MFX_EPI_GATE_RESIDUAL)
-                v = load_out<OUT>(rcol + static_cast<int64_t>(r0 + r) * p.res_row_stride) + gate_v * v;
-              if (!(p.dbg & 1)) store_out<OUT>(ycol + static_cast<int64_t>(r0 + r) * p.y_row_stride, v);
+          for (int g8 = 0; g8 < 4; ++g8) {
+            const int col = c * 32 + g8 * 8;
+            if (n0 + col >= p.N) break;
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(acc[g8 * 8 + j]) + bias_s[col + j];
+            if (p.epilogue == MFX_EPI_GELU_ERF) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = gelu_erf(v[j]);
+            } else if (p.epilogue == MFX_EPI_GELU_TANH) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = gelu_tanh(v[j]);
+            } else if (p.epilogue == MFX_EPI_SILU) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = silu(v[j]);
+            } else if (p.epilogue == MFX_EPI_GATE_RESIDUAL) {
+              float rs[8];
+              if constexpr (sizeof(OUT) == 4) {
+                const float4 r0 = *reinterpret_cast<const float4*>(rrow + col);
+                const float4 r1 = *reinterpret_cast<const float4*>(rrow + col + 4);
+                rs[0] = r0.x; rs[1] = r0.y; rs[2] = r0.z; rs[3] = r0.w;
+                rs[4] = r1.x; rs[5] = r1.y; rs[6] = r1.z; rs[7] = r1.w;
+              } else {
+                const uint4 raw = *reinterpret_cast<const uint4*>(rrow + col);
+                const __nv_bfloat16* hb = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) rs[j] = __bfloat162float(hb[j]);
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = rs[j] + gate_s[col + j] * v[j];
+            }
+            if constexpr (sizeof(OUT) == 4) {
+              *reinterpret_cast<float4*>(yrow + col) = make_float4(v[0], v[1], v[2], v[3]);
+              *reinterpret_cast<float4*>(yrow + col + 4) = make_float4(v[4], v[5], v[6], v[7]);
+            } else {
+              __nv_bfloat162 h[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+              *reinterpret_cast<uint4*>(yrow + col) = *reinterpret_cast<uint4*>(h);
             }
           }
         }
@@ -571,7 +564,7 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
   if (!a.x || !a.y) return MFX_ERR_NULL;
   if ((a.bits != 4 && a.bits != 8) || a.group_size != 64) return MFX_ERR_UNSUPPORTED_BITS;
   if (a.rows <= 0 || a.batch <= 0 || a.N <= 0 || a.K <= 0) return MFX_ERR_SHAPE;
-  if (a.K % 64 != 0 || a.N % 4 != 0) return MFX_ERR_SHAPE;
+  if (a.K % 64 != 0 || a.N % 8 != 0) return MFX_ERR_SHAPE;
   if (a.rows > (1 << 30) || a.N > (1 << 30) || a.K > (1 << 30) || a.batch > (1 << 20)) return MFX_ERR_TOO_LARGE;
   if (a.bias && !valid_dtype(a.bias_dtype)) return MFX_ERR_DTYPE;
   if (a.y_dtype != MFX_BF16 && a.y_dtype != MFX_F32) return MFX_ERR_DTYPE;
@@ -586,10 +579,14 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
   if (a.epilogue == MFX_EPI_GATE_RESIDUAL) {
     if (!a.gate || !a.residual) return MFX_ERR_NULL;
     if (!valid_dtype(a.gate_dtype)) return MFX_ERR_DTYPE;
-    if (reinterpret_cast<uintptr_t>(a.residual) % dtype_size(a.y_dtype) != 0) return MFX_ERR_ALIGN;
+    const size_t es = dtype_size(a.y_dtype);
+    if (!aligned16(a.residual) || (a.res_row_stride * es) % 16 != 0 || (a.res_batch_stride * es) % 16 != 0)
+      return MFX_ERR_ALIGN;
   }
   {
-    if (reinterpret_cast<uintptr_t>(a.y) % dtype_size(a.y_dtype) != 0) return MFX_ERR_ALIGN;
+    const size_t es = dtype_size(a.y_dtype);
+    if (!aligned16(a.y) || (a.y_row_stride * es) % 16 != 0 || (a.y_batch_stride * es) % 16 != 0)
+      return MFX_ERR_ALIGN;
     if (!aligned16(a.x) || (a.x_row_stride * 2) % 16 != 0 || (a.x_batch_stride * 2) % 16 != 0) return MFX_ERR_ALIGN;
   }
   if (int rc = check_arch()) return rc;
@@ -610,7 +607,7 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
     const uint64_t bstride = a.batch > 1 ? static_cast<uint64_t>(a.x_batch_stride) * 2
                                          : static_cast<uint64_t>(a.x_row_stride) * 2 * a.rows;
     const uint64_t strides[2] = {static_cast<uint64_t>(a.x_row_stride) * 2, bstride};
-    const uint32_t box[3] = {BK, BM, 1};  // activation rows are the MMA N dimension
+    const uint32_t box[3] = {BK, BM, 1};
     if (int rc = encode_tmap(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a.x, dims, strides, box,
                              CU_TENSOR_MAP_SWIZZLE_128B))
       return rc;
@@ -655,15 +652,14 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
   p.y = a.y;
   p.y_row_stride = a.y_row_stride;
   p.y_batch_stride = a.y_batch_stride;
-  { const char* e = getenv("MFX_QMM_DEBUG"); p.dbg = e ? atoi(e) : 0; }
   const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
   const bool f32 = a.y_dtype == MFX_F32;
   if (a.bits == 4) {
-    return f32 ? launch<4, FMT_BF16, 6, float>(tx, tw, tsb, p, grid, st)
-               : launch<4, FMT_BF16, 6, __nv_bfloat16>(tx, tw, tsb, p, grid, st);
+    return f32 ? launch<4, FMT_BF16, 4, float>(tx, tw, tsb, p, grid, st)
+               : launch<4, FMT_BF16, 4, __nv_bfloat16>(tx, tw, tsb, p, grid, st);
   }
-  return f32 ? launch<8, FMT_BF16, 6, float>(tx, tw, tsb, p, grid, st)
-             : launch<8, FMT_BF16, 6, __nv_bfloat16>(tx, tw, tsb, p, grid, st);
+  return f32 ? launch<8, FMT_BF16, 3, float>(tx, tw, tsb, p, grid, st)
+             : launch<8, FMT_BF16, 3, __nv_bfloat16>(tx, tw, tsb, p, grid, st);
 }
 
 }  // namespace qmm

@@ -60,7 +60,7 @@ def test_sweep_shapes(lib_built, bits, nk, m):
 
 
 @pytest.mark.parametrize("bits", [4, 8])
-@pytest.mark.parametrize("mnk", [(1, 64, 64), (7, 8, 128), (129, 260, 192), (300, 1000, 320), (128, 256, 64),
+@pytest.mark.parametrize("mnk", [(1, 64, 64), (7, 8, 128), (129, 264, 192), (300, 1000, 320), (128, 256, 64),
                                  (513, 520, 3840)])
 def test_ragged_edges(lib_built, bits, mnk):
     """Row, column and depth tails: M not a multiple of 128, N not a multiple of 256, one k-block."""
