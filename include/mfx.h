@@ -129,6 +129,58 @@ typedef struct mfx_qlinear_args {
 } mfx_qlinear_args;
 int mfx_qlinear_ex(const mfx_qlinear_args* args /* host */, void* stream);
 
+/* Replaces nn.LayerNorm(affine=False, eps)(x) * (1 + scale) + shift
+ * (src/mflux/models/flux/model/flux_transformer/ada_layer_norm_zero.py:20, ada_layer_norm_zero_single.py:17,
+ * joint_transformer_block.py:86-87, ada_layer_norm_continuous.py:19) and, with rms=1, nn.RMSNorm(weight, eps)
+ * optionally followed by the same modulation (z_image_transformer/transformer_block.py:29-34,
+ * qwen_transformer_rms_norm.py:11-23). x is `batch` samples of `rows` rows of D values (f32 or bf16),
+ * shift/scale are [batch, D] (nullable), weight is [D] (nullable); y is bf16. D % 8 == 0, D <= 4096. */
+typedef struct mfx_norm_args {
+  const void* x;
+  int x_dtype;
+  int64_t x_row_stride, x_batch_stride;
+  int64_t rows, batch, D;
+  const void* shift;
+  const void* scale;
+  int mod_dtype;
+  int64_t mod_batch_stride;
+  const void* weight;
+  int weight_dtype;
+  float eps;
+  int rms; /* 0 = LayerNorm with biased variance, 1 = RMSNorm */
+  void* y; /* bf16 */
+  int64_t y_row_stride, y_batch_stride;
+} mfx_norm_args;
+int mfx_norm_modulate(const mfx_norm_args* args /* host */, void* stream);
+
+/* Replaces AttentionUtils.process_qkv's per-head nn.RMSNorm(128) on Q and K plus AttentionUtils.apply_rope
+ * (src/mflux/models/flux/model/flux_transformer/common/attention_utils.py:30-34,75-80), in place on the
+ * fused activation buffer qkv [batch, seq, >= 3*heads*128] bf16 laid out q | k | v per token. Rows
+ * s < split use the (qw_a, kw_a) norm weights (text stream: norm_added_q/k), the others (qw_b, kw_b).
+ * cos_sin is f32 [seq, 64, 2] = (cos, sin) of each rotated (even, odd) pair (embed_nd.py:19-31). */
+int mfx_qknorm_rope(void* qkv, int64_t row_stride, int64_t batch_stride, int64_t seq, int64_t batch, int heads,
+                    int64_t split, const void* qw_a, const void* kw_a, const void* qw_b, const void* kw_b,
+                    int w_dtype, const float* cos_sin, float eps, void* stream);
+
+/* Replaces mx.fast.scaled_dot_product_attention(q, k, v, scale) without mask
+ * (attention_utils.py:48-52) for head dimension 128: softmax(Q K^T * scale) V per (sample, head).
+ * q, k, v are bf16 views [batch, seq, heads, 128] given by their token and batch strides (elements), e.g.
+ * the three sections of the fused qkv buffer; out is bf16 [batch, seq, heads*128] with its own strides,
+ * which is the layout AttentionUtils.compute_attention returns after its transpose + reshape. */
+int mfx_fmha(const void* q, const void* k, const void* v, int64_t qkv_row_stride, int64_t qkv_batch_stride,
+             int64_t seq, int64_t batch, int heads, float scale, void* out, int64_t out_row_stride,
+             int64_t out_batch_stride, void* stream);
+
+/* out = act(a + b + c) elementwise (b, c nullable; act 0 = identity, 1 = SiLU): the conditioning-vector
+ * arithmetic of time_text_embed.py:25-31 and the nn.silu in front of every AdaLN linear. */
+int mfx_vec_sum_act(const void* a, const void* b, const void* c, int in_dtype, int act, void* out, int out_dtype,
+                    int64_t n, void* stream);
+
+/* Replaces LinearScheduler.step (src/mflux/models/common/schedulers/linear_scheduler.py:56-58):
+ * out = latents + noise * dt, in the latents' dtype. */
+int mfx_euler_step(const void* latents, int lat_dtype, const void* noise, int noise_dtype, float dt, void* out,
+                   int64_t n, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -59,6 +59,31 @@ class QLinearArgs(ctypes.Structure):
     ]
 
 
+class NormArgs(ctypes.Structure):
+    """struct mfx_norm_args (include/mfx.h)."""
+
+    _fields_ = [
+        ("x", c_void_p),
+        ("x_dtype", c_int),
+        ("x_row_stride", c_int64),
+        ("x_batch_stride", c_int64),
+        ("rows", c_int64),
+        ("batch", c_int64),
+        ("D", c_int64),
+        ("shift", c_void_p),
+        ("scale", c_void_p),
+        ("mod_dtype", c_int),
+        ("mod_batch_stride", c_int64),
+        ("weight", c_void_p),
+        ("weight_dtype", c_int),
+        ("eps", ctypes.c_float),
+        ("rms", c_int),
+        ("y", c_void_p),
+        ("y_row_stride", c_int64),
+        ("y_batch_stride", c_int64),
+    ]
+
+
 # name -> (restype, argtypes); every symbol include/mfx.h declares
 SIGNATURES = {
     "mfx_version": (c_int, []),
@@ -84,6 +109,19 @@ SIGNATURES = {
          c_void_p, c_int, c_void_p, c_int, c_int64, c_void_p, ctypes.c_size_t, c_void_p],
     ),
     "mfx_qlinear_ex": (c_int, [ctypes.POINTER(QLinearArgs), c_void_p]),
+    "mfx_norm_modulate": (c_int, [ctypes.POINTER(NormArgs), c_void_p]),
+    "mfx_qknorm_rope": (
+        c_int,
+        [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+         c_void_p, ctypes.c_float, c_void_p],
+    ),
+    "mfx_fmha": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, ctypes.c_float, c_void_p, c_int64,
+         c_int64, c_void_p],
+    ),
+    "mfx_vec_sum_act": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int64, c_void_p]),
+    "mfx_euler_step": (c_int, [c_void_p, c_int, c_void_p, c_int, ctypes.c_float, c_void_p, c_int64, c_void_p]),
 }
 
 _lib = None

@@ -5,6 +5,9 @@ namespace mfx {
 namespace qmm {
 int read_status(int* out, cudaStream_t stream);
 }
+namespace fmha {
+int read_status(int* out, cudaStream_t stream);
+}
 }  // namespace mfx
 
 extern "C" {
@@ -12,11 +15,12 @@ extern "C" {
 int mfx_poll_device_status(int* status_out, void* stream) {
   if (!status_out) return MFX_ERR_NULL;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int v = 0;
-  if (mfx::qmm::read_status(&v, st) != 0) {
+  int v = 0, v2 = 0;
+  if (mfx::qmm::read_status(&v, st) != 0 || mfx::fmha::read_status(&v2, st) != 0) {
     mfx::set_cuda_error_text("reading the device status word failed");
     return MFX_ERR_CUDA;
   }
+  if (v == 0) v = v2;
   *status_out = v;
   return v == 0 ? MFX_OK : MFX_ERR_DEVICE_TIMEOUT;
 }

@@ -189,3 +189,131 @@ def qlinear(x: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, biases: tor
     rc = lib.mfx_qlinear_ex(byref(a), _stream())
     _lib.check(rc, "mfx_qlinear_ex")
     return ret
+
+
+def norm_modulate(x: torch.Tensor, shift: torch.Tensor | None = None, scale: torch.Tensor | None = None, *,
+                  weight: torch.Tensor | None = None, eps: float = 1e-6, rms: bool = False,
+                  out: torch.Tensor | None = None) -> torch.Tensor:
+    """LayerNorm(affine=False) or RMSNorm(weight) over the last dim, then * (1 + scale) + shift per sample.
+
+    x is [rows, D] or [batch, rows, D] (f32 or bf16, strided views allowed); shift/scale are [batch, D];
+    the result is bf16 (optionally written into the strided view `out`).
+    """
+    lib = _lib.load()
+    _cuda(x, "x")
+    xv, rows, batch, x_rs, x_bs = _rows_view(x, "x")
+    d = xv.shape[-1]
+    if out is None:
+        out = torch.empty(xv.shape, dtype=torch.bfloat16, device=x.device)
+        ret = out.reshape(x.shape)
+    else:
+        ret = out
+    ov, o_rows, o_batch, o_rs, o_bs = _rows_view(out, "out")
+    if ov.data_ptr() != out.data_ptr() or (o_rows, o_batch) != (rows, batch) or ov.dtype != torch.bfloat16:
+        raise ValueError("out must be a bf16 view shaped like x with a dense last dim")
+    a = _lib.NormArgs()
+    a.x, a.x_dtype, a.x_row_stride, a.x_batch_stride = xv.data_ptr(), _dt(xv), x_rs, x_bs
+    a.rows, a.batch, a.D = rows, batch, d
+    mods = [t for t in (shift, scale) if t is not None]
+    if mods:
+        md = mods[0]
+        for t in mods:
+            if t.dtype != md.dtype or t.shape[-1] != d or t.stride(-1) != 1 or t.reshape(-1, d).shape[0] != batch:
+                raise ValueError("shift/scale must be [batch, D] views of one dtype with a dense last dim")
+        strides = {t.stride(0) if t.dim() == 2 else 0 for t in mods}
+        if len(strides) != 1:
+            raise ValueError("shift and scale must share their batch stride")
+        a.mod_dtype, a.mod_batch_stride = _dt(md), strides.pop()
+        a.shift = 0 if shift is None else shift.data_ptr()
+        a.scale = 0 if scale is None else scale.data_ptr()
+    if weight is not None:
+        weight = weight.contiguous()
+        a.weight, a.weight_dtype = weight.data_ptr(), _dt(weight)
+    a.eps, a.rms = eps, int(rms)
+    a.y, a.y_row_stride, a.y_batch_stride = ov.data_ptr(), o_rs, o_bs
+    _lib.check(lib.mfx_norm_modulate(byref(a), _stream()), "mfx_norm_modulate")
+    return ret
+
+
+def qknorm_rope(qkv: torch.Tensor, heads: int, q_weight_a: torch.Tensor, k_weight_a: torch.Tensor,
+                q_weight_b: torch.Tensor, k_weight_b: torch.Tensor, split: int, cos_sin: torch.Tensor,
+                eps: float = 1e-5) -> torch.Tensor:
+    """In place on qkv [batch, seq, 3*heads*128] (bf16): per-head RMSNorm(128) of Q and K, then RoPE.
+
+    Rows s < split use the `_a` weights (text stream), the others the `_b` weights. cos_sin is f32
+    [seq, 64, 2] holding (cos, sin) of every rotated (even, odd) pair.
+    """
+    lib = _lib.load()
+    _cuda(qkv, "qkv")
+    if qkv.dtype != torch.bfloat16 or qkv.dim() != 3 or qkv.stride(-1) != 1:
+        raise ValueError("qkv must be a bf16 [batch, seq, 3*heads*128] view with a dense last dim")
+    batch, seq, width = qkv.shape
+    if width != 3 * heads * 128:
+        raise ValueError("last dim must be 3 * heads * 128")
+    ws = [w.contiguous() for w in (q_weight_a, k_weight_a, q_weight_b, k_weight_b)]
+    if len({w.dtype for w in ws}) != 1 or any(w.numel() != 128 for w in ws):
+        raise ValueError("norm weights must be four [128] tensors of one dtype")
+    cos_sin = cos_sin.contiguous()
+    if cos_sin.dtype != torch.float32 or tuple(cos_sin.shape) != (seq, 64, 2):
+        raise ValueError("cos_sin must be f32 [seq, 64, 2]")
+    rc = lib.mfx_qknorm_rope(_ptr(qkv), qkv.stride(1), qkv.stride(0), seq, batch, heads, split, _ptr(ws[0]),
+                             _ptr(ws[1]), _ptr(ws[2]), _ptr(ws[3]), _dt(ws[0]), _ptr(cos_sin), eps, _stream())
+    _lib.check(rc, "mfx_qknorm_rope")
+    return qkv
+
+
+def fmha(qkv: torch.Tensor, heads: int, scale: float | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """softmax(Q K^T * scale) V for head dim 128 on the fused buffer qkv [batch, seq, 3*heads*128] (bf16).
+
+    Returns (or fills the strided view `out`) bf16 [batch, seq, heads*128], the layout the reference
+    hands to the output projection.
+    """
+    lib = _lib.load()
+    _cuda(qkv, "qkv")
+    if qkv.dtype != torch.bfloat16 or qkv.dim() != 3 or qkv.stride(-1) != 1:
+        raise ValueError("qkv must be a bf16 [batch, seq, 3*heads*128] view with a dense last dim")
+    batch, seq, width = qkv.shape
+    hd = heads * 128
+    if width != 3 * hd:
+        raise ValueError("last dim must be 3 * heads * 128")
+    if out is None:
+        out = torch.empty((batch, seq, hd), dtype=torch.bfloat16, device=qkv.device)
+    if out.dtype != torch.bfloat16 or tuple(out.shape) != (batch, seq, hd) or out.stride(-1) != 1:
+        raise ValueError("out must be a bf16 [batch, seq, heads*128] view with a dense last dim")
+    es = qkv.element_size()
+    base = qkv.data_ptr()
+    rc = lib.mfx_fmha(c_void_p(base), c_void_p(base + hd * es), c_void_p(base + 2 * hd * es), qkv.stride(1),
+                      qkv.stride(0), seq, batch, heads, float(scale if scale is not None else 128 ** -0.5),
+                      _ptr(out), out.stride(1), out.stride(0), _stream())
+    _lib.check(rc, "mfx_fmha")
+    return out
+
+
+def vec_sum_act(a: torch.Tensor, b: torch.Tensor | None = None, c: torch.Tensor | None = None, act: str | None = None,
+                out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """act(a + b + c) elementwise; act is None or "silu"."""
+    lib = _lib.load()
+    _cuda(a, "a")
+    ts = [t.contiguous() if t is not None else None for t in (a, b, c)]
+    for t in ts[1:]:
+        if t is not None and (t.shape != ts[0].shape or t.dtype != ts[0].dtype):
+            raise ValueError("operands must share shape and dtype")
+    out = torch.empty(ts[0].shape, dtype=out_dtype, device=a.device)
+    rc = lib.mfx_vec_sum_act(_ptr(ts[0]), _ptr(ts[1]), _ptr(ts[2]), _dt(ts[0]), 1 if act == "silu" else 0, _ptr(out),
+                             _dt(out), out.numel(), _stream())
+    _lib.check(rc, "mfx_vec_sum_act")
+    return out
+
+
+def euler_step(latents: torch.Tensor, noise: torch.Tensor, dt: float) -> torch.Tensor:
+    """LinearScheduler.step: latents + noise * dt in the latents' dtype."""
+    lib = _lib.load()
+    _cuda(latents, "latents")
+    latents, noise = latents.contiguous(), noise.contiguous()
+    if latents.shape != noise.shape:
+        raise ValueError("latents and noise must share their shape")
+    out = torch.empty_like(latents)
+    rc = lib.mfx_euler_step(_ptr(latents), _dt(latents), _ptr(noise), _dt(noise), float(dt), _ptr(out),
+                            latents.numel(), _stream())
+    _lib.check(rc, "mfx_euler_step")
+    return out
