@@ -20,6 +20,12 @@ _EPI = {None: EPI_NONE, "none": EPI_NONE, "gelu": EPI_GELU_ERF, "gelu_erf": EPI_
         "silu": EPI_SILU}
 
 
+# Kernel launches issued through this module since import (bench.py reports the count of a timed region).
+LAUNCHES = [0]
+# When set to a list, qlinear appends (flops, start_event, end_event) for every launch (bench.py's roofline leg).
+QLINEAR_TRACE = None
+
+
 def _dt(t: torch.Tensor) -> int:
     try:
         return _DT[t.dtype]
@@ -69,6 +75,7 @@ def quantize_affine(w: torch.Tensor, group_size: int = 64, bits: int = 4, mode: 
     rc = lib.mfx_quantize_affine(_ptr(w), _dt(w), n, k, bits, group_size, qm, _ptr(wq), _ptr(scales), _ptr(biases),
                                  _stream())
     _lib.check(rc, "mfx_quantize_affine")
+    LAUNCHES[0] += 1
     return wq, scales, biases
 
 
@@ -84,6 +91,7 @@ def dequantize_affine(wq: torch.Tensor, scales: torch.Tensor, biases: torch.Tens
     rc = lib.mfx_dequantize_affine(_ptr(wq), _ptr(scales), _ptr(biases), _dt(scales), n, k, bits, group_size,
                                    _ptr(out), _dt(out), _stream())
     _lib.check(rc, "mfx_dequantize_affine")
+    LAUNCHES[0] += 1
     return out
 
 
@@ -105,6 +113,7 @@ def prepare_qlinear(wq: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor
     rc = lib.mfx_qlinear_prepare(_ptr(wq), _ptr(scales), _ptr(biases), _dt(scales), n, k, bits, group_size,
                                  _ptr(blob), nbytes, _stream())
     _lib.check(rc, "mfx_qlinear_prepare")
+    LAUNCHES[0] += 2
     return blob
 
 
@@ -186,8 +195,16 @@ def qlinear(x: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, biases: tor
         a.gate, a.gate_dtype, a.gate_batch_stride = gate.data_ptr(), _dt(gate), gate.stride(0)
         a.residual, a.res_row_stride, a.res_batch_stride = rv.data_ptr(), r_rs, r_bs
     a.y, a.y_dtype, a.y_row_stride, a.y_batch_stride = ov.data_ptr(), _dt(ov), o_rs, o_bs
+    trace = QLINEAR_TRACE
+    if trace is not None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
     rc = lib.mfx_qlinear_ex(byref(a), _stream())
     _lib.check(rc, "mfx_qlinear_ex")
+    if trace is not None:
+        e1.record()
+        trace.append((2.0 * rows * batch * n * k, e0, e1))
+    LAUNCHES[0] += 1 if prepared is not None else 3
     return ret
 
 
@@ -232,6 +249,7 @@ def norm_modulate(x: torch.Tensor, shift: torch.Tensor | None = None, scale: tor
     a.eps, a.rms = eps, int(rms)
     a.y, a.y_row_stride, a.y_batch_stride = ov.data_ptr(), o_rs, o_bs
     _lib.check(lib.mfx_norm_modulate(byref(a), _stream()), "mfx_norm_modulate")
+    LAUNCHES[0] += 1
     return ret
 
 
@@ -259,6 +277,7 @@ def qknorm_rope(qkv: torch.Tensor, heads: int, q_weight_a: torch.Tensor, k_weigh
     rc = lib.mfx_qknorm_rope(_ptr(qkv), qkv.stride(1), qkv.stride(0), seq, batch, heads, split, _ptr(ws[0]),
                              _ptr(ws[1]), _ptr(ws[2]), _ptr(ws[3]), _dt(ws[0]), _ptr(cos_sin), eps, _stream())
     _lib.check(rc, "mfx_qknorm_rope")
+    LAUNCHES[0] += 1
     return qkv
 
 
@@ -286,6 +305,7 @@ def fmha(qkv: torch.Tensor, heads: int, scale: float | None = None, out: torch.T
                       qkv.stride(0), seq, batch, heads, float(scale if scale is not None else 128 ** -0.5),
                       _ptr(out), out.stride(1), out.stride(0), _stream())
     _lib.check(rc, "mfx_fmha")
+    LAUNCHES[0] += 1
     return out
 
 
@@ -302,6 +322,7 @@ def vec_sum_act(a: torch.Tensor, b: torch.Tensor | None = None, c: torch.Tensor 
     rc = lib.mfx_vec_sum_act(_ptr(ts[0]), _ptr(ts[1]), _ptr(ts[2]), _dt(ts[0]), 1 if act == "silu" else 0, _ptr(out),
                              _dt(out), out.numel(), _stream())
     _lib.check(rc, "mfx_vec_sum_act")
+    LAUNCHES[0] += 1
     return out
 
 
@@ -316,4 +337,5 @@ def euler_step(latents: torch.Tensor, noise: torch.Tensor, dt: float) -> torch.T
     rc = lib.mfx_euler_step(_ptr(latents), _dt(latents), _ptr(noise), _dt(noise), float(dt), _ptr(out),
                             latents.numel(), _stream())
     _lib.check(rc, "mfx_euler_step")
+    LAUNCHES[0] += 1
     return out
