@@ -97,6 +97,26 @@ int mfx_qlinear(const void* x, int64_t M, int64_t K, int64_t ldx, const uint32_t
                 int bias_dtype, void* y, int y_dtype, int64_t ldy, void* workspace, size_t workspace_bytes,
                 void* stream);
 
+/* Allocation-free form of mfx_qlinear. It has no counterpart in the reference. It exists for callers that
+ * cannot hand the library a workspace because they cannot allocate device memory at the point of the call:
+ * a serving process whose allocator reserved all of HBM at start-up, a plugin host that forbids
+ * allocations inside its execution callbacks, a latency-critical loop that cannot afford the implicit
+ * device synchronisation of cudaMalloc/cudaFree. The scratch that mfx_qlinear takes as `workspace` is
+ * instead a fixed array of MFX_STATIC_SCRATCH_BYTES inside the library image; each GPU that loads the
+ * library holds it until the process exits. The call allocates nothing.
+ *  - Limit: mfx_qlinear_prepared_bytes(N, K, bits, 64) <= MFX_STATIC_SCRATCH_BYTES (e.g. a 12288 x 3072
+ *    weight at 4 bits needs 21.2 MB); larger weights return MFX_ERR_TOO_LARGE and nothing is launched.
+ *  - The first call on a device looks up the array's device address (once per device, with that device
+ *    current); make that first call before any stream capture begins.
+ *  - All calls share the one array and each call overwrites the part it uses, so nothing has to be cleared
+ *    between calls; but two calls that overlap on the GPU (different streams, or another thread) race on
+ *    it. Serialise them, or use mfx_qlinear with separate workspaces. */
+#define MFX_STATIC_SCRATCH_BYTES (32 * 1024 * 1024)
+int mfx_qlinear_static_scratch(const void* x, int64_t M, int64_t K, int64_t ldx, const uint32_t* wq,
+                               const void* scales, const void* biases, int sb_dtype, int64_t N, int bits,
+                               int group_size, const void* bias, int bias_dtype, void* y, int y_dtype, int64_t ldy,
+                               void* stream);
+
 /* Strided, batched form with fused epilogues. The activations are `batch` samples of `rows` rows:
  * element (b, r, k) at x + b*x_batch_stride + r*x_row_stride + k; y and residual likewise; gate is
  * [batch, N] with gate_batch_stride. This lets the joint text+image blocks read/write slices of one

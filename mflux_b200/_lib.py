@@ -21,6 +21,7 @@ QMODE_MLX, QMODE_DOC = 0, 1
 EPI_NONE, EPI_GELU_ERF, EPI_GELU_TANH, EPI_GATE_RESIDUAL, EPI_SILU = 0, 1, 2, 3, 4
 
 _VALUE_ERRORS = {-1, -2, -3, -4, -7, -9}
+STATIC_SCRATCH_BYTES = 32 * 1024 * 1024
 
 
 class QLinearArgs(ctypes.Structure):
@@ -107,6 +108,11 @@ SIGNATURES = {
         c_int,
         [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int,
          c_void_p, c_int, c_void_p, c_int, c_int64, c_void_p, ctypes.c_size_t, c_void_p],
+    ),
+    "mfx_qlinear_static_scratch": (
+        c_int,
+        [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int,
+         c_void_p, c_int, c_void_p, c_int, c_int64, c_void_p],
     ),
     "mfx_qlinear_ex": (c_int, [ctypes.POINTER(QLinearArgs), c_void_p]),
     "mfx_norm_modulate": (c_int, [ctypes.POINTER(NormArgs), c_void_p]),

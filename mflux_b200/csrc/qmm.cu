@@ -16,6 +16,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <mutex>
+
 #include "host_util.cuh"
 #include "ptx.cuh"
 
@@ -662,6 +664,33 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
              : launch<8, FMT_BF16, 3, __nv_bfloat16>(tx, tw, tsb, p, grid, st);
 }
 
+// ---------------------------------------------------------------- allocation-free variant
+// Scratch for mfx_qlinear_static_scratch: the prepared form of ONE weight. It is part of the library image,
+// so every GPU that loads the library carries these bytes until the process exits. In host code the name
+// below is only a handle: the device address is obtained per device with cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_static_scratch[MFX_STATIC_SCRATCH_BYTES];
+
+// Device address of g_static_scratch on the current device (looked up once per device).
+int static_scratch_address(void** out) {
+  static std::mutex mu;
+  static void* cached[64];
+  int dev = 0;
+  MFX_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return MFX_ERR_TOO_LARGE;
+  std::lock_guard<std::mutex> lk(mu);
+  if (cached[dev] == nullptr) {
+    void* ptr = nullptr;
+    MFX_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_static_scratch));
+    if (ptr == nullptr) {
+      set_cuda_error_text("cudaGetSymbolAddress returned a null address for the static scratch");
+      return MFX_ERR_CUDA;
+    }
+    cached[dev] = ptr;
+  }
+  *out = cached[dev];
+  return MFX_OK;
+}
+
 }  // namespace qmm
 }  // namespace mfx
 
@@ -709,6 +738,25 @@ int mfx_qlinear(const void* x, int64_t M, int64_t K, int64_t ldx, const uint32_t
   a.y_dtype = y_dtype;
   a.y_row_stride = ldy;
   return mfx_qlinear_ex(&a, stream);
+}
+
+int mfx_qlinear_static_scratch(const void* x, int64_t M, int64_t K, int64_t ldx, const uint32_t* wq,
+                               const void* scales, const void* biases, int sb_dtype, int64_t N, int bits,
+                               int group_size, const void* bias, int bias_dtype, void* y, int y_dtype, int64_t ldy,
+                               void* stream) {
+  const size_t need = mfx::qmm::prepared_bytes(N, K, bits, group_size);
+  if (need == 0) {
+    if ((bits != 4 && bits != 8) || group_size != 64) return MFX_ERR_UNSUPPORTED_BITS;
+    return MFX_ERR_SHAPE;
+  }
+  if (need > static_cast<size_t>(MFX_STATIC_SCRATCH_BYTES)) {
+    mfx::set_cuda_error_text("mfx_qlinear_static_scratch: the prepared weight does not fit the built-in scratch");
+    return MFX_ERR_TOO_LARGE;
+  }
+  void* scratch = nullptr;
+  if (int rc = mfx::qmm::static_scratch_address(&scratch)) return rc;
+  return mfx_qlinear(x, M, K, ldx, wq, scales, biases, sb_dtype, N, bits, group_size, bias, bias_dtype, y, y_dtype,
+                     ldy, scratch, static_cast<size_t>(MFX_STATIC_SCRATCH_BYTES), stream);
 }
 
 }  // extern "C"

@@ -339,3 +339,37 @@ def euler_step(latents: torch.Tensor, noise: torch.Tensor, dt: float) -> torch.T
     _lib.check(rc, "mfx_euler_step")
     LAUNCHES[0] += 1
     return out
+
+
+def qlinear_plain(x: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor,
+                  bias: torch.Tensor | None = None, *, bits: int = 4, static_scratch: bool = False) -> torch.Tensor:
+    """y[M, N] = x[M, K] . dequant(wq)^T + bias through the two plain C entry points.
+
+    static_scratch=False calls mfx_qlinear with a workspace tensor allocated here; static_scratch=True calls
+    mfx_qlinear_static_scratch, which allocates nothing and keeps the prepared weight in an array inside
+    the library (for callers that cannot allocate device memory when they call; one weight of at most
+    32 MiB prepared size, calls must not overlap on the GPU).
+    """
+    lib = _lib.load()
+    _cuda(x, "x")
+    if x.dim() != 2 or x.dtype != torch.bfloat16 or x.stride(1) != 1:
+        raise ValueError("x must be a bf16 [M, K] matrix with a dense last dim")
+    wq, scales, biases = wq.contiguous(), scales.contiguous(), biases.contiguous()
+    m, k = x.shape
+    n = wq.shape[0]
+    if wq.shape[1] * 32 // bits != k:
+        raise ValueError("x and wq disagree on K")
+    y = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+    bias_c = None if bias is None else bias.contiguous()
+    common = (_ptr(x), m, k, x.stride(0), _ptr(wq), _ptr(scales), _ptr(biases), _dt(scales), n, bits, 64,
+              _ptr(bias_c), 0 if bias_c is None else _dt(bias_c), _ptr(y), _dt(y), y.stride(0))
+    if static_scratch:
+        rc = lib.mfx_qlinear_static_scratch(*common, _stream())
+        _lib.check(rc, "mfx_qlinear_static_scratch")
+    else:
+        nbytes = lib.mfx_qlinear_prepared_bytes(n, k, bits, 64)
+        ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=x.device)
+        rc = lib.mfx_qlinear(*common, _ptr(ws), ws.numel(), _stream())
+        _lib.check(rc, "mfx_qlinear")
+    LAUNCHES[0] += 3
+    return y
