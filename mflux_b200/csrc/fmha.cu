@@ -179,6 +179,7 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       }
       tc_fence_after();
       const int keys_here = min(BKV, p.seq - j * BKV);
+      const bool tail = keys_here < BKV;  // only the last tile of a ragged sequence needs key masking
       // pass 1: row maximum of this tile
       float m_tile = -INFINITY;
 #pragma unroll 1
@@ -186,9 +187,19 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
         uint32_t s[32];
         tmem_ld_32x32(t_row + COL_S + c * 32, s);
         tmem_ld_wait();
+        if (!tail) {
+          float m0 = __uint_as_float(s[0]), m1 = __uint_as_float(s[1]);
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (c * 32 + i < keys_here) m_tile = fmaxf(m_tile, __uint_as_float(s[i]));
+          for (int i = 2; i < 32; i += 2) {
+            m0 = fmaxf(m0, __uint_as_float(s[i]));
+            m1 = fmaxf(m1, __uint_as_float(s[i + 1]));
+          }
+          m_tile = fmaxf(m_tile, fmaxf(m0, m1));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i < keys_here) m_tile = fmaxf(m_tile, __uint_as_float(s[i]));
+        }
       }
       m_tile *= p.scale_log2;
       // grow the reference maximum only when it would change the exponent range by more than 2^8
@@ -212,6 +223,7 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
         m_ref = m_new;
       }
       // pass 2: probabilities, packed to bf16 pairs over the columns S no longer needs
+      float l0 = 0.f, l1 = 0.f;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t s[32];
@@ -220,17 +232,20 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float p0 = ex2(__uint_as_float(s[2 * i]) * p.scale_log2 - m_ref);
-          float p1 = ex2(__uint_as_float(s[2 * i + 1]) * p.scale_log2 - m_ref);
-          if (c * 32 + 2 * i >= keys_here) p0 = 0.f;
-          if (c * 32 + 2 * i + 1 >= keys_here) p1 = 0.f;
+          float p0 = ex2(fmaf(__uint_as_float(s[2 * i]), p.scale_log2, -m_ref));
+          float p1 = ex2(fmaf(__uint_as_float(s[2 * i + 1]), p.scale_log2, -m_ref));
+          if (tail) {
+            if (c * 32 + 2 * i >= keys_here) p0 = 0.f;
+            if (c * 32 + 2 * i + 1 >= keys_here) p1 = 0.f;
+          }
+          l0 += p0;
+          l1 += p1;
           const __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
-          // sum what the tensor core will actually multiply (the rounded values)
-          l_sum += __bfloat162float(hh.x) + __bfloat162float(hh.y);
           pk[i] = *reinterpret_cast<const uint32_t*>(&hh);
         }
         tmem_st_32x16(t_row + COL_S + c * 16, pk);
       }
+      l_sum += l0 + l1;
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();

@@ -66,9 +66,9 @@ struct NormParams {
 
 // MAXV = number of 8-element vectors a lane may hold: D <= 32 * 8 * MAXV.
 template <typename XT, int MAXV>
-__global__ void __launch_bounds__(256) norm_modulate_kernel(const NormParams p) {
+__global__ void __launch_bounds__(128) norm_modulate_kernel(const NormParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t row_id = static_cast<int64_t>(blockIdx.x) * 8 + warp;
+  const int64_t row_id = static_cast<int64_t>(blockIdx.x) * 4 + warp;
   if (row_id >= static_cast<int64_t>(p.rows) * p.batch) return;
   const int b = static_cast<int>(row_id / p.rows);
   const int r = static_cast<int>(row_id % p.rows);
@@ -101,18 +101,39 @@ __global__ void __launch_bounds__(256) norm_modulate_kernel(const NormParams p) 
     }
   }
   const float rstd = rsqrtf(warp_sum(sq) / static_cast<float>(p.D) + p.eps);
+  // shift / scale / weight are read as 16-byte vectors when their dtype is bf16 (the usual case)
+  const bool vec_mod = p.mod_dtype == MFX_BF16;
+  const bool vec_w = p.weight_dtype == MFX_BF16;
 #pragma unroll
   for (int i = 0; i < MAXV; ++i) {
     const int c = lane + 32 * i;
     if (c < nvec) {
-      float o[8];
+      float o[8], sc[8], sh[8], wt[8];
+      const int64_t moff = b * p.mod_batch_stride + c * 8;
+      if (p.scale) {
+        if (vec_mod) load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(p.scale) + moff, sc);
+        else
+#pragma unroll
+          for (int j = 0; j < 8; ++j) sc[j] = ld_scalar(p.scale, p.mod_dtype, moff + j);
+      }
+      if (p.shift) {
+        if (vec_mod) load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(p.shift) + moff, sh);
+        else
+#pragma unroll
+          for (int j = 0; j < 8; ++j) sh[j] = ld_scalar(p.shift, p.mod_dtype, moff + j);
+      }
+      if (p.weight) {
+        if (vec_w) load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(p.weight) + c * 8, wt);
+        else
+#pragma unroll
+          for (int j = 0; j < 8; ++j) wt[j] = ld_scalar(p.weight, p.weight_dtype, c * 8 + j);
+      }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const int col = c * 8 + j;
         float t = (v[i][j] - mean) * rstd;
-        if (p.weight) t *= ld_scalar(p.weight, p.weight_dtype, col);
-        if (p.scale) t *= 1.0f + ld_scalar(p.scale, p.mod_dtype, b * p.mod_batch_stride + col);
-        if (p.shift) t += ld_scalar(p.shift, p.mod_dtype, b * p.mod_batch_stride + col);
+        if (p.weight) t *= wt[j];
+        if (p.scale) t *= 1.0f + sc[j];
+        if (p.shift) t += sh[j];
         o[j] = t;
       }
       store8_bf16(y + c * 8, o);
@@ -214,6 +235,10 @@ int mfx_norm_modulate(const mfx_norm_args* a, void* stream) {
   if (!aligned16(a->x) || (a->x_row_stride * xs) % 16 != 0 || (a->x_batch_stride * xs) % 16 != 0 ||
       !aligned16(a->y) || (a->y_row_stride * 2) % 16 != 0 || (a->y_batch_stride * 2) % 16 != 0)
     return MFX_ERR_ALIGN;
+  if (a->mod_dtype == MFX_BF16 && (a->shift || a->scale) &&
+      ((a->shift && !aligned16(a->shift)) || (a->scale && !aligned16(a->scale)) || (a->mod_batch_stride * 2) % 16 != 0))
+    return MFX_ERR_ALIGN;
+  if (a->weight && a->weight_dtype == MFX_BF16 && !aligned16(a->weight)) return MFX_ERR_ALIGN;
   if (int rc = check_arch()) return rc;
   NormParams p;
   p.x = a->x;
@@ -234,15 +259,15 @@ int mfx_norm_modulate(const mfx_norm_args* a, void* stream) {
   p.y_row_stride = a->y_row_stride;
   p.y_batch_stride = a->y_batch_stride;
   const int64_t total = a->rows * a->batch;
-  const unsigned blocks = static_cast<unsigned>((total + 7) / 8);
+  const unsigned blocks = static_cast<unsigned>((total + 3) / 4);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int nvec_lane = static_cast<int>((a->D / 8 + 31) / 32);
   if (a->x_dtype == MFX_F32) {
-    if (nvec_lane <= 12) norm_modulate_kernel<float, 12><<<blocks, 256, 0, st>>>(p);
-    else norm_modulate_kernel<float, 16><<<blocks, 256, 0, st>>>(p);
+    if (nvec_lane <= 12) norm_modulate_kernel<float, 12><<<blocks, 128, 0, st>>>(p);
+    else norm_modulate_kernel<float, 16><<<blocks, 128, 0, st>>>(p);
   } else {
-    if (nvec_lane <= 12) norm_modulate_kernel<__nv_bfloat16, 12><<<blocks, 256, 0, st>>>(p);
-    else norm_modulate_kernel<__nv_bfloat16, 16><<<blocks, 256, 0, st>>>(p);
+    if (nvec_lane <= 12) norm_modulate_kernel<__nv_bfloat16, 12><<<blocks, 128, 0, st>>>(p);
+    else norm_modulate_kernel<__nv_bfloat16, 16><<<blocks, 128, 0, st>>>(p);
   }
   MFX_CUDA_TRY(cudaGetLastError());
   return MFX_OK;

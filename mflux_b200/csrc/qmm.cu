@@ -4,12 +4,12 @@
 // group_size=64, bits) for every nn.Linear of the transformer blocks of the reference
 // (e.g. src/mflux/models/flux/model/flux_transformer/joint_attention.py:14-21, feed_forward.py:8-9).
 //
-// One persistent CTA per SM, 512 threads, warp-specialised:
+// One persistent CTA per SM, 512 (4 bits) or 768 (8 bits) threads, warp-specialised:
 //   warp 0      TMA producer: X tile [128 x 64] bf16 (128-byte swizzle) and the packed weight tile
 //               [256 rows x 64 codes] per k-block, 64 = one quantization group
 //   warp 1      allocates TMEM, issues tcgen05.mma (M=128, N=256, K=16, fp32 accumulate in TMEM)
 //   warps 4-7   epilogue: tcgen05.ld -> bias / activation / gated residual -> global
-//   warps 8-15  dequantizers: packed codes (smem) -> bf16 via exponent-magic + one fma with the
+//   warps 8-15 (4 bits) or 8-23 (8 bits: half a weight row per thread)  dequantizers: packed codes (smem) -> bf16 via exponent-magic + one fma with the
 //               group's scale and bias -> B operand tile in the 128-byte-swizzled K-major layout
 // Two accumulator stages (2 x 256 TMEM columns) let the epilogue of tile i overlap the main loop of
 // tile i+1. All mbarrier waits are bounded.
@@ -28,8 +28,7 @@ constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;
 constexpr int SD = 3;  // stages of the dequantized-weight ring
-constexpr int NUM_THREADS = 512;
-constexpr int NUM_DQ_WARPS = 8;
+constexpr int FIXED_WARPS = 8;  // producer, MMA, 2 spare, 4 epilogue
 constexpr int FIRST_DQ_WARP = 8;
 constexpr int FIRST_EPI_WARP = 4;
 constexpr int X_TILE_BYTES = BM * BK * 2;   // 16 KiB
@@ -131,15 +130,17 @@ __device__ __forceinline__ uint2 dequant_w8(uint32_t q, uint32_t s2, uint32_t b2
   return r;
 }
 
-__device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f)); }
-__device__ __forceinline__ float gelu_tanh(float v) {
+// Out of line on purpose: the epilogue runs beside the main loop of the next tile; a 32-fold unrolled inline
+// erf/tanh body would crowd the small hot loops of the other warps out of the instruction cache.
+__device__ __noinline__ float gelu_erf(float v) { return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f)); }
+__device__ __noinline__ float gelu_tanh(float v) {
   const float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
   return 0.5f * v * (1.0f + tanhf(u));
 }
 __device__ __forceinline__ float silu(float v) { return v / (1.0f + __expf(-v)); }
 
-template <int BITS, uint32_t WF, int ST, typename OUT>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+template <int BITS, uint32_t WF, int ST, typename OUT, int EPI, int NUM_DQ_WARPS>
+__global__ void __launch_bounds__((FIXED_WARPS + NUM_DQ_WARPS) * 32, 1)
 qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
            const __grid_constant__ CUtensorMap tmap_sb, const Params p) {
   using L = Smem<BITS, ST>;
@@ -268,22 +269,29 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     }
   } else if (warp >= FIRST_DQ_WARP) {
     // ------------------------------------------------------------ dequantizers
-    const int row = (warp - FIRST_DQ_WARP) * 32 + lane;  // row of the 256-row weight tile
+    // 16 warps: each thread dequantizes half a weight row per k-block; 8 warps: a whole row
+    constexpr int SPLIT = NUM_DQ_WARPS / 8;               // threads per row: 1 or 2
+    const int dq = warp - FIRST_DQ_WARP;
+    const int row = (dq / SPLIT) * 32 + lane;             // row of the 256-row weight tile
+    const int half = dq % SPLIT;                          // which part of the row's 64 k-values
     constexpr int ROW_BYTES = BK * BITS / 8;              // packed bytes per row per k-block
-    constexpr int RD_CHUNKS = ROW_BYTES / 16;
+    constexpr int RD_CHUNKS = ROW_BYTES / 16;             // 16-byte chunks per row: 2 (4 bits) or 4 (8 bits)
+    constexpr int MY_CHUNKS = RD_CHUNKS / SPLIT;          // packed chunks this thread reads
+    constexpr int MY_OUT = 8 / SPLIT;                     // 16-byte output chunks this thread writes
     // The packed tile is loaded with the TMA swizzle whose span equals one row (32 B for 4 bits,
     // 64 B for 8 bits): 16-byte chunk c of row r sits at chunk c ^ ((r*ROW_BYTES >> 7) & mask), which
     // spreads the per-row reads of a quarter-warp over all banks. Offsets are per-thread constants.
     const uint32_t rd_sw = (static_cast<uint32_t>(row * ROW_BYTES) >> 7) & (RD_CHUNKS - 1);
     const uint8_t* rd_base = smem_gen + L::OFF_WQ + row * ROW_BYTES;
-    uint32_t rd_off[RD_CHUNKS];
+    uint32_t rd_off[MY_CHUNKS];
 #pragma unroll
-    for (int h = 0; h < RD_CHUNKS; ++h) rd_off[h] = (static_cast<uint32_t>(h) ^ rd_sw) << 4;
-    // B operand tile: 128-byte rows, 16-byte chunk c of row r at chunk c ^ (r & 7)
+    for (int h = 0; h < MY_CHUNKS; ++h) rd_off[h] = (static_cast<uint32_t>(half * MY_CHUNKS + h) ^ rd_sw) << 4;
+    // B operand tile: 128-byte rows, 16-byte chunk c of row r at chunk c ^ (r & 7); this thread owns chunks 4*half..+3
     uint8_t* wr_base = smem_gen + L::OFF_WD + row * 128;
-    uint32_t wr_off[8];
+    uint32_t wr_off[MY_OUT];
 #pragma unroll
-    for (int c = 0; c < 8; ++c) wr_off[c] = (static_cast<uint32_t>(c) ^ static_cast<uint32_t>(row & 7)) << 4;
+    for (int c = 0; c < MY_OUT; ++c)
+      wr_off[c] = (static_cast<uint32_t>(half * MY_OUT + c) ^ static_cast<uint32_t>(row & 7)) << 4;
     const uint32_t* sb_base = reinterpret_cast<const uint32_t*>(smem_gen + L::OFF_SB) + row;
     int st = 0, sd = 0;
     uint32_t ph_t = 0, ph_d = 0;
@@ -300,19 +308,15 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         const uint32_t b2 = __byte_perm(sbv, sbv, 0x3232);  // (bias, bias)
         const uint8_t* src = rd_base + st * L::WQ_TILE_BYTES;
         uint8_t* dst = wr_base + sd * WD_TILE_BYTES;
-        if (BITS == 4) {
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const uint4 pk = *reinterpret_cast<const uint4*>(src + rd_off[h]);
+        for (int h = 0; h < MY_CHUNKS; ++h) {
+          const uint4 pk = *reinterpret_cast<const uint4*>(src + rd_off[h]);
+          if (BITS == 4) {  // 4 words x 8 codes -> 4 output chunks
             const uint32_t wds[4] = {pk.x, pk.y, pk.z, pk.w};
 #pragma unroll
             for (int j = 0; j < 4; ++j)
               *reinterpret_cast<uint4*>(dst + wr_off[h * 4 + j]) = dequant_w4<WF>(wds[j], s2, b2);
-          }
-        } else {
-#pragma unroll
-          for (int h = 0; h < 4; ++h) {
-            const uint4 pk = *reinterpret_cast<const uint4*>(src + rd_off[h]);
+          } else {          // 4 words x 4 codes -> 2 output chunks
             const uint2 lo0 = dequant_w8(pk.x, s2, b2);
             const uint2 hi0 = dequant_w8(pk.y, s2, b2);
             const uint2 lo1 = dequant_w8(pk.z, s2, b2);
@@ -359,7 +363,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         const int c = et + 128 * h;
         const int n = n0 + c;
         bias_s[c] = (p.bias != nullptr && n < p.N) ? load_scalar(p.bias, p.bias_dtype, n) : 0.f;
-        if (p.epilogue == MFX_EPI_GATE_RESIDUAL)
+        if (EPI == MFX_EPI_GATE_RESIDUAL)
           gate_s[c] = (n < p.N) ? load_scalar(p.gate, p.gate_dtype, b * p.gate_batch_stride + n) : 0.f;
       }
       named_bar_sync(1, 128);
@@ -371,7 +375,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
       const bool row_ok = r < p.rows;
       OUT* yrow = static_cast<OUT*>(p.y) + b * p.y_batch_stride + static_cast<int64_t>(r) * p.y_row_stride + n0;
       const OUT* rrow = nullptr;
-      if (p.epilogue == MFX_EPI_GATE_RESIDUAL)
+      if (EPI == MFX_EPI_GATE_RESIDUAL)
         rrow = static_cast<const OUT*>(p.residual) + b * p.res_batch_stride +
                static_cast<int64_t>(r) * p.res_row_stride + n0;
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + a * BN;
@@ -388,16 +392,16 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             float v[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(acc[g8 * 8 + j]) + bias_s[col + j];
-            if (p.epilogue == MFX_EPI_GELU_ERF) {
+            if (EPI == MFX_EPI_GELU_ERF) {
 #pragma unroll
               for (int j = 0; j < 8; ++j) v[j] = gelu_erf(v[j]);
-            } else if (p.epilogue == MFX_EPI_GELU_TANH) {
+            } else if (EPI == MFX_EPI_GELU_TANH) {
 #pragma unroll
               for (int j = 0; j < 8; ++j) v[j] = gelu_tanh(v[j]);
-            } else if (p.epilogue == MFX_EPI_SILU) {
+            } else if (EPI == MFX_EPI_SILU) {
 #pragma unroll
               for (int j = 0; j < 8; ++j) v[j] = silu(v[j]);
-            } else if (p.epilogue == MFX_EPI_GATE_RESIDUAL) {
+            } else if (EPI == MFX_EPI_GATE_RESIDUAL) {
               float rs[8];
               if constexpr (sizeof(OUT) == 4) {
                 const float4 r0 = *reinterpret_cast<const float4*>(rrow + col);
@@ -441,11 +445,15 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
 
 MFX_DEFINE_STATUS_READER(read_status)
 
-template <int BITS, uint32_t WF, int ST, typename OUT>
-int launch(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tsb, const Params& p, int grid,
-           cudaStream_t st) {
+template <int BITS, uint32_t WF, int ST, typename OUT, int EPI>
+int launch_epi(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tsb, const Params& p, int grid,
+               cudaStream_t st) {
   using L = Smem<BITS, ST>;
-  auto kern = qmm_kernel<BITS, WF, ST, OUT>;
+  // 4-bit codes need half the integer work per value: 8 dequantizer warps keep up and draw less power;
+  // 8-bit codes want 16
+  constexpr int NDQ = BITS == 4 ? 8 : 16;
+  constexpr int NUM_THREADS = (FIXED_WARPS + NDQ) * 32;
+  auto kern = qmm_kernel<BITS, WF, ST, OUT, EPI, NDQ>;
   static bool configured = false;  // attribute is per function; set once per process and device reuse is fine
   static int configured_dev = -1;
   int dev = 0;
@@ -458,6 +466,18 @@ int launch(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tsb,
   kern<<<grid, NUM_THREADS, L::DYN_BYTES, st>>>(tx, tw, tsb, p);
   MFX_CUDA_TRY(cudaGetLastError());
   return MFX_OK;
+}
+
+template <int BITS, uint32_t WF, int ST, typename OUT>
+int launch(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tsb, const Params& p, int grid,
+           cudaStream_t st) {
+  switch (p.epilogue) {
+    case MFX_EPI_GELU_ERF: return launch_epi<BITS, WF, ST, OUT, MFX_EPI_GELU_ERF>(tx, tw, tsb, p, grid, st);
+    case MFX_EPI_GELU_TANH: return launch_epi<BITS, WF, ST, OUT, MFX_EPI_GELU_TANH>(tx, tw, tsb, p, grid, st);
+    case MFX_EPI_GATE_RESIDUAL: return launch_epi<BITS, WF, ST, OUT, MFX_EPI_GATE_RESIDUAL>(tx, tw, tsb, p, grid, st);
+    case MFX_EPI_SILU: return launch_epi<BITS, WF, ST, OUT, MFX_EPI_SILU>(tx, tw, tsb, p, grid, st);
+    default: return launch_epi<BITS, WF, ST, OUT, MFX_EPI_NONE>(tx, tw, tsb, p, grid, st);
+  }
 }
 
 int sm_count() {
