@@ -4,15 +4,21 @@
 // group_size=64, bits) for every nn.Linear of the transformer blocks of the reference
 // (e.g. src/mflux/models/flux/model/flux_transformer/joint_attention.py:14-21, feed_forward.py:8-9).
 //
-// One persistent CTA per SM, 512 (4 bits) or 768 (8 bits) threads, warp-specialised:
-//   warp 0      TMA producer: X tile [128 x 64] bf16 (128-byte swizzle) and the packed weight tile
-//               [256 rows x 64 codes] per k-block, 64 = one quantization group
-//   warp 1      allocates TMEM, issues tcgen05.mma (M=128, N=256, K=16, fp32 accumulate in TMEM)
-//   warps 4-7   epilogue: tcgen05.ld -> bias / activation / gated residual -> global
-//   warps 8-15 (4 bits) or 8-23 (8 bits: half a weight row per thread)  dequantizers: packed codes (smem) -> bf16 via exponent-magic + one fma with the
-//               group's scale and bias -> B operand tile in the 128-byte-swizzled K-major layout
-// Two accumulator stages (2 x 256 TMEM columns) let the epilogue of tile i overlap the main loop of
-// tile i+1. All mbarrier waits are bounded.
+// Two CTAs on neighbouring SMs form a pair (cluster of 2, tcgen05 cta_group::2) and share one 256 x 256
+// output tile: each CTA loads the 128 activation rows of its half (A operand) and dequantizes 128 of the 256
+// weight rows (its half of the B operand); one MMA of the pair reads both halves. Per flop that halves the
+// dequantization work and the weight-operand shared-memory traffic of a single-CTA 128 x 256 tile, which is
+// what bounded it. A pipeline stage carries two quantization groups (128 k-values) because the issuing thread
+// loses a few hundred cycles around every wait + commit. Persistent, warp-specialised, per CTA:
+//   warp 0      TMA producer: per stage its X tile [128 x 128 k] bf16 as two 128-byte-swizzled slabs (counted
+//               on the leader's barrier), the packed codes of its 128 weight rows and their (scale, bias) pairs
+//   warp 1      allocates TMEM; in the leader CTA issues tcgen05.mma.cta_group::2 (M=256, N=256, K=16)
+//   warps 4-7   epilogue: tcgen05.ld -> bias / activation / gated residual -> global, overlapped with the
+//               main loop of the next tile (two 256-column TMEM accumulators)
+//   warps 8+    dequantizers (8 warps for 4-bit, 16 for 8-bit codes): codes (smem) -> bf16 by exponent-magic
+//               + one fma with the group's scale and bias -> B operand tile in the swizzled K-major layout
+// Barriers that both CTAs feed live in the leader; MMA completion is multicast to both CTAs. All mbarrier
+// waits are bounded.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -24,16 +30,17 @@
 namespace mfx {
 namespace qmm {
 
-constexpr int BM = 128;
-constexpr int BN = 256;
-constexpr int BK = 64;
-constexpr int SD = 3;  // stages of the dequantized-weight ring
+constexpr int BM = 128;       // activation rows per CTA (256 per pair)
+constexpr int BN = 256;       // weight rows (output columns) per pair tile
+constexpr int BN_HALF = 128;  // weight rows each CTA dequantizes
+constexpr int BK = 64;        // one quantization group
+constexpr int GPS = 2;        // quantization groups per pipeline stage
 constexpr int FIXED_WARPS = 8;  // producer, MMA, 2 spare, 4 epilogue
 constexpr int FIRST_DQ_WARP = 8;
 constexpr int FIRST_EPI_WARP = 4;
-constexpr int X_TILE_BYTES = BM * BK * 2;   // 16 KiB
-constexpr int WD_TILE_BYTES = BN * BK * 2;  // 32 KiB
-constexpr int SB_TILE_BYTES = BN * 4;         // one bf16 (scale, bias) pair per weight row
+constexpr int X_TILE_BYTES = BM * BK * 2;        // 16 KiB per group
+constexpr int WD_TILE_BYTES = BN_HALF * BK * 2;  // 16 KiB per group
+constexpr int SB_TILE_BYTES = BN_HALF * 4;       // one bf16 (scale, bias) pair per weight row
 constexpr uint32_t TMEM_COLS = 512;
 
 struct Params {
@@ -51,16 +58,21 @@ struct Params {
   int64_t y_row_stride, y_batch_stride;
 };
 
-template <int BITS, int ST>
+// ST = stages of the TMA ring, SD = stages of the dequantized-weight ring; one stage = GPS groups.
+template <int BITS, int ST, int SD>
 struct Smem {
-  static constexpr int WQ_TILE_BYTES = BN * BK * BITS / 8;
+  static constexpr int WQ_TILE_BYTES = BN_HALF * BK * BITS / 8;
+  static constexpr int X_STAGE = GPS * X_TILE_BYTES;
+  static constexpr int WD_STAGE = GPS * WD_TILE_BYTES;
+  static constexpr int WQ_STAGE = GPS * WQ_TILE_BYTES;
+  static constexpr int SB_STAGE = GPS * SB_TILE_BYTES;
   static constexpr int OFF_X = 0;
-  static constexpr int OFF_WD = OFF_X + ST * X_TILE_BYTES;
-  static constexpr int OFF_WQ = OFF_WD + SD * WD_TILE_BYTES;
-  static constexpr int OFF_SB = OFF_WQ + ST * WQ_TILE_BYTES;   // packed (scale, bias) pairs, 256 x 4 B per stage
-  static constexpr int OFF_VEC = OFF_SB + ST * SB_TILE_BYTES;  // bias[2][256] + gate[2][256] floats
+  static constexpr int OFF_WD = OFF_X + ST * X_STAGE;
+  static constexpr int OFF_WQ = OFF_WD + SD * WD_STAGE;
+  static constexpr int OFF_SB = OFF_WQ + ST * WQ_STAGE;
+  static constexpr int OFF_VEC = OFF_SB + ST * SB_STAGE;  // bias[2][256] + gate[2][256] floats
   static constexpr int OFF_BAR = OFF_VEC + 4 * BN * 4;
-  static constexpr int NUM_BARS = 2 * ST + 2 * SD + 4;
+  static constexpr int NUM_BARS = 3 * ST + 2 * SD + 4;
   static constexpr int OFF_TMEM = OFF_BAR + NUM_BARS * 8;
   static constexpr int TOTAL = OFF_TMEM + 16;
   static constexpr int DYN_BYTES = TOTAL + 1024;  // slack for manual 1024-byte alignment
@@ -139,11 +151,11 @@ __device__ __noinline__ float gelu_tanh(float v) {
 }
 __device__ __forceinline__ float silu(float v) { return v / (1.0f + __expf(-v)); }
 
-template <int BITS, uint32_t WF, int ST, typename OUT, int EPI, int NUM_DQ_WARPS>
-__global__ void __launch_bounds__((FIXED_WARPS + NUM_DQ_WARPS) * 32, 1)
+template <int BITS, uint32_t WF, int ST, int SD, typename OUT, int EPI, int NUM_DQ_WARPS>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((FIXED_WARPS + NUM_DQ_WARPS) * 32, 1)
 qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
            const __grid_constant__ CUtensorMap tmap_sb, const Params p) {
-  using L = Smem<BITS, ST>;
+  using L = Smem<BITS, ST, SD>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -154,30 +166,37 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
   const uint32_t sb_s = smem_base + L::OFF_SB;
   float* vec_s = reinterpret_cast<float*>(smem_gen + L::OFF_VEC);
   const uint32_t bar0 = smem_base + L::OFF_BAR;
-  auto t_full = [&](int s) { return bar0 + 8u * s; };
-  auto t_empty = [&](int s) { return bar0 + 8u * (ST + s); };
-  auto d_full = [&](int s) { return bar0 + 8u * (2 * ST + s); };
-  auto d_empty = [&](int s) { return bar0 + 8u * (2 * ST + SD + s); };
-  auto acc_full = [&](int s) { return bar0 + 8u * (2 * ST + 2 * SD + s); };
-  auto acc_empty = [&](int s) { return bar0 + 8u * (2 * ST + 2 * SD + 2 + s); };
+  auto w_full = [&](int s) { return bar0 + 8u * s; };              // local: codes + pairs landed
+  auto x_full = [&](int s) { return bar0 + 8u * (ST + s); };       // leader: X tiles of both CTAs landed
+  auto t_empty = [&](int s) { return bar0 + 8u * (2 * ST + s); };  // local: TMA stage may be refilled
+  constexpr int B0 = 3 * ST;
+  auto d_full = [&](int s) { return bar0 + 8u * (B0 + s); };             // leader: B halves of both CTAs written
+  auto d_empty = [&](int s) { return bar0 + 8u * (B0 + SD + s); };       // local: B stage consumed
+  auto acc_full = [&](int s) { return bar0 + 8u * (B0 + 2 * SD + s); };  // local
+  auto acc_empty = [&](int s) { return bar0 + 8u * (B0 + 2 * SD + 2 + s); };  // leader
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::OFF_TMEM);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_kb = p.K / BK;
+  const int num_st = (num_kb + GPS - 1) / GPS;  // a ragged last stage reads TMA zero fill for its missing group
+  const uint32_t rank = cluster_ctarank();      // 0 = leader of the pair
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < ST; ++s) {
-      mbar_init(t_full(s), 1);
-      mbar_init(t_empty(s), 1 + NUM_DQ_WARPS);
+      mbar_init(w_full(s), 1);
+      mbar_init(x_full(s), 1);                  // the leader's expect_tx covers both CTAs' X tiles
+      mbar_init(t_empty(s), 1 + NUM_DQ_WARPS);  // MMA commit (X tiles) + every local dequantizer warp (codes)
     }
     for (int s = 0; s < SD; ++s) {
-      mbar_init(d_full(s), NUM_DQ_WARPS);
+      mbar_init(d_full(s), 2 * NUM_DQ_WARPS);   // the dequantizer warps of both CTAs
       mbar_init(d_empty(s), 1);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(acc_full(s), 1);
-      mbar_init(acc_empty(s), 4);
+      mbar_init(acc_empty(s), 8);               // 4 epilogue warps in each CTA
     }
     fence_mbar_init();
     tma_prefetch_desc(&tmap_x);
@@ -185,11 +204,12 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     tma_prefetch_desc(&tmap_sb);
   }
   if (warp == 1) {
-    tmem_alloc(smem_base + L::OFF_TMEM, TMEM_COLS);
-    tmem_relinquish();
+    tmem_alloc_pair(smem_base + L::OFF_TMEM, TMEM_COLS);
+    tmem_relinquish_pair();
   }
   tc_fence_before();
   __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anyone signals across the pair
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -198,22 +218,28 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     int st = 0;
     uint32_t ph = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+    for (int tile = pair; tile < p.total_tiles && ok; tile += num_pairs) {
       const int tm = tile % p.tiles_m;
       const int tn = tile / p.tiles_m;
       const int b = tm / p.tiles_m_per_sample;
-      const int r0 = (tm % p.tiles_m_per_sample) * BM;
-      const int n0 = tn * BN;
-      for (int kb = 0; kb < num_kb; ++kb) {
+      const int r0 = (tm % p.tiles_m_per_sample) * (2 * BM) + static_cast<int>(rank) * BM;
+      const int n0 = tn * BN + static_cast<int>(rank) * BN_HALF;
+      for (int s = 0; s < num_st; ++s) {
         if (!mbar_wait_sleep(t_empty(st), ph ^ 1u, DEV_TIMEOUT_TMA_EMPTY)) {
           ok = false;
           break;
         }
         if (lane == 0) {
-          mbar_arrive_expect_tx(t_full(st), X_TILE_BYTES + L::WQ_TILE_BYTES + SB_TILE_BYTES);
-          tma_load_3d(x_s + st * X_TILE_BYTES, &tmap_x, t_full(st), kb * BK, r0, b);
-          tma_load_2d(wq_s + st * L::WQ_TILE_BYTES, &tmap_w, t_full(st), kb * (BK * BITS / 32), n0);
-          tma_load_2d(sb_s + st * SB_TILE_BYTES, &tmap_sb, t_full(st), n0, kb);
+          if (rank == 0) mbar_arrive_expect_tx(x_full(st), 2 * L::X_STAGE);
+          mbar_arrive_expect_tx(w_full(st), L::WQ_STAGE + L::SB_STAGE);
+#pragma unroll
+          for (int g = 0; g < GPS; ++g) {
+            const int kb = s * GPS + g;  // beyond K on a ragged last stage: the loads return zeros
+            tma_load_2d(wq_s + st * L::WQ_STAGE + g * L::WQ_TILE_BYTES, &tmap_w, w_full(st), kb * (BK * BITS / 32),
+                        n0);
+            tma_load_2d(sb_s + st * L::SB_STAGE + g * SB_TILE_BYTES, &tmap_sb, w_full(st), n0, kb);
+            tma_load_3d_pair(x_s + st * L::X_STAGE + g * X_TILE_BYTES, &tmap_x, x_full(st), kb * BK, r0, b);
+          }
         }
         __syncwarp();
         if (++st == ST) {
@@ -223,91 +249,100 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    constexpr uint32_t IDESC = make_idesc(FMT_BF16, WF, BM, BN);
-    int st = 0, sd = 0;
-    uint32_t ph_t = 0, ph_d = 0;
-    bool ok = true;
-    int it = 0;
-    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++it) {
-      const int a = it & 1;
-      const uint32_t aph = (it >> 1) & 1;
-      if (!mbar_wait(acc_empty(a), aph ^ 1u, DEV_TIMEOUT_ACC_EMPTY)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-      const uint32_t d_tmem = tmem_base + a * BN;
-      for (int kb = 0; kb < num_kb; ++kb) {
-        if (!mbar_wait(t_full(st), ph_t, DEV_TIMEOUT_TMA_FULL) || !mbar_wait(d_full(sd), ph_d, DEV_TIMEOUT_DQ_FULL)) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (rank == 0) {
+      constexpr uint32_t IDESC = make_idesc(FMT_BF16, WF, 2 * BM, BN);  // M = 256 over the pair, N = 256
+      int st = 0, sd = 0;
+      uint32_t ph_t = 0, ph_d = 0;
+      bool ok = true;
+      int it = 0;
+      for (int tile = pair; tile < p.total_tiles && ok; tile += num_pairs, ++it) {
+        const int a = it & 1;
+        const uint32_t aph = (it >> 1) & 1;
+        if (!mbar_wait(acc_empty(a), aph ^ 1u, DEV_TIMEOUT_ACC_EMPTY)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        if (lane == 0) {
-          const uint64_t adesc = smem_desc_sw128(x_s + st * X_TILE_BYTES);
-          const uint64_t bdesc = smem_desc_sw128(wd_s + sd * WD_TILE_BYTES);
-#pragma unroll
-          for (int k4 = 0; k4 < BK / 16; ++k4) {
-            // +32 bytes (>>4 = 2) per 16-element K step inside the 128-byte swizzle atom
-            umma_f16_ss(d_tmem, adesc + 2 * k4, bdesc + 2 * k4, IDESC, (kb | k4) != 0 ? 1u : 0u);
+        const uint32_t d_tmem = tmem_base + a * BN;
+        for (int s = 0; s < num_st; ++s) {
+          if (!mbar_wait(x_full(st), ph_t, DEV_TIMEOUT_TMA_FULL) || !mbar_wait(d_full(sd), ph_d, DEV_TIMEOUT_DQ_FULL)) {
+            ok = false;
+            break;
           }
-          umma_commit(t_empty(st));
-          umma_commit(d_empty(sd));
-          if (kb == num_kb - 1) umma_commit(acc_full(a));
-        }
-        __syncwarp();
-        if (++st == ST) {
-          st = 0;
-          ph_t ^= 1u;
-        }
-        if (++sd == SD) {
-          sd = 0;
-          ph_d ^= 1u;
+          tc_fence_after();
+          if (lane == 0) {
+#pragma unroll
+            for (int g = 0; g < GPS; ++g) {
+              const uint64_t adesc = smem_desc_sw128(x_s + st * L::X_STAGE + g * X_TILE_BYTES);
+              const uint64_t bdesc = smem_desc_sw128(wd_s + sd * L::WD_STAGE + g * WD_TILE_BYTES);
+#pragma unroll
+              for (int k4 = 0; k4 < BK / 16; ++k4) {
+                // +32 bytes (>>4 = 2) per 16-element K step inside the 128-byte swizzle atom
+                umma_f16_ss_pair(d_tmem, adesc + 2 * k4, bdesc + 2 * k4, IDESC, (s | g | k4) != 0 ? 1u : 0u);
+              }
+            }
+            umma_commit_pair(t_empty(st));
+            umma_commit_pair(d_empty(sd));
+            if (s == num_st - 1) umma_commit_pair(acc_full(a));
+          }
+          __syncwarp();
+          if (++st == ST) {
+            st = 0;
+            ph_t ^= 1u;
+          }
+          if (++sd == SD) {
+            sd = 0;
+            ph_d ^= 1u;
+          }
         }
       }
     }
   } else if (warp >= FIRST_DQ_WARP) {
     // ------------------------------------------------------------ dequantizers
-    // 16 warps: each thread dequantizes half a weight row per k-block; 8 warps: a whole row
-    constexpr int SPLIT = NUM_DQ_WARPS / 8;               // threads per row: 1 or 2
+    // Every warp serves one quantization group of the stage: with 8 warps (4-bit codes) four warps per
+    // group and one thread per weight row, with 16 warps (8-bit codes) eight per group and half a row
+    // per thread.
+    constexpr int WPG = NUM_DQ_WARPS / GPS;        // warps per group
+    constexpr int SPLIT = WPG / 4;                 // threads per weight row: 1 or 2
     const int dq = warp - FIRST_DQ_WARP;
-    const int row = (dq / SPLIT) * 32 + lane;             // row of the 256-row weight tile
-    const int half = dq % SPLIT;                          // which part of the row's 64 k-values
-    constexpr int ROW_BYTES = BK * BITS / 8;              // packed bytes per row per k-block
-    constexpr int RD_CHUNKS = ROW_BYTES / 16;             // 16-byte chunks per row: 2 (4 bits) or 4 (8 bits)
-    constexpr int MY_CHUNKS = RD_CHUNKS / SPLIT;          // packed chunks this thread reads
-    constexpr int MY_OUT = 8 / SPLIT;                     // 16-byte output chunks this thread writes
+    const int grp = dq / WPG;
+    const int row = ((dq % WPG) / SPLIT) * 32 + lane;  // row of this CTA's 128-row weight tile
+    const int part = dq % SPLIT;                       // which part of the row's 64 k-values
+    constexpr int ROW_BYTES = BK * BITS / 8;           // packed bytes per row per group
+    constexpr int RD_CHUNKS = ROW_BYTES / 16;          // 16-byte chunks per row: 2 (4 bits) or 4 (8 bits)
+    constexpr int MY_CHUNKS = RD_CHUNKS / SPLIT;       // packed chunks this thread reads
+    constexpr int MY_OUT = 8 / SPLIT;                  // 16-byte output chunks this thread writes
     // The packed tile is loaded with the TMA swizzle whose span equals one row (32 B for 4 bits,
     // 64 B for 8 bits): 16-byte chunk c of row r sits at chunk c ^ ((r*ROW_BYTES >> 7) & mask), which
     // spreads the per-row reads of a quarter-warp over all banks. Offsets are per-thread constants.
     const uint32_t rd_sw = (static_cast<uint32_t>(row * ROW_BYTES) >> 7) & (RD_CHUNKS - 1);
-    const uint8_t* rd_base = smem_gen + L::OFF_WQ + row * ROW_BYTES;
+    const uint8_t* rd_base = smem_gen + L::OFF_WQ + grp * L::WQ_TILE_BYTES + row * ROW_BYTES;
     uint32_t rd_off[MY_CHUNKS];
 #pragma unroll
-    for (int h = 0; h < MY_CHUNKS; ++h) rd_off[h] = (static_cast<uint32_t>(half * MY_CHUNKS + h) ^ rd_sw) << 4;
-    // B operand tile: 128-byte rows, 16-byte chunk c of row r at chunk c ^ (r & 7); this thread owns chunks 4*half..+3
-    uint8_t* wr_base = smem_gen + L::OFF_WD + row * 128;
+    for (int h = 0; h < MY_CHUNKS; ++h) rd_off[h] = (static_cast<uint32_t>(part * MY_CHUNKS + h) ^ rd_sw) << 4;
+    // B operand tile: 128-byte rows, 16-byte chunk c of row r at chunk c ^ (r & 7)
+    uint8_t* wr_base = smem_gen + L::OFF_WD + grp * WD_TILE_BYTES + row * 128;
     uint32_t wr_off[MY_OUT];
 #pragma unroll
     for (int c = 0; c < MY_OUT; ++c)
-      wr_off[c] = (static_cast<uint32_t>(half * MY_OUT + c) ^ static_cast<uint32_t>(row & 7)) << 4;
-    const uint32_t* sb_base = reinterpret_cast<const uint32_t*>(smem_gen + L::OFF_SB) + row;
+      wr_off[c] = (static_cast<uint32_t>(part * MY_OUT + c) ^ static_cast<uint32_t>(row & 7)) << 4;
+    const uint32_t* sb_base = reinterpret_cast<const uint32_t*>(smem_gen + L::OFF_SB + grp * SB_TILE_BYTES) + row;
     int st = 0, sd = 0;
     uint32_t ph_t = 0, ph_d = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
-      for (int kb = 0; kb < num_kb; ++kb) {
-        if (!mbar_wait(t_full(st), ph_t, DEV_TIMEOUT_TMA_FULL) ||
+    for (int tile = pair; tile < p.total_tiles && ok; tile += num_pairs) {
+      for (int s = 0; s < num_st; ++s) {
+        if (!mbar_wait(w_full(st), ph_t, DEV_TIMEOUT_TMA_FULL) ||
             !mbar_wait(d_empty(sd), ph_d ^ 1u, DEV_TIMEOUT_DQ_EMPTY)) {
           ok = false;
           break;
         }
-        const uint32_t sbv = sb_base[st * (SB_TILE_BYTES / 4)];
+        const uint32_t sbv = sb_base[st * (L::SB_STAGE / 4)];
         const uint32_t s2 = __byte_perm(sbv, sbv, 0x1010);  // (scale, scale)
         const uint32_t b2 = __byte_perm(sbv, sbv, 0x3232);  // (bias, bias)
-        const uint8_t* src = rd_base + st * L::WQ_TILE_BYTES;
-        uint8_t* dst = wr_base + sd * WD_TILE_BYTES;
+        const uint8_t* src = rd_base + st * L::WQ_STAGE;
+        uint8_t* dst = wr_base + sd * L::WD_STAGE;
 #pragma unroll
         for (int h = 0; h < MY_CHUNKS; ++h) {
           const uint4 pk = *reinterpret_cast<const uint4*>(src + rd_off[h]);
@@ -325,10 +360,10 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             *reinterpret_cast<uint4*>(dst + wr_off[2 * h + 1]) = make_uint4(lo1.x, lo1.y, hi1.x, hi1.y);
           }
         }
-        fence_proxy_async_smem();  // make these generic-proxy writes visible to the tensor core
+        fence_proxy_async_smem();  // make these generic-proxy writes visible to the tensor cores of the pair
         __syncwarp();
         if (lane == 0) {
-          mbar_arrive(d_full(sd));
+          mbar_arrive_leader(d_full(sd));
           mbar_arrive(t_empty(st));
         }
         if (++st == ST) {
@@ -348,13 +383,13 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     const int row = q * 32 + lane;
     bool ok = true;
     int it = 0;
-    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++it) {
+    for (int tile = pair; tile < p.total_tiles && ok; tile += num_pairs, ++it) {
       const int a = it & 1;
       const uint32_t aph = (it >> 1) & 1;
       const int tm = tile % p.tiles_m;
       const int tn = tile / p.tiles_m;
       const int b = tm / p.tiles_m_per_sample;
-      const int r = (tm % p.tiles_m_per_sample) * BM + row;
+      const int r = (tm % p.tiles_m_per_sample) * (2 * BM) + static_cast<int>(rank) * BM + row;
       const int n0 = tn * BN;
       float* bias_s = vec_s + a * BN;
       float* gate_s = vec_s + 2 * BN + a * BN;
@@ -431,29 +466,30 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(acc_empty(a));
+      if (lane == 0) mbar_arrive_leader(acc_empty(a));
     }
   }
 
   tc_fence_before();
   __syncthreads();
+  cluster_sync_all();  // the peer may still be reading this CTA's shared/tensor memory until here
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
 }
 
 MFX_DEFINE_STATUS_READER(read_status)
 
-template <int BITS, uint32_t WF, int ST, typename OUT, int EPI>
+template <int BITS, uint32_t WF, int ST, int SD, typename OUT, int EPI>
 int launch_epi(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tsb, const Params& p, int grid,
                cudaStream_t st) {
-  using L = Smem<BITS, ST>;
+  using L = Smem<BITS, ST, SD>;
   // 4-bit codes need half the integer work per value: 8 dequantizer warps keep up and draw less power;
   // 8-bit codes want 16
   constexpr int NDQ = BITS == 4 ? 8 : 16;
   constexpr int NUM_THREADS = (FIXED_WARPS + NDQ) * 32;
-  auto kern = qmm_kernel<BITS, WF, ST, OUT, EPI, NDQ>;
+  auto kern = qmm_kernel<BITS, WF, ST, SD, OUT, EPI, NDQ>;
   static bool configured = false;  // attribute is per function; set once per process and device reuse is fine
   static int configured_dev = -1;
   int dev = 0;
@@ -468,15 +504,15 @@ int launch_epi(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& 
   return MFX_OK;
 }
 
-template <int BITS, uint32_t WF, int ST, typename OUT>
+template <int BITS, uint32_t WF, int ST, int SD, typename OUT>
 int launch(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tsb, const Params& p, int grid,
            cudaStream_t st) {
   switch (p.epilogue) {
-    case MFX_EPI_GELU_ERF: return launch_epi<BITS, WF, ST, OUT, MFX_EPI_GELU_ERF>(tx, tw, tsb, p, grid, st);
-    case MFX_EPI_GELU_TANH: return launch_epi<BITS, WF, ST, OUT, MFX_EPI_GELU_TANH>(tx, tw, tsb, p, grid, st);
-    case MFX_EPI_GATE_RESIDUAL: return launch_epi<BITS, WF, ST, OUT, MFX_EPI_GATE_RESIDUAL>(tx, tw, tsb, p, grid, st);
-    case MFX_EPI_SILU: return launch_epi<BITS, WF, ST, OUT, MFX_EPI_SILU>(tx, tw, tsb, p, grid, st);
-    default: return launch_epi<BITS, WF, ST, OUT, MFX_EPI_NONE>(tx, tw, tsb, p, grid, st);
+    case MFX_EPI_GELU_ERF: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_GELU_ERF>(tx, tw, tsb, p, grid, st);
+    case MFX_EPI_GELU_TANH: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_GELU_TANH>(tx, tw, tsb, p, grid, st);
+    case MFX_EPI_GATE_RESIDUAL: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_GATE_RESIDUAL>(tx, tw, tsb, p, grid, st);
+    case MFX_EPI_SILU: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_SILU>(tx, tw, tsb, p, grid, st);
+    default: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_NONE>(tx, tw, tsb, p, grid, st);
   }
 }
 
@@ -638,7 +674,7 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
     const uint64_t words_per_row = static_cast<uint64_t>(a.K) * a.bits / 32;
     const uint64_t dims[2] = {words_per_row, static_cast<uint64_t>(a.N)};
     const uint64_t strides[1] = {words_per_row * 4};
-    const uint32_t box[2] = {static_cast<uint32_t>(BK * a.bits / 32), BN};
+    const uint32_t box[2] = {static_cast<uint32_t>(BK * a.bits / 32), BN_HALF};  // each CTA of a pair: 128 weight rows
     if (int rc = encode_tmap(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, codes, dims, strides, box,
                              a.bits == 4 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B))
       return rc;
@@ -646,7 +682,7 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(a.N), static_cast<uint64_t>(a.K / 64)};
     const uint64_t strides[1] = {static_cast<uint64_t>(a.N) * 4};
-    const uint32_t box[2] = {BN, 1};
+    const uint32_t box[2] = {BN_HALF, 1};
     if (int rc = encode_tmap(&tsb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, sb_packed, dims, strides, box,
                              CU_TENSOR_MAP_SWIZZLE_NONE))
       return rc;
@@ -656,7 +692,7 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
   p.batch = static_cast<int>(a.batch);
   p.N = static_cast<int>(a.N);
   p.K = static_cast<int>(a.K);
-  p.tiles_m_per_sample = static_cast<int>((a.rows + BM - 1) / BM);
+  p.tiles_m_per_sample = static_cast<int>((a.rows + 2 * BM - 1) / (2 * BM));  // a pair covers 256 activation rows
   p.tiles_m = p.tiles_m_per_sample * p.batch;
   p.tiles_n = static_cast<int>((a.N + BN - 1) / BN);
   const int64_t total = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
@@ -674,14 +710,15 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
   p.y = a.y;
   p.y_row_stride = a.y_row_stride;
   p.y_batch_stride = a.y_batch_stride;
-  const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
+  const int pairs = sm_count() / 2;
+  const int grid = 2 * (p.total_tiles < pairs ? p.total_tiles : pairs);
   const bool f32 = a.y_dtype == MFX_F32;
   if (a.bits == 4) {
-    return f32 ? launch<4, FMT_BF16, 4, float>(tx, tw, tsb, p, grid, st)
-               : launch<4, FMT_BF16, 4, __nv_bfloat16>(tx, tw, tsb, p, grid, st);
+    return f32 ? launch<4, FMT_BF16, 3, 3, float>(tx, tw, tsb, p, grid, st)
+               : launch<4, FMT_BF16, 3, 3, __nv_bfloat16>(tx, tw, tsb, p, grid, st);
   }
-  return f32 ? launch<8, FMT_BF16, 3, float>(tx, tw, tsb, p, grid, st)
-             : launch<8, FMT_BF16, 3, __nv_bfloat16>(tx, tw, tsb, p, grid, st);
+  return f32 ? launch<8, FMT_BF16, 3, 2, float>(tx, tw, tsb, p, grid, st)
+             : launch<8, FMT_BF16, 3, 2, __nv_bfloat16>(tx, tw, tsb, p, grid, st);
 }
 
 // ---------------------------------------------------------------- allocation-free variant
