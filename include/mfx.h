@@ -196,6 +196,21 @@ int mfx_fmha(const void* q, const void* k, const void* v, int64_t qkv_row_stride
 int mfx_vec_sum_act(const void* a, const void* b, const void* c, int in_dtype, int act, void* out, int out_dtype,
                     int64_t n, void* stream);
 
+/* out = residual + gate[sample] * (y + bias): the gated residual of joint_transformer_block.py:84-90 /
+ * qwen_transformer_block.py:56-57,64,69 as a stand-alone kernel, for tensor-parallel row-split linears whose
+ * partial sums are all-reduced before the gate can be applied (no counterpart in the single-device reference).
+ * y is [batch, rows, D] bf16 or f32 (dense), residual/out f32 (may alias), gate [batch, D], bias [D] nullable. */
+int mfx_gate_residual(const void* y, int y_dtype, const void* bias, int bias_dtype, const void* gate, int gate_dtype,
+                      int64_t gate_batch_stride, const float* residual, float* out, int64_t batch, int64_t rows,
+                      int64_t D, void* stream);
+
+/* Classifier-free-guidance combine of two noise predictions [rows, channels] into f32 `out`.
+ * mode 0: noise + g*(noise - negative)  (src/mflux/models/z_image/variants/z_image.py:209);
+ * mode 1: negative + g*(noise - negative), rescaled per row to the norm of `noise`
+ *         (QwenImage.compute_guided_noise, src/mflux/models/qwen/variants/txt2img/qwen_image.py:165-174). */
+int mfx_cfg_combine(const void* noise, const void* noise_negative, int dtype, float guidance, int mode, float* out,
+                    int64_t rows, int64_t channels, void* stream);
+
 /* Replaces LinearScheduler.step (src/mflux/models/common/schedulers/linear_scheduler.py:56-58):
  * out = latents + noise * dt, in the latents' dtype. */
 int mfx_euler_step(const void* latents, int lat_dtype, const void* noise, int noise_dtype, float dt, void* out,

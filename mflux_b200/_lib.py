@@ -127,6 +127,12 @@ SIGNATURES = {
          c_int64, c_void_p],
     ),
     "mfx_vec_sum_act": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int64, c_void_p]),
+    "mfx_gate_residual": (
+        c_int,
+        [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+         c_void_p],
+    ),
+    "mfx_cfg_combine": (c_int, [c_void_p, c_void_p, c_int, ctypes.c_float, c_int, c_void_p, c_int64, c_int64, c_void_p]),
     "mfx_euler_step": (c_int, [c_void_p, c_int, c_void_p, c_int, ctypes.c_float, c_void_p, c_int64, c_void_p]),
 }
 

@@ -216,6 +216,63 @@ __global__ void __launch_bounds__(256) euler_step_kernel(const void* latents, in
   else static_cast<__half*>(out)[i] = __float2half_rn(v);
 }
 
+
+// x[b, r, :] = residual[b, r, :] + gate[b, :] * (y[b, r, :] + bias[:]); residual/x float32 (in place allowed),
+// y bf16 or f32. Used after the all-reduce of a row-split (tensor-parallel) linear, where the gated residual
+// cannot be an epilogue of the matmul because the partial sums of all ranks must be added first.
+__global__ void __launch_bounds__(256) gate_residual_kernel(const void* __restrict__ y, int y_dtype,
+                                                            const void* __restrict__ bias, int bias_dtype,
+                                                            const void* __restrict__ gate, int gate_dtype,
+                                                            int64_t gate_batch_stride, const float* residual,
+                                                            float* out, int64_t rows_per_batch, int64_t D,
+                                                            int64_t n_vec) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;  // one 8-element vector
+  if (i >= n_vec) return;
+  const int64_t vec_per_row = D >> 3;
+  const int64_t row = i / vec_per_row;
+  const int col = static_cast<int>(i % vec_per_row) * 8;
+  const int64_t b = row / rows_per_batch;
+  float yv[8], rv[8];
+  if (y_dtype == MFX_F32) load8<float>(static_cast<const float*>(y) + i * 8, yv);
+  else load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(y) + i * 8, yv);
+  load8<float>(residual + i * 8, rv);
+  float o[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float bv = bias ? ld_scalar(bias, bias_dtype, col + j) : 0.f;
+    const float gv = ld_scalar(gate, gate_dtype, b * gate_batch_stride + col + j);
+    o[j] = rv[j] + gv * (yv[j] + bv);
+  }
+  *reinterpret_cast<float4*>(out + i * 8) = make_float4(o[0], o[1], o[2], o[3]);
+  *reinterpret_cast<float4*>(out + i * 8 + 4) = make_float4(o[4], o[5], o[6], o[7]);
+}
+
+// Classifier-free-guidance combine of two noise predictions, one warp per token row of C <= 1024 channels.
+// mode 0: out = n + g * (n - n_neg)                              (z_image.py:209)
+// mode 1: comb = n_neg + g * (n - n_neg); out = comb * ||n|| / ||comb|| over the channel axis, eps 1e-12
+//         (QwenImage.compute_guided_noise, qwen_image.py:165-174)
+__global__ void __launch_bounds__(256) cfg_combine_kernel(const void* __restrict__ n, const void* __restrict__ nn,
+                                                          int dtype, float g, int mode, float* __restrict__ out,
+                                                          int64_t rows, int C) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + warp;
+  if (row >= rows) return;
+  float sn = 0.f, sc = 0.f;
+  for (int c = lane; c < C; c += 32) {
+    const float a = ld_scalar(n, dtype, row * C + c), b = ld_scalar(nn, dtype, row * C + c);
+    const float comb = mode == 0 ? a + g * (a - b) : b + g * (a - b);
+    sn += a * a;
+    sc += comb * comb;
+  }
+  float ratio = 1.f;
+  if (mode == 1) ratio = sqrtf(warp_sum(sn) + 1e-12f) / sqrtf(warp_sum(sc) + 1e-12f);
+  for (int c = lane; c < C; c += 32) {
+    const float a = ld_scalar(n, dtype, row * C + c), b = ld_scalar(nn, dtype, row * C + c);
+    const float comb = mode == 0 ? a + g * (a - b) : b + g * (a - b);
+    out[row * C + c] = comb * ratio;
+  }
+}
+
 }  // namespace glue
 }  // namespace mfx
 
@@ -328,6 +385,36 @@ int mfx_euler_step(const void* latents, int lat_dtype, const void* noise, int no
   if (int rc = check_arch()) return rc;
   glue::euler_step_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       latents, lat_dtype, noise, noise_dtype, dt, out, n);
+  MFX_CUDA_TRY(cudaGetLastError());
+  return MFX_OK;
+}
+
+int mfx_gate_residual(const void* y, int y_dtype, const void* bias, int bias_dtype, const void* gate, int gate_dtype,
+                      int64_t gate_batch_stride, const float* residual, float* out, int64_t batch, int64_t rows,
+                      int64_t D, void* stream) {
+  using namespace mfx;
+  if (!y || !gate || !residual || !out) return MFX_ERR_NULL;
+  if (batch <= 0 || rows <= 0 || D <= 0 || D % 8 != 0) return MFX_ERR_SHAPE;
+  if ((y_dtype != MFX_F32 && y_dtype != MFX_BF16) || !valid_dtype(gate_dtype) || (bias && !valid_dtype(bias_dtype)))
+    return MFX_ERR_DTYPE;
+  if (!aligned16(y) || !aligned16(residual) || !aligned16(out)) return MFX_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  const int64_t n_vec = batch * rows * D / 8;
+  glue::gate_residual_kernel<<<static_cast<unsigned>((n_vec + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      y, y_dtype, bias, bias_dtype, gate, gate_dtype, gate_batch_stride, residual, out, rows, D, n_vec);
+  MFX_CUDA_TRY(cudaGetLastError());
+  return MFX_OK;
+}
+
+int mfx_cfg_combine(const void* noise, const void* noise_negative, int dtype, float guidance, int mode, float* out,
+                    int64_t rows, int64_t channels, void* stream) {
+  using namespace mfx;
+  if (!noise || !noise_negative || !out) return MFX_ERR_NULL;
+  if (rows <= 0 || channels <= 0 || channels > 1024 || (mode != 0 && mode != 1)) return MFX_ERR_SHAPE;
+  if (!valid_dtype(dtype)) return MFX_ERR_DTYPE;
+  if (int rc = check_arch()) return rc;
+  glue::cfg_combine_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      noise, noise_negative, dtype, guidance, mode, out, rows, static_cast<int>(channels));
   MFX_CUDA_TRY(cudaGetLastError());
   return MFX_OK;
 }

@@ -373,3 +373,43 @@ def qlinear_plain(x: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, biase
         _lib.check(rc, "mfx_qlinear")
     LAUNCHES[0] += 3
     return y
+
+
+def gate_residual(y: torch.Tensor, gate: torch.Tensor, residual: torch.Tensor, bias: torch.Tensor | None = None,
+                  out: torch.Tensor | None = None) -> torch.Tensor:
+    """residual + gate[sample] * (y + bias) in float32 (in place on `residual` when out is None).
+
+    y [batch, rows, D] bf16/f32 dense, residual f32 dense, gate [batch, D] (any batch stride), bias [D].
+    """
+    lib = _lib.load()
+    _cuda(y, "y")
+    if y.dim() != 3 or not y.is_contiguous() or not residual.is_contiguous() or residual.dtype != torch.float32:
+        raise ValueError("y must be dense [batch, rows, D]; residual must be dense float32 of the same shape")
+    if residual.shape != y.shape:
+        raise ValueError("residual must have y's shape")
+    out = residual if out is None else out
+    b, r, d = y.shape
+    gate = gate.reshape(b, d) if gate.stride(-1) == 1 else gate.reshape(b, d).contiguous()
+    bias_c = None if bias is None else bias.contiguous()
+    rc = lib.mfx_gate_residual(_ptr(y), _dt(y), _ptr(bias_c), 0 if bias_c is None else _dt(bias_c), _ptr(gate),
+                               _dt(gate), gate.stride(0), _ptr(residual), _ptr(out), b, r, d, _stream())
+    _lib.check(rc, "mfx_gate_residual")
+    LAUNCHES[0] += 1
+    return out
+
+
+def cfg_combine(noise: torch.Tensor, noise_negative: torch.Tensor, guidance: float, mode: str = "qwen") -> torch.Tensor:
+    """Guided noise in float32. mode "plain": n + g*(n - n_neg); "qwen": n_neg + g*(n - n_neg) rescaled per row
+    to ||n|| over the last axis."""
+    lib = _lib.load()
+    _cuda(noise, "noise")
+    noise, noise_negative = noise.contiguous(), noise_negative.contiguous()
+    if noise.shape != noise_negative.shape or noise.dtype != noise_negative.dtype:
+        raise ValueError("both predictions must share shape and dtype")
+    c = noise.shape[-1]
+    out = torch.empty(noise.shape, dtype=torch.float32, device=noise.device)
+    rc = lib.mfx_cfg_combine(_ptr(noise), _ptr(noise_negative), _dt(noise), float(guidance),
+                             {"plain": 0, "qwen": 1}[mode], _ptr(out), noise.numel() // c, c, _stream())
+    _lib.check(rc, "mfx_cfg_combine")
+    LAUNCHES[0] += 1
+    return out

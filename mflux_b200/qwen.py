@@ -1,0 +1,301 @@
+"""Qwen-Image-shaped dual-stream MMDiT denoising step on the B200 kernels, optionally tensor-parallel.
+
+Module tree, attribute names and arithmetic follow the reference's QwenTransformer
+(src/mflux/models/qwen/model/qwen_transformer/qwen_transformer.py:15-72, qwen_transformer_block.py:10-76,
+qwen_attention.py:8-158, qwen_feed_forward.py, qwen_rope.py, qwen_timesteps.py, qwen_transformer_rms_norm.py).
+As in flux.py, text and image tokens share one sequence buffer (text first, qwen_attention.py:67-69), q/k/v run
+as one matmul and gate*y+residual / GELU are matmul epilogues.
+
+Tensor parallelism (no counterpart in the single-device reference): to_q/k/v, add_*_proj and mlp_in are split by
+output rows (whole heads per rank), attn_to_out / to_add_out / mlp_out by input columns; the partial sums are
+all-reduced with NCCL and the gated residual is applied afterwards. Every rank quantizes its own shard; because
+quantization groups run along the input dimension and K / tp stays a multiple of 64, the shards' packed codes,
+scales and biases are slices of what quantizing the full weight would give. LayerNorm, modulation and the residual
+stream are replicated.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from . import nn, ops, resolution
+from .flux import AdaNorm, FusedRows, MLPEmbedder, RMSNorm, _call, _linear
+from .schedulers import LinearScheduler
+
+
+@dataclass
+class QwenConfig:
+    hidden: int = 3072
+    heads: int = 24
+    num_layers: int = 60
+    in_channels: int = 64
+    joint_attention_dim: int = 3584
+    mlp_ratio: int = 4
+
+    def __post_init__(self):
+        if self.hidden != self.heads * 128:
+            raise ValueError("hidden must equal heads * 128 (head dimension 128)")
+
+
+class _Ctx:
+    """Creates every linear from the same seeded stream on all ranks, keeps this rank's shard, quantizes it."""
+
+    def __init__(self, device, bits, std, seed, mode, tp_rank, tp_world):
+        self.device, self.bits, self.std, self.mode = device, bits, std, mode
+        self.rank, self.world = tp_rank, tp_world
+        self.gen = torch.Generator(device=device).manual_seed(seed)
+
+    def _finish(self, lin):
+        if self.bits is not None and lin.weight.shape[1] % 64 == 0:
+            return lin.to_quantized(group_size=64, bits=self.bits, mode=self.mode)
+        return lin
+
+    def linear(self, i, o, bias=True, split=None):
+        lin = _linear(i, o, bias, self.device, self.std, self.gen)
+        if split is not None and self.world > 1:
+            if split == "col":  # output rows
+                n = o // self.world
+                sl = slice(self.rank * n, (self.rank + 1) * n)
+                lin.weight = torch.nn.Parameter(lin.weight.data[sl].contiguous(), requires_grad=False)
+                if bias:
+                    lin.bias = torch.nn.Parameter(lin.bias.data[sl].contiguous(), requires_grad=False)
+            else:  # "row": input columns; the bias is added once, after the all-reduce
+                k = i // self.world
+                if k % 64 != 0:
+                    raise ValueError("K / tp must stay a multiple of the quantization group size 64")
+                sl = slice(self.rank * k, (self.rank + 1) * k)
+                lin.weight = torch.nn.Parameter(lin.weight.data[:, sl].contiguous(), requires_grad=False)
+        return self._finish(lin)
+
+
+class QwenFeedForward(nn.Module):
+    def __init__(self, ctx, d, ratio):
+        super().__init__()
+        self.mlp_in = ctx.linear(d, ratio * d, split="col")
+        self.mlp_out = ctx.linear(ratio * d, d, split="row")
+
+
+class QwenAttention(nn.Module):
+    def __init__(self, ctx, d):
+        super().__init__()
+        self.to_q, self.to_k, self.to_v = (ctx.linear(d, d, split="col") for _ in range(3))
+        self.add_q_proj, self.add_k_proj, self.add_v_proj = (ctx.linear(d, d, split="col") for _ in range(3))
+        self.norm_q, self.norm_k = RMSNorm(128, 1e-6, ctx.device), RMSNorm(128, 1e-6, ctx.device)
+        self.norm_added_q, self.norm_added_k = RMSNorm(128, 1e-6, ctx.device), RMSNorm(128, 1e-6, ctx.device)
+        self.attn_to_out = torch.nn.ModuleList([ctx.linear(d, d, split="row")])
+        self.to_add_out = ctx.linear(d, d, split="row")
+
+
+class QwenTransformerBlock(nn.Module):
+    def __init__(self, ctx, cfg):
+        super().__init__()
+        d = cfg.hidden
+        self.img_mod_linear = ctx.linear(d, 6 * d)
+        self.attn = QwenAttention(ctx, d)
+        self.img_ff = QwenFeedForward(ctx, d, cfg.mlp_ratio)
+        self.txt_mod_linear = ctx.linear(d, 6 * d)
+        self.txt_ff = QwenFeedForward(ctx, d, cfg.mlp_ratio)
+
+
+class QwenTimeTextEmbed(nn.Module):
+    def __init__(self, ctx, d):
+        super().__init__()
+        self.timestep_embedder = MLPEmbedder(ctx, 256, d)
+
+
+class QwenTransformer(nn.Module):
+    def __init__(self, cfg: QwenConfig = QwenConfig(), bits: int | None = 4, device="cuda", std: float = 0.02,
+                 seed: int = 0, mode: str = "mlx", tp_rank: int = 0, tp_world: int = 1, tp_group=None):
+        super().__init__()
+        if cfg.heads % tp_world != 0:
+            raise ValueError("the number of heads must be divisible by the tensor-parallel size")
+        self.cfg, self.bits = cfg, bits
+        self.tp_rank, self.tp_world, self.tp_group = tp_rank, tp_world, tp_group
+        ctx = _Ctx(device, bits, std, seed, mode, tp_rank, tp_world)
+        d = cfg.hidden
+        self.img_in = ctx.linear(cfg.in_channels, d)
+        self.txt_norm = RMSNorm(cfg.joint_attention_dim, 1e-6, device)
+        self.txt_in = ctx.linear(cfg.joint_attention_dim, d)
+        self.time_text_embed = QwenTimeTextEmbed(ctx, d)
+        self.transformer_blocks = torch.nn.ModuleList([QwenTransformerBlock(ctx, cfg) for _ in range(cfg.num_layers)])
+        self.norm_out = AdaNorm(ctx, d, 2, bias=False)
+        self.proj_out = ctx.linear(d, cfg.in_channels)
+        self._fused, self._rope, self._buffers_for = {}, {}, None
+
+    # ------------------------------------------------------------------ helpers
+    def _fuse(self, key, layers):
+        f = self._fused.get(key)
+        if f is None:
+            if all(isinstance(l, nn.QuantizedLinear) for l in layers):
+                f = FusedRows(layers)
+            else:
+                f = lambda x, out, ls=layers: out.copy_(torch.cat([l(x) for l in ls], dim=-1))  # noqa: E731
+            self._fused[key] = f
+        return f
+
+    def _workspace(self, b, s, device):
+        key = (b, s, str(device))
+        if self._buffers_for != key:
+            d, r, tp = self.cfg.hidden, self.cfg.mlp_ratio, self.tp_world
+            self.nbuf = torch.empty(b, s, d, dtype=torch.bfloat16, device=device)
+            self.qkv = torch.empty(b, s, 3 * d // tp, dtype=torch.bfloat16, device=device)
+            self.attn = torch.empty(b, s, d // tp, dtype=torch.bfloat16, device=device)
+            self.ffb = torch.empty(b, s, r * d // tp, dtype=torch.bfloat16, device=device)
+            self._buffers_for = key
+        return self.nbuf, self.qkv, self.attn, self.ffb
+
+    @staticmethod
+    def _rope_params(index: np.ndarray, dim: int, theta: float = 10000.0) -> np.ndarray:
+        omega = 1.0 / (theta ** (np.arange(0, dim, 2, dtype=np.float32) / dim))
+        f = np.outer(index.astype(np.float32), omega)
+        return np.stack([np.cos(f), np.sin(f)], axis=-1)
+
+    def rope_table(self, height, width, txt_len, device):
+        """QwenEmbedRopeMLX with scale_rope=True (qwen_rope.py:35-113): image rows/cols are centred
+        (-(h - h//2) .. h//2 - 1), the frame index is 0, text positions continue after max(h//2, w//2)."""
+        key = (height, width, txt_len, str(device))
+        t = self._rope.get(key)
+        if t is None:
+            lh, lw = height // 16, width // 16
+            rows = np.concatenate([np.arange(-(lh - lh // 2), 0), np.arange(0, lh // 2)])
+            cols = np.concatenate([np.arange(-(lw - lw // 2), 0), np.arange(0, lw // 2)])
+            fr = np.broadcast_to(self._rope_params(np.zeros(1), 16)[None], (lh, lw, 8, 2))
+            fh = np.broadcast_to(self._rope_params(rows, 56)[:, None], (lh, lw, 28, 2))
+            fw = np.broadcast_to(self._rope_params(cols, 56)[None, :], (lh, lw, 28, 2))
+            img = np.concatenate([fr, fh, fw], axis=2).reshape(lh * lw, 64, 2)
+            start = max(lh // 2, lw // 2)
+            tpos = np.arange(start, start + txt_len)
+            txt = np.concatenate([self._rope_params(tpos, 16), self._rope_params(tpos, 56),
+                                  self._rope_params(tpos, 56)], axis=1)
+            t = torch.from_numpy(np.concatenate([txt, img], axis=0).astype(np.float32)).contiguous().to(device)
+            self._rope[key] = t
+        return t
+
+    @staticmethod
+    def time_proj(timestep: torch.Tensor) -> torch.Tensor:
+        """QwenTimesteps (qwen_timesteps.py:15-34): the reference holds the timestep and the frequency table
+        in the activation dtype (bf16); scale 1000; [cos, sin] order."""
+        half = 128
+        freqs = torch.exp(-math.log(10000) * torch.arange(half, dtype=torch.float32, device=timestep.device) / half)
+        freqs = freqs.to(torch.bfloat16).float()
+        emb = 1000.0 * (timestep.to(torch.bfloat16).float()[:, None] * freqs[None, :])
+        return torch.cat([torch.cos(emb), torch.sin(emb)], dim=-1)
+
+    def _all_reduce(self, t):
+        if self.tp_world > 1:
+            dist.all_reduce(t, group=self.tp_group)
+        return t
+
+    def _row_parallel(self, layer, x, gate, residual):
+        """residual += gate * (x . W^T + bias) for a layer split by input columns."""
+        if self.tp_world == 1:
+            return _call(layer, x, epilogue="gate_residual", gate=gate, residual=residual, out=residual)
+        part = self.part_img if residual is self.x_img else self.part_txt
+        bias = layer.bias
+        if isinstance(layer, nn.QuantizedLinear):
+            ops.qlinear(x, layer.weight.data, layer.scales.data, layer.biases.data, None, bits=layer.bits, out=part,
+                        prepared=layer.prepared())
+        else:
+            part.copy_(torch.nn.functional.linear(x, layer.weight))
+        self._all_reduce(part)
+        return ops.gate_residual(part, gate, residual, None if bias is None else bias.data)
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, hidden_states: torch.Tensor, encoder_hidden_states: torch.Tensor, timestep: torch.Tensor,
+                height: int, width: int) -> torch.Tensor:
+        """latents [B, Si, C] + text states [B, St, joint_dim] + sigma [B] -> predicted noise [B, Si, C] (bf16).
+        The text mask of the reference is all ones here (it drops an all-ones mask, qwen_attention.py:131-132)."""
+        cfg = self.cfg
+        d, heads = cfg.hidden, cfg.heads // self.tp_world
+        b, si, _ = hidden_states.shape
+        st = encoder_hidden_states.shape[1]
+        dev = hidden_states.device
+        # two dense stream buffers (the all-reduced partial sums want dense operands)
+        nbuf, qkv, attn, ffb = self._workspace(b, st + si, dev)
+        if getattr(self, "_streams_for", None) != (b, si, st, str(dev)):
+            self.x_img = torch.empty(b, si, d, dtype=torch.float32, device=dev)   # residual streams
+            self.x_txt = torch.empty(b, st, d, dtype=torch.float32, device=dev)
+            if self.tp_world > 1:  # partial sums of the row-split linears, all-reduced in place
+                self.part_img = torch.empty(b, si, d, dtype=torch.bfloat16, device=dev)
+                self.part_txt = torch.empty(b, st, d, dtype=torch.bfloat16, device=dev)
+            self._streams_for = (b, si, st, str(dev))
+        x_img, x_txt = self.x_img, self.x_txt
+        n_img, n_txt = nbuf[:, st:], nbuf[:, :st]
+        cos_sin = self.rope_table(height, width, st, dev)
+
+        _call(self.img_in, hidden_states.to(torch.bfloat16), out=x_img)
+        tn = ops.norm_modulate(encoder_hidden_states.to(torch.bfloat16), weight=self.txt_norm.weight.data,
+                               eps=self.txt_norm.eps, rms=True)
+        _call(self.txt_in, tn, out=x_txt)
+        temb = self.time_text_embed.timestep_embedder(self.time_proj(timestep).to(torch.bfloat16))
+        sv = ops.vec_sum_act(temb, act="silu", out_dtype=torch.bfloat16)
+
+        for i, blk in enumerate(self.transformer_blocks):
+            a = blk.attn
+            mi = _call(blk.img_mod_linear, sv)   # [B, 6D]: (shift, scale, gate) x 2
+            mt = _call(blk.txt_mod_linear, sv)
+            ops.norm_modulate(x_img, mi[:, 0:d], mi[:, d:2 * d], out=n_img)
+            ops.norm_modulate(x_txt, mt[:, 0:d], mt[:, d:2 * d], out=n_txt)
+            self._fuse(("q", i), [a.to_q, a.to_k, a.to_v])(n_img, qkv[:, st:])
+            self._fuse(("a", i), [a.add_q_proj, a.add_k_proj, a.add_v_proj])(n_txt, qkv[:, :st])
+            ops.qknorm_rope(qkv, heads, a.norm_added_q.weight.data, a.norm_added_k.weight.data, a.norm_q.weight.data,
+                            a.norm_k.weight.data, st, cos_sin, a.norm_q.eps)
+            ops.fmha(qkv, heads, out=attn)
+            self._row_parallel(a.attn_to_out[0], attn[:, st:], mi[:, 2 * d:3 * d], x_img)
+            self._row_parallel(a.to_add_out, attn[:, :st], mt[:, 2 * d:3 * d], x_txt)
+            ops.norm_modulate(x_img, mi[:, 3 * d:4 * d], mi[:, 4 * d:5 * d], out=n_img)
+            ops.norm_modulate(x_txt, mt[:, 3 * d:4 * d], mt[:, 4 * d:5 * d], out=n_txt)
+            _call(blk.img_ff.mlp_in, n_img, epilogue="gelu_approx", out=ffb[:, st:])
+            self._row_parallel(blk.img_ff.mlp_out, ffb[:, st:], mi[:, 5 * d:6 * d], x_img)
+            _call(blk.txt_ff.mlp_in, n_txt, epilogue="gelu_approx", out=ffb[:, :st])
+            self._row_parallel(blk.txt_ff.mlp_out, ffb[:, :st], mt[:, 5 * d:6 * d], x_txt)
+
+        mod = _call(self.norm_out.linear, sv)   # [B, 2D]: scale, shift (ada_layer_norm_continuous.py:16-19)
+        ops.norm_modulate(x_img, mod[:, d:2 * d], mod[:, 0:d], out=n_img)
+        return _call(self.proj_out, n_img)
+
+
+class QwenImage:
+    """Denoise loop of the reference's QwenImage variant (variants/txt2img/qwen_image.py:99-128,165-174):
+    two denoiser evaluations per step (prompt and negative prompt, run as one batch of 2) and the
+    norm-preserving guidance combine."""
+
+    def __init__(self, quantize: int | None = None, model_config: QwenConfig | None = None, device="cuda",
+                 seed: int = 0, stored_quantization: int | None = None, tp_rank: int = 0, tp_world: int = 1,
+                 tp_group=None):
+        bits, warning = resolution.resolve(stored_quantization, quantize)
+        if warning:
+            print(f"Warning: {warning}")
+        resolution.check_supported(bits)
+        self.bits = bits
+        self.model_config = model_config or QwenConfig()
+        self.transformer = QwenTransformer(self.model_config, bits=bits, device=device, seed=seed, tp_rank=tp_rank,
+                                           tp_world=tp_world, tp_group=tp_group)
+
+    def denoise_step(self, latents, prompt_embeds, negative_prompt_embeds, sigma, dt, guidance, height, width):
+        b = latents.shape[0]
+        both = self.transformer(torch.cat([latents, latents]), torch.cat([prompt_embeds, negative_prompt_embeds]),
+                                torch.full((2 * b,), sigma, device=latents.device), height, width)
+        guided = ops.cfg_combine(both[:b], both[b:], guidance, mode="qwen")
+        return ops.euler_step(latents, guided, dt)
+
+    def generate_image(self, seed: int, prompt_embeds: torch.Tensor, negative_prompt_embeds: torch.Tensor,
+                       num_inference_steps: int = 20, height: int = 1328, width: int = 1328, guidance: float = 4.0,
+                       latents: torch.Tensor | None = None) -> torch.Tensor:
+        """Returns the final latents [B, (H/16)(W/16), C] (f32); prompt embeddings stand in for the text encoder."""
+        dev = prompt_embeds.device
+        b = prompt_embeds.shape[0]
+        sched = LinearScheduler(num_inference_steps, width, height, True)
+        if latents is None:
+            g = torch.Generator(device=dev).manual_seed(seed)
+            latents = torch.randn(b, (height // 16) * (width // 16), self.model_config.in_channels, device=dev,
+                                  generator=g)
+        latents = latents.float()
+        for t in range(num_inference_steps):
+            latents = self.denoise_step(latents, prompt_embeds, negative_prompt_embeds, float(sched.sigmas[t]),
+                                        sched.dt(t), guidance, height, width)
+        return latents

@@ -1,0 +1,38 @@
+"""Worker of the tensor-parallel test: launched by torchrun with 2 ranks; rank 0 also runs the tp=1 model."""
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+
+from mflux_b200.qwen import QwenConfig, QwenTransformer  # noqa: E402
+from oracle.quant import rel_l2  # noqa: E402
+
+
+def main():
+    out_dir = Path(sys.argv[1])
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
+    cfg = QwenConfig(hidden=512, heads=4, num_layers=2, joint_attention_dim=128)
+    g = torch.Generator(device="cpu").manual_seed(11)
+    lat = torch.randn(2, 6 * 9, 64, generator=g).cuda()
+    ctx = torch.randn(2, 40, 128, generator=g).to(torch.bfloat16).cuda()
+    sigma = torch.tensor([0.9, 0.3]).cuda()
+    tp = QwenTransformer(cfg, bits=4, device="cuda", seed=5, tp_rank=rank, tp_world=world)
+    y_tp = tp(lat, ctx, sigma, 96, 144).float()
+    torch.cuda.synchronize()
+    if rank == 0:
+        one = QwenTransformer(cfg, bits=4, device="cuda", seed=5)
+        y1 = one(lat, ctx, sigma, 96, 144).float()
+        (out_dir / "tp_err.txt").write_text(str(rel_l2(y_tp, y1.cpu().numpy())))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
