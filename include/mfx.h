@@ -50,7 +50,12 @@ typedef enum mfx_epilogue {
   MFX_EPI_GELU_ERF = 1,      /* y = gelu(v), erf form        (mlx.nn.gelu) */
   MFX_EPI_GELU_TANH = 2,     /* y = gelu(v), tanh form       (mlx.nn.gelu_approx) */
   MFX_EPI_GATE_RESIDUAL = 3, /* y = residual + gate[sample] * v */
-  MFX_EPI_SILU = 4           /* y = v * sigmoid(v) */
+  MFX_EPI_SILU = 4,          /* y = v * sigmoid(v) */
+  MFX_EPI_SWIGLU = 5         /* y[:, j] = silu(v[:, 2j]) * v[:, 2j+1]; y is N/2 wide, N % 16 == 0. The caller
+                                interleaves the rows of the gate and up projections (w1 row j -> row 2j, w3 row j
+                                -> row 2j+1), which turns silu(w1 x) * (w3 x) of the reference's FeedForward
+                                (src/mflux/models/z_image/model/z_image_transformer/feed_forward.py:13-14) into
+                                one matmul */
 } mfx_epilogue;
 
 int mfx_version(void);
@@ -191,8 +196,9 @@ int mfx_fmha(const void* q, const void* k, const void* v, int64_t qkv_row_stride
              int64_t seq, int64_t batch, int heads, float scale, void* out, int64_t out_row_stride,
              int64_t out_batch_stride, void* stream);
 
-/* out = act(a + b + c) elementwise (b, c nullable; act 0 = identity, 1 = SiLU): the conditioning-vector
- * arithmetic of time_text_embed.py:25-31 and the nn.silu in front of every AdaLN linear. */
+/* out = act(a + b + c) elementwise (b, c nullable; act 0 = identity, 1 = SiLU, 2 = tanh): the conditioning-vector
+ * arithmetic of time_text_embed.py:25-31, the nn.silu in front of every AdaLN linear and the mx.tanh on the
+ * Z-Image gates (z_image_transformer/transformer_block.py:26-27). */
 int mfx_vec_sum_act(const void* a, const void* b, const void* c, int in_dtype, int act, void* out, int out_dtype,
                     int64_t n, void* stream);
 
@@ -203,6 +209,16 @@ int mfx_vec_sum_act(const void* a, const void* b, const void* c, int in_dtype, i
 int mfx_gate_residual(const void* y, int y_dtype, const void* bias, int bias_dtype, const void* gate, int gate_dtype,
                       int64_t gate_batch_stride, const float* residual, float* out, int64_t batch, int64_t rows,
                       int64_t D, void* stream);
+
+/* residual += gate[sample] * RMSNorm(y) * weight, in place on the float32 residual stream: the post-norms
+ * attention_norm2 / ffn_norm2 of src/mflux/models/z_image/model/z_image_transformer/transformer_block.py:31,35
+ * (gate = tanh of the modulation, applied by the caller) and context_block.py:18,21 (gate == NULL).
+ * y is [batch, rows, D] bf16 or f32 given by its strides (elements), gate [batch, D], weight [D], D % 8 == 0,
+ * D <= 4096. */
+int mfx_norm_gate_residual(const void* y, int y_dtype, int64_t y_row_stride, int64_t y_batch_stride, int64_t rows,
+                           int64_t batch, int64_t D, const void* weight, int weight_dtype, float eps,
+                           const void* gate, int gate_dtype, int64_t gate_batch_stride, float* residual,
+                           int64_t res_row_stride, int64_t res_batch_stride, void* stream);
 
 /* Classifier-free-guidance combine of two noise predictions [rows, channels] into f32 `out`.
  * mode 0: noise + g*(noise - negative)  (src/mflux/models/z_image/variants/z_image.py:209);

@@ -18,7 +18,7 @@ F32, BF16, F16 = 0, 1, 2
 # mfx_qmode
 QMODE_MLX, QMODE_DOC = 0, 1
 # mfx_epilogue
-EPI_NONE, EPI_GELU_ERF, EPI_GELU_TANH, EPI_GATE_RESIDUAL, EPI_SILU = 0, 1, 2, 3, 4
+EPI_NONE, EPI_GELU_ERF, EPI_GELU_TANH, EPI_GATE_RESIDUAL, EPI_SILU, EPI_SWIGLU = 0, 1, 2, 3, 4, 5
 
 _VALUE_ERRORS = {-1, -2, -3, -4, -7, -9}
 STATIC_SCRATCH_BYTES = 32 * 1024 * 1024
@@ -132,6 +132,9 @@ SIGNATURES = {
         [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int64,
          c_void_p],
     ),
+    "mfx_norm_gate_residual": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_int,
+                                       ctypes.c_float, c_void_p, c_int, c_int64, c_void_p, c_int64, c_int64,
+                                       c_void_p]),
     "mfx_cfg_combine": (c_int, [c_void_p, c_void_p, c_int, ctypes.c_float, c_int, c_void_p, c_int64, c_int64, c_void_p]),
     "mfx_euler_step": (c_int, [c_void_p, c_int, c_void_p, c_int, ctypes.c_float, c_void_p, c_int64, c_void_p]),
 }

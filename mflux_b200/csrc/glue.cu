@@ -141,6 +141,76 @@ __global__ void __launch_bounds__(128) norm_modulate_kernel(const NormParams p) 
   }
 }
 
+struct PostNormParams {
+  const void* y;  // [batch, rows, D] bf16 or f32
+  int64_t y_row_stride, y_batch_stride;
+  int rows, batch, D;
+  const void* weight;  // RMSNorm weight [D]
+  int weight_dtype;
+  float eps;
+  const void* gate;  // [batch, D] or null (null = gate of one)
+  int gate_dtype;
+  int64_t gate_batch_stride;
+  float* residual;  // [batch, rows, D] f32, updated in place
+  int64_t res_row_stride, res_batch_stride;
+};
+
+// residual[b, r, :] += gate[b, :] * RMSNorm(y[b, r, :]) * weight: the "sandwich" post-norm of the Z-Image block
+// (z_image_transformer/transformer_block.py:31,35; context_block.py:18,21). The norm needs the whole output row
+// of the projection, so it cannot be an epilogue of a matmul tiled along N; this pass reads y once.
+template <typename YT, int MAXV>
+__global__ void __launch_bounds__(128) norm_gate_residual_kernel(const PostNormParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row_id = static_cast<int64_t>(blockIdx.x) * 4 + warp;
+  if (row_id >= static_cast<int64_t>(p.rows) * p.batch) return;
+  const int b = static_cast<int>(row_id / p.rows);
+  const int r = static_cast<int>(row_id % p.rows);
+  const YT* y = static_cast<const YT*>(p.y) + b * p.y_batch_stride + static_cast<int64_t>(r) * p.y_row_stride;
+  float* res = p.residual + b * p.res_batch_stride + static_cast<int64_t>(r) * p.res_row_stride;
+  const int nvec = p.D >> 3;
+  float v[MAXV][8];
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int c = lane + 32 * i;
+    if (c < nvec) {
+      load8<YT>(y + c * 8, v[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sq += v[i][j] * v[i][j];
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(sq) / static_cast<float>(p.D) + p.eps);
+  const bool vec_w = p.weight_dtype == MFX_BF16;
+  const bool vec_g = p.gate_dtype == MFX_BF16;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int c = lane + 32 * i;
+    if (c < nvec) {
+      float wt[8], gt[8], rs[8];
+      if (vec_w) load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(p.weight) + c * 8, wt);
+      else
+#pragma unroll
+        for (int j = 0; j < 8; ++j) wt[j] = ld_scalar(p.weight, p.weight_dtype, c * 8 + j);
+      if (p.gate) {
+        const int64_t goff = b * p.gate_batch_stride + c * 8;
+        if (vec_g) load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(p.gate) + goff, gt);
+        else
+#pragma unroll
+          for (int j = 0; j < 8; ++j) gt[j] = ld_scalar(p.gate, p.gate_dtype, goff + j);
+      }
+      load8<float>(res + c * 8, rs);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float t = v[i][j] * rstd * wt[j];
+        if (p.gate) t *= gt[j];
+        rs[j] += t;
+      }
+      *reinterpret_cast<float4*>(res + c * 8) = make_float4(rs[0], rs[1], rs[2], rs[3]);
+      *reinterpret_cast<float4*>(res + c * 8 + 4) = make_float4(rs[4], rs[5], rs[6], rs[7]);
+    }
+  }
+}
+
 struct RopeParams {
   __nv_bfloat16* qkv;  // [batch, seq, 3 * heads * 128]: q | k | v
   int64_t row_stride, batch_stride;
@@ -192,7 +262,7 @@ __global__ void __launch_bounds__(256) qknorm_rope_kernel(const RopeParams p) {
   }
 }
 
-// out[i] = f(a[i] (+ b[i]) (+ c[i])), f = identity or SiLU; out dtype bf16 or f32.
+// out[i] = f(a[i] (+ b[i]) (+ c[i])), f = identity, SiLU or tanh; out dtype bf16 or f32.
 __global__ void __launch_bounds__(256) vec_sum_act_kernel(const void* a, const void* b, const void* c, int in_dtype,
                                                           int act, void* out, int out_dtype, int64_t n) {
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -201,6 +271,7 @@ __global__ void __launch_bounds__(256) vec_sum_act_kernel(const void* a, const v
   if (b) v += ld_scalar(b, in_dtype, i);
   if (c) v += ld_scalar(c, in_dtype, i);
   if (act == 1) v = v / (1.0f + __expf(-v));
+  else if (act == 2) v = tanhf(v);
   if (out_dtype == MFX_F32) static_cast<float*>(out)[i] = v;
   else static_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(v);
 }
@@ -367,7 +438,7 @@ int mfx_vec_sum_act(const void* a, const void* b, const void* c, int in_dtype, i
                     int64_t n, void* stream) {
   using namespace mfx;
   if (!a || !out) return MFX_ERR_NULL;
-  if (n <= 0 || (act != 0 && act != 1)) return MFX_ERR_SHAPE;
+  if (n <= 0 || act < 0 || act > 2) return MFX_ERR_SHAPE;
   if (!valid_dtype(in_dtype) || (out_dtype != MFX_F32 && out_dtype != MFX_BF16)) return MFX_ERR_DTYPE;
   if (int rc = check_arch()) return rc;
   glue::vec_sum_act_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
@@ -402,6 +473,54 @@ int mfx_gate_residual(const void* y, int y_dtype, const void* bias, int bias_dty
   const int64_t n_vec = batch * rows * D / 8;
   glue::gate_residual_kernel<<<static_cast<unsigned>((n_vec + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       y, y_dtype, bias, bias_dtype, gate, gate_dtype, gate_batch_stride, residual, out, rows, D, n_vec);
+  MFX_CUDA_TRY(cudaGetLastError());
+  return MFX_OK;
+}
+
+int mfx_norm_gate_residual(const void* y, int y_dtype, int64_t y_row_stride, int64_t y_batch_stride, int64_t rows,
+                           int64_t batch, int64_t D, const void* weight, int weight_dtype, float eps,
+                           const void* gate, int gate_dtype, int64_t gate_batch_stride, float* residual,
+                           int64_t res_row_stride, int64_t res_batch_stride, void* stream) {
+  using namespace mfx;
+  using namespace mfx::glue;
+  if (!y || !weight || !residual) return MFX_ERR_NULL;
+  if (rows <= 0 || batch <= 0 || D <= 0 || D % 8 != 0) return MFX_ERR_SHAPE;
+  if (D > 32 * 8 * 16) return MFX_ERR_TOO_LARGE;
+  if ((y_dtype != MFX_F32 && y_dtype != MFX_BF16) || !valid_dtype(weight_dtype) || (gate && !valid_dtype(gate_dtype)))
+    return MFX_ERR_DTYPE;
+  const size_t ys = dtype_size(y_dtype);
+  if (!aligned16(y) || (y_row_stride * ys) % 16 != 0 || (y_batch_stride * ys) % 16 != 0 || !aligned16(residual) ||
+      (res_row_stride * 4) % 16 != 0 || (res_batch_stride * 4) % 16 != 0)
+    return MFX_ERR_ALIGN;
+  if (weight_dtype == MFX_BF16 && !aligned16(weight)) return MFX_ERR_ALIGN;
+  if (gate && gate_dtype == MFX_BF16 && (!aligned16(gate) || (gate_batch_stride * 2) % 16 != 0)) return MFX_ERR_ALIGN;
+  if (int rc = check_arch()) return rc;
+  PostNormParams p;
+  p.y = y;
+  p.y_row_stride = y_row_stride;
+  p.y_batch_stride = y_batch_stride;
+  p.rows = static_cast<int>(rows);
+  p.batch = static_cast<int>(batch);
+  p.D = static_cast<int>(D);
+  p.weight = weight;
+  p.weight_dtype = weight_dtype;
+  p.eps = eps;
+  p.gate = gate;
+  p.gate_dtype = gate_dtype;
+  p.gate_batch_stride = gate_batch_stride;
+  p.residual = residual;
+  p.res_row_stride = res_row_stride;
+  p.res_batch_stride = res_batch_stride;
+  const unsigned blocks = static_cast<unsigned>((rows * batch + 3) / 4);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int nvec_lane = static_cast<int>((D / 8 + 31) / 32);
+  if (y_dtype == MFX_F32) {
+    if (nvec_lane <= 12) norm_gate_residual_kernel<float, 12><<<blocks, 128, 0, st>>>(p);
+    else norm_gate_residual_kernel<float, 16><<<blocks, 128, 0, st>>>(p);
+  } else {
+    if (nvec_lane <= 12) norm_gate_residual_kernel<__nv_bfloat16, 12><<<blocks, 128, 0, st>>>(p);
+    else norm_gate_residual_kernel<__nv_bfloat16, 16><<<blocks, 128, 0, st>>>(p);
+  }
   MFX_CUDA_TRY(cudaGetLastError());
   return MFX_OK;
 }

@@ -408,7 +408,9 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
       }
       tc_fence_after();
       const bool row_ok = r < p.rows;
-      OUT* yrow = static_cast<OUT*>(p.y) + b * p.y_batch_stride + static_cast<int64_t>(r) * p.y_row_stride + n0;
+      // SwiGLU writes one value per (gate, up) column pair: output column n/2
+      OUT* yrow = static_cast<OUT*>(p.y) + b * p.y_batch_stride + static_cast<int64_t>(r) * p.y_row_stride +
+                  (EPI == MFX_EPI_SWIGLU ? n0 / 2 : n0);
       const OUT* rrow = nullptr;
       if (EPI == MFX_EPI_GATE_RESIDUAL)
         rrow = static_cast<const OUT*>(p.residual) + b * p.res_batch_stride +
@@ -452,7 +454,19 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
 #pragma unroll
               for (int j = 0; j < 8; ++j) v[j] = rs[j] + gate_s[col + j] * v[j];
             }
-            if constexpr (sizeof(OUT) == 4) {
+            if constexpr (EPI == MFX_EPI_SWIGLU) {
+              float o[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) o[j] = silu(v[2 * j]) * v[2 * j + 1];
+              if constexpr (sizeof(OUT) == 4) {
+                *reinterpret_cast<float4*>(yrow + col / 2) = make_float4(o[0], o[1], o[2], o[3]);
+              } else {
+                __nv_bfloat162 h[2];
+                h[0] = __floats2bfloat162_rn(o[0], o[1]);
+                h[1] = __floats2bfloat162_rn(o[2], o[3]);
+                *reinterpret_cast<uint2*>(yrow + col / 2) = *reinterpret_cast<uint2*>(h);
+              }
+            } else if constexpr (sizeof(OUT) == 4) {
               *reinterpret_cast<float4*>(yrow + col) = make_float4(v[0], v[1], v[2], v[3]);
               *reinterpret_cast<float4*>(yrow + col + 4) = make_float4(v[4], v[5], v[6], v[7]);
             } else {
@@ -512,6 +526,7 @@ int launch(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tsb,
     case MFX_EPI_GELU_TANH: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_GELU_TANH>(tx, tw, tsb, p, grid, st);
     case MFX_EPI_GATE_RESIDUAL: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_GATE_RESIDUAL>(tx, tw, tsb, p, grid, st);
     case MFX_EPI_SILU: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_SILU>(tx, tw, tsb, p, grid, st);
+    case MFX_EPI_SWIGLU: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_SWIGLU>(tx, tw, tsb, p, grid, st);
     default: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_NONE>(tx, tw, tsb, p, grid, st);
   }
 }
@@ -626,7 +641,8 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
   if (a.rows > (1 << 30) || a.N > (1 << 30) || a.K > (1 << 30) || a.batch > (1 << 20)) return MFX_ERR_TOO_LARGE;
   if (a.bias && !valid_dtype(a.bias_dtype)) return MFX_ERR_DTYPE;
   if (a.y_dtype != MFX_BF16 && a.y_dtype != MFX_F32) return MFX_ERR_DTYPE;
-  if (a.epilogue < MFX_EPI_NONE || a.epilogue > MFX_EPI_SILU) return MFX_ERR_SHAPE;
+  if (a.epilogue < MFX_EPI_NONE || a.epilogue > MFX_EPI_SWIGLU) return MFX_ERR_SHAPE;
+  if (a.epilogue == MFX_EPI_SWIGLU && a.N % 16 != 0) return MFX_ERR_SHAPE;
   const void* prepared = a.prepared;
   if (!prepared) {
     if (!a.wq || !a.scales || !a.biases || !a.workspace) return MFX_ERR_NULL;

@@ -11,13 +11,13 @@ from ctypes import byref, c_int, c_void_p
 import torch
 
 from . import _lib
-from ._lib import (BF16, EPI_GATE_RESIDUAL, EPI_GELU_ERF, EPI_GELU_TANH, EPI_NONE, EPI_SILU, F16, F32, QMODE_DOC,
+from ._lib import (BF16, EPI_GATE_RESIDUAL, EPI_GELU_ERF, EPI_GELU_TANH, EPI_NONE, EPI_SILU, EPI_SWIGLU, F16, F32, QMODE_DOC,
                    QMODE_MLX, QLinearArgs)
 
 _DT = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
 _EPI = {None: EPI_NONE, "none": EPI_NONE, "gelu": EPI_GELU_ERF, "gelu_erf": EPI_GELU_ERF,
         "gelu_approx": EPI_GELU_TANH, "gelu_tanh": EPI_GELU_TANH, "gate_residual": EPI_GATE_RESIDUAL,
-        "silu": EPI_SILU}
+        "silu": EPI_SILU, "swiglu": EPI_SWIGLU}
 
 
 # Kernel launches issued through this module since import (bench.py reports the count of a timed region).
@@ -140,8 +140,9 @@ def qlinear(x: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, biases: tor
     x is [rows, K] or [batch, rows, K] (bf16; row/batch strides may be arbitrary multiples of 8
     elements, the last dim must be dense). `out`, when given, may be a strided view of the same
     leading shape. epilogue "gate_residual" computes residual + gate[batch] * y with gate [batch, N].
-    `prepared` is the cached result of prepare_qlinear(wq, scales, biases); without it the weight is
-    prepared into a scratch tensor on every call.
+    epilogue "swiglu" returns silu(y[..., 0::2]) * y[..., 1::2], N/2 wide (rows of the gate and up
+    projections interleaved by the caller). `prepared` is the cached result of
+    prepare_qlinear(wq, scales, biases); without it the weight is prepared into a scratch tensor on every call.
     """
     lib = _lib.load()
     _cuda(x, "x")
@@ -159,14 +160,15 @@ def qlinear(x: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, biases: tor
         wq, scales, biases = wq.contiguous(), scales.contiguous(), biases.contiguous()
         workspace = torch.empty(lib.mfx_qlinear_prepared_bytes(n, k, bits, group_size), dtype=torch.uint8,
                                 device=x.device)
+    n_out = n // 2 if _EPI[epilogue] == EPI_SWIGLU else n
     if out is None:
         od = out_dtype or (residual.dtype if residual is not None else torch.bfloat16)
-        out = torch.empty((*xv.shape[:-1], n), dtype=od, device=x.device)
-        ret = out.reshape(*lead, n)
+        out = torch.empty((*xv.shape[:-1], n_out), dtype=od, device=x.device)
+        ret = out.reshape(*lead, n_out)
     else:
         ret = out
     ov, o_rows, o_batch, o_rs, o_bs = _rows_view(out, "out")
-    if ov.data_ptr() != out.data_ptr() or (o_rows, o_batch) != (rows, batch) or ov.shape[-1] != n:
+    if ov.data_ptr() != out.data_ptr() or (o_rows, o_batch) != (rows, batch) or ov.shape[-1] != n_out:
         raise ValueError("out must be a [.., rows, N] view with a dense last dim matching x")
     a = QLinearArgs()
     a.x, a.x_row_stride, a.x_batch_stride = xv.data_ptr(), x_rs, x_bs
@@ -311,7 +313,7 @@ def fmha(qkv: torch.Tensor, heads: int, scale: float | None = None, out: torch.T
 
 def vec_sum_act(a: torch.Tensor, b: torch.Tensor | None = None, c: torch.Tensor | None = None, act: str | None = None,
                 out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
-    """act(a + b + c) elementwise; act is None or "silu"."""
+    """act(a + b + c) elementwise; act is None, "silu" or "tanh"."""
     lib = _lib.load()
     _cuda(a, "a")
     ts = [t.contiguous() if t is not None else None for t in (a, b, c)]
@@ -319,7 +321,7 @@ def vec_sum_act(a: torch.Tensor, b: torch.Tensor | None = None, c: torch.Tensor 
         if t is not None and (t.shape != ts[0].shape or t.dtype != ts[0].dtype):
             raise ValueError("operands must share shape and dtype")
     out = torch.empty(ts[0].shape, dtype=out_dtype, device=a.device)
-    rc = lib.mfx_vec_sum_act(_ptr(ts[0]), _ptr(ts[1]), _ptr(ts[2]), _dt(ts[0]), 1 if act == "silu" else 0, _ptr(out),
+    rc = lib.mfx_vec_sum_act(_ptr(ts[0]), _ptr(ts[1]), _ptr(ts[2]), _dt(ts[0]), {None: 0, "silu": 1, "tanh": 2}[act], _ptr(out),
                              _dt(out), out.numel(), _stream())
     _lib.check(rc, "mfx_vec_sum_act")
     LAUNCHES[0] += 1
@@ -413,3 +415,31 @@ def cfg_combine(noise: torch.Tensor, noise_negative: torch.Tensor, guidance: flo
     _lib.check(rc, "mfx_cfg_combine")
     LAUNCHES[0] += 1
     return out
+
+
+def norm_gate_residual(y: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, gate: torch.Tensor | None = None,
+                       eps: float = 1e-5) -> torch.Tensor:
+    """residual += gate[sample] * RMSNorm(y) * weight, in place on the float32 view `residual`.
+
+    y is [rows, D] or [batch, rows, D] (bf16 or f32, strided views allowed), gate [batch, D] or None.
+    """
+    lib = _lib.load()
+    _cuda(y, "y")
+    yv, rows, batch, y_rs, y_bs = _rows_view(y, "y")
+    rv, r_rows, r_batch, r_rs, r_bs = _rows_view(residual, "residual")
+    d = yv.shape[-1]
+    if rv.data_ptr() != residual.data_ptr() or rv.dtype != torch.float32 or (r_rows, r_batch) != (rows, batch) \
+            or rv.shape[-1] != d:
+        raise ValueError("residual must be a float32 view shaped like y with a dense last dim")
+    weight = weight.contiguous()
+    g_ptr, g_dt, g_bs = c_void_p(None), 0, 0
+    if gate is not None:
+        gate = gate.reshape(-1, d) if gate.stride(-1) == 1 else gate.reshape(-1, d).contiguous()
+        if gate.shape[0] != batch:
+            raise ValueError("gate must be [batch, D]")
+        g_ptr, g_dt, g_bs = _ptr(gate), _dt(gate), gate.stride(0)
+    rc = lib.mfx_norm_gate_residual(_ptr(yv), _dt(yv), y_rs, y_bs, rows, batch, d, _ptr(weight), _dt(weight),
+                                    float(eps), g_ptr, g_dt, g_bs, _ptr(rv), r_rs, r_bs, _stream())
+    _lib.check(rc, "mfx_norm_gate_residual")
+    LAUNCHES[0] += 1
+    return residual

@@ -65,3 +65,30 @@ def test_unsupported_bits_rejected():
     resolution.check_supported(None)
     resolution.check_supported(4)
     resolution.check_supported(8)
+
+
+def test_zimage_token_layout_matches_oracle():
+    """Patch order, padding to multiples of 32 and position ids of the Z-Image path (host logic, no GPU)."""
+    import numpy as np
+    import torch
+
+    from mflux_b200.zimage import ZImageConfig, ZImageTransformer
+    from oracle import zimage as oz
+
+    cfg = ZImageConfig(dim=256, n_layers=0, n_refiner_layers=0, n_heads=2, cap_feat_dim=64, ffn_hidden=704)
+    model = ZImageTransformer(cfg, bits=None, device="cpu")
+    g = torch.Generator().manual_seed(0)
+    lat = torch.randn(2, 16, 1, 18, 14, generator=g)
+    cap = torch.randn(20, 64, generator=g)
+    tokens = model.patchify(lat)
+    img, cap_p, size, x_ids, cap_ids, x_mask, cap_mask = oz.patchify(lat[1], cap)
+    assert torch.equal(tokens[1], img[:63]) and img.shape[0] == 64 and torch.equal(img[63], img[62])
+    assert cap_p.shape[0] == 32 and int(cap_mask.sum()) == 12 and int(x_mask.sum()) == 1
+    # caption ids count from 1 on axis 0; image ids start one past the padded caption, pad tokens sit at 0
+    assert cap_ids[0].tolist() == [1, 0, 0] and cap_ids[-1].tolist() == [32, 0, 0]
+    assert x_ids[0].tolist() == [33, 0, 0] and x_ids[8].tolist() == [33, 1, 1] and x_ids[63].tolist() == [0, 0, 0]
+    mine_img, mine_cap = model.position_ids((1, 9, 7), 20)
+    assert np.array_equal(mine_img, x_ids) and np.array_equal(mine_cap, cap_ids)
+    out = model.unpatchify(torch.cat([tokens, tokens[:, -1:]], dim=1), (1, 18, 14))
+    assert torch.equal(out, lat)
+    assert torch.equal(oz.unpatchify(img, size, 16), lat[1])
