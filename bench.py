@@ -1,12 +1,18 @@
 """Benchmark of the quantized DiT denoising step: FLUX.1-shaped 12B MMDiT, W4 group 64, 1024x1024.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--small]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--small] [--workload NAME]
 
 One process per GPU (torchrun for N > 1). A step is one denoiser evaluation plus the Euler update for a
 batch of 16 images (4096 image + 512 text tokens each) on synthetic inputs with random-init weights.
 The batch is the unit that shards: every rank runs its own 16-image batch with replicated weights and no
 collective on the data path (weak scaling); `value` = steps all ranks completed / max-over-ranks device
 time. Rank 0 prints one JSON line.
+
+`--workload` selects another configuration of the same path (the default, `flux`, is the headline):
+`zimage` (Z-Image-shaped 6B single-stream DiT, W8, 8 images, batch-sharded like flux), `qwen` (Qwen-Image-shaped
+20B dual-stream DiT, W4, prompt/negative-prompt pair at 1328x1328; with N > 1 the weights are tensor-parallel
+over the N ranks with an NCCL all-reduce per row-split linear, strong scaling) and `sweep` (single quantized
+linears over bits x (N, K) x M, reporting TFLOP/s per shape).
 
 `--impl reference` times the CPU oracle (the restatement of the reference's MLX arithmetic; MLX itself is
 not installable offline) on the host cores on a bounded sample of the same workload and prints the same
@@ -26,8 +32,10 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-METRIC = "flux1_w4_dit_steps_per_sec_1024px_batch16"
-UNIT = "steps/s (one step = 16 images x 4608 tokens through 19+38 blocks)"
+# Mean DRAM bytes (read + write) per quantized-matmul launch of the full flux step, from an ncu capture of
+# dram__bytes_read.sum + dram__bytes_write.sum on the reduced-depth model at the same per-GPU batch, weighted by
+# the block counts of the full model (every block of one kind launches the same shapes). None until captured.
+QMM_TRAFFIC_PER_LAUNCH = None
 
 
 def step_flops(cfg, batch, si, st):
@@ -113,11 +121,11 @@ def cpu_sample(seconds_target: float = 12.0):
     return 2.0 * m * n * k / dt / 1e12, desc, cores
 
 
-def run_reference(args, cfg, batch, si, st):
+def run_reference(args, spec):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    lin, attn = step_flops(cfg, batch, si, st)
+    flops = spec["lin"] + spec["attn"]
     vals = []
     desc, cores = "", 1
     for i in range(args.warmup + args.steps):
@@ -125,22 +133,197 @@ def run_reference(args, cfg, batch, si, st):
         if i >= args.warmup:
             vals.append(tf)
     tflops = sum(vals) / len(vals)
-    value = tflops * 1e12 / (lin + attn)
+    value = tflops * 1e12 / flops
     line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "impl": "reference", "metric": spec["metric"], "value": value, "unit": spec["unit"], "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / value, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(cfg, batch, si, st), "note": "CPU oracle port of the MLX arithmetic; "
+        "scaling": spec["scaling"], "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": spec["workload"], "note": "CPU oracle port of the MLX arithmetic; "
                    "MLX itself is not installable offline"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
-        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "cpu_baseline": {"value": value, "unit": spec["unit"], "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": spec["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
-def workload_name(cfg, batch, si, st):
-    return (f"FLUX.1-shaped MMDiT {cfg.num_joint}+{cfg.num_single} blocks, hidden {cfg.hidden}, {cfg.heads}x128 heads, "
-            f"W4 g64, batch {batch}, {si} image + {st} text tokens, guidance-embedded, CFG-free")
+# --------------------------------------------------------------------------- workloads
+# A spec is plain data (no GPU needed): names, algorithmic flops of one step, how the step scales over ranks.
+# build(dev, rank, world, steps) returns (pinned host inputs, pinned host output, step(i, *device inputs)).
+
+def flux_spec(args):
+    from mflux_b200.flux import FluxConfig
+
+    cfg = FluxConfig(num_joint=1, num_single=1) if args.small else FluxConfig()
+    batch = args.batch or (2 if args.small else 16)
+    height = width = 1024
+    si, st = (height // 16) * (width // 16), 512
+    lin, attn = step_flops(cfg, batch, si, st)
+
+    def build(dev, rank, world, steps):
+        import torch
+
+        from mflux_b200 import ops
+        from mflux_b200.flux import Transformer
+        from mflux_b200.schedulers import LinearScheduler
+
+        model = Transformer(cfg, bits=4, device=dev, seed=1234)  # same weights on every rank (replicated)
+        g = torch.Generator(device="cpu").manual_seed(100 + rank)  # every rank has its own batch of images
+        lat_h = torch.randn(batch, si, cfg.in_channels, generator=g).pin_memory()
+        ctx_h = torch.randn(batch, st, cfg.context_dim, generator=g).to(torch.bfloat16).pin_memory()
+        pool_h = torch.randn(batch, cfg.pooled_dim, generator=g).to(torch.bfloat16).pin_memory()
+        out_h = torch.empty(batch, si, cfg.in_channels).pin_memory()
+        sched = LinearScheduler(max(steps, 2), width, height, True)
+        gvec = torch.full((batch,), 3.5 * cfg.num_train_steps, device=dev)
+
+        def step(i, lat_d, ctx_d, pool_d):
+            j = i % len(sched.timesteps)
+            ts = torch.full((batch,), float(sched.sigmas[j]) * cfg.num_train_steps, device=dev)
+            noise = model(lat_d, ctx_d, pool_d, ts, gvec, height, width)
+            return ops.euler_step(lat_d, noise, sched.dt(j))
+
+        return [lat_h, ctx_h, pool_h], out_h, step
+
+    return {
+        "metric": "flux1_w4_dit_steps_per_sec_1024px_batch16",
+        "unit": "steps/s (one step = 16 images x 4608 tokens through 19+38 blocks)",
+        "workload": (f"FLUX.1-shaped MMDiT {cfg.num_joint}+{cfg.num_single} blocks, hidden {cfg.hidden}, "
+                     f"{cfg.heads}x128 heads, W4 g64, batch {batch}, {si} image + {st} text tokens, "
+                     f"guidance-embedded, CFG-free"),
+        "scaling": "weak", "lin": lin, "attn": attn, "per_gpu_batch": batch, "build": build,
+        "l2_policy": "inputs larger than L2 (6.7 GB of packed weights stream every step)",
+    }
+
+
+def zimage_spec(args):
+    from mflux_b200.zimage import ZImageConfig
+
+    cfg = ZImageConfig()
+    batch = args.batch or 8
+    height = width = 1024
+    si, sc = (height // 16) * (width // 16), 512
+    d, h, s = cfg.dim, cfg.ffn_hidden, si + sc
+    per_row = 2 * (4 * d * d + 3 * d * h)
+    rows = cfg.n_layers * s + cfg.n_refiner_layers * (si + sc)
+    lin = batch * rows * per_row + 2 * batch * (si * cfg.embed_dim * d * 2 + sc * cfg.cap_feat_dim * d)
+    lin += 2 * batch * 256 * 4 * d * (cfg.n_layers + cfg.n_refiner_layers)
+    attn = 4 * batch * cfg.n_heads * 128 * (cfg.n_layers * s * s + cfg.n_refiner_layers * (si * si + sc * sc))
+
+    def build(dev, rank, world, steps):
+        import torch
+
+        from mflux_b200 import ops
+        from mflux_b200.schedulers import LinearScheduler
+        from mflux_b200.zimage import ZImageTransformer
+
+        model = ZImageTransformer(cfg, bits=8, device=dev, seed=1234)
+        g = torch.Generator(device="cpu").manual_seed(100 + rank)
+        lat_h = torch.randn(batch, cfg.in_channels, 1, height // 8, width // 8, generator=g).pin_memory()
+        cap_h = torch.randn(batch, sc, cfg.cap_feat_dim, generator=g).to(torch.bfloat16).pin_memory()
+        out_h = torch.empty_like(lat_h).pin_memory()
+        sched = LinearScheduler(max(steps, 2), width, height, True)
+
+        def step(i, lat_d, cap_d):
+            j = i % len(sched.timesteps)
+            t = torch.full((batch,), 1.0 - float(sched.sigmas[j]), device=dev)
+            return ops.euler_step(lat_d, model(lat_d, t, cap_d), sched.dt(j))
+
+        return [lat_h, cap_h], out_h, step
+
+    return {
+        "metric": "zimage_w8_dit_steps_per_sec_1024px_batch8",
+        "unit": "steps/s (one step = 8 images x 4608 tokens through 2+2 refiner and 30 main blocks)",
+        "workload": (f"Z-Image-shaped single-stream DiT {cfg.n_layers} blocks + 2x{cfg.n_refiner_layers} refiners, hidden "
+                     f"{d}, {cfg.n_heads}x128 heads, SwiGLU {h}, W8 g64, batch {batch}, {si} image + {sc} caption tokens"),
+        "scaling": "weak", "lin": lin, "attn": attn, "per_gpu_batch": batch, "build": build,
+        "l2_policy": "inputs larger than L2 (6.2 GB of packed weights stream every step)",
+    }
+
+
+def qwen_spec(args):
+    from mflux_b200.qwen import QwenConfig
+
+    cfg = QwenConfig()
+    height = width = 1328
+    si, st = (height // 16) * (width // 16), 256
+    b, d = 2, cfg.hidden   # the prompt / negative-prompt pair of one image
+    s = si + st
+    lin = cfg.num_layers * (2 * b * s * 12 * d * d + 2 * 2 * b * d * 6 * d)
+    lin += 2 * b * (si * cfg.in_channels * d * 2 + st * cfg.joint_attention_dim * d)
+    attn = cfg.num_layers * 4 * b * cfg.heads * s * s * 128
+
+    def build(dev, rank, world, steps):
+        import torch
+
+        from mflux_b200 import ops
+        from mflux_b200.qwen import QwenTransformer
+        from mflux_b200.schedulers import LinearScheduler
+
+        model = QwenTransformer(cfg, bits=4, device=dev, seed=1234, tp_rank=rank, tp_world=world)
+        g = torch.Generator(device="cpu").manual_seed(100)   # tensor parallel: every rank sees the same image
+        lat_h = torch.randn(1, si, cfg.in_channels, generator=g).pin_memory()
+        emb_h = torch.randn(b, st, cfg.joint_attention_dim, generator=g).to(torch.bfloat16).pin_memory()
+        out_h = torch.empty_like(lat_h).pin_memory()
+        sched = LinearScheduler(max(steps, 2), width, height, True)
+
+        def step(i, lat_d, emb_d):
+            j = i % len(sched.timesteps)
+            sig = torch.full((b,), float(sched.sigmas[j]), device=dev)
+            both = model(torch.cat([lat_d, lat_d]), emb_d, sig, height, width)
+            return ops.euler_step(lat_d, ops.cfg_combine(both[:1], both[1:], 4.0, mode="qwen"), sched.dt(j))
+
+        return [lat_h, emb_h], out_h, step
+
+    return {
+        "metric": "qwen_image_w4_dit_steps_per_sec_1328px_cfg2",
+        "unit": "steps/s (one step = prompt + negative prompt of one image, 2 x 7145 tokens through 60 blocks)",
+        "workload": (f"Qwen-Image-shaped dual-stream MMDiT {cfg.num_layers} blocks, hidden {d}, {cfg.heads}x128 heads, "
+                     f"W4 g64, CFG batch 2, {si} image + {st} text tokens, tensor-parallel over all ranks"),
+        "scaling": "strong", "lin": lin, "attn": attn, "per_gpu_batch": b, "build": build,
+        "l2_policy": "inputs larger than L2 (10 GB of packed weights, split over the ranks, stream every step)",
+    }
+
+
+SPECS = {"flux": flux_spec, "zimage": zimage_spec, "qwen": qwen_spec}
+
+
+def run_sweep(args, dev):
+    """Single quantized linears: bits x (N, K) x M. Every shape cycles through enough weight/activation copies
+    that consecutive launches never find their operands in L2."""
+    import torch
+
+    from mflux_b200 import ops
+
+    peak, _, burst = measured_peaks()
+    rows = []
+    g = torch.Generator(device=dev).manual_seed(0)
+    for bits in (4, 8):
+        for n, k in ((3072, 3072), (9216, 3072), (12288, 3072), (3072, 12288)):
+            w = torch.randn(n, k, device=dev, generator=g) * 0.02
+            wq, sc, bi = ops.quantize_affine(w, 64, bits)
+            bias = (torch.randn(n, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+            del w
+            for m in (256, 1024, 4096, 4608, 16384):
+                per = n * k * bits // 8 + 2 * m * k + 2 * m * n
+                copies = max(2, min(64, -(-400_000_000 // per)))
+                preps = [ops.prepare_qlinear(wq, sc, bi, bits, 64) for _ in range(copies)]
+                xs = [torch.randn(m, k, device=dev, generator=g).to(torch.bfloat16) for _ in range(copies)]
+                ys = [torch.empty(m, n, device=dev, dtype=torch.bfloat16) for _ in range(copies)]
+                reps = max(copies, 20)
+                for i in range(max(3, args.warmup)):
+                    ops.qlinear(xs[i % copies], wq, None, None, bias, bits=bits, out=ys[i % copies], prepared=preps[i % copies])
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                e0.record()
+                for i in range(reps):
+                    ops.qlinear(xs[i % copies], wq, None, None, bias, bits=bits, out=ys[i % copies], prepared=preps[i % copies])
+                e1.record()
+                torch.cuda.synchronize()
+                us = e0.elapsed_time(e1) * 1e3 / reps
+                tf = 2.0 * m * n * k / us / 1e6
+                rows.append({"bits": bits, "N": n, "K": k, "M": m, "us": round(us, 1), "tflops": round(tf, 1),
+                             "frac_burst_peak": round(tf / burst, 3) if burst else None, "copies": copies})
+                del preps, xs, ys
+    return rows
 
 
 def main():
@@ -149,32 +332,26 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--small", action="store_true", help="reduced model for profiler captures (not a bench value)")
-    ap.add_argument("--batch", type=int, default=16)
+    ap.add_argument("--workload", default="flux", choices=["flux", "zimage", "qwen", "sweep"])
+    ap.add_argument("--small", action="store_true", help="flux at reduced depth for profiler captures (not a bench value)")
+    ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (default: the workload's own)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
 
-    from mflux_b200.flux import FluxConfig
-
-    if args.small:
-        cfg = FluxConfig(num_joint=1, num_single=1)
-        batch = min(args.batch, 2)
+    if args.workload == "sweep":
+        spec = None
     else:
-        cfg = FluxConfig()
-        batch = args.batch
-    height = width = 1024
-    si, st = (height // 16) * (width // 16), 512
+        spec = SPECS[args.workload](args)
+        if args.impl == "reference":
+            run_reference(args, spec)
+            return
 
-    if args.impl == "reference":
-        run_reference(args, cfg, batch, si, st)
-        return
+    import math
 
     import torch
     import torch.distributed as dist
 
     from mflux_b200 import ops
-    from mflux_b200.flux import Transformer
-    from mflux_b200.schedulers import LinearScheduler
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -183,23 +360,29 @@ def main():
         raise RuntimeError("bench.py needs a CUDA device: there is no CPU path")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+
+    if spec is None:   # single-GPU table of quantized linears
+        if rank == 0:
+            sampler = ClockSampler(local)
+            sampler.start()
+            rows = run_sweep(args, dev)
+            clocks = sampler.stop()
+            peak, _, burst = measured_peaks()
+            geo = math.exp(sum(math.log(r["tflops"]) for r in rows) / len(rows))
+            print(json.dumps({
+                "metric": "qlinear_sweep_geomean_tflops", "value": geo, "unit": "TFLOP/s", "n_gpus": 1, "steps": 1,
+                "warmup": max(3, args.warmup), "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": "quantized-linear sweep, bits {4,8} x (N,K) x M, group 64, bias, bf16 out",
+                           "l2_policy": "operand copies rotated so that more than 400 MB pass between reuses",
+                           "burst_peak_tflops": burst, "device_status": ops.poll_device_status()},
+                "clocks": clocks, "sweep": rows}), flush=True)
+        return
+
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    model = Transformer(cfg, bits=4, device=dev, seed=1234)  # same weights on every rank (replicated)
-    g = torch.Generator(device="cpu").manual_seed(100 + rank)  # every rank has its own batch of images
-    lat_h = torch.randn(batch, si, cfg.in_channels, generator=g).pin_memory()
-    ctx_h = torch.randn(batch, st, cfg.context_dim, generator=g).to(torch.bfloat16).pin_memory()
-    pool_h = torch.randn(batch, cfg.pooled_dim, generator=g).to(torch.bfloat16).pin_memory()
-    out_h = torch.empty(batch, si, cfg.in_channels).pin_memory()
-    sched = LinearScheduler(max(args.steps + args.warmup, 2), width, height, True)
-    gvec = torch.full((batch,), 3.5 * cfg.num_train_steps, device=dev)
-    lat, ctx, pool = lat_h.to(dev), ctx_h.to(dev), pool_h.to(dev)
-
-    def step(i, lat_d, ctx_d, pool_d):
-        ts = torch.full((batch,), float(sched.sigmas[i % len(sched.timesteps)]) * cfg.num_train_steps, device=dev)
-        noise = model(lat_d, ctx_d, pool_d, ts, gvec, height, width)
-        return ops.euler_step(lat_d, noise, sched.dt(i % len(sched.timesteps)))
+    host_in, out_h, step = spec["build"](dev, rank, world, args.steps + args.warmup)
+    dev_in = [t.to(dev) for t in host_in]
 
     def barrier():
         if world > 1:
@@ -207,7 +390,7 @@ def main():
         torch.cuda.synchronize()
 
     for i in range(args.warmup):
-        step(i, lat, ctx, pool)
+        step(i, *dev_in)
     barrier()
 
     sampler = ClockSampler(local)
@@ -216,9 +399,9 @@ def main():
     launches0 = ops.LAUNCHES[0]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    cur = lat
+    cur = dev_in[0]
     for i in range(args.steps):
-        cur = step(i, cur, ctx, pool)
+        cur = step(i, cur, *dev_in[1:])
     e1.record()
     barrier()
     launches = ops.LAUNCHES[0] - launches0
@@ -230,10 +413,7 @@ def main():
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0.record()
     for i in range(args.steps):
-        lat_d = lat_h.to(dev, non_blocking=True)
-        ctx_d = ctx_h.to(dev, non_blocking=True)
-        pool_d = pool_h.to(dev, non_blocking=True)
-        res = step(i, lat_d, ctx_d, pool_d)
+        res = step(i, *[t.to(dev, non_blocking=True) for t in host_in])
         out_h.copy_(res, non_blocking=True)
     t1.record()
     barrier()
@@ -247,35 +427,37 @@ def main():
     ms, ms_e2e = float(times[0]), float(times[1])
 
     if rank == 0:
-        value = world * args.steps / (ms / 1e3)
-        e2e_value = world * args.steps / (ms_e2e / 1e3)
+        units = world if spec["scaling"] == "weak" else 1   # weak: every rank finishes its own steps
+        value = units * args.steps / (ms / 1e3)
+        e2e_value = units * args.steps / (ms_e2e / 1e3)
         q_flops = sum(t[0] for t in trace)
         q_ms = sum(t[1].elapsed_time(t[2]) for t in trace)
         peak, peak_kind, burst = measured_peaks()
         achieved = q_flops / (q_ms / 1e3) / 1e12 if q_ms > 0 else 0.0
-        lin, attn = step_flops(cfg, batch, si, st)
+        flops = spec["lin"] + spec["attn"]
+        traffic = QMM_TRAFFIC_PER_LAUNCH if (args.workload == "flux" and not args.small and
+                                             spec["per_gpu_batch"] == 16) else None
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": workload_name(cfg, batch, si, st), "per_gpu_batch": batch,
-                       "l2_policy": "inputs larger than L2 (6.7 GB of packed weights stream every step)",
-                       "algorithmic_tflop_per_step": (lin + attn) / 1e12, "device_status": status,
-                       "small": bool(args.small)},
-            "e2e": {"value": e2e_value, "unit": UNIT,
-                    "h2d_bytes_per_step": lat_h.numel() * 4 + ctx_h.numel() * 2 + pool_h.numel() * 2,
-                    "d2h_bytes_per_step": out_h.numel() * 4},
+            "metric": spec["metric"], "value": value, "unit": spec["unit"], "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": spec["scaling"], "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": spec["workload"], "per_gpu_batch": spec["per_gpu_batch"],
+                       "l2_policy": spec["l2_policy"], "algorithmic_tflop_per_step": flops / 1e12,
+                       "device_status": status, "small": bool(args.small)},
+            "e2e": {"value": e2e_value, "unit": spec["unit"],
+                    "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in host_in),
+                    "d2h_bytes_per_step": out_h.numel() * out_h.element_size()},
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": {"bound": "tensor", "kernel": "qmm_kernel (quantized linear)", "achieved": achieved,
                          "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak if peak else None,
                          "peak_kind": peak_kind, "burst_peak": burst, "launches": len(trace),
-                         "share_of_step_time": q_ms / ms if ms > 0 else None, "traffic": None},
-            "step_tflops": (lin + attn) / 1e12 * args.steps / (ms / 1e3),
+                         "share_of_step_time": q_ms / ms if ms > 0 else None, "traffic": traffic},
+            "step_tflops": flops / 1e12 * args.steps / (ms / 1e3) / (world if spec["scaling"] == "strong" else 1),
         }
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and world == 1:
             tf, desc, cores = cpu_sample()
-            line["cpu_baseline"] = {"value": tf * 1e12 / (lin + attn), "unit": UNIT, "cores": cores, "kind": "port",
+            line["cpu_baseline"] = {"value": tf * 1e12 / flops, "unit": spec["unit"], "cores": cores, "kind": "port",
                                     "sample": desc}
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -46,6 +46,7 @@ constexpr uint32_t TMEM_COLS = 512;
 struct Params {
   int rows, batch, N, K;
   int tiles_m_per_sample, tiles_m, tiles_n, total_tiles;
+  int band_n;  // n-tiles per band of the tile order (see tile_coords)
   const void* bias;
   int bias_dtype;
   int epilogue;
@@ -142,6 +143,20 @@ __device__ __forceinline__ uint2 dequant_w8(uint32_t q, uint32_t s2, uint32_t b2
   return r;
 }
 
+// Tile order. The weight rows are cut into bands of band_n n-tiles whose packed codes, scales and biases fit in
+// L2 together; inside a band the tiles run m-tile by m-tile with the n-tile index fastest. The pairs that run at
+// the same time then share one or two activation tiles (read from HBM once per band) and sweep a band of weights
+// that stays in L2, instead of each streaming its own activation tile from HBM once per n-tile.
+__device__ __forceinline__ void tile_coords(const Params& p, int tile, int& tm, int& tn) {
+  const int per_band = p.tiles_m * p.band_n;
+  const int band = tile / per_band;
+  const int r = tile - band * per_band;
+  const int n_first = band * p.band_n;
+  const int width = min(p.band_n, p.tiles_n - n_first);
+  tm = r / width;
+  tn = n_first + r - tm * width;
+}
+
 // Out of line on purpose: the epilogue runs beside the main loop of the next tile; a 32-fold unrolled inline
 // erf/tanh body would crowd the small hot loops of the other warps out of the instruction cache.
 __device__ __noinline__ float gelu_erf(float v) { return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f)); }
@@ -219,8 +234,8 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     uint32_t ph = 0;
     bool ok = true;
     for (int tile = pair; tile < p.total_tiles && ok; tile += num_pairs) {
-      const int tm = tile % p.tiles_m;
-      const int tn = tile / p.tiles_m;
+      int tm, tn;
+      tile_coords(p, tile, tm, tn);
       const int b = tm / p.tiles_m_per_sample;
       const int r0 = (tm % p.tiles_m_per_sample) * (2 * BM) + static_cast<int>(rank) * BM;
       const int n0 = tn * BN + static_cast<int>(rank) * BN_HALF;
@@ -386,8 +401,8 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     for (int tile = pair; tile < p.total_tiles && ok; tile += num_pairs, ++it) {
       const int a = it & 1;
       const uint32_t aph = (it >> 1) & 1;
-      const int tm = tile % p.tiles_m;
-      const int tn = tile / p.tiles_m;
+      int tm, tn;
+      tile_coords(p, tile, tm, tn);
       const int b = tm / p.tiles_m_per_sample;
       const int r = (tm % p.tiles_m_per_sample) * (2 * BM) + static_cast<int>(rank) * BM + row;
       const int n0 = tn * BN;
@@ -714,6 +729,14 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
   const int64_t total = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
   if (total > (1ll << 30)) return MFX_ERR_TOO_LARGE;
   p.total_tiles = static_cast<int>(total);
+  {
+    // bands of weight rows that stay L2-resident while every activation tile passes over them: 32 MB leaves room
+    // for the activation and output tiles in flight even if each die's half of the L2 keeps its own copy
+    const int64_t n_tile_bytes = static_cast<int64_t>(BN) * (a.K * a.bits / 8 + a.K / 64 * 4);
+    const int64_t bands = (n_tile_bytes * p.tiles_n + (32ll << 20) - 1) / (32ll << 20);
+    p.band_n = static_cast<int>((p.tiles_n + bands - 1) / bands);
+    if (p.band_n < 1) p.band_n = 1;
+  }
   p.bias = a.bias;
   p.bias_dtype = a.bias_dtype;
   p.epilogue = a.epilogue;
