@@ -7,7 +7,8 @@
 //                 (reference: flux_transformer/common/attention_utils.py:8-36,75-80)
 //   vec_ops       conditioning-vector helpers (sum of embeddings, SiLU) and the Euler step
 //                 (reference: time_text_embed.py:25-31, linear_scheduler.py:56-58)
-// One warp owns one row; nothing here waits on another thread block.
+// The norms give one 128-thread block to a row, the others one warp to a row or head; nothing here waits on
+// another thread block.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -64,79 +65,110 @@ struct NormParams {
   int64_t y_row_stride, y_batch_stride;
 };
 
-// MAXV = number of 8-element vectors a lane may hold: D <= 32 * 8 * MAXV.
-template <typename XT, int MAXV>
-__global__ void __launch_bounds__(128) norm_modulate_kernel(const NormParams p) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t row_id = static_cast<int64_t>(blockIdx.x) * 4 + warp;
-  if (row_id >= static_cast<int64_t>(p.rows) * p.batch) return;
+// E consecutive elements of a f32 / bf16 / f16 array as floats; E = 4 or 8. bf16 goes as one 8- or 16-byte load.
+template <int E>
+__device__ __forceinline__ void load_vec(const void* p, int dtype, int64_t off, float (&o)[E]) {
+  if (dtype == MFX_BF16) {
+    const __nv_bfloat16* q = static_cast<const __nv_bfloat16*>(p) + off;
+    if constexpr (E == 8) {
+      load8<__nv_bfloat16>(q, o);
+    } else {
+      const uint2 raw = *reinterpret_cast<const uint2*>(q);
+      const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o[i] = __bfloat162float(h[i]);
+    }
+  } else if (dtype == MFX_F32) {
+    const float* q = static_cast<const float*>(p) + off;
+#pragma unroll
+    for (int i = 0; i < E; i += 4) {
+      const float4 a = *reinterpret_cast<const float4*>(q + i);
+      o[i] = a.x; o[i + 1] = a.y; o[i + 2] = a.z; o[i + 3] = a.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < E; ++i) o[i] = ld_scalar(p, dtype, off + i);
+  }
+}
+template <int E>
+__device__ __forceinline__ void store_vec_bf16(__nv_bfloat16* p, const float (&v)[E]) {
+  if constexpr (E == 8) {
+    store8_bf16(p, v);
+  } else {
+    __nv_bfloat162 h[2] = {__floats2bfloat162_rn(v[0], v[1]), __floats2bfloat162_rn(v[2], v[3])};
+    *reinterpret_cast<uint2*>(p) = *reinterpret_cast<uint2*>(h);
+  }
+}
+// Sum over the 128 threads of a block; `red` is a 4-float shared array used by this call only.
+__device__ __forceinline__ float block_sum_128(float v, float* red) {
+  v = warp_sum(v);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  return (red[0] + red[1]) + (red[2] + red[3]);
+}
+
+constexpr int NORM_THREADS = 128;
+constexpr int NORM_MAX_D = 4096;
+
+// One 128-thread block per row. Thread t holds the 16-byte vectors t, t+128, ... of the row in registers (at
+// most 32 floats), so every warp-level load or store covers 512 contiguous bytes and enough blocks are resident
+// per SM to keep HBM busy; mean and variance are two block reductions over the registers (two-pass variance).
+template <typename XT>
+__global__ void __launch_bounds__(NORM_THREADS) norm_modulate_kernel(const NormParams p) {
+  constexpr int E = 16 / sizeof(XT);
+  constexpr int MAXV = NORM_MAX_D / E / NORM_THREADS;
+  __shared__ float red[2][4];
+  const int t = threadIdx.x;
+  const int64_t row_id = blockIdx.x;
   const int b = static_cast<int>(row_id / p.rows);
   const int r = static_cast<int>(row_id % p.rows);
   const XT* x = static_cast<const XT*>(p.x) + b * p.x_batch_stride + static_cast<int64_t>(r) * p.x_row_stride;
   __nv_bfloat16* y = p.y + b * p.y_batch_stride + static_cast<int64_t>(r) * p.y_row_stride;
-  const int nvec = p.D >> 3;
-  float v[MAXV][8];
+  const int nvec = p.D / E;
+  float v[MAXV][E];
   float sum = 0.f;
 #pragma unroll
   for (int i = 0; i < MAXV; ++i) {
-    const int c = lane + 32 * i;
+    const int c = t + NORM_THREADS * i;
     if (c < nvec) {
-      load8<XT>(x + c * 8, v[i]);
+      load_vec<E>(x, sizeof(XT) == 4 ? MFX_F32 : MFX_BF16, static_cast<int64_t>(c) * E, v[i]);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) sum += v[i][j];
+      for (int j = 0; j < E; ++j) sum += v[i][j];
     }
   }
   float mean = 0.f;
-  if (!p.rms) mean = warp_sum(sum) / static_cast<float>(p.D);
+  if (!p.rms) mean = block_sum_128(sum, red[0]) / static_cast<float>(p.D);
   float sq = 0.f;
 #pragma unroll
   for (int i = 0; i < MAXV; ++i) {
-    const int c = lane + 32 * i;
+    const int c = t + NORM_THREADS * i;
     if (c < nvec) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < E; ++j) {
         const float d = v[i][j] - mean;
         sq += d * d;
       }
     }
   }
-  const float rstd = rsqrtf(warp_sum(sq) / static_cast<float>(p.D) + p.eps);
-  // shift / scale / weight are read as 16-byte vectors when their dtype is bf16 (the usual case)
-  const bool vec_mod = p.mod_dtype == MFX_BF16;
-  const bool vec_w = p.weight_dtype == MFX_BF16;
+  const float rstd = rsqrtf(block_sum_128(sq, red[1]) / static_cast<float>(p.D) + p.eps);
 #pragma unroll
   for (int i = 0; i < MAXV; ++i) {
-    const int c = lane + 32 * i;
+    const int c = t + NORM_THREADS * i;
     if (c < nvec) {
-      float o[8], sc[8], sh[8], wt[8];
-      const int64_t moff = b * p.mod_batch_stride + c * 8;
-      if (p.scale) {
-        if (vec_mod) load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(p.scale) + moff, sc);
-        else
+      float o[E], sc[E], sh[E], wt[E];
+      const int64_t moff = b * p.mod_batch_stride + static_cast<int64_t>(c) * E;
+      if (p.scale) load_vec<E>(p.scale, p.mod_dtype, moff, sc);
+      if (p.shift) load_vec<E>(p.shift, p.mod_dtype, moff, sh);
+      if (p.weight) load_vec<E>(p.weight, p.weight_dtype, static_cast<int64_t>(c) * E, wt);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) sc[j] = ld_scalar(p.scale, p.mod_dtype, moff + j);
+      for (int j = 0; j < E; ++j) {
+        float u = (v[i][j] - mean) * rstd;
+        if (p.weight) u *= wt[j];
+        if (p.scale) u *= 1.0f + sc[j];
+        if (p.shift) u += sh[j];
+        o[j] = u;
       }
-      if (p.shift) {
-        if (vec_mod) load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(p.shift) + moff, sh);
-        else
-#pragma unroll
-          for (int j = 0; j < 8; ++j) sh[j] = ld_scalar(p.shift, p.mod_dtype, moff + j);
-      }
-      if (p.weight) {
-        if (vec_w) load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(p.weight) + c * 8, wt);
-        else
-#pragma unroll
-          for (int j = 0; j < 8; ++j) wt[j] = ld_scalar(p.weight, p.weight_dtype, c * 8 + j);
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float t = (v[i][j] - mean) * rstd;
-        if (p.weight) t *= wt[j];
-        if (p.scale) t *= 1.0f + sc[j];
-        if (p.shift) t += sh[j];
-        o[j] = t;
-      }
-      store8_bf16(y + c * 8, o);
+      store_vec_bf16<E>(y + static_cast<int64_t>(c) * E, o);
     }
   }
 }
@@ -158,55 +190,46 @@ struct PostNormParams {
 // residual[b, r, :] += gate[b, :] * RMSNorm(y[b, r, :]) * weight: the "sandwich" post-norm of the Z-Image block
 // (z_image_transformer/transformer_block.py:31,35; context_block.py:18,21). The norm needs the whole output row
 // of the projection, so it cannot be an epilogue of a matmul tiled along N; this pass reads y once.
-template <typename YT, int MAXV>
-__global__ void __launch_bounds__(128) norm_gate_residual_kernel(const PostNormParams p) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t row_id = static_cast<int64_t>(blockIdx.x) * 4 + warp;
-  if (row_id >= static_cast<int64_t>(p.rows) * p.batch) return;
+// One 128-thread block per row, 4 elements per vector (8-byte loads of bf16 y, 16-byte of the f32 residual).
+template <typename YT>
+__global__ void __launch_bounds__(NORM_THREADS) norm_gate_residual_kernel(const PostNormParams p) {
+  constexpr int E = 4;
+  constexpr int MAXV = NORM_MAX_D / E / NORM_THREADS;
+  __shared__ float red[4];
+  const int t = threadIdx.x;
+  const int64_t row_id = blockIdx.x;
   const int b = static_cast<int>(row_id / p.rows);
   const int r = static_cast<int>(row_id % p.rows);
   const YT* y = static_cast<const YT*>(p.y) + b * p.y_batch_stride + static_cast<int64_t>(r) * p.y_row_stride;
   float* res = p.residual + b * p.res_batch_stride + static_cast<int64_t>(r) * p.res_row_stride;
-  const int nvec = p.D >> 3;
-  float v[MAXV][8];
+  const int nvec = p.D / E;
+  float v[MAXV][E];
   float sq = 0.f;
 #pragma unroll
   for (int i = 0; i < MAXV; ++i) {
-    const int c = lane + 32 * i;
+    const int c = t + NORM_THREADS * i;
     if (c < nvec) {
-      load8<YT>(y + c * 8, v[i]);
+      load_vec<E>(y, sizeof(YT) == 4 ? MFX_F32 : MFX_BF16, static_cast<int64_t>(c) * E, v[i]);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) sq += v[i][j] * v[i][j];
+      for (int j = 0; j < E; ++j) sq += v[i][j] * v[i][j];
     }
   }
-  const float rstd = rsqrtf(warp_sum(sq) / static_cast<float>(p.D) + p.eps);
-  const bool vec_w = p.weight_dtype == MFX_BF16;
-  const bool vec_g = p.gate_dtype == MFX_BF16;
+  const float rstd = rsqrtf(block_sum_128(sq, red) / static_cast<float>(p.D) + p.eps);
 #pragma unroll
   for (int i = 0; i < MAXV; ++i) {
-    const int c = lane + 32 * i;
+    const int c = t + NORM_THREADS * i;
     if (c < nvec) {
-      float wt[8], gt[8], rs[8];
-      if (vec_w) load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(p.weight) + c * 8, wt);
-      else
+      float wt[E], gt[E], rs[E];
+      load_vec<E>(p.weight, p.weight_dtype, static_cast<int64_t>(c) * E, wt);
+      if (p.gate) load_vec<E>(p.gate, p.gate_dtype, b * p.gate_batch_stride + static_cast<int64_t>(c) * E, gt);
+      load_vec<E>(res, MFX_F32, static_cast<int64_t>(c) * E, rs);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) wt[j] = ld_scalar(p.weight, p.weight_dtype, c * 8 + j);
-      if (p.gate) {
-        const int64_t goff = b * p.gate_batch_stride + c * 8;
-        if (vec_g) load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(p.gate) + goff, gt);
-        else
-#pragma unroll
-          for (int j = 0; j < 8; ++j) gt[j] = ld_scalar(p.gate, p.gate_dtype, goff + j);
+      for (int j = 0; j < E; ++j) {
+        float u = v[i][j] * rstd * wt[j];
+        if (p.gate) u *= gt[j];
+        rs[j] += u;
       }
-      load8<float>(res + c * 8, rs);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float t = v[i][j] * rstd * wt[j];
-        if (p.gate) t *= gt[j];
-        rs[j] += t;
-      }
-      *reinterpret_cast<float4*>(res + c * 8) = make_float4(rs[0], rs[1], rs[2], rs[3]);
-      *reinterpret_cast<float4*>(res + c * 8 + 4) = make_float4(rs[4], rs[5], rs[6], rs[7]);
+      *reinterpret_cast<float4*>(res + static_cast<int64_t>(c) * E) = make_float4(rs[0], rs[1], rs[2], rs[3]);
     }
   }
 }
@@ -225,40 +248,58 @@ struct RopeParams {
   float eps;
 };
 
-// One warp per (token, head): lane l holds elements 4l..4l+3 of Q and of K, i.e. rotary pairs 2l and 2l+1.
+// A warp handles ROPE_HEADS consecutive heads of one token: lanes 0-15 hold the 128 elements of a head's Q,
+// lanes 16-31 those of its K, 8 consecutive elements (one 16-byte load, rotary pairs 4l..4l+3) per lane. The
+// token's cos/sin and the norm weights are loaded once per warp and all heads' loads are issued before any
+// arithmetic; the RMS reduction runs inside a half warp.
+constexpr int ROPE_HEADS = 4;
 __global__ void __launch_bounds__(256) qknorm_rope_kernel(const RopeParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int groups = (p.heads + ROPE_HEADS - 1) / ROPE_HEADS;
   const int64_t item = static_cast<int64_t>(blockIdx.x) * 8 + warp;
-  const int64_t total = static_cast<int64_t>(p.batch) * p.seq * p.heads;
+  const int64_t total = static_cast<int64_t>(p.batch) * p.seq * groups;
   if (item >= total) return;
-  const int h = static_cast<int>(item % p.heads);
-  const int64_t tok = item / p.heads;
+  const int h0 = static_cast<int>(item % groups) * ROPE_HEADS;
+  const int64_t tok = item / groups;
   const int s = static_cast<int>(tok % p.seq);
   const int b = static_cast<int>(tok / p.seq);
-  __nv_bfloat16* row = p.qkv + b * p.batch_stride + static_cast<int64_t>(s) * p.row_stride;
-  const float4 cs = __ldg(reinterpret_cast<const float4*>(p.cos_sin + (static_cast<int64_t>(s) * 64 + 2 * lane) * 2));
-  const void* qw = s < p.split ? p.qw_a : p.qw_b;
-  const void* kw = s < p.split ? p.kw_a : p.kw_b;
+  const int which = lane >> 4, l = lane & 15;
+  __nv_bfloat16* base = p.qkv + b * p.batch_stride + static_cast<int64_t>(s) * p.row_stride +
+                        (which * p.heads + h0) * 128 + l * 8;
+  uint4 raw[ROPE_HEADS];
 #pragma unroll
-  for (int which = 0; which < 2; ++which) {
-    __nv_bfloat16* ptr = row + (which * p.heads + h) * 128 + lane * 4;
-    const void* w = which == 0 ? qw : kw;
-    const uint2 raw = *reinterpret_cast<const uint2*>(ptr);
-    const __nv_bfloat16* hb = reinterpret_cast<const __nv_bfloat16*>(&raw);
-    float x[4];
+  for (int i = 0; i < ROPE_HEADS; ++i)
+    if (h0 + i < p.heads) raw[i] = *reinterpret_cast<const uint4*>(base + i * 128);
+  const float4* csp = reinterpret_cast<const float4*>(p.cos_sin + (static_cast<int64_t>(s) * 64 + 4 * l) * 2);
+  const float4 cs0 = __ldg(csp), cs1 = __ldg(csp + 1);
+  const void* w = which == 0 ? (s < p.split ? p.qw_a : p.qw_b) : (s < p.split ? p.kw_a : p.kw_b);
+  float wt[8];
+  load_vec<8>(w, p.w_dtype, l * 8, wt);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) x[j] = __bfloat162float(hb[j]);
-    const float ss = warp_sum(x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3]);
+  for (int i = 0; i < ROPE_HEADS; ++i) {
+    if (h0 + i >= p.heads) break;
+    const __nv_bfloat16* hb = reinterpret_cast<const __nv_bfloat16*>(&raw[i]);
+    float x[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] = __bfloat162float(hb[j]);
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += x[j] * x[j];
+#pragma unroll
+    for (int o = 8; o >= 1; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     const float r = rsqrtf(ss * (1.0f / 128.0f) + p.eps);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) x[j] = x[j] * r * ld_scalar(w, p.w_dtype, lane * 4 + j);
-    float o[4];
-    o[0] = cs.x * x[0] - cs.y * x[1];
-    o[1] = cs.y * x[0] + cs.x * x[1];
-    o[2] = cs.z * x[2] - cs.w * x[3];
-    o[3] = cs.w * x[2] + cs.z * x[3];
-    __nv_bfloat162 out2[2] = {__floats2bfloat162_rn(o[0], o[1]), __floats2bfloat162_rn(o[2], o[3])};
-    *reinterpret_cast<uint2*>(ptr) = *reinterpret_cast<uint2*>(out2);
+    for (int j = 0; j < 8; ++j) x[j] = x[j] * r * wt[j];
+    float o[8];
+    o[0] = cs0.x * x[0] - cs0.y * x[1];
+    o[1] = cs0.y * x[0] + cs0.x * x[1];
+    o[2] = cs0.z * x[2] - cs0.w * x[3];
+    o[3] = cs0.w * x[2] + cs0.z * x[3];
+    o[4] = cs1.x * x[4] - cs1.y * x[5];
+    o[5] = cs1.y * x[4] + cs1.x * x[5];
+    o[6] = cs1.z * x[6] - cs1.w * x[7];
+    o[7] = cs1.w * x[6] + cs1.z * x[7];
+    store8_bf16(base + i * 128, o);
   }
 }
 
@@ -355,7 +396,7 @@ int mfx_norm_modulate(const mfx_norm_args* a, void* stream) {
   if (!a) return MFX_ERR_NULL;
   if (!a->x || !a->y) return MFX_ERR_NULL;
   if (a->rows <= 0 || a->batch <= 0 || a->D <= 0 || a->D % 8 != 0) return MFX_ERR_SHAPE;
-  if (a->D > 32 * 8 * 16) return MFX_ERR_TOO_LARGE;
+  if (a->D > NORM_MAX_D) return MFX_ERR_TOO_LARGE;
   if (a->x_dtype != MFX_F32 && a->x_dtype != MFX_BF16) return MFX_ERR_DTYPE;
   if ((a->shift || a->scale) && !valid_dtype(a->mod_dtype)) return MFX_ERR_DTYPE;
   if (a->weight && !valid_dtype(a->weight_dtype)) return MFX_ERR_DTYPE;
@@ -363,10 +404,12 @@ int mfx_norm_modulate(const mfx_norm_args* a, void* stream) {
   if (!aligned16(a->x) || (a->x_row_stride * xs) % 16 != 0 || (a->x_batch_stride * xs) % 16 != 0 ||
       !aligned16(a->y) || (a->y_row_stride * 2) % 16 != 0 || (a->y_batch_stride * 2) % 16 != 0)
     return MFX_ERR_ALIGN;
-  if (a->mod_dtype == MFX_BF16 && (a->shift || a->scale) &&
-      ((a->shift && !aligned16(a->shift)) || (a->scale && !aligned16(a->scale)) || (a->mod_batch_stride * 2) % 16 != 0))
+  // bf16 and f32 vectors are read with 8- or 16-byte loads
+  if (a->mod_dtype != MFX_F16 && (a->shift || a->scale) &&
+      ((a->shift && !aligned16(a->shift)) || (a->scale && !aligned16(a->scale)) ||
+       (a->mod_batch_stride * dtype_size(a->mod_dtype)) % 16 != 0))
     return MFX_ERR_ALIGN;
-  if (a->weight && a->weight_dtype == MFX_BF16 && !aligned16(a->weight)) return MFX_ERR_ALIGN;
+  if (a->weight && a->weight_dtype != MFX_F16 && !aligned16(a->weight)) return MFX_ERR_ALIGN;
   if (int rc = check_arch()) return rc;
   NormParams p;
   p.x = a->x;
@@ -387,16 +430,11 @@ int mfx_norm_modulate(const mfx_norm_args* a, void* stream) {
   p.y_row_stride = a->y_row_stride;
   p.y_batch_stride = a->y_batch_stride;
   const int64_t total = a->rows * a->batch;
-  const unsigned blocks = static_cast<unsigned>((total + 3) / 4);
+  if (total > 0x7fffffffll) return MFX_ERR_TOO_LARGE;
+  const unsigned blocks = static_cast<unsigned>(total);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int nvec_lane = static_cast<int>((a->D / 8 + 31) / 32);
-  if (a->x_dtype == MFX_F32) {
-    if (nvec_lane <= 12) norm_modulate_kernel<float, 12><<<blocks, 128, 0, st>>>(p);
-    else norm_modulate_kernel<float, 16><<<blocks, 128, 0, st>>>(p);
-  } else {
-    if (nvec_lane <= 12) norm_modulate_kernel<__nv_bfloat16, 12><<<blocks, 128, 0, st>>>(p);
-    else norm_modulate_kernel<__nv_bfloat16, 16><<<blocks, 128, 0, st>>>(p);
-  }
+  if (a->x_dtype == MFX_F32) norm_modulate_kernel<float><<<blocks, NORM_THREADS, 0, st>>>(p);
+  else norm_modulate_kernel<__nv_bfloat16><<<blocks, NORM_THREADS, 0, st>>>(p);
   MFX_CUDA_TRY(cudaGetLastError());
   return MFX_OK;
 }
@@ -409,7 +447,8 @@ int mfx_qknorm_rope(void* qkv, int64_t row_stride, int64_t batch_stride, int64_t
   if (!qkv || !qw_a || !kw_a || !qw_b || !kw_b || !cos_sin) return MFX_ERR_NULL;
   if (seq <= 0 || batch <= 0 || heads <= 0 || split < 0) return MFX_ERR_SHAPE;
   if (!valid_dtype(w_dtype)) return MFX_ERR_DTYPE;
-  if ((reinterpret_cast<uintptr_t>(qkv) & 7u) || row_stride % 4 != 0 || batch_stride % 4 != 0 || !aligned16(cos_sin))
+  if (!aligned16(qkv) || row_stride % 8 != 0 || batch_stride % 8 != 0 || !aligned16(cos_sin) ||
+      (w_dtype != MFX_F16 && (!aligned16(qw_a) || !aligned16(kw_a) || !aligned16(qw_b) || !aligned16(kw_b))))
     return MFX_ERR_ALIGN;
   if (row_stride < 3ll * heads * 128) return MFX_ERR_SHAPE;
   if (int rc = check_arch()) return rc;
@@ -428,7 +467,7 @@ int mfx_qknorm_rope(void* qkv, int64_t row_stride, int64_t batch_stride, int64_t
   p.w_dtype = w_dtype;
   p.cos_sin = cos_sin;
   p.eps = eps;
-  const int64_t total = seq * batch * heads;
+  const int64_t total = seq * batch * ((heads + glue::ROPE_HEADS - 1) / glue::ROPE_HEADS);
   qknorm_rope_kernel<<<static_cast<unsigned>((total + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
   MFX_CUDA_TRY(cudaGetLastError());
   return MFX_OK;
@@ -485,15 +524,16 @@ int mfx_norm_gate_residual(const void* y, int y_dtype, int64_t y_row_stride, int
   using namespace mfx::glue;
   if (!y || !weight || !residual) return MFX_ERR_NULL;
   if (rows <= 0 || batch <= 0 || D <= 0 || D % 8 != 0) return MFX_ERR_SHAPE;
-  if (D > 32 * 8 * 16) return MFX_ERR_TOO_LARGE;
+  if (D > NORM_MAX_D) return MFX_ERR_TOO_LARGE;
   if ((y_dtype != MFX_F32 && y_dtype != MFX_BF16) || !valid_dtype(weight_dtype) || (gate && !valid_dtype(gate_dtype)))
     return MFX_ERR_DTYPE;
   const size_t ys = dtype_size(y_dtype);
   if (!aligned16(y) || (y_row_stride * ys) % 16 != 0 || (y_batch_stride * ys) % 16 != 0 || !aligned16(residual) ||
       (res_row_stride * 4) % 16 != 0 || (res_batch_stride * 4) % 16 != 0)
     return MFX_ERR_ALIGN;
-  if (weight_dtype == MFX_BF16 && !aligned16(weight)) return MFX_ERR_ALIGN;
-  if (gate && gate_dtype == MFX_BF16 && (!aligned16(gate) || (gate_batch_stride * 2) % 16 != 0)) return MFX_ERR_ALIGN;
+  if (weight_dtype != MFX_F16 && !aligned16(weight)) return MFX_ERR_ALIGN;
+  if (gate && gate_dtype != MFX_F16 && (!aligned16(gate) || (gate_batch_stride * dtype_size(gate_dtype)) % 16 != 0))
+    return MFX_ERR_ALIGN;
   if (int rc = check_arch()) return rc;
   PostNormParams p;
   p.y = y;
@@ -511,16 +551,11 @@ int mfx_norm_gate_residual(const void* y, int y_dtype, int64_t y_row_stride, int
   p.residual = residual;
   p.res_row_stride = res_row_stride;
   p.res_batch_stride = res_batch_stride;
-  const unsigned blocks = static_cast<unsigned>((rows * batch + 3) / 4);
+  if (rows * batch > 0x7fffffffll) return MFX_ERR_TOO_LARGE;
+  const unsigned blocks = static_cast<unsigned>(rows * batch);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int nvec_lane = static_cast<int>((D / 8 + 31) / 32);
-  if (y_dtype == MFX_F32) {
-    if (nvec_lane <= 12) norm_gate_residual_kernel<float, 12><<<blocks, 128, 0, st>>>(p);
-    else norm_gate_residual_kernel<float, 16><<<blocks, 128, 0, st>>>(p);
-  } else {
-    if (nvec_lane <= 12) norm_gate_residual_kernel<__nv_bfloat16, 12><<<blocks, 128, 0, st>>>(p);
-    else norm_gate_residual_kernel<__nv_bfloat16, 16><<<blocks, 128, 0, st>>>(p);
-  }
+  if (y_dtype == MFX_F32) norm_gate_residual_kernel<float><<<blocks, NORM_THREADS, 0, st>>>(p);
+  else norm_gate_residual_kernel<__nv_bfloat16><<<blocks, NORM_THREADS, 0, st>>>(p);
   MFX_CUDA_TRY(cudaGetLastError());
   return MFX_OK;
 }
