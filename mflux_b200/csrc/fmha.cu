@@ -3,15 +3,21 @@
 // Replaces mx.fast.scaled_dot_product_attention(q, k, v, scale) as called by the reference's
 // AttentionUtils.compute_attention (src/mflux/models/flux/model/flux_transformer/common/attention_utils.py:48-52).
 //
-// One CTA = one (sample, head, 128-query tile); two CTAs share an SM so that the softmax of one overlaps
-// the tensor-core work of the other. 192 threads:
-//   warp 0     TMA producer: Q once, then K and V tiles of 128 keys (128-byte swizzle, two 64-wide halves of d)
-//   warp 1     allocates 256 TMEM columns, issues tcgen05.mma:
-//                S[128 q x 128 keys] = Q K^T            (both operands from shared memory, K-major)
-//                O[128 q x 128 d]   += P V              (P bf16 from tensor memory, V MN-major from shared memory)
-//   warps 2-5  softmax: tcgen05.ld S (thread = query row), running max kept stale until it would grow by
-//              more than 2^8 (then O and the row sum are rescaled), exp2, P -> tcgen05.st over the S columns,
-//              finally O / rowsum -> global
+// One CTA = one (sample, head, 128-query tile); two CTAs share an SM. Keys go in tiles of 64 and the score tile
+// S is double-buffered in tensor memory, so S of tile j+1 is computed while the softmax of tile j runs and the
+// softmax warps never wait for a matmul in steady state. 352 threads:
+//   warp 0     TMA producer: Q once, then K tiles of 64 keys into two stages (128-byte swizzle, two 64-wide
+//              halves of d); warp 10 does the same for V
+//   warp 1     allocates 256 TMEM columns (S0 | S1 | O), issues tcgen05.mma in the order S(0), then per tile j:
+//              S(j+1), O += P(j) V(j):
+//                S[128 q x 64 keys] = Q K^T             (both operands from shared memory, K-major)
+//                O[128 q x 128 d]  += P V               (P bf16 from tensor memory, V MN-major from shared memory)
+//   warps 2-9  softmax, two warps per 32-row quarter of the tile, each owning 32 of the 64 key columns
+//              (thread = query row): one tcgen05.ld of its S columns into registers, row maximum exchanged
+//              with the partner warp through shared memory, running max kept stale until it would grow by
+//              more than 2^8 (then O and the row sums are rescaled), exp2 (three quarters on the special-function
+//              unit, one quarter as a cubic on the FMA pipe), P -> tcgen05.st over the warp's own S columns,
+//              finally O / rowsum -> global (each warp its 64 columns of d)
 // All waits are bounded.
 #include <cuda_bf16.h>
 
@@ -22,22 +28,29 @@ namespace mfx {
 namespace fmha {
 
 constexpr int BQ = 128;
-constexpr int BKV = 128;
+constexpr int BKV = 64;
 constexpr int HD = 128;
-constexpr int NUM_THREADS = 192;
-constexpr int TILE_BYTES = 128 * HD * 2;  // 32 KiB: [128 rows][128 d] bf16 as two 16 KiB halves of d
-constexpr int HALF_BYTES = TILE_BYTES / 2;
+constexpr int NUM_THREADS = 352;
+constexpr int V_PRODUCER_WARP = 10;
+constexpr int NUM_SOFTMAX_WARPS = 8;
+constexpr int Q_BYTES = BQ * HD * 2;        // 32 KiB: [128 rows][128 d] bf16 as two 16 KiB halves of d
+constexpr int Q_HALF = Q_BYTES / 2;
+constexpr int KV_BYTES = BKV * HD * 2;      // 16 KiB: [64 keys][128 d] as two 8 KiB halves of d
+constexpr int KV_HALF = KV_BYTES / 2;
 constexpr uint32_t TMEM_COLS = 256;
-constexpr uint32_t COL_S = 0;    // S fp32 [0,128); P bf16 pairs reuse [0,64)
+constexpr uint32_t COL_S = 0;    // two S buffers of 64 fp32 columns; P (bf16 pairs) of a warp's 32 keys goes over
+                                 // the first 16 of the 32 S columns that warp owns
 constexpr uint32_t COL_O = 128;  // O fp32 [128,256)
 
 constexpr int OFF_Q = 0;
-constexpr int OFF_K = OFF_Q + TILE_BYTES;
-constexpr int OFF_V = OFF_K + TILE_BYTES;
-constexpr int OFF_BAR = OFF_V + TILE_BYTES;
-constexpr int NUM_BARS = 9;
+constexpr int OFF_K = OFF_Q + Q_BYTES;          // 2 stages
+constexpr int OFF_V = OFF_K + 2 * KV_BYTES;     // 2 stages
+constexpr int OFF_BAR = OFF_V + 2 * KV_BYTES;
+constexpr int NUM_BARS = 14;
 constexpr int OFF_TMEM = OFF_BAR + NUM_BARS * 8;
-constexpr int DYN_BYTES = OFF_TMEM + 16 + 1024;
+constexpr int OFF_XCH = OFF_TMEM + 16;                // float [2 parities][4 quarters][2 halves][32 rows]
+constexpr int XCH_BYTES = 2 * 4 * 2 * 32 * 4;
+constexpr int DYN_BYTES = OFF_XCH + XCH_BYTES + 1024;
 
 struct Params {
   int seq, batch, heads;
@@ -65,6 +78,88 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// Packed pairs of floats in one 64-bit register: sm_100 executes add/fma on both halves in one instruction.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// max(m, all 32 values) with two independent chains of 3-input max.
+__device__ __forceinline__ float max_chunk(const uint32_t (&s)[32], float m) {
+  float a = m, b = __uint_as_float(s[0]);
+#pragma unroll
+  for (int i = 0; i < 32; i += 4) {
+    a = max3(a, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+    b = max3(b, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+  }
+  return fmaxf(a, b);
+}
+
+// 2^x for a pair on the FMA and integer pipes instead of the special-function unit: n = rint(x) by the
+// magic-number add, 2^(x-n) by a cubic fitted on [-0.5, 0.5] (max relative error 7.5e-5, far below the bf16
+// rounding the result gets), n added into the exponent field. x is clamped at -126 to keep the exponent in range.
+__device__ __forceinline__ void exp2_poly2(uint64_t x2, float& p0, float& p1) {
+  float x0, x1;
+  unpack2(x2, x0, x1);
+  x2 = pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+  const uint64_t magic = pack2(12582912.f, 12582912.f), nmagic = pack2(-12582912.f, -12582912.f);
+  const uint64_t t2 = add2(x2, magic);
+  const uint64_t n2 = add2(t2, nmagic);
+  const uint64_t f2 = fma2(n2, pack2(-1.f, -1.f), x2);
+  uint64_t r2 = fma2(f2, pack2(0.0551716685f, 0.0551716685f), pack2(0.2426111251f, 0.2426111251f));
+  r2 = fma2(r2, f2, pack2(0.6932609677f, 0.6932609677f));
+  r2 = fma2(r2, f2, pack2(0.9999280572f, 0.9999280572f));
+  float t0, t1, r0, r1;
+  unpack2(t2, t0, t1);
+  unpack2(r2, r0, r1);
+  p0 = __uint_as_float(__float_as_uint(r0) + (__float_as_uint(t0) << 23));
+  p1 = __uint_as_float(__float_as_uint(r1) + (__float_as_uint(t1) << 23));
+}
+
+// Pairs (by index within a 32-column chunk) whose exponential runs on the FMA pipe; the rest use ex2 on the
+// special-function unit. One pair in four balances the two pipes against the tensor pipe's time per tile.
+constexpr uint32_t POLY_PAIRS = 0x8888u;
+
+// p = 2^(s * scale - m) for 32 scores, bf16 pairs into pk, float sums into lsum2.
+__device__ __forceinline__ void exp_chunk(const uint32_t (&s)[32], uint64_t scale2, uint64_t negm2, uint64_t& lsum2,
+                                          uint32_t (&pk)[16]) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const uint64_t x2 = fma2(pack2(__uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1])), scale2, negm2);
+    float p0, p1;
+    if ((POLY_PAIRS >> i) & 1u) {
+      exp2_poly2(x2, p0, p1);
+    } else {
+      float x0, x1;
+      unpack2(x2, x0, x1);
+      p0 = ex2(x0);
+      p1 = ex2(x1);
+    }
+    lsum2 = add2(lsum2, pack2(p0, p1));
+    const __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
+    pk[i] = *reinterpret_cast<const uint32_t*>(&hh);
+  }
+}
+
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
             const __grid_constant__ CUtensorMap tmap_v, const Params p) {
@@ -73,8 +168,9 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t q_s = smem_base + OFF_Q, k_s = smem_base + OFF_K, v_s = smem_base + OFF_V;
   const uint32_t bar0 = smem_base + OFF_BAR;
-  const uint32_t q_full = bar0, k_full = bar0 + 8, v_full = bar0 + 16, k_empty = bar0 + 24, v_empty = bar0 + 32,
-                 s_full = bar0 + 40, p_full = bar0 + 48, o_full = bar0 + 56;
+  // per-stage barriers are pairs: index + 8 * stage
+  const uint32_t q_full = bar0, o_full = bar0 + 8, k_full = bar0 + 16, v_full = bar0 + 32,
+                 v_empty = bar0 + 64, s_full = bar0 + 80, p_full = bar0 + 96;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + OFF_TMEM);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -85,13 +181,15 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    mbar_init(k_full, 1);
-    mbar_init(v_full, 1);
-    mbar_init(k_empty, 1);
-    mbar_init(v_empty, 1);
-    mbar_init(s_full, 1);
-    mbar_init(p_full, 4);
     mbar_init(o_full, 1);
+#pragma unroll
+    for (int st = 0; st < 2; ++st) {
+      mbar_init(k_full + 8 * st, 1);
+      mbar_init(v_full + 8 * st, 1);
+      mbar_init(v_empty + 8 * st, 1);
+      mbar_init(s_full + 8 * st, 1);
+      mbar_init(p_full + 8 * st, NUM_SOFTMAX_WARPS);
+    }
     fence_mbar_init();
     tma_prefetch_desc(&tmap_q);
     tma_prefetch_desc(&tmap_k);
@@ -109,24 +207,33 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      mbar_arrive_expect_tx(q_full, TILE_BYTES);
+      mbar_arrive_expect_tx(q_full, Q_BYTES);
       tma_load_4d(q_s, &tmap_q, q_full, 0, h, q0, b);
-      tma_load_4d(q_s + HALF_BYTES, &tmap_q, q_full, 64, h, q0, b);
+      tma_load_4d(q_s + Q_HALF, &tmap_q, q_full, 64, h, q0, b);
     }
-    bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      const uint32_t ph = static_cast<uint32_t>(j & 1);
-      if (!mbar_wait(k_empty, ph ^ 1u, DEV_TIMEOUT_ATTN)) break;
+    // K stream (the V stream has its own warp): a K stage frees as soon as S of that tile is done, a V stage only
+    // after the tile's P V product, and K of the next tiles must not wait behind V
+    for (int j = 0; j < n_tiles; ++j) {
+      const int st = j & 1;
+      const uint32_t ph = static_cast<uint32_t>((j >> 1) & 1);
+      // the stage is free once S of the tile that used it (j - 2) is complete: that is what s_full signals
+      if (j >= 2 && !mbar_wait(s_full + 8 * st, ph ^ 1u, DEV_TIMEOUT_ATTN)) break;
       if (lane == 0) {
-        mbar_arrive_expect_tx(k_full, TILE_BYTES);
-        tma_load_4d(k_s, &tmap_k, k_full, 0, h, j * BKV, b);
-        tma_load_4d(k_s + HALF_BYTES, &tmap_k, k_full, 64, h, j * BKV, b);
+        mbar_arrive_expect_tx(k_full + 8 * st, KV_BYTES);
+        tma_load_4d(k_s + st * KV_BYTES, &tmap_k, k_full + 8 * st, 0, h, j * BKV, b);
+        tma_load_4d(k_s + st * KV_BYTES + KV_HALF, &tmap_k, k_full + 8 * st, 64, h, j * BKV, b);
       }
-      if (!mbar_wait(v_empty, ph ^ 1u, DEV_TIMEOUT_ATTN)) break;
+      __syncwarp();
+    }
+  } else if (warp == V_PRODUCER_WARP) {
+    for (int j = 0; j < n_tiles; ++j) {
+      const int st = j & 1;
+      const uint32_t ph = static_cast<uint32_t>((j >> 1) & 1);
+      if (!mbar_wait(v_empty + 8 * st, ph ^ 1u, DEV_TIMEOUT_ATTN)) break;
       if (lane == 0) {
-        mbar_arrive_expect_tx(v_full, TILE_BYTES);
-        tma_load_4d(v_s, &tmap_v, v_full, 0, h, j * BKV, b);
-        tma_load_4d(v_s + HALF_BYTES, &tmap_v, v_full, 64, h, j * BKV, b);
+        mbar_arrive_expect_tx(v_full + 8 * st, KV_BYTES);
+        tma_load_4d(v_s + st * KV_BYTES, &tmap_v, v_full + 8 * st, 0, h, j * BKV, b);
+        tma_load_4d(v_s + st * KV_BYTES + KV_HALF, &tmap_v, v_full + 8 * st, 64, h, j * BKV, b);
       }
       __syncwarp();
     }
@@ -134,132 +241,155 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
     // ------------------------------------------------------------ MMA issuer
     constexpr uint32_t IDESC_S = make_idesc(FMT_BF16, FMT_BF16, BQ, BKV);       // K-major x K-major
     constexpr uint32_t IDESC_O = make_idesc_b_mn(FMT_BF16, FMT_BF16, BQ, HD);   // P (TMEM) x V (MN-major)
-    bool ok = mbar_wait(q_full, 0, DEV_TIMEOUT_ATTN);
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      const uint32_t ph = static_cast<uint32_t>(j & 1);
-      if (!mbar_wait(k_full, ph, DEV_TIMEOUT_ATTN)) break;
+    // S(t) = Q K(t)^T into S buffer t & 1
+    auto issue_s = [&](int t) -> bool {
+      const int st = t & 1;
+      if (!mbar_wait(k_full + 8 * st, static_cast<uint32_t>((t >> 1) & 1), DEV_TIMEOUT_ATTN)) return false;
       tc_fence_after();
       if (lane == 0) {
 #pragma unroll
         for (int i = 0; i < HD / 16; ++i) {
-          const uint32_t off = (i >> 2) * HALF_BYTES + (i & 3) * 32;  // half of d, then 32 B per 16 d
-          umma_f16_ss(tmem_base + COL_S, smem_desc_sw128(q_s + off), smem_desc_sw128(k_s + off), IDESC_S,
-                      i != 0 ? 1u : 0u);
+          // half of d, then 32 B per 16 d inside the 128-byte rows
+          const uint32_t qoff = (i >> 2) * Q_HALF + (i & 3) * 32, koff = (i >> 2) * KV_HALF + (i & 3) * 32;
+          umma_f16_ss(tmem_base + COL_S + 64 * st, smem_desc_sw128(q_s + qoff),
+                      smem_desc_sw128(k_s + st * KV_BYTES + koff), IDESC_S, i != 0 ? 1u : 0u);
         }
-        umma_commit(s_full);
-        umma_commit(k_empty);
+        umma_commit(s_full + 8 * st);
       }
       __syncwarp();
-      if (!mbar_wait(p_full, ph, DEV_TIMEOUT_ATTN) || !mbar_wait(v_full, ph, DEV_TIMEOUT_ATTN)) break;
+      return true;
+    };
+    bool ok = mbar_wait(q_full, 0, DEV_TIMEOUT_ATTN) && issue_s(0);
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int st = j & 1;
+      const uint32_t ph = static_cast<uint32_t>((j >> 1) & 1);
+      // the buffer S(j+1) goes to held P(j-1), whose P V product was issued one iteration ago and runs first
+      if (j + 1 < n_tiles && !issue_s(j + 1)) break;
+      if (!mbar_wait(p_full + 8 * st, ph, DEV_TIMEOUT_ATTN) || !mbar_wait(v_full + 8 * st, ph, DEV_TIMEOUT_ATTN))
+        break;
       tc_fence_after();
       if (lane == 0) {
 #pragma unroll
         for (int i = 0; i < BKV / 16; ++i) {
-          // A: 16 keys of P = 8 TMEM columns; B: 16 key rows of V = 2048 B further, d halves 16 KiB apart
-          umma_f16_ts(tmem_base + COL_O, tmem_base + COL_S + 8 * i, smem_desc_sw128_mn(v_s + i * 2048, HALF_BYTES),
-                      IDESC_O, (j | i) != 0 ? 1u : 0u);
+          // A: 16 keys of P = 8 TMEM columns (keys 0-31 at columns 0-15 of the buffer, keys 32-63 at 32-47);
+          // B: 16 key rows of V = 2048 B further, d halves 8 KiB apart
+          umma_f16_ts(tmem_base + COL_O, tmem_base + COL_S + 64 * st + (i >> 1) * 32 + 8 * (i & 1),
+                      smem_desc_sw128_mn(v_s + st * KV_BYTES + i * 2048, KV_HALF), IDESC_O, (j | i) != 0 ? 1u : 0u);
         }
-        umma_commit(v_empty);
+        umma_commit(v_empty + 8 * st);
         if (j == n_tiles - 1) umma_commit(o_full);
       }
       __syncwarp();
     }
   } else {
     // ------------------------------------------------------------ softmax + output (thread = query row)
-    const int qd = warp & 3;  // TMEM lane quarter
+    const int qd = warp & 3;          // TMEM lane quarter this warp may access
+    const int hf = (warp - 2) >> 2;   // which 32 of the tile's 64 key columns (and 64 of the 128 d columns at the end)
     const int row = qd * 32 + lane;
     const uint32_t t_row = tmem_base + (static_cast<uint32_t>(qd * 32) << 16);
+    const uint32_t t_o = t_row + COL_O + hf * 64;   // own O columns
+    float* xch = reinterpret_cast<float*>(smem_gen + OFF_XCH);
+    const int xch_mine = (qd * 2 + hf) * 32 + lane, xch_other = (qd * 2 + (hf ^ 1)) * 32 + lane;
     float m_ref = -INFINITY, l_sum = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
-      const uint32_t ph = static_cast<uint32_t>(j & 1);
-      if (!mbar_wait(s_full, ph, DEV_TIMEOUT_ATTN)) {
+      const int st = j & 1;
+      const uint32_t ph = static_cast<uint32_t>((j >> 1) & 1);
+      if (!mbar_wait(s_full + 8 * st, ph, DEV_TIMEOUT_ATTN)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      const int keys_here = min(BKV, p.seq - j * BKV);
-      const bool tail = keys_here < BKV;  // only the last tile of a ragged sequence needs key masking
-      // pass 1: row maximum of this tile
-      float m_tile = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t s[32];
-        tmem_ld_32x32(t_row + COL_S + c * 32, s);
-        tmem_ld_wait();
-        if (!tail) {
-          float m0 = __uint_as_float(s[0]), m1 = __uint_as_float(s[1]);
+      const uint32_t t_s = t_row + COL_S + 64 * st + 32 * hf;   // own S columns; own P goes over the first 16
+      const int keys_here = min(BKV, p.seq - j * BKV) - hf * 32;  // valid keys among this warp's 32 columns
+      const bool tail = keys_here < 32;  // only the last tile of a ragged sequence needs key masking
+      uint32_t sA[32];
+      tmem_ld_32x32(t_s, sA);
+      tmem_ld_fence(sA);
+      float m_mine;
+      if (!tail) {
+        m_mine = max_chunk(sA, -INFINITY);
+      } else {
+        m_mine = -INFINITY;
 #pragma unroll
-          for (int i = 2; i < 32; i += 2) {
-            m0 = fmaxf(m0, __uint_as_float(s[i]));
-            m1 = fmaxf(m1, __uint_as_float(s[i + 1]));
-          }
-          m_tile = fmaxf(m_tile, fmaxf(m0, m1));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (c * 32 + i < keys_here) m_tile = fmaxf(m_tile, __uint_as_float(s[i]));
-        }
+        for (int i = 0; i < 32; ++i)
+          if (i < keys_here) m_mine = fmaxf(m_mine, __uint_as_float(sA[i]));
       }
-      m_tile *= p.scale_log2;
-      // grow the reference maximum only when it would change the exponent range by more than 2^8
+      // the partner warp holds the other 32 columns of the same rows: swap maxima (two buffers by tile parity;
+      // the barrier per tile keeps the two warps at most one tile apart)
+      xch[st * 256 + xch_mine] = m_mine;
+      named_bar_sync(1 + qd, 64);
+      const float m_tile = fmaxf(m_mine, xch[st * 256 + xch_other]) * p.scale_log2;
+      // grow the reference maximum only when it would change the exponent range by more than 2^8; both warps
+      // of a quarter see the same maxima and take the same branch, each rescaling its own half of O
       const bool grow = m_tile > m_ref + 8.0f;
       if (__any_sync(0xffffffffu, grow)) {
         const float m_new = fmaxf(m_ref, m_tile);
         const float alpha = (m_ref == -INFINITY) ? 0.f : ex2(m_ref - m_new);
         l_sum *= alpha;
         if (j > 0) {
+          // O still receives P(j-1) V(j-1): wait until that product has finished (its commit frees the V stage)
+          if (!mbar_wait(v_empty + 8 * (st ^ 1), static_cast<uint32_t>(((j - 1) >> 1) & 1), DEV_TIMEOUT_ATTN)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
-            uint32_t o[32];
-            tmem_ld_32x32(t_row + COL_O + c * 32, o);
+            uint32_t o[16];
+            tmem_ld_32x16(t_o + c * 16, o);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st_32x32(t_row + COL_O + c * 32, o);
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x16(t_o + c * 16, o);
           }
           tmem_st_wait();
         }
         m_ref = m_new;
       }
-      // pass 2: probabilities, packed to bf16 pairs over the columns S no longer needs
-      float l0 = 0.f, l1 = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t s[32];
-        tmem_ld_32x32(t_row + COL_S + c * 32, s);
-        tmem_ld_wait();
-        uint32_t pk[16];
+      // probabilities from the registers, packed to bf16 pairs over this warp's own (already read) S columns
+      uint64_t l2 = pack2(0.f, 0.f);
+      uint32_t pk[16];
+      if (!tail) {
+        exp_chunk(sA, pack2(p.scale_log2, p.scale_log2), pack2(-m_ref, -m_ref), l2, pk);
+      } else {
+        float l0 = 0.f, l1 = 0.f;
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float p0 = ex2(fmaf(__uint_as_float(s[2 * i]), p.scale_log2, -m_ref));
-          float p1 = ex2(fmaf(__uint_as_float(s[2 * i + 1]), p.scale_log2, -m_ref));
-          if (tail) {
-            if (c * 32 + 2 * i >= keys_here) p0 = 0.f;
-            if (c * 32 + 2 * i + 1 >= keys_here) p1 = 0.f;
-          }
+          float p0 = ex2(fmaf(__uint_as_float(sA[2 * i]), p.scale_log2, -m_ref));
+          float p1 = ex2(fmaf(__uint_as_float(sA[2 * i + 1]), p.scale_log2, -m_ref));
+          if (2 * i >= keys_here) p0 = 0.f;
+          if (2 * i + 1 >= keys_here) p1 = 0.f;
           l0 += p0;
           l1 += p1;
           const __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);
           pk[i] = *reinterpret_cast<const uint32_t*>(&hh);
         }
-        tmem_st_32x16(t_row + COL_S + c * 16, pk);
+        l2 = pack2(l0, l1);
       }
+      tmem_st_32x16(t_s, pk);
+      float l0, l1;
+      unpack2(l2, l0, l1);
       l_sum += l0 + l1;
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0) mbar_arrive(p_full + 8 * st);
     }
     if (ok && mbar_wait(o_full, 0, DEV_TIMEOUT_ATTN)) {
       tc_fence_after();
-      const float inv = 1.0f / l_sum;
+      // total row sum = this warp's part + the partner's
+      const int ph = n_tiles & 1;
+      xch[ph * 256 + xch_mine] = l_sum;
+      named_bar_sync(1 + qd, 64);
+      const float inv = 1.0f / (l_sum + xch[ph * 256 + xch_other]);
       const int q = q0 + row;
-      __nv_bfloat16* dst = p.out + b * p.out_batch_stride + static_cast<int64_t>(q) * p.out_row_stride + h * HD;
+      __nv_bfloat16* dst = p.out + b * p.out_batch_stride + static_cast<int64_t>(q) * p.out_row_stride + h * HD +
+                           hf * 64;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t o[32];
-        tmem_ld_32x32(t_row + COL_O + c * 32, o);
+        tmem_ld_32x32(t_o + c * 32, o);
         tmem_ld_wait();
         if (q < p.seq) {
 #pragma unroll
@@ -309,12 +439,12 @@ int mfx_fmha(const void* q, const void* k, const void* v, int64_t qkv_row_stride
   const uint64_t bstride = batch > 1 ? static_cast<uint64_t>(qkv_batch_stride) * 2
                                      : static_cast<uint64_t>(qkv_row_stride) * 2 * seq;
   const uint64_t strides[3] = {HD * 2, static_cast<uint64_t>(qkv_row_stride) * 2, bstride};
-  const uint32_t box[4] = {64, 1, 128, 1};
+  const uint32_t box_q[4] = {64, 1, BQ, 1}, box_kv[4] = {64, 1, BKV, 1};
   const void* ptrs[3] = {q, k, v};
   CUtensorMap* maps[3] = {&tq, &tk, &tv};
   for (int i = 0; i < 3; ++i)
-    if (int rc = encode_tmap(maps[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, ptrs[i], dims, strides, box,
-                             CU_TENSOR_MAP_SWIZZLE_128B))
+    if (int rc = encode_tmap(maps[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, ptrs[i], dims, strides,
+                             i == 0 ? box_q : box_kv, CU_TENSOR_MAP_SWIZZLE_128B))
       return rc;
   Params p;
   p.seq = static_cast<int>(seq);
