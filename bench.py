@@ -295,6 +295,8 @@ def run_sweep(args, dev):
     from mflux_b200 import ops
 
     peak, _, burst = measured_peaks()
+    f = ROOT / "MEASURED_PEAKS.json"
+    hbm = json.loads(f.read_text()).get("hbm_gbs") if f.exists() else 6650.0
     rows = []
     g = torch.Generator(device=dev).manual_seed(0)
     for bits in (4, 8):
@@ -303,26 +305,45 @@ def run_sweep(args, dev):
             wq, sc, bi = ops.quantize_affine(w, 64, bits)
             bias = (torch.randn(n, device=dev, generator=g) * 0.02).to(torch.bfloat16)
             del w
-            for m in (256, 1024, 4096, 4608, 16384):
+            for m in (1, 16, 256, 1024, 4096, 4608, 16384):
                 per = n * k * bits // 8 + 2 * m * k + 2 * m * n
                 copies = max(2, min(64, -(-400_000_000 // per)))
                 preps = [ops.prepare_qlinear(wq, sc, bi, bits, 64) for _ in range(copies)]
                 xs = [torch.randn(m, k, device=dev, generator=g).to(torch.bfloat16) for _ in range(copies)]
                 ys = [torch.empty(m, n, device=dev, dtype=torch.bfloat16) for _ in range(copies)]
                 reps = max(copies, 20)
+                def launch_all():
+                    for i in range(reps):
+                        ops.qlinear(xs[i % copies], wq, None, None, bias, bits=bits, out=ys[i % copies],
+                                    prepared=preps[i % copies])
                 for i in range(max(3, args.warmup)):
                     ops.qlinear(xs[i % copies], wq, None, None, bias, bits=bits, out=ys[i % copies], prepared=preps[i % copies])
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 torch.cuda.synchronize()
-                e0.record()
-                for i in range(reps):
-                    ops.qlinear(xs[i % copies], wq, None, None, bias, bits=bits, out=ys[i % copies], prepared=preps[i % copies])
-                e1.record()
+                if m <= 16:
+                    # launches of a few microseconds: replay them from a CUDA graph so that the host's launch
+                    # rate is not what gets timed
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph):
+                        launch_all()
+                    graph.replay()
+                    torch.cuda.synchronize()
+                    e0.record()
+                    graph.replay()
+                    e1.record()
+                else:
+                    e0.record()
+                    launch_all()
+                    e1.record()
                 torch.cuda.synchronize()
                 us = e0.elapsed_time(e1) * 1e3 / reps
                 tf = 2.0 * m * n * k / us / 1e6
-                rows.append({"bits": bits, "N": n, "K": k, "M": m, "us": round(us, 1), "tflops": round(tf, 1),
-                             "frac_burst_peak": round(tf / burst, 3) if burst else None, "copies": copies})
+                row = {"bits": bits, "N": n, "K": k, "M": m, "us": round(us, 1), "tflops": round(tf, 1),
+                       "frac_burst_peak": round(tf / burst, 3) if burst else None, "copies": copies}
+                if m <= 16:   # weight-streaming kernel: HBM-bound, report bytes per second as well
+                    gbs = (n * k * bits // 8 + n * (k // 64) * 4 + 2 * m * k + 2 * m * n) / us / 1e3
+                    row.update({"gbs": round(gbs, 1), "frac_hbm_peak": round(gbs / hbm, 3) if hbm else None})
+                rows.append(row)
                 del preps, xs, ys
     return rows
 
@@ -369,7 +390,8 @@ def main():
             rows = run_sweep(args, dev)
             clocks = sampler.stop()
             peak, _, burst = measured_peaks()
-            geo = math.exp(sum(math.log(r["tflops"]) for r in rows) / len(rows))
+            big = [r for r in rows if r["M"] > 16]
+            geo = math.exp(sum(math.log(r["tflops"]) for r in big) / len(big))
             print(json.dumps({
                 "metric": "qlinear_sweep_geomean_tflops", "value": geo, "unit": "TFLOP/s", "n_gpus": 1, "steps": 1,
                 "warmup": max(3, args.warmup), "higher_is_better": True, "dtype": "bf16", "data": "synthetic",

@@ -26,6 +26,7 @@
 
 #include "host_util.cuh"
 #include "ptx.cuh"
+#include "qmv.cuh"
 
 namespace mfx {
 namespace qmm {
@@ -685,6 +686,7 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
       return rc;
     prepared = a.workspace;
   }
+  if (qmv::eligible(a)) return qmv::run(a, prepared, codes_bytes_padded(a.N, a.K, a.bits), st);
   const void* codes = prepared;
   const void* sb_packed = static_cast<const uint8_t*>(prepared) + codes_bytes_padded(a.N, a.K, a.bits);
 

@@ -42,19 +42,25 @@ def test_step_matches_oracle(lib_built, bits):
 
 
 def test_batch_equals_independent_samples(lib_built):
-    """The reference runs one image per call; a batched call must equal the per-sample calls."""
+    """The reference runs one image per call; a batched call must equal the per-sample calls: bit for bit while
+    every linear takes the same kernel in both runs (more than 16 token rows per sample), within rounding noise
+    when a single sample's 16 rows go through the small-M kernel and the batch through the tcgen05 kernel."""
     from mflux_b200.flux import FluxConfig, Transformer
 
     cfg = FluxConfig(hidden=256, heads=2, num_joint=1, num_single=1, context_dim=128, pooled_dim=64)
     model = Transformer(cfg, bits=4, device="cuda", seed=2)
-    lat, ctx, pooled = _inputs(cfg, 3, 64, 64, 16, 5)
     ts = torch.tensor([100.0, 500.0, 900.0])
     gd = torch.full((3,), 3500.0)
-    full = model(lat.cuda(), ctx.cuda(), pooled.cuda(), ts.cuda(), gd.cuda(), 64, 64).clone()
-    for i in range(3):
-        one = model(lat[i:i + 1].cuda(), ctx[i:i + 1].cuda(), pooled[i:i + 1].cuda(), ts[i:i + 1].cuda(),
-                    gd[i:i + 1].cuda(), 64, 64)
-        assert torch.equal(one[0], full[i])
+    for size, txt, exact in ((128, 24, True), (64, 16, False)):
+        lat, ctx, pooled = _inputs(cfg, 3, size, size, txt, 5)
+        full = model(lat.cuda(), ctx.cuda(), pooled.cuda(), ts.cuda(), gd.cuda(), size, size).clone()
+        for i in range(3):
+            one = model(lat[i:i + 1].cuda(), ctx[i:i + 1].cuda(), pooled[i:i + 1].cuda(), ts[i:i + 1].cuda(),
+                        gd[i:i + 1].cuda(), size, size)
+            if exact:
+                assert torch.equal(one[0], full[i])
+            else:
+                assert rel_l2(one[0], full[i].float().cpu().numpy()) <= 3e-3
 
 
 def test_generate_image_loop_and_resolution_rules(lib_built):

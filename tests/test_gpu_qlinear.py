@@ -161,3 +161,42 @@ def test_rejects_bad_arguments(lib_built):
         ops.qlinear(x.cuda()[:, :64], wq, s, bi, None, bits=4)  # K mismatch
     with pytest.raises(RuntimeError):
         ops.qlinear(x, wq, s, bi, None, bits=4)  # CPU tensor
+
+
+# ---------------------------------------------------------------- at most 16 rows: the weight-streaming kernel
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("m", [1, 3, 16])
+@pytest.mark.parametrize("nk", [(3072, 3072), (18432, 3072), (15360, 256), (1032, 192), (3072, 12288)])
+def test_small_m_streaming_kernel(lib_built, bits, m, nk):
+    """AdaLN / embedder shapes: narrow and wide N, K = 256 (Z-Image modulation), K = 192 (ragged last 128-wide
+    slice of 4-bit rows), N = 1032 (a last block of 8 rows that is only partly used in the 32-row variant)."""
+    n, k = nk
+    w, x, b = _case(m, n, k, bits, hash((bits, n, k, m, 7)) % (2**31), torch.bfloat16)
+    _, _, _, ref = _oracle(w, x, b, bits, "bf16")
+    _, _, _, y = _run(w, x, b, bits)
+    assert y.shape == (m, n) and y.dtype == torch.bfloat16
+    err = quant.rel_l2(y, ref)
+    assert err <= TOL, err
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_small_m_matches_large_m_kernel_and_epilogues(lib_built, bits):
+    """The same 16 rows through the streaming kernel and (as part of 17 rows) through the tcgen05 kernel; SiLU
+    epilogue, float32 output, strided input rows and an output view."""
+    from mflux_b200 import ops
+
+    n, k = 6144, 3072
+    w, x17, b = _case(17, n, k, bits, 99 + bits, torch.bfloat16)
+    wq, s, bi = ops.quantize_affine(w.cuda(), 64, bits)
+    big = ops.qlinear(x17.cuda(), wq, s, bi, b.cuda(), bits=bits, epilogue="silu", out_dtype=torch.float32)
+    xs = torch.zeros(16, 2 * k, dtype=torch.bfloat16, device="cuda")
+    xs[:, :k] = x17[:16].cuda()
+    out = torch.full((16, n + 64), 7.0, dtype=torch.float32, device="cuda")
+    ops.qlinear(xs[:, :k], wq, s, bi, b.cuda(), bits=bits, epilogue="silu", out=out[:, :n])
+    torch.cuda.synchronize()
+    assert ops.poll_device_status() == 0
+    assert quant.rel_l2(out[:, :n], big[:16].cpu().numpy()) <= 2e-3
+    assert torch.all(out[:, n:] == 7.0)
+    ref = quant.qlinear(x17[:16], *quant.quantize_affine(w, 64, bits, dtype="bf16"), b, 64, bits)
+    ref = ref / (1 + np.exp(-ref))
+    assert quant.rel_l2(out[:, :n], ref) <= TOL
