@@ -30,6 +30,17 @@ def dense(layer):
 
 
 def lin(layer, x):
+    """Linear / QuantizedLinear, or a LoRA wrapper around one: LoRALinear.__call__
+    (src/mflux/models/common/lora/layer/linear_lora_layer.py:50-53) and FusedLoRALinear.__call__
+    (fused_linear_lora_layer.py:13-20)."""
+    if hasattr(layer, "loras"):
+        y = lin(layer.base_linear, x)
+        for lo in layer.loras:
+            y = y + lo.scale * (x.float() @ lo.lora_A.detach().float().cpu()) @ lo.lora_B.detach().float().cpu()
+        return y
+    if hasattr(layer, "lora_A"):
+        return lin(layer.linear, x) + layer.scale * (x.float() @ layer.lora_A.detach().float().cpu()) \
+            @ layer.lora_B.detach().float().cpu()
     w, b = dense(layer)
     y = x.float() @ w.T
     return y if b is None else y + b
