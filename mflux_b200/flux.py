@@ -350,6 +350,21 @@ class Flux1:
         self.model_config = model_config or FluxConfig()
         self.transformer = Transformer(self.model_config, bits=bits, device=device, seed=seed)
 
+    def save_model(self, base_path: str) -> None:
+        """ModelSaver.save_model for the component this class owns: `<base_path>/transformer/{i}.safetensors` plus
+        the index file, in the reference's format (the other components stay with the caller)."""
+        from . import checkpoint
+
+        checkpoint.save_weights(base_path, self.bits, self.transformer, "transformer")
+
+    def load_model(self, base_path: str) -> None:
+        """Loads `<base_path>/transformer` as saved by `save_model` or by the reference's ModelSaver."""
+        from . import checkpoint
+
+        checkpoint.load_into(self.transformer, base_path, "transformer", self.bits)
+        if hasattr(self.transformer, "_fused"):
+            self.transformer._fused = {}
+
     def generate_image(self, seed: int, prompt_embeds: torch.Tensor, pooled_prompt_embeds: torch.Tensor,
                        num_inference_steps: int = 4, height: int = 1024, width: int = 1024, guidance: float = 3.5,
                        latents: torch.Tensor | None = None) -> torch.Tensor:

@@ -276,6 +276,21 @@ class QwenImage:
         self.transformer = QwenTransformer(self.model_config, bits=bits, device=device, seed=seed, tp_rank=tp_rank,
                                            tp_world=tp_world, tp_group=tp_group)
 
+    def save_model(self, base_path: str) -> None:
+        """ModelSaver.save_model for the component this class owns: `<base_path>/transformer/{i}.safetensors` plus
+        the index file, in the reference's format (the other components stay with the caller)."""
+        from . import checkpoint
+
+        checkpoint.save_weights(base_path, self.bits, self.transformer, "transformer")
+
+    def load_model(self, base_path: str) -> None:
+        """Loads `<base_path>/transformer` as saved by `save_model` or by the reference's ModelSaver."""
+        from . import checkpoint
+
+        checkpoint.load_into(self.transformer, base_path, "transformer", self.bits)
+        if hasattr(self.transformer, "_fused"):
+            self.transformer._fused = {}
+
     def denoise_step(self, latents, prompt_embeds, negative_prompt_embeds, sigma, dt, guidance, height, width):
         b = latents.shape[0]
         both = self.transformer(torch.cat([latents, latents]), torch.cat([prompt_embeds, negative_prompt_embeds]),

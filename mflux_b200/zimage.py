@@ -346,6 +346,21 @@ class ZImage:
         self.model_config = model_config or ZImageConfig()
         self.transformer = ZImageTransformer(self.model_config, bits=bits, device=device, seed=seed)
 
+    def save_model(self, base_path: str) -> None:
+        """ModelSaver.save_model for the component this class owns: `<base_path>/transformer/{i}.safetensors` plus
+        the index file, in the reference's format (the other components stay with the caller)."""
+        from . import checkpoint
+
+        checkpoint.save_weights(base_path, self.bits, self.transformer, "transformer")
+
+    def load_model(self, base_path: str) -> None:
+        """Loads `<base_path>/transformer` as saved by `save_model` or by the reference's ModelSaver."""
+        from . import checkpoint
+
+        checkpoint.load_into(self.transformer, base_path, "transformer", self.bits)
+        if hasattr(self.transformer, "_fused"):
+            self.transformer._fused = {}
+
     def denoise_step(self, latents, cap_feats, negative_cap_feats, sigma, dt, guidance):
         b = latents.shape[0]
         t = torch.full((b,), 1.0 - sigma, device=latents.device)

@@ -76,3 +76,24 @@ def test_generate_image_loop_and_resolution_rules(lib_built):
     assert torch.equal(lat1, lat2)  # deterministic
     with pytest.raises(ValueError):
         Flux1(quantize=3, model_config=cfg)
+
+
+def test_save_and_reload_quantized_model(lib_built, tmp_path):
+    """The reference's save/reload identity (tests/model_saving/test_model_saving.py:50-54) on the transformer:
+    a model saved in the mflux format and loaded into a differently initialised one gives the same output."""
+    from mflux_b200.flux import Flux1, FluxConfig
+
+    cfg = FluxConfig(hidden=256, heads=2, num_joint=1, num_single=1, context_dim=128, pooled_dim=64)
+    a = Flux1(quantize=4, model_config=cfg, seed=1)
+    b = Flux1(quantize=4, model_config=cfg, seed=2)
+    lat, ctx, pooled = _inputs(cfg, 2, 64, 64, 24, 3)
+    args = (lat.cuda(), ctx.cuda(), pooled.cuda(), torch.tensor([300.0, 600.0]).cuda(), torch.full((2,), 3500.0).cuda(),
+            64, 64)
+    ya = a.transformer(*args).clone()
+    assert not torch.equal(ya, b.transformer(*args))
+    a.save_model(str(tmp_path))
+    assert (tmp_path / "transformer" / "0.safetensors").exists()
+    b.load_model(str(tmp_path))
+    assert torch.equal(ya, b.transformer(*args))
+    with pytest.raises(ValueError):
+        Flux1(quantize=8, model_config=cfg).load_model(str(tmp_path))

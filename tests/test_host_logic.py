@@ -92,3 +92,60 @@ def test_zimage_token_layout_matches_oracle():
     out = model.unpatchify(torch.cat([tokens, tokens[:, -1:]], dim=1), (1, 18, 14))
     assert torch.equal(out, lat)
     assert torch.equal(oz.unpatchify(img, size, 16), lat[1])
+
+
+def test_checkpoint_format_round_trip(tmp_path):
+    """Shard naming, metadata, index file and key layout of the reference's saved-model format; packed uint32
+    weights survive bit for bit (host logic, no GPU)."""
+    import json
+
+    import torch
+    from safetensors import safe_open
+
+    from mflux_b200 import checkpoint, nn
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.to_q = nn.QuantizedLinear(128, 64, bias=True, bits=4)
+            self.to_out = torch.nn.ModuleList([nn.QuantizedLinear(128, 64, bias=False, bits=4)])
+
+    class Tiny(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.bits = 4
+            self.transformer_blocks = torch.nn.ModuleList([Block(), Block()])
+            self.norm = torch.nn.Parameter(torch.ones(8, dtype=torch.bfloat16), requires_grad=False)
+
+    g = torch.Generator().manual_seed(1)
+    src = Tiny()
+    for p in src.parameters():
+        if p.dtype == torch.uint32:
+            p.data = torch.randint(0, 2**31 - 1, p.shape, generator=g, dtype=torch.int64).to(torch.uint32)
+        else:
+            p.data = torch.randn(p.shape, generator=g).to(p.dtype)
+    names = checkpoint.save_weights(tmp_path, 4, src, max_file_size_bytes=6000)
+    assert names == [f"{i}.safetensors" for i in range(len(names))] and len(names) > 1
+    index = json.loads((tmp_path / "transformer" / "model.safetensors.index.json").read_text())
+    assert index["metadata"]["quantization_level"] == "4"
+    assert index["weight_map"]["transformer_blocks.1.to_out.0.scales"] in names
+    assert set(index["weight_map"]) == set(dict(src.named_parameters()))
+    with safe_open(str(tmp_path / "transformer" / "0.safetensors"), framework="pt") as f:
+        assert f.metadata()["quantization_level"] == "4" and "mflux_version" in f.metadata()
+        k = "transformer_blocks.0.to_q.weight"
+        assert f.get_tensor(k).dtype == torch.uint32 and tuple(f.get_tensor(k).shape) == (64, 16)
+    dst = Tiny()
+    assert checkpoint.load_into(dst, tmp_path, requested_bits=8) == 4      # the stored level wins
+    for (k, a), (_, b) in zip(src.named_parameters(), dst.named_parameters()):
+        assert torch.equal(a.view(torch.uint8) if a.dtype == torch.uint32 else a,
+                           b.view(torch.uint8) if b.dtype == torch.uint32 else b), k
+    # a directory of plain safetensors without the metadata is not this format
+    other = tmp_path / "plain"
+    other.mkdir()
+    from safetensors.torch import save_file
+    save_file({"x": torch.zeros(2)}, str(other / "0.safetensors"))
+    assert checkpoint.load_weights(other) == (None, None, None)
+    dst.bits = 8
+    import pytest
+    with pytest.raises(ValueError):
+        checkpoint.load_into(dst, tmp_path)
