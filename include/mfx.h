@@ -205,10 +205,12 @@ int mfx_vec_sum_act(const void* a, const void* b, const void* c, int in_dtype, i
 /* out = residual + gate[sample] * (y + bias): the gated residual of joint_transformer_block.py:84-90 /
  * qwen_transformer_block.py:56-57,64,69 as a stand-alone kernel, for tensor-parallel row-split linears whose
  * partial sums are all-reduced before the gate can be applied (no counterpart in the single-device reference).
- * y is [batch, rows, D] bf16 or f32 (dense), residual/out f32 (may alias), gate [batch, D], bias [D] nullable. */
+ * y is [batch, rows, D] bf16 or f32 (dense), gate [batch, D], bias [D] nullable; residual and out are f32
+ * [batch, rows, D] views that share their row and batch strides in elements (they may be the same view, or a row
+ * range of the residual stream when the linear is evaluated in chunks). */
 int mfx_gate_residual(const void* y, int y_dtype, const void* bias, int bias_dtype, const void* gate, int gate_dtype,
-                      int64_t gate_batch_stride, const float* residual, float* out, int64_t batch, int64_t rows,
-                      int64_t D, void* stream);
+                      int64_t gate_batch_stride, const float* residual, float* out, int64_t res_row_stride,
+                      int64_t res_batch_stride, int64_t batch, int64_t rows, int64_t D, void* stream);
 
 /* residual += gate[sample] * RMSNorm(y) * weight, in place on the float32 residual stream: the post-norms
  * attention_norm2 / ffn_norm2 of src/mflux/models/z_image/model/z_image_transformer/transformer_block.py:31,35

@@ -130,7 +130,7 @@ SIGNATURES = {
     "mfx_gate_residual": (
         c_int,
         [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int64,
-         c_void_p],
+         c_int64, c_int64, c_void_p],
     ),
     "mfx_norm_gate_residual": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_int,
                                        ctypes.c_float, c_void_p, c_int, c_int64, c_void_p, c_int64, c_int64,

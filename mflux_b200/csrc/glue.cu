@@ -336,18 +336,20 @@ __global__ void __launch_bounds__(256) gate_residual_kernel(const void* __restri
                                                             const void* __restrict__ bias, int bias_dtype,
                                                             const void* __restrict__ gate, int gate_dtype,
                                                             int64_t gate_batch_stride, const float* residual,
-                                                            float* out, int64_t rows_per_batch, int64_t D,
-                                                            int64_t n_vec) {
+                                                            float* out, int64_t res_row_stride,
+                                                            int64_t res_batch_stride, int64_t rows_per_batch,
+                                                            int64_t D, int64_t n_vec) {
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;  // one 8-element vector
   if (i >= n_vec) return;
   const int64_t vec_per_row = D >> 3;
   const int64_t row = i / vec_per_row;
   const int col = static_cast<int>(i % vec_per_row) * 8;
   const int64_t b = row / rows_per_batch;
+  const int64_t roff = b * res_batch_stride + (row - b * rows_per_batch) * res_row_stride + col;
   float yv[8], rv[8];
   if (y_dtype == MFX_F32) load8<float>(static_cast<const float*>(y) + i * 8, yv);
   else load8<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(y) + i * 8, yv);
-  load8<float>(residual + i * 8, rv);
+  load8<float>(residual + roff, rv);
   float o[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
@@ -355,8 +357,8 @@ __global__ void __launch_bounds__(256) gate_residual_kernel(const void* __restri
     const float gv = ld_scalar(gate, gate_dtype, b * gate_batch_stride + col + j);
     o[j] = rv[j] + gv * (yv[j] + bv);
   }
-  *reinterpret_cast<float4*>(out + i * 8) = make_float4(o[0], o[1], o[2], o[3]);
-  *reinterpret_cast<float4*>(out + i * 8 + 4) = make_float4(o[4], o[5], o[6], o[7]);
+  *reinterpret_cast<float4*>(out + roff) = make_float4(o[0], o[1], o[2], o[3]);
+  *reinterpret_cast<float4*>(out + roff + 4) = make_float4(o[4], o[5], o[6], o[7]);
 }
 
 // Classifier-free-guidance combine of two noise predictions, one warp per token row of C <= 1024 channels.
@@ -500,18 +502,21 @@ int mfx_euler_step(const void* latents, int lat_dtype, const void* noise, int no
 }
 
 int mfx_gate_residual(const void* y, int y_dtype, const void* bias, int bias_dtype, const void* gate, int gate_dtype,
-                      int64_t gate_batch_stride, const float* residual, float* out, int64_t batch, int64_t rows,
-                      int64_t D, void* stream) {
+                      int64_t gate_batch_stride, const float* residual, float* out, int64_t res_row_stride,
+                      int64_t res_batch_stride, int64_t batch, int64_t rows, int64_t D, void* stream) {
   using namespace mfx;
   if (!y || !gate || !residual || !out) return MFX_ERR_NULL;
   if (batch <= 0 || rows <= 0 || D <= 0 || D % 8 != 0) return MFX_ERR_SHAPE;
   if ((y_dtype != MFX_F32 && y_dtype != MFX_BF16) || !valid_dtype(gate_dtype) || (bias && !valid_dtype(bias_dtype)))
     return MFX_ERR_DTYPE;
-  if (!aligned16(y) || !aligned16(residual) || !aligned16(out)) return MFX_ERR_ALIGN;
+  if (!aligned16(y) || !aligned16(residual) || !aligned16(out) || res_row_stride % 4 != 0 || res_batch_stride % 4 != 0)
+    return MFX_ERR_ALIGN;
+  if (res_row_stride < D) return MFX_ERR_SHAPE;
   if (int rc = check_arch()) return rc;
   const int64_t n_vec = batch * rows * D / 8;
   glue::gate_residual_kernel<<<static_cast<unsigned>((n_vec + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      y, y_dtype, bias, bias_dtype, gate, gate_dtype, gate_batch_stride, residual, out, rows, D, n_vec);
+      y, y_dtype, bias, bias_dtype, gate, gate_dtype, gate_batch_stride, residual, out, res_row_stride, res_batch_stride, rows,
+      D, n_vec);
   MFX_CUDA_TRY(cudaGetLastError());
   return MFX_OK;
 }

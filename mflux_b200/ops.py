@@ -381,20 +381,25 @@ def gate_residual(y: torch.Tensor, gate: torch.Tensor, residual: torch.Tensor, b
                   out: torch.Tensor | None = None) -> torch.Tensor:
     """residual + gate[sample] * (y + bias) in float32 (in place on `residual` when out is None).
 
-    y [batch, rows, D] bf16/f32 dense, residual f32 dense, gate [batch, D] (any batch stride), bias [D].
+    y [batch, rows, D] bf16/f32 dense; residual (and out) float32 [batch, rows, D] views with a dense last dim,
+    e.g. a row range of the residual stream; gate [batch, D] (any batch stride), bias [D].
     """
     lib = _lib.load()
     _cuda(y, "y")
-    if y.dim() != 3 or not y.is_contiguous() or not residual.is_contiguous() or residual.dtype != torch.float32:
-        raise ValueError("y must be dense [batch, rows, D]; residual must be dense float32 of the same shape")
-    if residual.shape != y.shape:
-        raise ValueError("residual must have y's shape")
+    if y.dim() != 3 or not y.is_contiguous():
+        raise ValueError("y must be dense [batch, rows, D]")
     out = residual if out is None else out
     b, r, d = y.shape
+    for t, name in ((residual, "residual"), (out, "out")):
+        if t.dtype != torch.float32 or tuple(t.shape) != (b, r, d) or t.stride(2) != 1:
+            raise ValueError(f"{name} must be a float32 [batch, rows, D] view with a dense last dim")
+    if (out.stride(0), out.stride(1)) != (residual.stride(0), residual.stride(1)):
+        raise ValueError("residual and out must share their strides")
     gate = gate.reshape(b, d) if gate.stride(-1) == 1 else gate.reshape(b, d).contiguous()
     bias_c = None if bias is None else bias.contiguous()
     rc = lib.mfx_gate_residual(_ptr(y), _dt(y), _ptr(bias_c), 0 if bias_c is None else _dt(bias_c), _ptr(gate),
-                               _dt(gate), gate.stride(0), _ptr(residual), _ptr(out), b, r, d, _stream())
+                               _dt(gate), gate.stride(0), _ptr(residual), _ptr(out), residual.stride(1),
+                               residual.stride(0) if b > 1 else r * residual.stride(1), b, r, d, _stream())
     _lib.check(rc, "mfx_gate_residual")
     LAUNCHES[0] += 1
     return out

@@ -7,8 +7,9 @@ As in flux.py, text and image tokens share one sequence buffer (text first, qwen
 as one matmul and gate*y+residual / GELU are matmul epilogues.
 
 Tensor parallelism (no counterpart in the single-device reference): to_q/k/v, add_*_proj and mlp_in are split by
-output rows (whole heads per rank), attn_to_out / to_add_out / mlp_out by input columns; the partial sums are
-all-reduced with NCCL and the gated residual is applied afterwards. Every rank quantizes its own shard; because
+output rows (whole heads per rank), attn_to_out / to_add_out / mlp_out by input columns; their partial sums are
+all-reduced with NCCL in row chunks, each chunk's all-reduce running beside the next chunk's matmul, and the gated
+residual is applied chunk by chunk afterwards. Every rank quantizes its own shard; because
 quantization groups run along the input dimension and K / tp stays a multiple of 64, the shards' packed codes,
 scales and biases are slices of what quantizing the full weight would give. LayerNorm, modulation and the residual
 stream are replicated.
@@ -125,6 +126,7 @@ class QwenTransformer(nn.Module):
         self.norm_out = AdaNorm(ctx, d, 2, bias=False)
         self.proj_out = ctx.linear(d, cfg.in_channels)
         self._fused, self._rope, self._buffers_for = {}, {}, None
+        self._partials, self.tp_chunks, self.tp_chunk_min_rows = {}, 4, 512
 
     # ------------------------------------------------------------------ helpers
     def _fuse(self, key, layers):
@@ -185,24 +187,43 @@ class QwenTransformer(nn.Module):
         emb = 1000.0 * (timestep.to(torch.bfloat16).float()[:, None] * freqs[None, :])
         return torch.cat([torch.cos(emb), torch.sin(emb)], dim=-1)
 
-    def _all_reduce(self, t):
-        if self.tp_world > 1:
-            dist.all_reduce(t, group=self.tp_group)
-        return t
-
     def _row_parallel(self, layer, x, gate, residual):
-        """residual += gate * (x . W^T + bias) for a layer split by input columns."""
+        """residual += gate * (x . W^T + bias) for a layer split by input columns.
+
+        With several ranks the rows go in chunks: the matmul of a chunk is followed by an asynchronous all-reduce of
+        its partial sums, which NCCL runs beside the next chunk's matmul; the gated residual is applied chunk by
+        chunk once the sums have arrived."""
         if self.tp_world == 1:
             return _call(layer, x, epilogue="gate_residual", gate=gate, residual=residual, out=residual)
-        part = self.part_img if residual is self.x_img else self.part_txt
+        b, rows, _ = x.shape
+        d = residual.shape[-1]
+        n_chunks = self.tp_chunks if rows >= self.tp_chunk_min_rows * self.tp_chunks else 1
+        bounds = [rows * c // n_chunks for c in range(n_chunks + 1)]
         bias = layer.bias
-        if isinstance(layer, nn.QuantizedLinear):
-            ops.qlinear(x, layer.weight.data, layer.scales.data, layer.biases.data, None, bits=layer.bits, out=part,
-                        prepared=layer.prepared())
-        else:
-            part.copy_(torch.nn.functional.linear(x, layer.weight))
-        self._all_reduce(part)
-        return ops.gate_residual(part, gate, residual, None if bias is None else bias.data)
+        pending = []
+        for c in range(n_chunks):
+            r0, r1 = bounds[c], bounds[c + 1]
+            part = self._partial(rows, c, b, r1 - r0, d, x.device)
+            if isinstance(layer, nn.QuantizedLinear):
+                ops.qlinear(x[:, r0:r1], layer.weight.data, layer.scales.data, layer.biases.data, None, bits=layer.bits,
+                            out=part, prepared=layer.prepared())
+            else:
+                part.copy_(torch.nn.functional.linear(x[:, r0:r1], layer.weight))
+            work = dist.all_reduce(part, group=self.tp_group, async_op=True)
+            pending.append((work, part, r0, r1))
+        for work, part, r0, r1 in pending:
+            work.wait()
+            ops.gate_residual(part, gate, residual[:, r0:r1], None if bias is None else bias.data)
+        return residual
+
+    def _partial(self, rows, chunk, b, n, d, device):
+        """Dense bf16 buffers for the partial sums (NCCL wants contiguous operands), one per (stream length, chunk)."""
+        key = (rows, chunk, b, n, d, str(device))
+        t = self._partials.get(key)
+        if t is None:
+            t = torch.empty(b, n, d, dtype=torch.bfloat16, device=device)
+            self._partials[key] = t
+        return t
 
     # ------------------------------------------------------------------ forward
     def forward(self, hidden_states: torch.Tensor, encoder_hidden_states: torch.Tensor, timestep: torch.Tensor,
@@ -219,9 +240,6 @@ class QwenTransformer(nn.Module):
         if getattr(self, "_streams_for", None) != (b, si, st, str(dev)):
             self.x_img = torch.empty(b, si, d, dtype=torch.float32, device=dev)   # residual streams
             self.x_txt = torch.empty(b, st, d, dtype=torch.float32, device=dev)
-            if self.tp_world > 1:  # partial sums of the row-split linears, all-reduced in place
-                self.part_img = torch.empty(b, si, d, dtype=torch.bfloat16, device=dev)
-                self.part_txt = torch.empty(b, st, d, dtype=torch.bfloat16, device=dev)
             self._streams_for = (b, si, st, str(dev))
         x_img, x_txt = self.x_img, self.x_txt
         n_img, n_txt = nbuf[:, st:], nbuf[:, :st]

@@ -126,3 +126,24 @@ def test_vec_ops_and_euler(lib_built):
     noise = torch.randn(2, 4096, 64, generator=g).to(torch.bfloat16)
     out = ops.euler_step(lat.cuda(), noise.cuda(), -0.03125)
     torch.testing.assert_close(out.cpu(), lat + noise.float() * -0.03125, rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("y_dtype", [torch.bfloat16, torch.float32])
+def test_gate_residual_dense_and_row_range(lib_built, y_dtype):
+    """out = residual + gate * (y + bias) on the whole stream and on a row range of it (a chunk of a linear
+    evaluated in pieces), in place."""
+    from mflux_b200 import ops
+
+    g = torch.Generator(device="cuda").manual_seed(21)
+    b, s, d = 3, 50, 256
+    stream = torch.randn(b, s, d, device="cuda", generator=g)
+    gate = torch.randn(b, 3 * d, device="cuda", generator=g).to(torch.bfloat16)[:, d:2 * d]   # strided gate rows
+    bias = torch.randn(d, device="cuda", generator=g).to(torch.bfloat16)
+    for lo, hi in ((0, s), (7, 31)):
+        y = torch.randn(b, hi - lo, d, device="cuda", generator=g).to(y_dtype)
+        before = stream.clone()
+        ops.gate_residual(y, gate, stream[:, lo:hi], bias)
+        torch.cuda.synchronize()
+        ref = before[:, lo:hi] + gate.float()[:, None] * (y.float() + bias.float())
+        torch.testing.assert_close(stream[:, lo:hi], ref, rtol=1e-6, atol=1e-6)
+        assert torch.equal(stream[:, :lo], before[:, :lo]) and torch.equal(stream[:, hi:], before[:, hi:])

@@ -24,6 +24,7 @@ def main():
     ctx = torch.randn(2, 40, 128, generator=g).to(torch.bfloat16).cuda()
     sigma = torch.tensor([0.9, 0.3]).cuda()
     tp = QwenTransformer(cfg, bits=4, device="cuda", seed=5, tp_rank=rank, tp_world=world)
+    tp.tp_chunks, tp.tp_chunk_min_rows = 3, 8   # 54 image rows in 3 chunks, 40 text rows in 3: the overlapped path
     y_tp = tp(lat, ctx, sigma, 96, 144).float()
     torch.cuda.synchronize()
     if rank == 0:
