@@ -79,7 +79,8 @@ def test_qknorm_rope(lib_built):
     assert torch.equal(out[..., 2 * hd:].cpu(), qkv[..., 2 * hd:])  # V untouched
 
 
-@pytest.mark.parametrize("shape", [(1, 128, 1), (2, 256, 2), (1, 384, 3), (2, 200, 2), (1, 1000, 1)])
+@pytest.mark.parametrize("shape", [(1, 128, 1), (2, 256, 2), (1, 384, 3), (2, 200, 2), (1, 1000, 1), (1, 17, 1), (2, 97, 2),
+                                   (1, 161, 1)])
 def test_fmha(lib_built, shape):
     from mflux_b200 import ops
 

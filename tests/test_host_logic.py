@@ -149,3 +149,36 @@ def test_checkpoint_format_round_trip(tmp_path):
     import pytest
     with pytest.raises(ValueError):
         checkpoint.load_into(dst, tmp_path)
+
+
+def test_flow_match_euler_discrete_scheduler():
+    """Default schedule: starts at 1, ends at the terminal 0.02 before the appended 0, strictly decreasing;
+    empirical mu follows the two published lines; set_mu equals the linear scheduler's shift for the same mu."""
+    import math
+
+    import numpy as np
+
+    from mflux_b200.schedulers import FlowMatchEulerDiscreteScheduler as FM, LinearScheduler
+
+    s = FM(20)
+    assert s.sigmas.shape == (21,) and s.timesteps.shape == (20,)
+    assert abs(s.sigmas[0] - 1.0) < 1e-6 and abs(s.sigmas[19] - 0.02) < 1e-6 and s.sigmas[20] == 0.0
+    assert np.all(np.diff(s.sigmas) < 0)
+    # second sigma by hand: t = 1000 - 999/19, sigma = t/1000 shifted with mu = 1, then stretched
+    sig1 = (1000 - 999 / 19) / 1000
+    shifted = math.e / (math.e + (1 / sig1 - 1))
+    last = math.e / (math.e + (1 / 0.001 - 1))
+    expect = 1 - (1 - shifted) / ((1 - last) / 0.98)
+    assert abs(s.sigmas[1] - expect) < 1e-6
+    assert abs(FM.compute_empirical_mu(5000, 20) - (0.00016927 * 5000 + 0.45666666)) < 1e-9
+    m200, m10 = 0.00016927 * 4096 + 0.45666666, 8.73809524e-05 * 4096 + 1.89833333
+    a = (m200 - m10) / 190
+    assert abs(FM.compute_empirical_mu(4096, 20) - (a * 20 + m200 - 200 * a)) < 1e-9
+    assert abs(FM.compute_linear_mu(4096) - 1.15) < 1e-12 and abs(FM.compute_linear_mu(256) - 0.5) < 1e-12
+    s.set_mu(1.15)
+    lin = LinearScheduler(20, 1024, 1024, True)   # 4096 image tokens -> mu = 1.15
+    np.testing.assert_allclose(s.sigmas, lin.sigmas, rtol=1e-6)
+    np.testing.assert_allclose(s.timesteps, lin.sigmas[:-1] * 1000, rtol=1e-6)
+    import torch
+    lat, noise = torch.ones(4), torch.full((4,), 2.0)
+    assert torch.allclose(s.step(noise, 3, lat), lat + 2.0 * float(s.sigmas[4] - s.sigmas[3]))
