@@ -28,19 +28,24 @@ namespace mfx {
 namespace fmha {
 
 constexpr int BQ = 128;
-constexpr int BKV = 64;
+constexpr int PARTS = 2;                     // softmax warps per 32-row quarter, each owning 32 key columns.
+                                             // 4 (128-key tiles, all 512 TMEM columns, one CTA per SM) also works
+                                             // and measured 8 % slower: nothing hides a CTA's prologue and epilogue
+constexpr int BKV = 32 * PARTS;              // keys per tile
 constexpr int HD = 128;
-constexpr int NUM_THREADS = 352;
-constexpr int V_PRODUCER_WARP = 10;
-constexpr int NUM_SOFTMAX_WARPS = 8;
+constexpr int NUM_SOFTMAX_WARPS = 4 * PARTS;
+constexpr int V_PRODUCER_WARP = 2 + NUM_SOFTMAX_WARPS;
+constexpr int NUM_THREADS = (V_PRODUCER_WARP + 1) * 32;
+constexpr int CTAS_PER_SM = PARTS == 2 ? 2 : 1;
+constexpr int OC = HD / PARTS;               // columns of O a softmax warp rescales and writes out
 constexpr int Q_BYTES = BQ * HD * 2;        // 32 KiB: [128 rows][128 d] bf16 as two 16 KiB halves of d
 constexpr int Q_HALF = Q_BYTES / 2;
-constexpr int KV_BYTES = BKV * HD * 2;      // 16 KiB: [64 keys][128 d] as two 8 KiB halves of d
+constexpr int KV_BYTES = BKV * HD * 2;      // [BKV keys][128 d] as two halves of d (16 KiB for 64 keys)
 constexpr int KV_HALF = KV_BYTES / 2;
-constexpr uint32_t TMEM_COLS = 256;
-constexpr uint32_t COL_S = 0;    // two S buffers of 64 fp32 columns; P (bf16 pairs) of a warp's 32 keys goes over
+constexpr uint32_t TMEM_COLS = 2 * BKV + HD <= 256 ? 256 : 512;
+constexpr uint32_t COL_S = 0;    // two S buffers of BKV fp32 columns; P (bf16 pairs) of a warp's 32 keys goes over
                                  // the first 16 of the 32 S columns that warp owns
-constexpr uint32_t COL_O = 128;  // O fp32 [128,256)
+constexpr uint32_t COL_O = 2 * BKV;  // O fp32, 128 columns after the two S buffers
 
 constexpr int OFF_Q = 0;
 constexpr int OFF_K = OFF_Q + Q_BYTES;          // 2 stages
@@ -49,7 +54,8 @@ constexpr int OFF_BAR = OFF_V + 2 * KV_BYTES;
 constexpr int NUM_BARS = 14;
 constexpr int OFF_TMEM = OFF_BAR + NUM_BARS * 8;
 constexpr int OFF_XCH = OFF_TMEM + 16;                // float [2 parities][4 quarters][2 halves][32 rows]
-constexpr int XCH_BYTES = 2 * 4 * 2 * 32 * 4;
+constexpr int XCH_FLOATS = 4 * PARTS * 32;        // one value per softmax thread
+constexpr int XCH_BYTES = 2 * XCH_FLOATS * 4;     // two buffers by tile parity
 constexpr int DYN_BYTES = OFF_XCH + XCH_BYTES + 1024;
 
 struct Params {
@@ -160,7 +166,7 @@ __device__ __forceinline__ void exp_chunk(const uint32_t (&s)[32], uint64_t scal
   }
 }
 
-__global__ void __launch_bounds__(NUM_THREADS, 2)
+__global__ void __launch_bounds__(NUM_THREADS, CTAS_PER_SM)
 fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
             const __grid_constant__ CUtensorMap tmap_v, const Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -251,7 +257,7 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
         for (int i = 0; i < HD / 16; ++i) {
           // half of d, then 32 B per 16 d inside the 128-byte rows
           const uint32_t qoff = (i >> 2) * Q_HALF + (i & 3) * 32, koff = (i >> 2) * KV_HALF + (i & 3) * 32;
-          umma_f16_ss(tmem_base + COL_S + 64 * st, smem_desc_sw128(q_s + qoff),
+          umma_f16_ss(tmem_base + COL_S + BKV * st, smem_desc_sw128(q_s + qoff),
                       smem_desc_sw128(k_s + st * KV_BYTES + koff), IDESC_S, i != 0 ? 1u : 0u);
         }
         umma_commit(s_full + 8 * st);
@@ -273,7 +279,7 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
         for (int i = 0; i < BKV / 16; ++i) {
           // A: 16 keys of P = 8 TMEM columns (keys 0-31 at columns 0-15 of the buffer, keys 32-63 at 32-47);
           // B: 16 key rows of V = 2048 B further, d halves 8 KiB apart
-          umma_f16_ts(tmem_base + COL_O, tmem_base + COL_S + 64 * st + (i >> 1) * 32 + 8 * (i & 1),
+          umma_f16_ts(tmem_base + COL_O, tmem_base + COL_S + BKV * st + (i >> 1) * 32 + 8 * (i & 1),
                       smem_desc_sw128_mn(v_s + st * KV_BYTES + i * 2048, KV_HALF), IDESC_O, (j | i) != 0 ? 1u : 0u);
         }
         umma_commit(v_empty + 8 * st);
@@ -284,12 +290,12 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
   } else {
     // ------------------------------------------------------------ softmax + output (thread = query row)
     const int qd = warp & 3;          // TMEM lane quarter this warp may access
-    const int hf = (warp - 2) >> 2;   // which 32 of the tile's 64 key columns (and 64 of the 128 d columns at the end)
+    const int pt = (warp - 2) >> 2;   // which 32 of the tile's key columns (and which OC columns of d at the end)
     const int row = qd * 32 + lane;
     const uint32_t t_row = tmem_base + (static_cast<uint32_t>(qd * 32) << 16);
-    const uint32_t t_o = t_row + COL_O + hf * 64;   // own O columns
+    const uint32_t t_o = t_row + COL_O + pt * OC;   // own O columns
     float* xch = reinterpret_cast<float*>(smem_gen + OFF_XCH);
-    const int xch_mine = (qd * 2 + hf) * 32 + lane, xch_other = (qd * 2 + (hf ^ 1)) * 32 + lane;
+    const int xch_row = qd * PARTS * 32 + lane;   // + 32 * part
     float m_ref = -INFINITY, l_sum = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
@@ -300,8 +306,8 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
         break;
       }
       tc_fence_after();
-      const uint32_t t_s = t_row + COL_S + 64 * st + 32 * hf;   // own S columns; own P goes over the first 16
-      const int keys_here = min(BKV, p.seq - j * BKV) - hf * 32;  // valid keys among this warp's 32 columns
+      const uint32_t t_s = t_row + COL_S + BKV * st + 32 * pt;   // own S columns; own P goes over the first 16
+      const int keys_here = min(BKV, p.seq - j * BKV) - pt * 32;  // valid keys among this warp's 32 columns
       const bool tail = keys_here < 32;  // only the last tile of a ragged sequence needs key masking
       uint32_t sA[32];
       tmem_ld_32x32(t_s, sA);
@@ -317,9 +323,12 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       }
       // the partner warp holds the other 32 columns of the same rows: swap maxima (two buffers by tile parity;
       // the barrier per tile keeps the two warps at most one tile apart)
-      xch[st * 256 + xch_mine] = m_mine;
-      named_bar_sync(1 + qd, 64);
-      const float m_tile = fmaxf(m_mine, xch[st * 256 + xch_other]) * p.scale_log2;
+      xch[st * XCH_FLOATS + xch_row + 32 * pt] = m_mine;
+      named_bar_sync(1 + qd, 32 * PARTS);
+      float m_all = m_mine;
+#pragma unroll
+      for (int o = 0; o < PARTS; ++o) m_all = fmaxf(m_all, xch[st * XCH_FLOATS + xch_row + 32 * o]);
+      const float m_tile = m_all * p.scale_log2;
       // grow the reference maximum only when it would change the exponent range by more than 2^8; both warps
       // of a quarter see the same maxima and take the same branch, each rescaling its own half of O
       const bool grow = m_tile > m_ref + 8.0f;
@@ -335,7 +344,7 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
           }
           tc_fence_after();
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < OC / 16; ++c) {
             uint32_t o[16];
             tmem_ld_32x16(t_o + c * 16, o);
             tmem_ld_wait();
@@ -380,14 +389,17 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       tc_fence_after();
       // total row sum = this warp's part + the partner's
       const int ph = n_tiles & 1;
-      xch[ph * 256 + xch_mine] = l_sum;
-      named_bar_sync(1 + qd, 64);
-      const float inv = 1.0f / (l_sum + xch[ph * 256 + xch_other]);
+      xch[ph * XCH_FLOATS + xch_row + 32 * pt] = l_sum;
+      named_bar_sync(1 + qd, 32 * PARTS);
+      float l_all = 0.f;
+#pragma unroll
+      for (int o = 0; o < PARTS; ++o) l_all += xch[ph * XCH_FLOATS + xch_row + 32 * o];
+      const float inv = 1.0f / l_all;
       const int q = q0 + row;
       __nv_bfloat16* dst = p.out + b * p.out_batch_stride + static_cast<int64_t>(q) * p.out_row_stride + h * HD +
-                           hf * 64;
+                           pt * OC;
 #pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < OC / 32; ++c) {
         uint32_t o[32];
         tmem_ld_32x32(t_o + c * 32, o);
         tmem_ld_wait();
