@@ -15,8 +15,9 @@
 //   warp 1      allocates TMEM; in the leader CTA issues tcgen05.mma.cta_group::2 (M=256, N=256, K=16)
 //   warps 4-7   epilogue: tcgen05.ld -> bias / activation / gated residual -> global, overlapped with the
 //               main loop of the next tile (two 256-column TMEM accumulators)
-//   warps 8+    dequantizers (8 warps for 4-bit, 16 for 8-bit codes): codes (smem) -> bf16 by exponent-magic
-//               + one fma with the group's scale and bias -> B operand tile in the swizzled K-major layout
+//   warps 8-15  dequantizers: codes (smem) -> bf16 -> B operand tile in the swizzled K-major layout. 4-bit codes
+//               by the bf16 exponent-magic (128 + code) and one bf16 fma with the group's scale and bias; 8-bit
+//               codes by the float32 magic (2^23 + code) and packed f32x2 add + fma, rounded to bf16 at the end
 // Barriers that both CTAs feed live in the leader; MMA completion is multicast to both CTAs. All mbarrier
 // waits are bounded.
 #include <cuda_bf16.h>
@@ -120,27 +121,27 @@ __device__ __forceinline__ uint4 dequant_w4(uint32_t q, uint32_t s2, uint32_t b2
   return r;
 }
 
-// Two eight-bit codes -> two bf16 values. A code (0..255) is rebuilt exactly as 16*hi + lo from its
-// nibbles (each through the exponent-magic), then one fma with scale and bias.
-// (tcgen05.mma kind::f16 wants A and B in the same 16-bit format, so f16 is not an option for B.)
-__device__ __forceinline__ uint32_t w8_pair(uint32_t lo, uint32_t hi, uint32_t s2, uint32_t b2) {
-  constexpr uint32_t MAGIC = 0x43004300u;    // (128.0, 128.0)
-  constexpr uint32_t SIXTEEN = 0x41804180u;  // (16.0, 16.0)
-  uint32_t d;
-  asm("{\n\t.reg .b32 l, h, q;\n\t"
-      "sub.rn.bf16x2 l, %1, %3;\n\t"
-      "sub.rn.bf16x2 h, %2, %3;\n\t"
-      "fma.rn.bf16x2 q, h, %4, l;\n\t"
-      "fma.rn.bf16x2 %0, q, %5, %6;\n\t}"
-      : "=r"(d)
-      : "r"(lo | MAGIC), "r"(hi | MAGIC), "r"(MAGIC), "r"(SIXTEEN), "r"(s2), "r"(b2));
-  return d;
-}
-// 4 eight-bit codes of one prepared uint32 (byte order e0,e2,e1,e3) -> 4 values in K order.
-__device__ __forceinline__ uint2 dequant_w8(uint32_t q, uint32_t s2, uint32_t b2) {
+// 4 eight-bit codes of one prepared uint32 (byte order e0,e2,e1,e3) -> 4 values in K order, through float32:
+// a byte placed under the exponent of 2^23 is the float 2^23 + code exactly; subtracting 2^23 and one fma with
+// the group's scale and bias (packed f32x2 instructions) give the value, rounded once more when packed to bf16.
+// sc2 / bi2 are (scale, scale) / (bias, bias) as float32 pairs.
+__device__ __forceinline__ uint2 dequant_w8_f32(uint32_t q, uint64_t sc2, uint64_t bi2) {
+  constexpr uint32_t TWO23 = 0x4B000000u;
+  const uint64_t neg = 0xCB000000CB000000ull;  // (-2^23, -2^23)
+  uint64_t v01, v23;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v01) : "r"(__byte_perm(q, TWO23, 0x7440)), "r"(__byte_perm(q, TWO23, 0x7442)));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v23) : "r"(__byte_perm(q, TWO23, 0x7441)), "r"(__byte_perm(q, TWO23, 0x7443)));
+  asm("add.rn.f32x2 %0, %0, %1;" : "+l"(v01) : "l"(neg));
+  asm("add.rn.f32x2 %0, %0, %1;" : "+l"(v23) : "l"(neg));
+  asm("fma.rn.f32x2 %0, %0, %1, %2;" : "+l"(v01) : "l"(sc2), "l"(bi2));
+  asm("fma.rn.f32x2 %0, %0, %1, %2;" : "+l"(v23) : "l"(sc2), "l"(bi2));
+  float a, b, c, d;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v01));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(c), "=f"(d) : "l"(v23));
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
   uint2 r;
-  r.x = w8_pair(q & 0x000F000Fu, (q >> 4) & 0x000F000Fu, s2, b2);           // (e0, e1)
-  r.y = w8_pair((q >> 8) & 0x000F000Fu, (q >> 12) & 0x000F000Fu, s2, b2);  // (e2, e3)
+  r.x = *reinterpret_cast<const uint32_t*>(&lo);
+  r.y = *reinterpret_cast<const uint32_t*>(&hi);
   return r;
 }
 
@@ -316,9 +317,8 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     }
   } else if (warp >= FIRST_DQ_WARP) {
     // ------------------------------------------------------------ dequantizers
-    // Every warp serves one quantization group of the stage: with 8 warps (4-bit codes) four warps per
-    // group and one thread per weight row, with 16 warps (8-bit codes) eight per group and half a row
-    // per thread.
+    // Every warp serves one quantization group of the stage: with 8 warps four warps per group and one thread
+    // per weight row (16 warps would give eight per group and half a row per thread).
     constexpr int WPG = NUM_DQ_WARPS / GPS;        // warps per group
     constexpr int SPLIT = WPG / 4;                 // threads per weight row: 1 or 2
     const int dq = warp - FIRST_DQ_WARP;
@@ -368,10 +368,14 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             for (int j = 0; j < 4; ++j)
               *reinterpret_cast<uint4*>(dst + wr_off[h * 4 + j]) = dequant_w4<WF>(wds[j], s2, b2);
           } else {          // 4 words x 4 codes -> 2 output chunks
-            const uint2 lo0 = dequant_w8(pk.x, s2, b2);
-            const uint2 hi0 = dequant_w8(pk.y, s2, b2);
-            const uint2 lo1 = dequant_w8(pk.z, s2, b2);
-            const uint2 hi1 = dequant_w8(pk.w, s2, b2);
+            const uint32_t sf = sbv << 16, bf = sbv & 0xFFFF0000u;   // scale and bias as float32 bit patterns
+            uint64_t sc2, bi2;
+            asm("mov.b64 %0, {%1, %1};" : "=l"(sc2) : "r"(sf));
+            asm("mov.b64 %0, {%1, %1};" : "=l"(bi2) : "r"(bf));
+            const uint2 lo0 = dequant_w8_f32(pk.x, sc2, bi2);
+            const uint2 hi0 = dequant_w8_f32(pk.y, sc2, bi2);
+            const uint2 lo1 = dequant_w8_f32(pk.z, sc2, bi2);
+            const uint2 hi1 = dequant_w8_f32(pk.w, sc2, bi2);
             *reinterpret_cast<uint4*>(dst + wr_off[2 * h]) = make_uint4(lo0.x, lo0.y, hi0.x, hi0.y);
             *reinterpret_cast<uint4*>(dst + wr_off[2 * h + 1]) = make_uint4(lo1.x, lo1.y, hi1.x, hi1.y);
           }
@@ -515,9 +519,9 @@ template <int BITS, uint32_t WF, int ST, int SD, typename OUT, int EPI>
 int launch_epi(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tsb, const Params& p, int grid,
                cudaStream_t st) {
   using L = Smem<BITS, ST, SD>;
-  // 4-bit codes need half the integer work per value: 8 dequantizer warps keep up and draw less power;
-  // 8-bit codes want 16
-  constexpr int NDQ = BITS == 4 ? 8 : 16;
+  // eight dequantizer warps keep up with the tensor pipe for both widths (8-bit codes go through packed float32
+  // arithmetic, five instructions per pair) and draw less power than sixteen
+  constexpr int NDQ = 8;
   constexpr int NUM_THREADS = (FIXED_WARPS + NDQ) * 32;
   auto kern = qmm_kernel<BITS, WF, ST, SD, OUT, EPI, NDQ>;
   static bool configured = false;  // attribute is per function; set once per process and device reuse is fine
