@@ -71,14 +71,26 @@ __device__ __forceinline__ uint32_t deq4(uint32_t w, int i, uint32_t scale2, uin
   const uint32_t v = ((w >> (4 * i)) & 0x000F000Fu) | MAGIC;
   return fma_bf16x2(sub_bf16x2(v, MAGIC), scale2, bias2);
 }
-// Two neighbouring weights of an 8-bit row: half h (0 = bytes e0,e1; 1 = e2,e3) of a prepared word; the code is
-// rebuilt exactly as 16 * high nibble + low nibble before the single rounding of code * scale + bias.
-__device__ __forceinline__ uint32_t deq8(uint32_t w, int h, uint32_t scale2, uint32_t bias2) {
-  const uint32_t b = (w >> (8 * h)) & 0x00FF00FFu;
-  const uint32_t lo = sub_bf16x2((b & 0x000F000Fu) | MAGIC, MAGIC);
-  const uint32_t hi = sub_bf16x2(((b >> 4) & 0x000F000Fu) | MAGIC, MAGIC);
-  const uint32_t code = fma_bf16x2(hi, 0x41804180u /* 16.0 */, lo);
-  return fma_bf16x2(code, scale2, bias2);
+// The four weights of one prepared 8-bit word (bytes e0,e2,e1,e3) as two bf16 pairs (e0,e1), (e2,e3), through
+// float32: a byte under the exponent of 2^23 is the float 2^23 + code; packed f32x2 add and fma, one rounding to
+// bf16 at the end (the same arithmetic as the large-M kernel's 8-bit path). sc2 / bi2: (scale, scale) and
+// (bias, bias) as float32 pairs.
+__device__ __forceinline__ void deq8_word(uint32_t w, uint64_t sc2, uint64_t bi2, uint32_t& b0, uint32_t& b1) {
+  constexpr uint32_t TWO23 = 0x4B000000u;
+  const uint64_t neg = 0xCB000000CB000000ull;  // (-2^23, -2^23)
+  uint64_t v01, v23;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v01) : "r"(__byte_perm(w, TWO23, 0x7440)), "r"(__byte_perm(w, TWO23, 0x7442)));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v23) : "r"(__byte_perm(w, TWO23, 0x7441)), "r"(__byte_perm(w, TWO23, 0x7443)));
+  asm("add.rn.f32x2 %0, %0, %1;" : "+l"(v01) : "l"(neg));
+  asm("add.rn.f32x2 %0, %0, %1;" : "+l"(v23) : "l"(neg));
+  asm("fma.rn.f32x2 %0, %0, %1, %2;" : "+l"(v01) : "l"(sc2), "l"(bi2));
+  asm("fma.rn.f32x2 %0, %0, %1, %2;" : "+l"(v23) : "l"(sc2), "l"(bi2));
+  float a, b, c, d;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v01));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(c), "=f"(d) : "l"(v23));
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  b0 = *reinterpret_cast<const uint32_t*>(&lo);
+  b1 = *reinterpret_cast<const uint32_t*>(&hi);
 }
 
 // R = groups of 8 weight rows per warp (the A fragments are reused across them). BITS = 4 or 8.
@@ -139,6 +151,11 @@ __global__ void __launch_bounds__(THREADS) qmv_kernel(const Params p) {
       const int n = n_base + 8 * r + g;
       const uint32_t sbv = (live && n < p.N) ? __ldg(p.sb + static_cast<int64_t>(group) * p.N + n) : 0u;
       const uint32_t scale2 = __byte_perm(sbv, sbv, 0x1010), bias2 = __byte_perm(sbv, sbv, 0x3232);
+      uint64_t sc2 = 0, bi2 = 0;
+      if (BITS == 8) {   // the same scale and bias as float32 pairs
+        asm("mov.b64 %0, {%1, %1};" : "=l"(sc2) : "r"(sbv << 16));
+        asm("mov.b64 %0, {%1, %1};" : "=l"(bi2) : "r"(sbv & 0xFFFF0000u));
+      }
       const uint32_t w[4] = {wv[r].x, wv[r].y, wv[r].z, wv[r].w};
 #pragma unroll
       for (int st = 0; st < STEPS; ++st) {
@@ -147,8 +164,7 @@ __global__ void __launch_bounds__(THREADS) qmv_kernel(const Params p) {
           b0 = deq4(w[st >> 1], 2 * (st & 1), scale2, bias2);
           b1 = deq4(w[st >> 1], 2 * (st & 1) + 1, scale2, bias2);
         } else {
-          b0 = deq8(w[st], 0, scale2, bias2);
-          b1 = deq8(w[st], 1, scale2, bias2);
+          deq8_word(w[st], sc2, bi2, b0, b1);
         }
         mma_16816(acc[r], xa[2 * st], xb[2 * st], xa[2 * st + 1], xb[2 * st + 1], b0, b1);
       }
