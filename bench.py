@@ -254,13 +254,24 @@ def qwen_spec(args):
 
     def build(dev, rank, world, steps):
         import torch
+        import torch.distributed as dist
 
-        from mflux_b200 import ops
-        from mflux_b200.qwen import QwenTransformer
+        from mflux_b200.qwen import QwenImage
         from mflux_b200.schedulers import LinearScheduler
 
-        model = QwenTransformer(cfg, bits=4, device=dev, seed=1234, tp_rank=rank, tp_world=world)
-        g = torch.Generator(device="cpu").manual_seed(100)   # tensor parallel: every rank sees the same image
+        # 1 rank: both branches as a batch of 2. Even rank counts: the prompt branch on the first half of the
+        # ranks, the negative-prompt branch on the second half, tensor parallelism inside each half.
+        if world > 1 and args.qwen_parallel == "cfg+tp":
+            tp = world // 2
+            branch, tp_rank = rank // tp, rank % tp
+            tp_groups = [dist.new_group(list(range(g * tp, (g + 1) * tp))) for g in range(2)]
+            cfg_groups = [dist.new_group([r, r + tp]) for r in range(tp)]
+            pipe = QwenImage(quantize=4, model_config=cfg, device=dev, seed=1234, tp_rank=tp_rank, tp_world=tp,
+                             tp_group=tp_groups[branch] if tp > 1 else None, cfg_rank=branch,
+                             cfg_group=cfg_groups[tp_rank])
+        else:
+            pipe = QwenImage(quantize=4, model_config=cfg, device=dev, seed=1234, tp_rank=rank, tp_world=world)
+        g = torch.Generator(device="cpu").manual_seed(100)   # every rank sees the same image and prompts
         lat_h = torch.randn(1, si, cfg.in_channels, generator=g).pin_memory()
         emb_h = torch.randn(b, st, cfg.joint_attention_dim, generator=g).to(torch.bfloat16).pin_memory()
         out_h = torch.empty_like(lat_h).pin_memory()
@@ -268,17 +279,18 @@ def qwen_spec(args):
 
         def step(i, lat_d, emb_d):
             j = i % len(sched.timesteps)
-            sig = torch.full((b,), float(sched.sigmas[j]), device=dev)
-            both = model(torch.cat([lat_d, lat_d]), emb_d, sig, height, width)
-            return ops.euler_step(lat_d, ops.cfg_combine(both[:1], both[1:], 4.0, mode="qwen"), sched.dt(j))
+            return pipe.denoise_step(lat_d, emb_d[:1], emb_d[1:], float(sched.sigmas[j]), sched.dt(j), 4.0, height,
+                                     width)
 
         return [lat_h, emb_h], out_h, step
 
+    par = "1 GPU" if args.gpus == 1 else (f"prompt / negative-prompt branch x tensor-parallel {args.gpus // 2}"
+                                          if args.qwen_parallel == "cfg+tp" else f"tensor-parallel {args.gpus}")
     return {
         "metric": "qwen_image_w4_dit_steps_per_sec_1328px_cfg2",
         "unit": "steps/s (one step = prompt + negative prompt of one image, 2 x 7145 tokens through 60 blocks)",
         "workload": (f"Qwen-Image-shaped dual-stream MMDiT {cfg.num_layers} blocks, hidden {d}, {cfg.heads}x128 heads, "
-                     f"W4 g64, CFG batch 2, {si} image + {st} text tokens, tensor-parallel over all ranks"),
+                     f"W4 g64, CFG batch 2, {si} image + {st} text tokens, {par}"),
         "scaling": "strong", "lin": lin, "attn": attn, "per_gpu_batch": b, "build": build,
         "l2_policy": "inputs larger than L2 (10 GB of packed weights, split over the ranks, stream every step)",
     }
@@ -358,6 +370,9 @@ def main():
     ap.add_argument("--small", action="store_true", help="flux at reduced depth for profiler captures (not a bench value)")
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (default: the workload's own)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--qwen-parallel", default="cfg+tp", choices=["cfg+tp", "tp"],
+                    help="qwen on N > 1 GPUs: split the two guidance branches over the halves of the ranks and use "
+                         "tensor parallelism inside each half (default), or tensor parallelism over all ranks")
     args = ap.parse_args()
 
     if args.workload == "sweep":

@@ -279,18 +279,23 @@ class QwenTransformer(nn.Module):
 
 class QwenImage:
     """Denoise loop of the reference's QwenImage variant (variants/txt2img/qwen_image.py:99-128,165-174):
-    two denoiser evaluations per step (prompt and negative prompt, run as one batch of 2) and the
-    norm-preserving guidance combine."""
+    two denoiser evaluations per step (prompt and negative prompt) and the norm-preserving guidance combine.
+
+    On one rank the two evaluations run as one batch of 2. With `cfg_group` (a process group of two ranks, or of
+    two tensor-parallel groups' matching ranks) every rank evaluates only the branch `cfg_rank` (0 = prompt,
+    1 = negative prompt) and the two predictions are exchanged with one small all-gather before the combine, so
+    the pair needs no other communication; this composes with tensor parallelism inside each branch."""
 
     def __init__(self, quantize: int | None = None, model_config: QwenConfig | None = None, device="cuda",
                  seed: int = 0, stored_quantization: int | None = None, tp_rank: int = 0, tp_world: int = 1,
-                 tp_group=None):
+                 tp_group=None, cfg_rank: int | None = None, cfg_group=None):
         bits, warning = resolution.resolve(stored_quantization, quantize)
         if warning:
             print(f"Warning: {warning}")
         resolution.check_supported(bits)
         self.bits = bits
         self.model_config = model_config or QwenConfig()
+        self.cfg_rank, self.cfg_group = cfg_rank, cfg_group
         self.transformer = QwenTransformer(self.model_config, bits=bits, device=device, seed=seed, tp_rank=tp_rank,
                                            tp_world=tp_world, tp_group=tp_group)
 
@@ -309,11 +314,22 @@ class QwenImage:
         if hasattr(self.transformer, "_fused"):
             self.transformer._fused = {}
 
-    def denoise_step(self, latents, prompt_embeds, negative_prompt_embeds, sigma, dt, guidance, height, width):
+    def predict_noise(self, latents, prompt_embeds, negative_prompt_embeds, sigma, height, width):
+        """(noise for the prompt, noise for the negative prompt), each [B, Si, C]."""
         b = latents.shape[0]
-        both = self.transformer(torch.cat([latents, latents]), torch.cat([prompt_embeds, negative_prompt_embeds]),
-                                torch.full((2 * b,), sigma, device=latents.device), height, width)
-        guided = ops.cfg_combine(both[:b], both[b:], guidance, mode="qwen")
+        if self.cfg_group is None:
+            both = self.transformer(torch.cat([latents, latents]), torch.cat([prompt_embeds, negative_prompt_embeds]),
+                                    torch.full((2 * b,), sigma, device=latents.device), height, width)
+            return both[:b], both[b:]
+        mine = self.transformer(latents, prompt_embeds if self.cfg_rank == 0 else negative_prompt_embeds,
+                                torch.full((b,), sigma, device=latents.device), height, width).contiguous()
+        parts = [torch.empty_like(mine), torch.empty_like(mine)]
+        dist.all_gather(parts, mine, group=self.cfg_group)
+        return parts[0], parts[1]
+
+    def denoise_step(self, latents, prompt_embeds, negative_prompt_embeds, sigma, dt, guidance, height, width):
+        noise, noise_negative = self.predict_noise(latents, prompt_embeds, negative_prompt_embeds, sigma, height, width)
+        guided = ops.cfg_combine(noise, noise_negative, guidance, mode="qwen")
         return ops.euler_step(latents, guided, dt)
 
     def generate_image(self, seed: int, prompt_embeds: torch.Tensor, negative_prompt_embeds: torch.Tensor,

@@ -78,7 +78,8 @@ def test_denoise_loop_runs(lib_built):
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="tensor parallelism needs two GPUs")
 def test_tensor_parallel_matches_single_gpu(lib_built, tmp_path):
-    """Two ranks (NCCL, NVLS off) against one: same seeded weights, outputs within tolerance."""
+    """Two ranks (NCCL, NVLS off) against one: same seeded weights, outputs within tolerance, for the
+    tensor-parallel transformer and for the denoise step with the two guidance branches on two ranks."""
     script = ROOT / "tests" / "tp_worker.py"
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
@@ -87,3 +88,5 @@ def test_tensor_parallel_matches_single_gpu(lib_built, tmp_path):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     err = float((tmp_path / "tp_err.txt").read_text())
     assert err <= TOL, err
+    cfg_err = float((tmp_path / "cfg_err.txt").read_text())
+    assert cfg_err <= 2e-3, cfg_err

@@ -9,7 +9,7 @@ import torch.distributed as dist
 ROOT = Path(__file__).resolve().parent.parent
 sys.path.insert(0, str(ROOT))
 
-from mflux_b200.qwen import QwenConfig, QwenTransformer  # noqa: E402
+from mflux_b200.qwen import QwenConfig, QwenImage, QwenTransformer  # noqa: E402
 from oracle.quant import rel_l2  # noqa: E402
 
 
@@ -31,6 +31,15 @@ def main():
         one = QwenTransformer(cfg, bits=4, device="cuda", seed=5)
         y1 = one(lat, ctx, sigma, 96, 144).float()
         (out_dir / "tp_err.txt").write_text(str(rel_l2(y_tp, y1.cpu().numpy())))
+    # guidance-branch parallelism: rank 0 evaluates the prompt, rank 1 the negative prompt, one all-gather per step
+    neg = torch.randn(2, 40, 128, generator=g).to(torch.bfloat16).cuda()
+    split = QwenImage(quantize=4, model_config=cfg, seed=5, cfg_rank=rank, cfg_group=dist.group.WORLD)
+    z_split = split.denoise_step(lat, ctx, neg, 0.7, -0.05, 4.0, 96, 144)
+    torch.cuda.synchronize()
+    if rank == 0:
+        whole = QwenImage(quantize=4, model_config=cfg, seed=5)
+        z = whole.denoise_step(lat, ctx, neg, 0.7, -0.05, 4.0, 96, 144)
+        (out_dir / "cfg_err.txt").write_text(str(rel_l2(z_split, z.cpu().numpy())))
     dist.barrier()
     dist.destroy_process_group()
 
