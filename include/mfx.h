@@ -222,6 +222,34 @@ int mfx_norm_gate_residual(const void* y, int y_dtype, int64_t y_row_stride, int
                            const void* gate, int gate_dtype, int64_t gate_batch_stride, float* residual,
                            int64_t res_row_stride, int64_t res_batch_stride, void* stream);
 
+/* mfx_norm_gate_residual followed, in the same pass, by the pre-norm of the next sub-layer on the updated stream:
+ * next_out = RMSNorm(residual) * next_weight * (1 + next_scale[sample]) as bf16, i.e. ffn_norm1 and scale_mlp after
+ * the attention post-norm (transformer_block.py:34 after :31) or the following block's attention_norm1 and
+ * scale_msa after the FFN post-norm (:29-30 after :35). next_out == NULL leaves only the first stage. */
+typedef struct mfx_post_pre_norm_args {
+  const void* y;
+  int y_dtype;
+  int64_t y_row_stride, y_batch_stride;
+  int64_t rows, batch, D;
+  const void* weight;
+  int weight_dtype;
+  float eps;
+  const void* gate; /* [batch, D] or NULL */
+  int gate_dtype;
+  int64_t gate_batch_stride;
+  float* residual;
+  int64_t res_row_stride, res_batch_stride;
+  void* next_out; /* bf16 [batch, rows, D] or NULL */
+  int64_t next_row_stride, next_batch_stride;
+  const void* next_weight;
+  int next_weight_dtype;
+  const void* next_scale; /* [batch, D] or NULL */
+  int next_scale_dtype;
+  int64_t next_scale_batch_stride;
+  float next_eps;
+} mfx_post_pre_norm_args;
+int mfx_post_pre_norm(const mfx_post_pre_norm_args* args /* host */, void* stream);
+
 /* Classifier-free-guidance combine of two noise predictions [rows, channels] into f32 `out`.
  * mode 0: noise + g*(noise - negative)  (src/mflux/models/z_image/variants/z_image.py:209);
  * mode 1: negative + g*(noise - negative), rescaled per row to the norm of `noise`

@@ -86,6 +86,38 @@ class NormArgs(ctypes.Structure):
 
 
 # name -> (restype, argtypes); every symbol include/mfx.h declares
+class PostPreNormArgs(ctypes.Structure):
+    """struct mfx_post_pre_norm_args (include/mfx.h)."""
+
+    _fields_ = [
+        ("y", c_void_p),
+        ("y_dtype", c_int),
+        ("y_row_stride", c_int64),
+        ("y_batch_stride", c_int64),
+        ("rows", c_int64),
+        ("batch", c_int64),
+        ("D", c_int64),
+        ("weight", c_void_p),
+        ("weight_dtype", c_int),
+        ("eps", ctypes.c_float),
+        ("gate", c_void_p),
+        ("gate_dtype", c_int),
+        ("gate_batch_stride", c_int64),
+        ("residual", c_void_p),
+        ("res_row_stride", c_int64),
+        ("res_batch_stride", c_int64),
+        ("next_out", c_void_p),
+        ("next_row_stride", c_int64),
+        ("next_batch_stride", c_int64),
+        ("next_weight", c_void_p),
+        ("next_weight_dtype", c_int),
+        ("next_scale", c_void_p),
+        ("next_scale_dtype", c_int),
+        ("next_scale_batch_stride", c_int64),
+        ("next_eps", ctypes.c_float),
+    ]
+
+
 SIGNATURES = {
     "mfx_version": (c_int, []),
     "mfx_status_str": (c_char_p, [c_int]),
@@ -135,6 +167,7 @@ SIGNATURES = {
     "mfx_norm_gate_residual": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p, c_int,
                                        ctypes.c_float, c_void_p, c_int, c_int64, c_void_p, c_int64, c_int64,
                                        c_void_p]),
+    "mfx_post_pre_norm": (c_int, [ctypes.POINTER(PostPreNormArgs), c_void_p]),
     "mfx_cfg_combine": (c_int, [c_void_p, c_void_p, c_int, ctypes.c_float, c_int, c_void_p, c_int64, c_int64, c_void_p]),
     "mfx_euler_step": (c_int, [c_void_p, c_int, c_void_p, c_int, ctypes.c_float, c_void_p, c_int64, c_void_p]),
 }

@@ -185,17 +185,28 @@ struct PostNormParams {
   int64_t gate_batch_stride;
   float* residual;  // [batch, rows, D] f32, updated in place
   int64_t res_row_stride, res_batch_stride;
+  // optional second stage: next_out = RMSNorm(updated residual) * next_weight * (1 + next_scale[b]) as bf16
+  __nv_bfloat16* next_out;  // null = no second stage
+  int64_t next_row_stride, next_batch_stride;
+  const void* next_weight;  // [D]
+  int next_weight_dtype;
+  const void* next_scale;   // [batch, D] or null
+  int next_scale_dtype;
+  int64_t next_scale_batch_stride;
+  float next_eps;
 };
 
 // residual[b, r, :] += gate[b, :] * RMSNorm(y[b, r, :]) * weight: the "sandwich" post-norm of the Z-Image block
 // (z_image_transformer/transformer_block.py:31,35; context_block.py:18,21). The norm needs the whole output row
 // of the projection, so it cannot be an epilogue of a matmul tiled along N; this pass reads y once.
 // One 128-thread block per row, 4 elements per vector (8-byte loads of bf16 y, 16-byte of the f32 residual).
+// With next_out the block goes on to the pre-norm of the following sub-layer on the row it just updated
+// (transformer_block.py:34 after :31, and the next block's :29-30 after :35), which saves reading the stream again.
 template <typename YT>
 __global__ void __launch_bounds__(NORM_THREADS) norm_gate_residual_kernel(const PostNormParams p) {
   constexpr int E = 4;
   constexpr int MAXV = NORM_MAX_D / E / NORM_THREADS;
-  __shared__ float red[4];
+  __shared__ float red[4], red2[4];
   const int t = threadIdx.x;
   const int64_t row_id = blockIdx.x;
   const int b = static_cast<int>(row_id / p.rows);
@@ -228,8 +239,38 @@ __global__ void __launch_bounds__(NORM_THREADS) norm_gate_residual_kernel(const 
         float u = v[i][j] * rstd * wt[j];
         if (p.gate) u *= gt[j];
         rs[j] += u;
+        v[i][j] = rs[j];   // the updated stream stays in registers for the optional second stage
       }
       *reinterpret_cast<float4*>(res + static_cast<int64_t>(c) * E) = make_float4(rs[0], rs[1], rs[2], rs[3]);
+    }
+  }
+  if (p.next_out == nullptr) return;   // uniform over the grid
+  float sq2 = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int c = t + NORM_THREADS * i;
+    if (c < nvec) {
+#pragma unroll
+      for (int j = 0; j < E; ++j) sq2 += v[i][j] * v[i][j];
+    }
+  }
+  const float rstd2 = rsqrtf(block_sum_128(sq2, red2) / static_cast<float>(p.D) + p.next_eps);
+  __nv_bfloat16* out = p.next_out + b * p.next_batch_stride + static_cast<int64_t>(r) * p.next_row_stride;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int c = t + NORM_THREADS * i;
+    if (c < nvec) {
+      float wt[E], sc[E], o[E];
+      load_vec<E>(p.next_weight, p.next_weight_dtype, static_cast<int64_t>(c) * E, wt);
+      if (p.next_scale)
+        load_vec<E>(p.next_scale, p.next_scale_dtype, b * p.next_scale_batch_stride + static_cast<int64_t>(c) * E, sc);
+#pragma unroll
+      for (int j = 0; j < E; ++j) {
+        float u = v[i][j] * rstd2 * wt[j];
+        if (p.next_scale) u *= 1.0f + sc[j];
+        o[j] = u;
+      }
+      store_vec_bf16<E>(out + static_cast<int64_t>(c) * E, o);
     }
   }
 }
@@ -521,48 +562,91 @@ int mfx_gate_residual(const void* y, int y_dtype, const void* bias, int bias_dty
   return MFX_OK;
 }
 
+int mfx_post_pre_norm(const mfx_post_pre_norm_args* a, void* stream) {
+  using namespace mfx;
+  using namespace mfx::glue;
+  if (!a || !a->y || !a->weight || !a->residual) return MFX_ERR_NULL;
+  if (a->rows <= 0 || a->batch <= 0 || a->D <= 0 || a->D % 8 != 0) return MFX_ERR_SHAPE;
+  if (a->D > NORM_MAX_D) return MFX_ERR_TOO_LARGE;
+  if ((a->y_dtype != MFX_F32 && a->y_dtype != MFX_BF16) || !valid_dtype(a->weight_dtype) ||
+      (a->gate && !valid_dtype(a->gate_dtype)))
+    return MFX_ERR_DTYPE;
+  const size_t ys = dtype_size(a->y_dtype);
+  if (!aligned16(a->y) || (a->y_row_stride * ys) % 16 != 0 || (a->y_batch_stride * ys) % 16 != 0 ||
+      !aligned16(a->residual) || (a->res_row_stride * 4) % 16 != 0 || (a->res_batch_stride * 4) % 16 != 0)
+    return MFX_ERR_ALIGN;
+  if (a->weight_dtype != MFX_F16 && !aligned16(a->weight)) return MFX_ERR_ALIGN;
+  if (a->gate && a->gate_dtype != MFX_F16 &&
+      (!aligned16(a->gate) || (a->gate_batch_stride * dtype_size(a->gate_dtype)) % 16 != 0))
+    return MFX_ERR_ALIGN;
+  if (a->next_out) {
+    if (!a->next_weight) return MFX_ERR_NULL;
+    if (!valid_dtype(a->next_weight_dtype) || (a->next_scale && !valid_dtype(a->next_scale_dtype))) return MFX_ERR_DTYPE;
+    if (!aligned16(a->next_out) || (a->next_row_stride * 2) % 16 != 0 || (a->next_batch_stride * 2) % 16 != 0)
+      return MFX_ERR_ALIGN;
+    if (a->next_weight_dtype != MFX_F16 && !aligned16(a->next_weight)) return MFX_ERR_ALIGN;
+    if (a->next_scale && a->next_scale_dtype != MFX_F16 &&
+        (!aligned16(a->next_scale) || (a->next_scale_batch_stride * dtype_size(a->next_scale_dtype)) % 16 != 0))
+      return MFX_ERR_ALIGN;
+  }
+  if (int rc = check_arch()) return rc;
+  PostNormParams p;
+  p.y = a->y;
+  p.y_row_stride = a->y_row_stride;
+  p.y_batch_stride = a->y_batch_stride;
+  p.rows = static_cast<int>(a->rows);
+  p.batch = static_cast<int>(a->batch);
+  p.D = static_cast<int>(a->D);
+  p.weight = a->weight;
+  p.weight_dtype = a->weight_dtype;
+  p.eps = a->eps;
+  p.gate = a->gate;
+  p.gate_dtype = a->gate_dtype;
+  p.gate_batch_stride = a->gate_batch_stride;
+  p.residual = a->residual;
+  p.res_row_stride = a->res_row_stride;
+  p.res_batch_stride = a->res_batch_stride;
+  p.next_out = static_cast<__nv_bfloat16*>(a->next_out);
+  p.next_row_stride = a->next_row_stride;
+  p.next_batch_stride = a->next_batch_stride;
+  p.next_weight = a->next_weight;
+  p.next_weight_dtype = a->next_weight_dtype;
+  p.next_scale = a->next_scale;
+  p.next_scale_dtype = a->next_scale_dtype;
+  p.next_scale_batch_stride = a->next_scale_batch_stride;
+  p.next_eps = a->next_eps;
+  if (a->rows * a->batch > 0x7fffffffll) return MFX_ERR_TOO_LARGE;
+  const unsigned blocks = static_cast<unsigned>(a->rows * a->batch);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (a->y_dtype == MFX_F32) norm_gate_residual_kernel<float><<<blocks, NORM_THREADS, 0, st>>>(p);
+  else norm_gate_residual_kernel<__nv_bfloat16><<<blocks, NORM_THREADS, 0, st>>>(p);
+  MFX_CUDA_TRY(cudaGetLastError());
+  return MFX_OK;
+}
+
 int mfx_norm_gate_residual(const void* y, int y_dtype, int64_t y_row_stride, int64_t y_batch_stride, int64_t rows,
                            int64_t batch, int64_t D, const void* weight, int weight_dtype, float eps,
                            const void* gate, int gate_dtype, int64_t gate_batch_stride, float* residual,
                            int64_t res_row_stride, int64_t res_batch_stride, void* stream) {
-  using namespace mfx;
-  using namespace mfx::glue;
-  if (!y || !weight || !residual) return MFX_ERR_NULL;
-  if (rows <= 0 || batch <= 0 || D <= 0 || D % 8 != 0) return MFX_ERR_SHAPE;
-  if (D > NORM_MAX_D) return MFX_ERR_TOO_LARGE;
-  if ((y_dtype != MFX_F32 && y_dtype != MFX_BF16) || !valid_dtype(weight_dtype) || (gate && !valid_dtype(gate_dtype)))
-    return MFX_ERR_DTYPE;
-  const size_t ys = dtype_size(y_dtype);
-  if (!aligned16(y) || (y_row_stride * ys) % 16 != 0 || (y_batch_stride * ys) % 16 != 0 || !aligned16(residual) ||
-      (res_row_stride * 4) % 16 != 0 || (res_batch_stride * 4) % 16 != 0)
-    return MFX_ERR_ALIGN;
-  if (weight_dtype != MFX_F16 && !aligned16(weight)) return MFX_ERR_ALIGN;
-  if (gate && gate_dtype != MFX_F16 && (!aligned16(gate) || (gate_batch_stride * dtype_size(gate_dtype)) % 16 != 0))
-    return MFX_ERR_ALIGN;
-  if (int rc = check_arch()) return rc;
-  PostNormParams p;
-  p.y = y;
-  p.y_row_stride = y_row_stride;
-  p.y_batch_stride = y_batch_stride;
-  p.rows = static_cast<int>(rows);
-  p.batch = static_cast<int>(batch);
-  p.D = static_cast<int>(D);
-  p.weight = weight;
-  p.weight_dtype = weight_dtype;
-  p.eps = eps;
-  p.gate = gate;
-  p.gate_dtype = gate_dtype;
-  p.gate_batch_stride = gate_batch_stride;
-  p.residual = residual;
-  p.res_row_stride = res_row_stride;
-  p.res_batch_stride = res_batch_stride;
-  if (rows * batch > 0x7fffffffll) return MFX_ERR_TOO_LARGE;
-  const unsigned blocks = static_cast<unsigned>(rows * batch);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (y_dtype == MFX_F32) norm_gate_residual_kernel<float><<<blocks, NORM_THREADS, 0, st>>>(p);
-  else norm_gate_residual_kernel<__nv_bfloat16><<<blocks, NORM_THREADS, 0, st>>>(p);
-  MFX_CUDA_TRY(cudaGetLastError());
-  return MFX_OK;
+  mfx_post_pre_norm_args a;
+  memset(&a, 0, sizeof(a));
+  a.y = y;
+  a.y_dtype = y_dtype;
+  a.y_row_stride = y_row_stride;
+  a.y_batch_stride = y_batch_stride;
+  a.rows = rows;
+  a.batch = batch;
+  a.D = D;
+  a.weight = weight;
+  a.weight_dtype = weight_dtype;
+  a.eps = eps;
+  a.gate = gate;
+  a.gate_dtype = gate_dtype;
+  a.gate_batch_stride = gate_batch_stride;
+  a.residual = residual;
+  a.res_row_stride = res_row_stride;
+  a.res_batch_stride = res_batch_stride;
+  return mfx_post_pre_norm(&a, stream);
 }
 
 int mfx_cfg_combine(const void* noise, const void* noise_negative, int dtype, float guidance, int mode, float* out,

@@ -423,10 +423,14 @@ def cfg_combine(noise: torch.Tensor, noise_negative: torch.Tensor, guidance: flo
 
 
 def norm_gate_residual(y: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, gate: torch.Tensor | None = None,
-                       eps: float = 1e-5) -> torch.Tensor:
+                       eps: float = 1e-5, *, next_weight: torch.Tensor | None = None,
+                       next_scale: torch.Tensor | None = None, next_out: torch.Tensor | None = None,
+                       next_eps: float | None = None) -> torch.Tensor:
     """residual += gate[sample] * RMSNorm(y) * weight, in place on the float32 view `residual`.
 
-    y is [rows, D] or [batch, rows, D] (bf16 or f32, strided views allowed), gate [batch, D] or None.
+    y is [rows, D] or [batch, rows, D] (bf16 or f32, strided views allowed), gate [batch, D] or None. With
+    `next_out` (a bf16 view shaped like y) the same pass also writes the next sub-layer's pre-norm of the updated
+    stream: next_out = RMSNorm(residual) * next_weight * (1 + next_scale[sample]).
     """
     lib = _lib.load()
     _cuda(y, "y")
@@ -436,15 +440,34 @@ def norm_gate_residual(y: torch.Tensor, weight: torch.Tensor, residual: torch.Te
     if rv.data_ptr() != residual.data_ptr() or rv.dtype != torch.float32 or (r_rows, r_batch) != (rows, batch) \
             or rv.shape[-1] != d:
         raise ValueError("residual must be a float32 view shaped like y with a dense last dim")
+    a = _lib.PostPreNormArgs()
+    a.y, a.y_dtype, a.y_row_stride, a.y_batch_stride = yv.data_ptr(), _dt(yv), y_rs, y_bs
+    a.rows, a.batch, a.D = rows, batch, d
     weight = weight.contiguous()
-    g_ptr, g_dt, g_bs = c_void_p(None), 0, 0
+    a.weight, a.weight_dtype, a.eps = weight.data_ptr(), _dt(weight), float(eps)
     if gate is not None:
         gate = gate.reshape(-1, d) if gate.stride(-1) == 1 else gate.reshape(-1, d).contiguous()
         if gate.shape[0] != batch:
             raise ValueError("gate must be [batch, D]")
-        g_ptr, g_dt, g_bs = _ptr(gate), _dt(gate), gate.stride(0)
-    rc = lib.mfx_norm_gate_residual(_ptr(yv), _dt(yv), y_rs, y_bs, rows, batch, d, _ptr(weight), _dt(weight),
-                                    float(eps), g_ptr, g_dt, g_bs, _ptr(rv), r_rs, r_bs, _stream())
-    _lib.check(rc, "mfx_norm_gate_residual")
+        a.gate, a.gate_dtype, a.gate_batch_stride = gate.data_ptr(), _dt(gate), gate.stride(0)
+    a.residual, a.res_row_stride, a.res_batch_stride = rv.data_ptr(), r_rs, r_bs
+    if next_out is not None:
+        if next_weight is None:
+            raise ValueError("next_out needs next_weight")
+        ov, o_rows, o_batch, o_rs, o_bs = _rows_view(next_out, "next_out")
+        if ov.data_ptr() != next_out.data_ptr() or ov.dtype != torch.bfloat16 or (o_rows, o_batch) != (rows, batch) \
+                or ov.shape[-1] != d:
+            raise ValueError("next_out must be a bf16 view shaped like y with a dense last dim")
+        next_weight = next_weight.contiguous()
+        a.next_out, a.next_row_stride, a.next_batch_stride = ov.data_ptr(), o_rs, o_bs
+        a.next_weight, a.next_weight_dtype = next_weight.data_ptr(), _dt(next_weight)
+        a.next_eps = float(eps if next_eps is None else next_eps)
+        if next_scale is not None:
+            next_scale = next_scale.reshape(-1, d) if next_scale.stride(-1) == 1 else next_scale.reshape(-1, d).contiguous()
+            if next_scale.shape[0] != batch:
+                raise ValueError("next_scale must be [batch, D]")
+            a.next_scale, a.next_scale_dtype = next_scale.data_ptr(), _dt(next_scale)
+            a.next_scale_batch_stride = next_scale.stride(0)
+    _lib.check(lib.mfx_post_pre_norm(byref(a), _stream()), "mfx_post_pre_norm")
     LAUNCHES[0] += 1
     return residual

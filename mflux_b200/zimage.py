@@ -9,7 +9,8 @@ timestep_embedder.py:7-38), so parameter paths such as `layers.7.attention.to_q.
     the order of transformer.py:121); the refiners run on strided views of it, so the concatenation is free;
   * to_q/to_k/to_v run as one matmul over row-concatenated packed weights, and w1/w3 as one matmul over
     row-interleaved packed weights whose epilogue writes silu(w1 x) * (w3 x) directly;
-  * the post-norms (attention_norm2 / ffn_norm2), the tanh gate and the residual add are one pass;
+  * the post-norms (attention_norm2 / ffn_norm2), the tanh gate, the residual add and the pre-norm (with its
+    modulation) of the sub-layer that follows are one pass over the stream;
   * the reference evaluates one image at a time; here B images of one shape (and one caption length) run as
     a batch, every sample with its own timestep.
 The text encoder and the VAE of the reference are outside this path: callers pass caption features and
@@ -262,28 +263,46 @@ class ZImageTransformer(nn.Module):
         return t.reshape(b, c, f, h, w)
 
     # ------------------------------------------------------------------ one block on a view of the stream
-    def _block(self, blk, lo, hi, cos_sin, t_emb):
+    def _modulation(self, blk, t_emb):
+        """(scale_msa, gate_msa, scale_mlp, gate_mlp) of a block, or four Nones for an unmodulated one: the scales
+        as views of the adaLN output (the kernels add the 1), the gates through tanh."""
+        if not blk.modulated:
+            return None, None, None, None
+        d = self.cfg.dim
+        mod = _call(blk.adaLN_modulation[0], t_emb)          # [B, 4D]: scale_msa, gate_msa, scale_mlp, gate_mlp
+        return (mod[:, 0:d], ops.vec_sum_act(mod[:, d:2 * d], act="tanh"), mod[:, 2 * d:3 * d],
+                ops.vec_sum_act(mod[:, 3 * d:4 * d], act="tanh"))
+
+    def _run_blocks(self, blocks, lo, hi, cos_sin, t_emb):
+        """A run of blocks on rows lo:hi of the stream. Every post-norm + gated residual also writes the pre-norm
+        of whatever comes next on the same rows (this block's FFN, or the next block's attention), so the stream is
+        read once per sub-layer instead of twice."""
         xs, nbuf, qkv, attn, ybuf, ffb = (t[:, lo:hi] for t in (self.xs, self.nbuf, self.qkv, self.attn, self.ybuf,
                                                                 self.ffb))
-        d, heads, eps = self.cfg.dim, self.cfg.n_heads, self.cfg.norm_eps
-        a, ff = blk.attention, blk.feed_forward
-        scale_msa = gate_msa = scale_mlp = gate_mlp = None
-        if blk.modulated:
-            mod = _call(blk.adaLN_modulation[0], t_emb)          # [B, 4D]: scale_msa, gate_msa, scale_mlp, gate_mlp
-            scale_msa, scale_mlp = mod[:, 0:d], mod[:, 2 * d:3 * d]
-            gate_msa = ops.vec_sum_act(mod[:, d:2 * d], act="tanh")
-            gate_mlp = ops.vec_sum_act(mod[:, 3 * d:4 * d], act="tanh")
-        ops.norm_modulate(xs, None, scale_msa, weight=blk.attention_norm1.weight.data, eps=eps, rms=True, out=nbuf)
-        self._qkv(blk)(nbuf, qkv)
-        ops.qknorm_rope(qkv, heads, a.norm_q.weight.data, a.norm_k.weight.data, a.norm_q.weight.data,
-                        a.norm_k.weight.data, 0, cos_sin, a.norm_q.eps)
-        ops.fmha(qkv, heads, out=attn)
-        _call(a.to_out[0], attn, out=ybuf)
-        ops.norm_gate_residual(ybuf, blk.attention_norm2.weight.data, xs, gate_msa, eps)
-        ops.norm_modulate(xs, None, scale_mlp, weight=blk.ffn_norm1.weight.data, eps=eps, rms=True, out=nbuf)
-        self._swiglu(blk)(nbuf, ffb)
-        _call(ff.w2, ffb, out=ybuf)
-        ops.norm_gate_residual(ybuf, blk.ffn_norm2.weight.data, xs, gate_mlp, eps)
+        heads, eps = self.cfg.n_heads, self.cfg.norm_eps
+        mods = [self._modulation(blk, t_emb) for blk in blocks]
+        for i, blk in enumerate(blocks):
+            a, ff = blk.attention, blk.feed_forward
+            scale_msa, gate_msa, scale_mlp, gate_mlp = mods[i]
+            if i == 0:
+                ops.norm_modulate(xs, None, scale_msa, weight=blk.attention_norm1.weight.data, eps=eps, rms=True,
+                                  out=nbuf)
+            self._qkv(blk)(nbuf, qkv)
+            ops.qknorm_rope(qkv, heads, a.norm_q.weight.data, a.norm_k.weight.data, a.norm_q.weight.data,
+                            a.norm_k.weight.data, 0, cos_sin, a.norm_q.eps)
+            ops.fmha(qkv, heads, out=attn)
+            _call(a.to_out[0], attn, out=ybuf)
+            ops.norm_gate_residual(ybuf, blk.attention_norm2.weight.data, xs, gate_msa, eps,
+                                   next_weight=blk.ffn_norm1.weight.data, next_scale=scale_mlp, next_out=nbuf)
+            self._swiglu(blk)(nbuf, ffb)
+            _call(ff.w2, ffb, out=ybuf)
+            if i + 1 < len(blocks):
+                nxt = blocks[i + 1]
+                ops.norm_gate_residual(ybuf, blk.ffn_norm2.weight.data, xs, gate_mlp, eps,
+                                       next_weight=nxt.attention_norm1.weight.data, next_scale=mods[i + 1][0],
+                                       next_out=nbuf)
+            else:
+                ops.norm_gate_residual(ybuf, blk.ffn_norm2.weight.data, xs, gate_mlp, eps)
 
     # ------------------------------------------------------------------ forward
     def forward(self, x: torch.Tensor, timestep: torch.Tensor, cap_feats: torch.Tensor) -> torch.Tensor:
@@ -310,19 +329,16 @@ class ZImageTransformer(nn.Module):
         _call(self.all_x_embedder[cfg.key], tokens.contiguous(), out=xs[:, :si])
         if si > n_img:
             xs[:, n_img:si] = self.x_pad_token.data.float()
-        for blk in self.noise_refiner:
-            self._block(blk, 0, si, cs_img, t_emb)
+        self._run_blocks(list(self.noise_refiner), 0, si, cs_img, t_emb)
 
         cn = ops.norm_modulate(cap.contiguous(), weight=self.cap_embedder[0].weight.data, eps=self.cap_embedder[0].eps,
                                rms=True)
         _call(self.cap_embedder[1], cn, out=xs[:, si:])
         if sc > n_cap:
             xs[:, si + n_cap:] = self.cap_pad_token.data.float()
-        for blk in self.context_refiner:
-            self._block(blk, si, si + sc, cs_cap, None)
+        self._run_blocks(list(self.context_refiner), si, si + sc, cs_cap, None)
 
-        for blk in self.layers:
-            self._block(blk, 0, si + sc, cs_all, t_emb)
+        self._run_blocks(list(self.layers), 0, si + sc, cs_all, t_emb)
 
         fl = self.all_final_layer[cfg.key]
         scale = _call(fl.adaLN_modulation[0], ops.vec_sum_act(t_emb, act="silu"))

@@ -156,3 +156,28 @@ def test_denoise_loop_with_and_without_guidance(lib_built):
     step = zi.denoise_step(lat, cap, neg, 0.7, -0.1, 3.0)
     ref = lat + (n_pos + 3.0 * (n_pos - n_neg)) * -0.1
     torch.testing.assert_close(step, ref, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("scaled", [True, False])
+def test_norm_gate_residual_with_following_pre_norm(lib_built, scaled):
+    """The fused second stage equals norm_modulate(rms) applied to the updated stream."""
+    from mflux_b200 import ops
+
+    g = torch.Generator(device="cuda").manual_seed(17)
+    b, s, d, lo, hi = 2, 40, 3840, 4, 36
+    y = (torch.randn(b, s, d, device="cuda", generator=g) * 2).to(torch.bfloat16)
+    res = torch.randn(b, s, d, device="cuda", generator=g)
+    w1 = (1 + 0.1 * torch.randn(d, device="cuda", generator=g)).to(torch.bfloat16)
+    w2 = (1 + 0.1 * torch.randn(d, device="cuda", generator=g)).to(torch.bfloat16)
+    gate = torch.tanh(torch.randn(b, d, device="cuda", generator=g)).to(torch.bfloat16)
+    scale = (0.3 * torch.randn(b, 4 * d, device="cuda", generator=g)).to(torch.bfloat16)[:, 2 * d:3 * d] if scaled else None
+    res_a, res_b = res.clone(), res.clone()
+    nb = torch.zeros(b, s, d, device="cuda", dtype=torch.bfloat16)
+    ops.norm_gate_residual(y[:, lo:hi], w1, res_a[:, lo:hi], gate, 1e-5, next_weight=w2, next_scale=scale,
+                           next_out=nb[:, lo:hi])
+    ops.norm_gate_residual(y[:, lo:hi], w1, res_b[:, lo:hi], gate, 1e-5)
+    ref = ops.norm_modulate(res_b[:, lo:hi], None, scale, weight=w2, eps=1e-5, rms=True)
+    torch.cuda.synchronize()
+    assert torch.equal(res_a, res_b)
+    assert rel_l2(nb[:, lo:hi], ref.float().cpu().numpy()) <= 1e-3
+    assert (nb[:, :lo] == 0).all() and (nb[:, hi:] == 0).all()
