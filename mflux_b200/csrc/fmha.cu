@@ -5,13 +5,14 @@
 //
 // One CTA = one (sample, head, 128-query tile); two CTAs share an SM. Keys go in tiles of 64 and the score tile
 // S is double-buffered in tensor memory, so S of tile j+1 is computed while the softmax of tile j runs and the
-// softmax warps never wait for a matmul in steady state. 352 threads:
+// softmax warps never wait for a matmul in steady state. 384 threads:
 //   warp 0     TMA producer: Q once, then K tiles of 64 keys into two stages (128-byte swizzle, two 64-wide
 //              halves of d); warp 10 does the same for V
-//   warp 1     allocates 256 TMEM columns (S0 | S1 | O), issues tcgen05.mma in the order S(0), then per tile j:
-//              S(j+1), O += P(j) V(j):
-//                S[128 q x 64 keys] = Q K^T             (both operands from shared memory, K-major)
-//                O[128 q x 128 d]  += P V               (P bf16 from tensor memory, V MN-major from shared memory)
+//   warp 1     allocates 256 TMEM columns (S0 | S1 | O) and issues S(t) = Q K(t)^T (both operands from shared
+//              memory, K-major) into buffer t & 1 once P(t-2) V(t-2), which read that buffer, has completed
+//   warp 11    issues O += P(j) V(j) (P bf16 from tensor memory, V MN-major from shared memory). Two issuing warps
+//              because tcgen05.mma issue blocks while the pipe is busy: with one warp the waits and commits of one
+//              kind of product delayed the other by a third of the tile time
 //   warps 2-9  softmax, two warps per 32-row quarter of the tile, each owning 32 of the 64 key columns
 //              (thread = query row): one tcgen05.ld of its S columns into registers, row maximum exchanged
 //              with the partner warp through shared memory, running max kept stale until it would grow by
@@ -35,7 +36,8 @@ constexpr int BKV = 32 * PARTS;              // keys per tile
 constexpr int HD = 128;
 constexpr int NUM_SOFTMAX_WARPS = 4 * PARTS;
 constexpr int V_PRODUCER_WARP = 2 + NUM_SOFTMAX_WARPS;
-constexpr int NUM_THREADS = (V_PRODUCER_WARP + 1) * 32;
+constexpr int PV_ISSUER_WARP = V_PRODUCER_WARP + 1;   // warp 1 issues S = Q K^T, this one O += P V
+constexpr int NUM_THREADS = (PV_ISSUER_WARP + 1) * 32;
 constexpr int CTAS_PER_SM = PARTS == 2 ? 2 : 1;
 constexpr int OC = HD / PARTS;               // columns of O a softmax warp rescales and writes out
 constexpr int Q_BYTES = BQ * HD * 2;        // 32 KiB: [128 rows][128 d] bf16 as two 16 KiB halves of d
@@ -244,13 +246,17 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       __syncwarp();
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------ issuer of S(t) = Q K(t)^T into S buffer t & 1
+    // Two issuing warps, so that the barrier waits and commits of one kind of product do not hold up the other.
+    // S(t) overwrites the buffer that held P(t-2): it waits for the completion of P(t-2) V(t-2), which the other
+    // issuer commits to v_empty.
     constexpr uint32_t IDESC_S = make_idesc(FMT_BF16, FMT_BF16, BQ, BKV);       // K-major x K-major
-    constexpr uint32_t IDESC_O = make_idesc_b_mn(FMT_BF16, FMT_BF16, BQ, HD);   // P (TMEM) x V (MN-major)
-    // S(t) = Q K(t)^T into S buffer t & 1
-    auto issue_s = [&](int t) -> bool {
+    bool ok = mbar_wait(q_full, 0, DEV_TIMEOUT_ATTN);
+    for (int t = 0; t < n_tiles && ok; ++t) {
       const int st = t & 1;
-      if (!mbar_wait(k_full + 8 * st, static_cast<uint32_t>((t >> 1) & 1), DEV_TIMEOUT_ATTN)) return false;
+      const uint32_t ph = static_cast<uint32_t>((t >> 1) & 1);
+      if (!mbar_wait(k_full + 8 * st, ph, DEV_TIMEOUT_ATTN)) break;
+      if (t >= 2 && !mbar_wait(v_empty + 8 * st, ph ^ 1u, DEV_TIMEOUT_ATTN)) break;
       tc_fence_after();
       if (lane == 0) {
 #pragma unroll
@@ -263,22 +269,21 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
         umma_commit(s_full + 8 * st);
       }
       __syncwarp();
-      return true;
-    };
-    bool ok = mbar_wait(q_full, 0, DEV_TIMEOUT_ATTN) && issue_s(0);
-    for (int j = 0; j < n_tiles && ok; ++j) {
+    }
+  } else if (warp == PV_ISSUER_WARP) {
+    // ------------------------------------------------------------ issuer of O += P(j) V(j)
+    constexpr uint32_t IDESC_O = make_idesc_b_mn(FMT_BF16, FMT_BF16, BQ, HD);   // P (TMEM) x V (MN-major)
+    for (int j = 0; j < n_tiles; ++j) {
       const int st = j & 1;
       const uint32_t ph = static_cast<uint32_t>((j >> 1) & 1);
-      // the buffer S(j+1) goes to held P(j-1), whose P V product was issued one iteration ago and runs first
-      if (j + 1 < n_tiles && !issue_s(j + 1)) break;
       if (!mbar_wait(p_full + 8 * st, ph, DEV_TIMEOUT_ATTN) || !mbar_wait(v_full + 8 * st, ph, DEV_TIMEOUT_ATTN))
         break;
       tc_fence_after();
       if (lane == 0) {
 #pragma unroll
         for (int i = 0; i < BKV / 16; ++i) {
-          // A: 16 keys of P = 8 TMEM columns (keys 0-31 at columns 0-15 of the buffer, keys 32-63 at 32-47);
-          // B: 16 key rows of V = 2048 B further, d halves 8 KiB apart
+          // A: 16 keys of P = 8 TMEM columns (the 32 keys of softmax part p at columns 32 p .. 32 p + 15 of the
+          // buffer); B: 16 key rows of V = 2048 B further, d halves KV_HALF apart
           umma_f16_ts(tmem_base + COL_O, tmem_base + COL_S + BKV * st + (i >> 1) * 32 + 8 * (i & 1),
                       smem_desc_sw128_mn(v_s + st * KV_BYTES + i * 2048, KV_HALF), IDESC_O, (j | i) != 0 ? 1u : 0u);
         }
@@ -287,7 +292,7 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       }
       __syncwarp();
     }
-  } else {
+  } else if (warp >= 2 && warp < V_PRODUCER_WARP) {
     // ------------------------------------------------------------ softmax + output (thread = query row)
     const int qd = warp & 3;          // TMEM lane quarter this warp may access
     const int pt = (warp - 2) >> 2;   // which 32 of the tile's key columns (and which OC columns of d at the end)
