@@ -349,8 +349,8 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     bool ok = true;
     for (int tile = pair; tile < p.total_tiles && ok; tile += num_pairs) {
       for (int s = 0; s < num_st; ++s) {
-        if (!mbar_wait(w_full(st), ph_t, DEV_TIMEOUT_TMA_FULL) ||
-            !mbar_wait(d_empty(sd), ph_d ^ 1u, DEV_TIMEOUT_DQ_EMPTY)) {
+        if (!mbar_wait_sleep(d_empty(sd), ph_d ^ 1u, DEV_TIMEOUT_DQ_EMPTY) ||
+            !mbar_wait(w_full(st), ph_t, DEV_TIMEOUT_TMA_FULL)) {
           ok = false;
           break;
         }
