@@ -56,3 +56,41 @@ def test_argument_validation_needs_no_gpu(lib_built):
     assert lib.mfx_qlinear_prepared_bytes(12288, 3072, 4, 64) == 12288 * 3072 // 2 + 12288 * 48 * 4
     assert lib.mfx_qlinear_prepared_bytes(12288, 3000, 4, 64) == 0
     assert lib.mfx_qlinear_prepared_bytes(10, 64, 4, 64) == 512 + 40  # 320 code bytes padded to 256s + pairs
+
+
+def test_validation_of_the_later_entry_points(lib_built):
+    """SwiGLU epilogue, post/pre-norm, gated residual, guidance combine and attention reject malformed calls on the
+    host (status codes of include/mfx.h: -1 shape, -2 alignment, -4 dtype, -7 null, -9 too large)."""
+    lib = _lib.load()
+    a = _lib.QLinearArgs()
+    a.x = a.wq = a.scales = a.biases = a.y = a.workspace = 1024
+    a.rows, a.batch, a.K, a.N, a.bits, a.group_size = 128, 1, 128, 24, 4, 64
+    a.workspace_bytes = 1 << 20
+    a.x_row_stride, a.y_row_stride, a.y_dtype = 128, 24, _lib.BF16
+    a.epilogue = _lib.EPI_SWIGLU
+    assert lib.mfx_qlinear_ex(a, None) == -1          # N = 24 is not a multiple of 16
+    a.epilogue = 6
+    assert lib.mfx_qlinear_ex(a, None) == -1          # unknown epilogue
+    p = _lib.PostPreNormArgs()
+    assert lib.mfx_post_pre_norm(p, None) == -7
+    assert lib.mfx_post_pre_norm(None, None) == -7
+    p.y = p.weight = p.residual = 1024
+    p.y_dtype, p.weight_dtype = _lib.BF16, _lib.BF16
+    p.rows, p.batch, p.D = 4, 1, 100
+    assert lib.mfx_post_pre_norm(p, None) == -1       # D % 8
+    p.D = 8192
+    assert lib.mfx_post_pre_norm(p, None) == -9       # wider than the kernel holds in registers
+    p.D, p.y_row_stride, p.res_row_stride = 256, 256, 250
+    assert lib.mfx_post_pre_norm(p, None) == -2       # residual rows not 16-byte aligned
+    p.res_row_stride, p.y_dtype = 256, _lib.F16
+    assert lib.mfx_post_pre_norm(p, None) == -4
+    p.y_dtype, p.next_out = _lib.BF16, 2048
+    assert lib.mfx_post_pre_norm(p, None) == -7       # second stage without its norm weight
+    assert lib.mfx_gate_residual(1024, _lib.BF16, None, 0, 1024, _lib.BF16, 256, 1024, 1024, 250, 0, 1, 4, 256, None) == -2
+    assert lib.mfx_gate_residual(1024, _lib.BF16, None, 0, 1024, _lib.BF16, 256, 1024, 1024, 128, 0, 1, 4, 256, None) == -1
+    assert lib.mfx_gate_residual(None, _lib.BF16, None, 0, 1024, _lib.BF16, 256, 1024, 1024, 256, 0, 1, 4, 256, None) == -7
+    assert lib.mfx_cfg_combine(1024, 1024, _lib.BF16, 3.0, 2, 1024, 4, 64, None) == -1   # unknown mode
+    assert lib.mfx_cfg_combine(1024, 1024, _lib.BF16, 3.0, 0, 1024, 4, 2048, None) == -1  # more channels than a warp holds
+    assert lib.mfx_fmha(1024, 1024, 1024, 384, 0, 0, 1, 1, 1.0, 1024, 128, 0, None) == -1
+    assert lib.mfx_fmha(1024, 1024, 1028, 384, 0, 16, 1, 1, 1.0, 1024, 128, 0, None) == -2
+    assert lib.mfx_vec_sum_act(1024, None, None, _lib.BF16, 3, 1024, _lib.BF16, 8, None) == -1
