@@ -182,3 +182,36 @@ def test_flow_match_euler_discrete_scheduler():
     import torch
     lat, noise = torch.ones(4), torch.full((4,), 2.0)
     assert torch.allclose(s.step(noise, 3, lat), lat + 2.0 * float(s.sigmas[4] - s.sigmas[3]))
+
+
+def test_tensor_parallel_shards_are_slices_of_the_full_quantization():
+    """Quantizing a shard equals slicing the quantized full weight: output-row shards trivially, input-column
+    shards because groups of 64 run along K and K / tp stays a multiple of 64 (the rule QwenTransformer enforces)."""
+    import numpy as np
+
+    from oracle import quant
+
+    rng = np.random.default_rng(5)
+    n, k, tp = 48, 512, 4
+    w = (rng.standard_normal((n, k)) * 0.05).astype(np.float32)
+    for bits in (4, 8):
+        full_q, full_s, full_b = quant.quantize_affine(w, 64, bits)
+        words = k * bits // 32
+        for r in range(tp):
+            rows = slice(r * n // tp, (r + 1) * n // tp)
+            q, s, b = quant.quantize_affine(w[rows], 64, bits)
+            assert np.array_equal(q, full_q[rows]) and np.array_equal(s, full_s[rows]) and np.array_equal(b, full_b[rows])
+            cols = slice(r * k // tp, (r + 1) * k // tp)
+            q, s, b = quant.quantize_affine(np.ascontiguousarray(w[:, cols]), 64, bits)
+            assert np.array_equal(q, full_q[:, r * words // tp:(r + 1) * words // tp])
+            assert np.array_equal(s, full_s[:, r * (k // 64) // tp:(r + 1) * (k // 64) // tp])
+            assert np.array_equal(b, full_b[:, r * (k // 64) // tp:(r + 1) * (k // 64) // tp])
+        # and the row-split products add up to the full product
+        x = rng.standard_normal((5, k)).astype(np.float32)
+        y_full = quant.qlinear(x, full_q, full_s, full_b, None, 64, bits)
+        y_sum = sum(quant.qlinear(x[:, r * k // tp:(r + 1) * k // tp],
+                                  full_q[:, r * words // tp:(r + 1) * words // tp],
+                                  full_s[:, r * (k // 64) // tp:(r + 1) * (k // 64) // tp],
+                                  full_b[:, r * (k // 64) // tp:(r + 1) * (k // 64) // tp], None, 64, bits)
+                    for r in range(tp))
+        np.testing.assert_allclose(y_sum, y_full, rtol=1e-4, atol=1e-4)
