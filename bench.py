@@ -259,6 +259,7 @@ def qwen_spec(args):
         from mflux_b200.qwen import QwenImage
         from mflux_b200.schedulers import LinearScheduler
 
+        graph = not args.no_cuda_graph
         # 1 rank: both branches as a batch of 2. Even rank counts: the prompt branch on the first half of the
         # ranks, the negative-prompt branch on the second half, tensor parallelism inside each half.
         if world > 1 and args.qwen_parallel == "cfg+tp":
@@ -268,9 +269,10 @@ def qwen_spec(args):
             cfg_groups = [dist.new_group([r, r + tp]) for r in range(tp)]
             pipe = QwenImage(quantize=4, model_config=cfg, device=dev, seed=1234, tp_rank=tp_rank, tp_world=tp,
                              tp_group=tp_groups[branch] if tp > 1 else None, cfg_rank=branch,
-                             cfg_group=cfg_groups[tp_rank])
+                             cfg_group=cfg_groups[tp_rank], cuda_graph=graph)
         else:
-            pipe = QwenImage(quantize=4, model_config=cfg, device=dev, seed=1234, tp_rank=rank, tp_world=world)
+            pipe = QwenImage(quantize=4, model_config=cfg, device=dev, seed=1234, tp_rank=rank, tp_world=world,
+                             cuda_graph=graph)
         g = torch.Generator(device="cpu").manual_seed(100)   # every rank sees the same image and prompts
         lat_h = torch.randn(1, si, cfg.in_channels, generator=g).pin_memory()
         emb_h = torch.randn(b, st, cfg.joint_attention_dim, generator=g).to(torch.bfloat16).pin_memory()
@@ -282,6 +284,15 @@ def qwen_spec(args):
             return pipe.denoise_step(lat_d, emb_d[:1], emb_d[1:], float(sched.sigmas[j]), sched.dt(j), 4.0, height,
                                      width)
 
+        def eager(i, lat_d, emb_d):   # the same step launch by launch (the per-launch event pairs need it)
+            pipe.cuda_graph = False
+            try:
+                return step(i, lat_d, emb_d)
+            finally:
+                pipe.cuda_graph = graph
+
+        step.eager = eager
+        step.release = pipe.release_graphs   # recorded collectives must go before the process group does
         return [lat_h, emb_h], out_h, step
 
     par = "1 GPU" if args.gpus == 1 else (f"prompt / negative-prompt branch x tensor-parallel {args.gpus // 2}"
@@ -290,7 +301,8 @@ def qwen_spec(args):
         "metric": "qwen_image_w4_dit_steps_per_sec_1328px_cfg2",
         "unit": "steps/s (one step = prompt + negative prompt of one image, 2 x 7145 tokens through 60 blocks)",
         "workload": (f"Qwen-Image-shaped dual-stream MMDiT {cfg.num_layers} blocks, hidden {d}, {cfg.heads}x128 heads, "
-                     f"W4 g64, CFG batch 2, {si} image + {st} text tokens, {par}"),
+                     f"W4 g64, CFG batch 2, {si} image + {st} text tokens, {par}, "
+                     f"{'launches issued one by one' if args.no_cuda_graph else 'step replayed as a CUDA graph'}"),
         "scaling": "strong", "lin": lin, "attn": attn, "per_gpu_batch": b, "build": build,
         "l2_policy": "inputs larger than L2 (10 GB of packed weights, split over the ranks, stream every step)",
     }
@@ -373,6 +385,8 @@ def main():
     ap.add_argument("--qwen-parallel", default="cfg+tp", choices=["cfg+tp", "tp"],
                     help="qwen on N > 1 GPUs: split the two guidance branches over the halves of the ranks and use "
                          "tensor parallelism inside each half (default), or tensor parallelism over all ranks")
+    ap.add_argument("--no-cuda-graph", action="store_true",
+                    help="qwen: issue the step's launches one by one instead of replaying them as a CUDA graph")
     args = ap.parse_args()
 
     if args.workload == "sweep":
@@ -457,6 +471,15 @@ def main():
     barrier()
     ms_e2e = t0.elapsed_time(t1)
     clocks = sampler.stop()
+    trace_steps = args.steps
+    if not trace and hasattr(step, "eager"):
+        # a replayed graph has no per-launch events: time the quantized linears on launch-by-launch passes
+        trace_steps = min(2, args.steps)
+        ops.QLINEAR_TRACE = []
+        for i in range(trace_steps):
+            step.eager(i, *dev_in)
+        barrier()
+        trace, ops.QLINEAR_TRACE = ops.QLINEAR_TRACE, None
     status = ops.poll_device_status()
 
     times = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
@@ -490,7 +513,7 @@ def main():
             "roofline": {"bound": "tensor", "kernel": "qmm_kernel (quantized linear)", "achieved": achieved,
                          "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak if peak else None,
                          "peak_kind": peak_kind, "burst_peak": burst, "launches": len(trace),
-                         "share_of_step_time": q_ms / ms if ms > 0 else None, "traffic": traffic,
+                         "share_of_step_time": (q_ms / trace_steps) / (ms / args.steps) if ms > 0 else None, "traffic": traffic,
                          "traffic_unit": "DRAM bytes per launch, mean over the step's launches (ncu)"},
             "step_tflops": flops / 1e12 * args.steps / (ms / 1e3) / (world if spec["scaling"] == "strong" else 1),
         }
@@ -499,6 +522,7 @@ def main():
             line["cpu_baseline"] = {"value": tf * 1e12 / flops, "unit": spec["unit"], "cores": cores, "kind": "port",
                                     "sample": desc}
         print(json.dumps(line), flush=True)
+    getattr(step, "release", lambda: None)()
     if world > 1:
         dist.destroy_process_group()
 

@@ -288,7 +288,7 @@ class QwenImage:
 
     def __init__(self, quantize: int | None = None, model_config: QwenConfig | None = None, device="cuda",
                  seed: int = 0, stored_quantization: int | None = None, tp_rank: int = 0, tp_world: int = 1,
-                 tp_group=None, cfg_rank: int | None = None, cfg_group=None):
+                 tp_group=None, cfg_rank: int | None = None, cfg_group=None, cuda_graph: bool = False):
         bits, warning = resolution.resolve(stored_quantization, quantize)
         if warning:
             print(f"Warning: {warning}")
@@ -296,6 +296,7 @@ class QwenImage:
         self.bits = bits
         self.model_config = model_config or QwenConfig()
         self.cfg_rank, self.cfg_group = cfg_rank, cfg_group
+        self.cuda_graph, self._captured = cuda_graph, {}
         self.transformer = QwenTransformer(self.model_config, bits=bits, device=device, seed=seed, tp_rank=tp_rank,
                                            tp_world=tp_world, tp_group=tp_group)
 
@@ -313,23 +314,54 @@ class QwenImage:
         checkpoint.load_into(self.transformer, base_path, "transformer", self.bits)
         if hasattr(self.transformer, "_fused"):
             self.transformer._fused = {}
+        self.release_graphs()   # recorded graphs hold the prepared weights of the old parameters
 
     def predict_noise(self, latents, prompt_embeds, negative_prompt_embeds, sigma, height, width):
-        """(noise for the prompt, noise for the negative prompt), each [B, Si, C]."""
+        """(noise for the prompt, noise for the negative prompt), each [B, Si, C]. `sigma` is a number or a
+        one-element tensor on the device."""
         b = latents.shape[0]
+        if not torch.is_tensor(sigma):
+            sigma = torch.full((1,), sigma, device=latents.device)
+        sigma = sigma.reshape(1).float()
         if self.cfg_group is None:
             both = self.transformer(torch.cat([latents, latents]), torch.cat([prompt_embeds, negative_prompt_embeds]),
-                                    torch.full((2 * b,), sigma, device=latents.device), height, width)
+                                    sigma.expand(2 * b), height, width)
             return both[:b], both[b:]
         mine = self.transformer(latents, prompt_embeds if self.cfg_rank == 0 else negative_prompt_embeds,
-                                torch.full((b,), sigma, device=latents.device), height, width).contiguous()
-        parts = [torch.empty_like(mine), torch.empty_like(mine)]
-        dist.all_gather(parts, mine, group=self.cfg_group)
+                                sigma.expand(b), height, width).contiguous()
+        parts = torch.empty(2, *mine.shape, dtype=mine.dtype, device=mine.device)
+        dist.all_gather_into_tensor(parts, mine, group=self.cfg_group)
         return parts[0], parts[1]
 
+    def guided_noise(self, latents, prompt_embeds, negative_prompt_embeds, sigma, guidance, height, width):
+        """The guidance-combined prediction of one step. With `cuda_graph=True` the two evaluations, their
+        collectives and the combine replay as one CUDA graph (one graph per shape, guidance scale and image size);
+        the result is then the graph's output buffer, valid until the next call."""
+        def run(lat, pos, neg, sig):
+            noise, noise_negative = self.predict_noise(lat, pos, neg, sig, height, width)
+            return ops.cfg_combine(noise, noise_negative, guidance, mode="qwen")
+
+        if not torch.is_tensor(sigma):
+            sigma = torch.full((1,), sigma, device=latents.device)
+        if not self.cuda_graph:
+            return run(latents, prompt_embeds, negative_prompt_embeds, sigma)
+        from .graphs import CapturedStep
+
+        key = (float(guidance), height, width)
+        step = self._captured.get(key)
+        if step is None:
+            step = self._captured[key] = CapturedStep(run)
+        return step(latents, prompt_embeds, negative_prompt_embeds, sigma.reshape(1).float())
+
+    def release_graphs(self) -> None:
+        """Drops every recorded CUDA graph (call before `torch.distributed.destroy_process_group`: a live graph
+        with recorded collectives keeps the communicator from shutting down)."""
+        for step in self._captured.values():
+            step.release()
+        self._captured = {}
+
     def denoise_step(self, latents, prompt_embeds, negative_prompt_embeds, sigma, dt, guidance, height, width):
-        noise, noise_negative = self.predict_noise(latents, prompt_embeds, negative_prompt_embeds, sigma, height, width)
-        guided = ops.cfg_combine(noise, noise_negative, guidance, mode="qwen")
+        guided = self.guided_noise(latents, prompt_embeds, negative_prompt_embeds, sigma, guidance, height, width)
         return ops.euler_step(latents, guided, dt)
 
     def generate_image(self, seed: int, prompt_embeds: torch.Tensor, negative_prompt_embeds: torch.Tensor,

@@ -76,6 +76,36 @@ def test_denoise_loop_runs(lib_built):
     assert lat.shape == (1, 16, 64) and torch.isfinite(lat).all()
 
 
+def test_cuda_graph_replay_equals_eager_step(lib_built):
+    """The recorded step takes latents, embeddings and the noise level as tensors: replays with new values equal
+    the launch-by-launch step bit for bit, and the launch counter advances by the recorded launches."""
+    from mflux_b200 import ops
+    from mflux_b200.qwen import QwenConfig, QwenImage
+
+    cfg = QwenConfig(hidden=256, heads=2, num_layers=2, joint_attention_dim=64)
+    eager = QwenImage(quantize=4, model_config=cfg, seed=7)
+    graphed = QwenImage(quantize=4, model_config=cfg, seed=7, cuda_graph=True)
+    lat, ctx = _inputs(cfg, 1, 64, 96, 24, 1)
+    _, neg = _inputs(cfg, 1, 64, 96, 24, 2)
+    lat, ctx, neg = lat.cuda().float(), ctx.cuda(), neg.cuda()
+    counts, seen = [], []
+    for sig, scale in ((0.9, 1.0), (0.4, 0.7), (0.1, 1.3)):
+        n0 = ops.LAUNCHES[0]
+        b = graphed.denoise_step(lat * scale, ctx, neg * scale, sig, -0.1, 4.0, 64, 96)
+        counts.append(ops.LAUNCHES[0] - n0)
+        a = eager.denoise_step(lat * scale, ctx, neg * scale, sig, -0.1, 4.0, 64, 96)
+        torch.cuda.synchronize()
+        assert torch.equal(a, b)
+        seen.append(b.clone())
+    assert not torch.equal(seen[0], seen[1]) and not torch.equal(seen[1], seen[2])
+    assert counts[1] == counts[2] > 20          # replays count the recorded launches (+ the Euler update)
+    assert len(graphed._captured) == 1
+    # another image size records its own graph
+    lat2, _ = _inputs(cfg, 1, 96, 64, 24, 3)
+    graphed.denoise_step(lat2.cuda().float(), ctx, neg, 0.5, -0.1, 4.0, 96, 64)
+    assert len(graphed._captured) == 2
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="tensor parallelism needs two GPUs")
 def test_tensor_parallel_matches_single_gpu(lib_built, tmp_path):
     """Two ranks (NCCL, NVLS off) against one: same seeded weights, outputs within tolerance, for the
@@ -90,3 +120,5 @@ def test_tensor_parallel_matches_single_gpu(lib_built, tmp_path):
     assert err <= TOL, err
     cfg_err = float((tmp_path / "cfg_err.txt").read_text())
     assert cfg_err <= 2e-3, cfg_err
+    graph_err = float((tmp_path / "graph_err.txt").read_text())
+    assert graph_err <= 1e-5, graph_err

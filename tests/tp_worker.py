@@ -40,6 +40,21 @@ def main():
         whole = QwenImage(quantize=4, model_config=cfg, seed=5)
         z = whole.denoise_step(lat, ctx, neg, 0.7, -0.05, 4.0, 96, 144)
         (out_dir / "cfg_err.txt").write_text(str(rel_l2(z_split, z.cpu().numpy())))
+    # the tensor-parallel step (chunked all-reduces included) replayed as a CUDA graph equals the same step issued
+    # launch by launch, also for a noise level and latents the graph was not recorded with
+    eager = QwenImage(quantize=4, model_config=cfg, seed=5, tp_rank=rank, tp_world=world)
+    graphed = QwenImage(quantize=4, model_config=cfg, seed=5, tp_rank=rank, tp_world=world, cuda_graph=True)
+    for pipe in (eager, graphed):
+        pipe.transformer.tp_chunks, pipe.transformer.tp_chunk_min_rows = 3, 8
+    worst = 0.0
+    for sig, scale in ((0.7, 1.0), (0.2, 0.5), (0.45, 2.0)):
+        z_e = eager.denoise_step(lat * scale, ctx, neg, sig, -0.05, 4.0, 96, 144)
+        z_g = graphed.denoise_step(lat * scale, ctx, neg, sig, -0.05, 4.0, 96, 144)
+        torch.cuda.synchronize()
+        worst = max(worst, rel_l2(z_g, z_e.cpu().numpy()))
+    if rank == 0:
+        (out_dir / "graph_err.txt").write_text(str(worst))
+    graphed.release_graphs()   # a live graph with recorded collectives would keep the communicator from closing
     dist.barrier()
     dist.destroy_process_group()
 
