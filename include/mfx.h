@@ -151,6 +151,18 @@ typedef struct mfx_qlinear_args {
   void* y;
   int y_dtype;              /* MFX_BF16 or MFX_F32 */
   int64_t y_row_stride, y_batch_stride;
+  /* Optional low-rank term, added to the product before bias and epilogue (lora_r == 0: none). Replaces
+   * `scale * (x @ lora_A) @ lora_B` of LoRALinear.__call__ (src/mflux/models/common/lora/layer/
+   * linear_lora_layer.py:50-53) and the sum over adapters of FusedLoRALinear.__call__
+   * (fused_linear_lora_layer.py:13-20): the caller passes t = x @ [A_1 | A_2 | ...] and
+   * lora_b[n, :] = [scale_1 * B_1[:, n] | scale_2 * B_2[:, n] | ...]; the kernel runs them as extra K columns
+   * of the same tensor-core accumulation. Both are bf16 with rows of lora_ld values (a multiple of 64, at most
+   * 1024); columns at and after lora_r must be zero. */
+  const void* lora_t;       /* [batch, rows, lora_ld] */
+  int64_t lora_t_row_stride, lora_t_batch_stride;
+  const void* lora_b;       /* [N, lora_ld], dense */
+  int64_t lora_ld;
+  int64_t lora_r;
 } mfx_qlinear_args;
 int mfx_qlinear_ex(const mfx_qlinear_args* args /* host */, void* stream);
 

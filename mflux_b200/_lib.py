@@ -57,6 +57,12 @@ class QLinearArgs(ctypes.Structure):
         ("y_dtype", c_int),
         ("y_row_stride", c_int64),
         ("y_batch_stride", c_int64),
+        ("lora_t", c_void_p),
+        ("lora_t_row_stride", c_int64),
+        ("lora_t_batch_stride", c_int64),
+        ("lora_b", c_void_p),
+        ("lora_ld", c_int64),
+        ("lora_r", c_int64),
     ]
 
 

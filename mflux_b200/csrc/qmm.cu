@@ -49,6 +49,10 @@ struct Params {
   int rows, batch, N, K;
   int tiles_m_per_sample, tiles_m, tiles_n, total_tiles;
   int band_n;  // n-tiles per band of the tile order (see tile_coords)
+  // Low-rank extension: after the K / 64 quantized groups every tile runs num_ext more stages whose B operand is a
+  // dense bf16 matrix lb [N, r] (read through the codes' staging buffer and copied instead of dequantized) and whose
+  // A operand is t [batch, rows, r]; ext_r is the rank rounded up to 16. num_ext == 0: plain quantized matmul.
+  int num_ext, ext_r;
   const void* bias;
   int bias_dtype;
   int epilogue;
@@ -171,7 +175,8 @@ __device__ __forceinline__ float silu(float v) { return v / (1.0f + __expf(-v));
 template <int BITS, uint32_t WF, int ST, int SD, typename OUT, int EPI, int NUM_DQ_WARPS>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((FIXED_WARPS + NUM_DQ_WARPS) * 32, 1)
 qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
-           const __grid_constant__ CUtensorMap tmap_sb, const Params p) {
+           const __grid_constant__ CUtensorMap tmap_sb, const __grid_constant__ CUtensorMap tmap_t,
+           const __grid_constant__ CUtensorMap tmap_lb, const Params p) {
   using L = Smem<BITS, ST, SD>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -197,6 +202,10 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
   const int lane = threadIdx.x & 31;
   const int num_kb = p.K / BK;
   const int num_st = (num_kb + GPS - 1) / GPS;  // a ragged last stage reads TMA zero fill for its missing group
+  // An extension stage moves as many bytes through the codes' staging buffer as a quantized one: per group
+  // 128 rows x EXT_KG dense bf16 values, 16 (4-bit codes) or 32 (8-bit codes) k-values of the low-rank term.
+  constexpr int EXT_KG = 4 * BITS;
+  const int num_all = num_st + p.num_ext;
   const uint32_t rank = cluster_ctarank();      // 0 = leader of the pair
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
@@ -241,7 +250,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
       const int b = tm / p.tiles_m_per_sample;
       const int r0 = (tm % p.tiles_m_per_sample) * (2 * BM) + static_cast<int>(rank) * BM;
       const int n0 = tn * BN + static_cast<int>(rank) * BN_HALF;
-      for (int s = 0; s < num_st; ++s) {
+      for (int s = 0; s < num_all; ++s) {
         if (!mbar_wait_sleep(t_empty(st), ph ^ 1u, DEV_TIMEOUT_TMA_EMPTY)) {
           ok = false;
           break;
@@ -249,13 +258,26 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         if (lane == 0) {
           if (rank == 0) mbar_arrive_expect_tx(x_full(st), 2 * L::X_STAGE);
           mbar_arrive_expect_tx(w_full(st), L::WQ_STAGE + L::SB_STAGE);
+          if (s < num_st) {
 #pragma unroll
-          for (int g = 0; g < GPS; ++g) {
-            const int kb = s * GPS + g;  // beyond K on a ragged last stage: the loads return zeros
-            tma_load_2d(wq_s + st * L::WQ_STAGE + g * L::WQ_TILE_BYTES, &tmap_w, w_full(st), kb * (BK * BITS / 32),
-                        n0);
-            tma_load_2d(sb_s + st * L::SB_STAGE + g * SB_TILE_BYTES, &tmap_sb, w_full(st), n0, kb);
-            tma_load_3d_pair(x_s + st * L::X_STAGE + g * X_TILE_BYTES, &tmap_x, x_full(st), kb * BK, r0, b);
+            for (int g = 0; g < GPS; ++g) {
+              const int kb = s * GPS + g;  // beyond K on a ragged last stage: the loads return zeros
+              tma_load_2d(wq_s + st * L::WQ_STAGE + g * L::WQ_TILE_BYTES, &tmap_w, w_full(st),
+                          kb * (BK * BITS / 32), n0);
+              tma_load_2d(sb_s + st * L::SB_STAGE + g * SB_TILE_BYTES, &tmap_sb, w_full(st), n0, kb);
+              tma_load_3d_pair(x_s + st * L::X_STAGE + g * X_TILE_BYTES, &tmap_x, x_full(st), kb * BK, r0, b);
+            }
+          } else {
+            // Extension stage: the same byte counts on the same barriers. The dense tile lands where the codes
+            // would, the (scale, bias) load reads past the last group (zero fill, unused), and the activation
+            // tile comes from t: its first EXT_KG columns are the ones the tensor cores will read.
+#pragma unroll
+            for (int g = 0; g < GPS; ++g) {
+              const int k0 = ((s - num_st) * GPS + g) * EXT_KG;
+              tma_load_2d(wq_s + st * L::WQ_STAGE + g * L::WQ_TILE_BYTES, &tmap_lb, w_full(st), k0, n0);
+              tma_load_2d(sb_s + st * L::SB_STAGE + g * SB_TILE_BYTES, &tmap_sb, w_full(st), n0, num_kb + g);
+              tma_load_3d_pair(x_s + st * L::X_STAGE + g * X_TILE_BYTES, &tmap_t, x_full(st), k0, r0, b);
+            }
           }
         }
         __syncwarp();
@@ -282,26 +304,41 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + a * BN;
-        for (int s = 0; s < num_st; ++s) {
+        for (int s = 0; s < num_all; ++s) {
           if (!mbar_wait(x_full(st), ph_t, DEV_TIMEOUT_TMA_FULL) || !mbar_wait(d_full(sd), ph_d, DEV_TIMEOUT_DQ_FULL)) {
             ok = false;
             break;
           }
           tc_fence_after();
           if (lane == 0) {
+            if (s < num_st) {
 #pragma unroll
-            for (int g = 0; g < GPS; ++g) {
-              const uint64_t adesc = smem_desc_sw128(x_s + st * L::X_STAGE + g * X_TILE_BYTES);
-              const uint64_t bdesc = smem_desc_sw128(wd_s + sd * L::WD_STAGE + g * WD_TILE_BYTES);
+              for (int g = 0; g < GPS; ++g) {
+                const uint64_t adesc = smem_desc_sw128(x_s + st * L::X_STAGE + g * X_TILE_BYTES);
+                const uint64_t bdesc = smem_desc_sw128(wd_s + sd * L::WD_STAGE + g * WD_TILE_BYTES);
 #pragma unroll
-              for (int k4 = 0; k4 < BK / 16; ++k4) {
-                // +32 bytes (>>4 = 2) per 16-element K step inside the 128-byte swizzle atom
-                umma_f16_ss_pair(d_tmem, adesc + 2 * k4, bdesc + 2 * k4, IDESC, (s | g | k4) != 0 ? 1u : 0u);
+                for (int k4 = 0; k4 < BK / 16; ++k4) {
+                  // +32 bytes (>>4 = 2) per 16-element K step inside the 128-byte swizzle atom
+                  umma_f16_ss_pair(d_tmem, adesc + 2 * k4, bdesc + 2 * k4, IDESC, (s | g | k4) != 0 ? 1u : 0u);
+                }
+              }
+            } else {
+              // extension stage: only the first EXT_KG k-values of each group's tiles carry data, and only up
+              // to the rank (the tile always starts with a quantized stage, so these always accumulate)
+#pragma unroll
+              for (int g = 0; g < GPS; ++g) {
+                const uint64_t adesc = smem_desc_sw128(x_s + st * L::X_STAGE + g * X_TILE_BYTES);
+                const uint64_t bdesc = smem_desc_sw128(wd_s + sd * L::WD_STAGE + g * WD_TILE_BYTES);
+                const int k0 = ((s - num_st) * GPS + g) * EXT_KG;
+#pragma unroll
+                for (int k4 = 0; k4 < EXT_KG / 16; ++k4) {
+                  if (k0 + 16 * k4 < p.ext_r) umma_f16_ss_pair(d_tmem, adesc + 2 * k4, bdesc + 2 * k4, IDESC, 1u);
+                }
               }
             }
             umma_commit_pair(t_empty(st));
             umma_commit_pair(d_empty(sd));
-            if (s == num_st - 1) umma_commit_pair(acc_full(a));
+            if (s == num_all - 1) umma_commit_pair(acc_full(a));
           }
           __syncwarp();
           if (++st == ST) {
@@ -348,11 +385,38 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     uint32_t ph_t = 0, ph_d = 0;
     bool ok = true;
     for (int tile = pair; tile < p.total_tiles && ok; tile += num_pairs) {
-      for (int s = 0; s < num_st; ++s) {
+      for (int s = 0; s < num_all; ++s) {
         if (!mbar_wait_sleep(d_empty(sd), ph_d ^ 1u, DEV_TIMEOUT_DQ_EMPTY) ||
             !mbar_wait(w_full(st), ph_t, DEV_TIMEOUT_TMA_FULL)) {
           ok = false;
           break;
+        }
+        if (s >= num_st) {
+          // extension stage: the staged bytes are bf16 values already; chunk c of the row goes to chunk c of the
+          // B tile row (the tensor cores read no further than EXT_KG k-values of these stages)
+          const uint8_t* esrc = rd_base + st * L::WQ_STAGE;
+          uint8_t* edst = wr_base + sd * L::WD_STAGE;
+#pragma unroll
+          for (int h = 0; h < MY_CHUNKS; ++h) {
+            const uint32_t c = static_cast<uint32_t>(part * MY_CHUNKS + h);
+            *reinterpret_cast<uint4*>(edst + ((c ^ static_cast<uint32_t>(row & 7)) << 4)) =
+                *reinterpret_cast<const uint4*>(esrc + rd_off[h]);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive_leader(d_full(sd));
+            mbar_arrive(t_empty(st));
+          }
+          if (++st == ST) {
+            st = 0;
+            ph_t ^= 1u;
+          }
+          if (++sd == SD) {
+            sd = 0;
+            ph_d ^= 1u;
+          }
+          continue;
         }
         const uint32_t sbv = sb_base[st * (L::SB_STAGE / 4)];
         const uint32_t s2 = __byte_perm(sbv, sbv, 0x1010);  // (scale, scale)
@@ -516,8 +580,8 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
 MFX_DEFINE_STATUS_READER(read_status)
 
 template <int BITS, uint32_t WF, int ST, int SD, typename OUT, int EPI>
-int launch_epi(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tsb, const Params& p, int grid,
-               cudaStream_t st) {
+int launch_epi(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tsb, const CUtensorMap& tt,
+               const CUtensorMap& tlb, const Params& p, int grid, cudaStream_t st) {
   using L = Smem<BITS, ST, SD>;
   // eight dequantizer warps keep up with the tensor pipe for both widths (8-bit codes go through packed float32
   // arithmetic, five instructions per pair) and draw less power than sixteen
@@ -533,21 +597,21 @@ int launch_epi(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& 
     configured = true;
     configured_dev = dev;
   }
-  kern<<<grid, NUM_THREADS, L::DYN_BYTES, st>>>(tx, tw, tsb, p);
+  kern<<<grid, NUM_THREADS, L::DYN_BYTES, st>>>(tx, tw, tsb, tt, tlb, p);
   MFX_CUDA_TRY(cudaGetLastError());
   return MFX_OK;
 }
 
 template <int BITS, uint32_t WF, int ST, int SD, typename OUT>
-int launch(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tsb, const Params& p, int grid,
-           cudaStream_t st) {
+int launch(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tsb, const CUtensorMap& tt,
+           const CUtensorMap& tlb, const Params& p, int grid, cudaStream_t st) {
   switch (p.epilogue) {
-    case MFX_EPI_GELU_ERF: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_GELU_ERF>(tx, tw, tsb, p, grid, st);
-    case MFX_EPI_GELU_TANH: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_GELU_TANH>(tx, tw, tsb, p, grid, st);
-    case MFX_EPI_GATE_RESIDUAL: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_GATE_RESIDUAL>(tx, tw, tsb, p, grid, st);
-    case MFX_EPI_SILU: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_SILU>(tx, tw, tsb, p, grid, st);
-    case MFX_EPI_SWIGLU: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_SWIGLU>(tx, tw, tsb, p, grid, st);
-    default: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_NONE>(tx, tw, tsb, p, grid, st);
+    case MFX_EPI_GELU_ERF: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_GELU_ERF>(tx, tw, tsb, tt, tlb, p, grid, st);
+    case MFX_EPI_GELU_TANH: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_GELU_TANH>(tx, tw, tsb, tt, tlb, p, grid, st);
+    case MFX_EPI_GATE_RESIDUAL: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_GATE_RESIDUAL>(tx, tw, tsb, tt, tlb, p, grid, st);
+    case MFX_EPI_SILU: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_SILU>(tx, tw, tsb, tt, tlb, p, grid, st);
+    case MFX_EPI_SWIGLU: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_SWIGLU>(tx, tw, tsb, tt, tlb, p, grid, st);
+    default: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_NONE>(tx, tw, tsb, tt, tlb, p, grid, st);
   }
 }
 
@@ -683,6 +747,15 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
       return MFX_ERR_ALIGN;
     if (!aligned16(a.x) || (a.x_row_stride * 2) % 16 != 0 || (a.x_batch_stride * 2) % 16 != 0) return MFX_ERR_ALIGN;
   }
+  const bool low_rank = a.lora_r > 0;
+  if (a.lora_r < 0) return MFX_ERR_SHAPE;
+  if (low_rank) {
+    if (!a.lora_t || !a.lora_b) return MFX_ERR_NULL;
+    if (a.lora_ld <= 0 || a.lora_ld % 64 != 0 || a.lora_r > a.lora_ld || a.lora_ld > 1024) return MFX_ERR_SHAPE;
+    if (!aligned16(a.lora_t) || !aligned16(a.lora_b) || (a.lora_t_row_stride * 2) % 16 != 0 ||
+        (a.lora_t_batch_stride * 2) % 16 != 0 || a.lora_t_row_stride < a.lora_ld)
+      return MFX_ERR_ALIGN;
+  }
   if (int rc = check_arch()) return rc;
   if (!prepared) {
     if (int rc = prepare(a.wq, a.scales, a.biases, a.sb_dtype, a.N, a.K, a.bits, a.group_size, a.workspace,
@@ -690,11 +763,11 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
       return rc;
     prepared = a.workspace;
   }
-  if (qmv::eligible(a)) return qmv::run(a, prepared, codes_bytes_padded(a.N, a.K, a.bits), st);
+  if (!low_rank && qmv::eligible(a)) return qmv::run(a, prepared, codes_bytes_padded(a.N, a.K, a.bits), st);
   const void* codes = prepared;
   const void* sb_packed = static_cast<const uint8_t*>(prepared) + codes_bytes_padded(a.N, a.K, a.bits);
 
-  CUtensorMap tx, tw, tsb;
+  CUtensorMap tx, tw, tsb, tt, tlb;
   {
     const uint64_t dims[3] = {static_cast<uint64_t>(a.K), static_cast<uint64_t>(a.rows),
                               static_cast<uint64_t>(a.batch)};
@@ -724,7 +797,30 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
                              CU_TENSOR_MAP_SWIZZLE_NONE))
       return rc;
   }
+  if (low_rank) {
+    const uint64_t dims[3] = {static_cast<uint64_t>(a.lora_ld), static_cast<uint64_t>(a.rows),
+                              static_cast<uint64_t>(a.batch)};
+    const uint64_t bstride = a.batch > 1 ? static_cast<uint64_t>(a.lora_t_batch_stride) * 2
+                                         : static_cast<uint64_t>(a.lora_t_row_stride) * 2 * a.rows;
+    const uint64_t strides[2] = {static_cast<uint64_t>(a.lora_t_row_stride) * 2, bstride};
+    const uint32_t box[3] = {BK, BM, 1};
+    if (int rc = encode_tmap(&tt, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, a.lora_t, dims, strides, box,
+                             CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+    // the dense tile takes the place of the packed codes in shared memory: same bytes per row (32 or 64), same swizzle
+    const uint64_t bdims[2] = {static_cast<uint64_t>(a.lora_ld), static_cast<uint64_t>(a.N)};
+    const uint64_t bstrides[1] = {static_cast<uint64_t>(a.lora_ld) * 2};
+    const uint32_t bbox[2] = {static_cast<uint32_t>(4 * a.bits), BN_HALF};
+    if (int rc = encode_tmap(&tlb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.lora_b, bdims, bstrides, bbox,
+                             a.bits == 4 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B))
+      return rc;
+  } else {
+    tt = tx;   // never read: the kernel runs no extension stage
+    tlb = tw;
+  }
   Params p;
+  p.ext_r = low_rank ? static_cast<int>((a.lora_r + 15) / 16 * 16) : 0;
+  p.num_ext = low_rank ? (p.ext_r + GPS * 4 * a.bits - 1) / (GPS * 4 * a.bits) : 0;
   p.rows = static_cast<int>(a.rows);
   p.batch = static_cast<int>(a.batch);
   p.N = static_cast<int>(a.N);
@@ -759,11 +855,11 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
   const int grid = 2 * (p.total_tiles < pairs ? p.total_tiles : pairs);
   const bool f32 = a.y_dtype == MFX_F32;
   if (a.bits == 4) {
-    return f32 ? launch<4, FMT_BF16, 3, 3, float>(tx, tw, tsb, p, grid, st)
-               : launch<4, FMT_BF16, 3, 3, __nv_bfloat16>(tx, tw, tsb, p, grid, st);
+    return f32 ? launch<4, FMT_BF16, 3, 3, float>(tx, tw, tsb, tt, tlb, p, grid, st)
+               : launch<4, FMT_BF16, 3, 3, __nv_bfloat16>(tx, tw, tsb, tt, tlb, p, grid, st);
   }
-  return f32 ? launch<8, FMT_BF16, 3, 2, float>(tx, tw, tsb, p, grid, st)
-             : launch<8, FMT_BF16, 3, 2, __nv_bfloat16>(tx, tw, tsb, p, grid, st);
+  return f32 ? launch<8, FMT_BF16, 3, 2, float>(tx, tw, tsb, tt, tlb, p, grid, st)
+             : launch<8, FMT_BF16, 3, 2, __nv_bfloat16>(tx, tw, tsb, tt, tlb, p, grid, st);
 }
 
 // ---------------------------------------------------------------- allocation-free variant

@@ -173,8 +173,9 @@ class FusedRows:
 
 
 def _call(layer, x, **kw):
-    """Run a Linear or QuantizedLinear; epilogues of dense layers fall back to separate torch ops."""
-    if isinstance(layer, nn.QuantizedLinear):
+    """Run a Linear or QuantizedLinear (or a LoRA wrapper over one); epilogues of dense layers fall back to
+    separate torch ops."""
+    if isinstance(layer, nn.QuantizedLinear) or getattr(layer, "fuses_epilogue", False):
         return layer(x, **kw)
     y = layer(x)
     epi = kw.get("epilogue")

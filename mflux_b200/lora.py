@@ -5,10 +5,13 @@
 `FusedLoRALinear` (fused_linear_lora_layer.py:7-20): `base_linear` plus a list `loras`, y = base(x) + sum of the
 adapters' scaled low-rank products.
 
-Execution: the frozen base runs on the quantized-matmul kernel; the two thin matmuls of an adapter are plain library
-GEMMs, the second one accumulating in place into the base output (one extra pass over y per adapter). Epilogues
-that the unwrapped layer fuses into its matmul (activation, gate * y + residual) are applied afterwards by the
-caller for wrapped layers, because the adapter's term has to be added before them.
+Execution over a quantized base: t = x @ [A_1 | A_2 | ...] is one thin library GEMM; the second product runs inside
+the quantized-matmul kernel as extra K columns of the same tensor-core accumulation (operands t and the dense
+[N, r] matrix of scale_i * B_i^T), so the output is written once and the layer keeps the fused epilogues of the
+unwrapped one (activation, gate * y + residual) -- the adapters' term is in the accumulator before they run.
+Over a dense base, or with more than 1024 adapter columns, both thin matmuls are library GEMMs, the second one
+accumulating in place into the base output (one extra pass over y per adapter), and the caller applies epilogues
+afterwards.
 """
 from __future__ import annotations
 
@@ -31,6 +34,52 @@ def _low_rank_add(y: torch.Tensor, x: torch.Tensor, a: torch.Tensor, b: torch.Te
         return y.add_(torch.matmul(t, b), alpha=scale)
     y3.baddbmm_(t3, b.unsqueeze(0).expand(t3.shape[0], -1, -1), alpha=scale)
     return y
+
+
+MAX_FUSED_COLUMNS = 1024   # the kernel's limit on the row length of the low-rank operands
+
+
+class _FusedTerms:
+    """Caches [A_1 | A_2 | ...] ([K, ld]) and the rows scale_i * B_i[:, n] ([N, ld]) of a list of adapters,
+    zero-padded to ld = a multiple of 64 columns; rebuilt when an adapter's tensors or scale change."""
+
+    def __init__(self):
+        self.key, self.a_cat, self.b_rows, self.rank = None, None, None, 0
+
+    def get(self, adapters):
+        key = tuple((l.lora_A.data_ptr(), l.lora_A._version, l.lora_B.data_ptr(), l.lora_B._version, float(l.scale))
+                    for l in adapters)
+        if key != self.key:
+            rank = sum(l.lora_A.shape[1] for l in adapters)
+            ld = -(-rank // 64) * 64
+            k, n = adapters[0].lora_A.shape[0], adapters[0].lora_B.shape[1]
+            dev = adapters[0].lora_A.device
+            a_cat = torch.zeros(k, ld, dtype=torch.bfloat16, device=dev)
+            b_rows = torch.zeros(n, ld, dtype=torch.bfloat16, device=dev)
+            col = 0
+            for l in adapters:
+                r = l.lora_A.shape[1]
+                a_cat[:, col:col + r] = l.lora_A.data
+                b_rows[:, col:col + r] = (float(l.scale) * l.lora_B.data.float()).t()
+                col += r
+            self.key, self.a_cat, self.b_rows, self.rank = key, a_cat, b_rows, rank
+        return self.a_cat, self.b_rows, self.rank
+
+
+def _fusable(base, adapters, x) -> bool:
+    return (isinstance(base, nn.QuantizedLinear) and x.is_cuda and len(adapters) > 0
+            and sum(l.lora_A.shape[1] for l in adapters) <= MAX_FUSED_COLUMNS)
+
+
+def _fused_forward(base: "nn.QuantizedLinear", terms: _FusedTerms, adapters, x: torch.Tensor, **kw) -> torch.Tensor:
+    from . import ops
+
+    a_cat, b_rows, rank = terms.get(adapters)
+    xb = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+    t = torch.matmul(xb, a_cat)                              # [..., ld], rounded to bf16 like the reference's product
+    return ops.qlinear(xb, base.weight.data, base.scales.data, base.biases.data,
+                       None if base.bias is None else base.bias.data, bits=base.bits, group_size=base.group_size,
+                       prepared=base.prepared(), lora_t=t, lora_b=b_rows, lora_r=rank, **kw)
 
 
 class LoRALinear(nn.Module):
@@ -58,7 +107,18 @@ class LoRALinear(nn.Module):
         lora_lin.linear = linear
         return lora_lin
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    @property
+    def fuses_epilogue(self) -> bool:
+        """True when forward() accepts the quantized layer's epilogue arguments (quantized base)."""
+        return isinstance(self.linear, nn.QuantizedLinear) and self.lora_A.shape[1] <= MAX_FUSED_COLUMNS
+
+    def forward(self, x: torch.Tensor, **kw) -> torch.Tensor:
+        if _fusable(self.linear, [self], x):
+            if not hasattr(self, "_terms"):
+                self._terms = _FusedTerms()
+            return _fused_forward(self.linear, self._terms, [self], x, **kw)
+        if kw:
+            raise ValueError("epilogue arguments need a quantized base layer")
         base_out = self.linear(x)
         return _low_rank_add(base_out, x, self.lora_A.data, self.lora_B.data, self.scale)
 
@@ -69,7 +129,19 @@ class FusedLoRALinear(nn.Module):
         self.base_linear = base_linear
         self.loras = torch.nn.ModuleList(loras)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    @property
+    def fuses_epilogue(self) -> bool:
+        return (isinstance(self.base_linear, nn.QuantizedLinear) and len(self.loras) > 0
+                and sum(l.lora_A.shape[1] for l in self.loras) <= MAX_FUSED_COLUMNS)
+
+    def forward(self, x: torch.Tensor, **kw) -> torch.Tensor:
+        loras = list(self.loras)
+        if _fusable(self.base_linear, loras, x):
+            if not hasattr(self, "_terms"):
+                self._terms = _FusedTerms()
+            return _fused_forward(self.base_linear, self._terms, loras, x, **kw)
+        if kw:
+            raise ValueError("epilogue arguments need a quantized base layer")
         out = self.base_linear(x)
         for lora in self.loras:
             _low_rank_add(out, x, lora.lora_A.data, lora.lora_B.data, lora.scale)

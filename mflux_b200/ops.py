@@ -134,8 +134,13 @@ def qlinear(x: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, biases: tor
             bias: torch.Tensor | None = None, *, bits: int = 4, group_size: int = 64, epilogue: str | None = None,
             gate: torch.Tensor | None = None, residual: torch.Tensor | None = None,
             out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
-            prepared: torch.Tensor | None = None) -> torch.Tensor:
+            prepared: torch.Tensor | None = None, lora_t: torch.Tensor | None = None,
+            lora_b: torch.Tensor | None = None, lora_r: int = 0) -> torch.Tensor:
     """nn.QuantizedLinear.__call__: y[..., N] = x[..., K] . dequant(wq)^T + bias, with optional fused epilogue.
+
+    Low-rank term (LoRA adapters over the frozen layer): with `lora_t` [..., ld] (= x @ A, same leading shape as
+    x) and `lora_b` [N, ld] (row n = scale * B[:, n]), both bf16 with ld a multiple of 64 and zero columns from
+    `lora_r` on, the kernel adds lora_t . lora_b^T inside the same accumulation, before bias and epilogue.
 
     x is [rows, K] or [batch, rows, K] (bf16; row/batch strides may be arbitrary multiples of 8
     elements, the last dim must be dense). `out`, when given, may be a strided view of the same
@@ -197,6 +202,20 @@ def qlinear(x: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, biases: tor
         a.gate, a.gate_dtype, a.gate_batch_stride = gate.data_ptr(), _dt(gate), gate.stride(0)
         a.residual, a.res_row_stride, a.res_batch_stride = rv.data_ptr(), r_rs, r_bs
     a.y, a.y_dtype, a.y_row_stride, a.y_batch_stride = ov.data_ptr(), _dt(ov), o_rs, o_bs
+    if lora_r:
+        if lora_t is None or lora_b is None:
+            raise ValueError("a low-rank term needs lora_t and lora_b")
+        _cuda(lora_t, "lora_t")
+        if lora_t.dtype != torch.bfloat16 or lora_b.dtype != torch.bfloat16:
+            raise ValueError("lora_t and lora_b must be bf16")
+        if lora_t.dim() == 1:
+            lora_t = lora_t.unsqueeze(0)
+        tv, t_rows, t_batch, t_rs, t_bs = _rows_view(lora_t, "lora_t")
+        ld = tv.shape[-1]
+        if (t_rows, t_batch) != (rows, batch) or tuple(lora_b.shape) != (n, ld) or not lora_b.is_contiguous():
+            raise ValueError("lora_t must be [.., rows, ld] like x and lora_b a dense [N, ld]")
+        a.lora_t, a.lora_t_row_stride, a.lora_t_batch_stride = tv.data_ptr(), t_rs, t_bs
+        a.lora_b, a.lora_ld, a.lora_r = lora_b.data_ptr(), ld, int(lora_r)
     trace = QLINEAR_TRACE
     if trace is not None:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -76,3 +76,123 @@ def test_flux_step_with_adapters(lib_built):
     out2 = model(lat.cuda(), ctx.cuda(), pooled.cuda(), *args)
     ref2 = oflux.forward(model, lat.to(torch.bfloat16), ctx, pooled, ts, gd, height, width)
     assert rel_l2(out2, ref2.numpy()) <= TOL
+
+
+def _dense_ref(x, q, bits, t, b_rows, bias):
+    from oracle.quant import dequantize_affine
+
+    w = torch.from_numpy(dequantize_affine(q[0].cpu().numpy(), q[1].float().cpu().numpy(), q[2].float().cpu().numpy(),
+                                           64, bits))
+    y = x.float().cpu() @ w.T + t.float().cpu() @ b_rows.float().cpu().T
+    return y if bias is None else y + bias.float().cpu()
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("rank", [4, 16, 40, 64, 100, 256])
+def test_low_rank_term_inside_the_kernel(lib_built, bits, rank):
+    """y = x . W^T + t . lb^T + bias with t, lb as extra K columns of the tensor-core accumulation: ragged rows,
+    N off the 256-wide tile, an odd number of quantization groups (the last quantized stage is half empty)."""
+    from mflux_b200 import ops
+
+    g = torch.Generator(device="cuda").manual_seed(100 * bits + rank)
+    m, k, n = 333, 448, 328
+    ld = -(-rank // 64) * 64
+    x = torch.randn(2, m, k, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    q = ops.quantize_affine(w, 64, bits)
+    bias = (torch.randn(n, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    t = torch.zeros(2, m, ld, device="cuda", dtype=torch.bfloat16)
+    lb = torch.zeros(n, ld, device="cuda", dtype=torch.bfloat16)
+    t[..., :rank] = torch.randn(2, m, rank, device="cuda", generator=g).to(torch.bfloat16)
+    lb[:, :rank] = (torch.randn(n, rank, device="cuda", generator=g) * 0.2).to(torch.bfloat16)
+    y = ops.qlinear(x, *q, bias, bits=bits, lora_t=t, lora_b=lb, lora_r=rank, out_dtype=torch.float32)
+    plain = ops.qlinear(x, *q, bias, bits=bits, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert ops.poll_device_status() == 0
+    ref = _dense_ref(x, q, bits, t, lb, bias)
+    assert rel_l2(y, ref.numpy()) <= 2e-3
+    assert rel_l2(plain, ref.numpy()) > 0.05          # the term matters at these scales
+    # the low-rank part alone, isolated by subtraction, is itself right to bf16-product accuracy
+    low = (t.float() @ lb.float().T).cpu()
+    assert rel_l2((y - plain).cpu(), low.numpy()) <= 1e-2
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_low_rank_term_small_m_and_epilogues(lib_built, bits):
+    from mflux_b200 import ops
+
+    g = torch.Generator(device="cuda").manual_seed(7 + bits)
+    k, n, rank, ld = 64, 256, 24, 64                   # one quantization group, then one extension stage
+    w = (torch.randn(n, k, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    q = ops.quantize_affine(w, 64, bits)
+    lb = torch.zeros(n, ld, device="cuda", dtype=torch.bfloat16)
+    lb[:, :rank] = (torch.randn(n, rank, device="cuda", generator=g) * 0.2).to(torch.bfloat16)
+    for m in (1, 9, 16, 130):                          # at most 16 rows would otherwise take the small-M kernel
+        x = torch.randn(m, k, device="cuda", generator=g).to(torch.bfloat16)
+        t = torch.zeros(m, ld, device="cuda", dtype=torch.bfloat16)
+        t[:, :rank] = torch.randn(m, rank, device="cuda", generator=g).to(torch.bfloat16)
+        y = ops.qlinear(x, *q, None, bits=bits, lora_t=t, lora_b=lb, lora_r=rank, out_dtype=torch.float32)
+        ref = _dense_ref(x, q, bits, t, lb, None)
+        assert rel_l2(y, ref.numpy()) <= 2e-3, m
+        # gelu and gate * y + residual see the sum, not the base product alone
+        ge = ops.qlinear(x, *q, None, bits=bits, lora_t=t, lora_b=lb, lora_r=rank, epilogue="gelu_approx")
+        assert rel_l2(ge, torch.nn.functional.gelu(ref, approximate="tanh").numpy()) <= 1e-2
+        res = torch.randn(1, m, n, device="cuda", generator=g)
+        gate = torch.randn(1, n, device="cuda", generator=g).to(torch.bfloat16)
+        before = res.clone()
+        ops.qlinear(x.unsqueeze(0), *q, None, bits=bits, lora_t=t.unsqueeze(0), lora_b=lb, lora_r=rank,
+                    epilogue="gate_residual", gate=gate, residual=res, out=res)
+        want = before.cpu() + gate.float().cpu()[:, None] * ref
+        assert rel_l2(res, want.numpy()) <= 2e-3
+    assert ops.poll_device_status() == 0
+
+
+def test_low_rank_arguments_are_validated(lib_built):
+    from mflux_b200 import ops
+
+    x = torch.zeros(32, 64, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(64, 64, device="cuda").to(torch.bfloat16)
+    q = ops.quantize_affine(w, 64, 4)
+    t = torch.zeros(32, 48, device="cuda", dtype=torch.bfloat16)       # row length not a multiple of 64
+    lb = torch.zeros(64, 48, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(Exception):
+        ops.qlinear(x, *q, None, bits=4, lora_t=t, lora_b=lb, lora_r=16)
+    t, lb = torch.zeros(32, 64, device="cuda", dtype=torch.bfloat16), torch.zeros(64, 64, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(Exception):
+        ops.qlinear(x, *q, None, bits=4, lora_t=t, lora_b=lb, lora_r=65)    # rank beyond the row length
+    with pytest.raises(Exception):
+        ops.qlinear(x, *q, None, bits=4, lora_t=t[:16], lora_b=lb, lora_r=8)   # rows differ from x
+    with pytest.raises(Exception):
+        ops.qlinear(x, *q, None, bits=4, lora_t=t.float(), lora_b=lb, lora_r=8)
+
+
+def test_wrappers_take_the_fused_path_and_match_the_library_path(lib_built):
+    """Over a quantized base the wrapper's output (low-rank term inside the kernel) agrees with base output plus
+    library GEMMs, and it accepts the quantized layer's epilogues."""
+    from mflux_b200 import nn
+    from mflux_b200.lora import FusedLoRALinear, LoRALinear, _low_rank_add
+
+    g = torch.Generator(device="cpu").manual_seed(21)
+    lin = nn.Linear(256, 512, bias=True, device="cuda")
+    q = lin.to_quantized(bits=4)
+    one = LoRALinear.from_linear(q, r=16, scale=0.9)
+    two = LoRALinear.from_linear(q, r=72, scale=-0.4)
+    for l, r in ((one, 16), (two, 72)):
+        a, b = _adapter(g, 256, 512, r)
+        l.lora_A.data, l.lora_B.data = a.to(torch.bfloat16), b.to(torch.bfloat16)
+    fused = FusedLoRALinear(q, [one, two])
+    assert one.fuses_epilogue and fused.fuses_epilogue
+    x = torch.randn(3, 200, 256, generator=g).to(torch.bfloat16).cuda()
+    y = fused(x, out_dtype=torch.float32)
+    lib = q(x, out_dtype=torch.float32)
+    for l in (one, two):
+        _low_rank_add(lib, x, l.lora_A.data, l.lora_B.data, l.scale)
+    assert rel_l2(y, lib.cpu().numpy()) <= 5e-3
+    act = fused(x, epilogue="gelu_approx")
+    assert rel_l2(act, torch.nn.functional.gelu(lib, approximate="tanh").cpu().numpy()) <= 1e-2
+    # changing a scale rebuilds the cached operands
+    one.scale = 0.0
+    y0 = one(x, out_dtype=torch.float32)
+    assert rel_l2(y0, q(x, out_dtype=torch.float32).cpu().numpy()) <= 1e-6
+    dense = LoRALinear.from_linear(lin, r=8)
+    assert not dense.fuses_epilogue
