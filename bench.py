@@ -311,6 +311,72 @@ def qwen_spec(args):
 SPECS = {"flux": flux_spec, "zimage": zimage_spec, "qwen": qwen_spec}
 
 
+def run_lora(args, dev):
+    """Adapters over the single-linear configuration (M 4096, N 12288, K 3072, group 64): per call the frozen layer
+    alone, the wrapper with the low-rank product inside the quantized-matmul kernel, and the wrapper with both
+    thin products as library GEMMs accumulating into the output. Operand copies rotate past the L2."""
+    import torch
+
+    from mflux_b200 import nn
+    from mflux_b200.lora import FusedLoRALinear, LoRALinear, _low_rank_add
+
+    m, n, k = 4096, 12288, 3072
+    rows = []
+    g = torch.Generator(device=dev).manual_seed(0)
+    copies = 4
+    for bits in (4, 8):
+        layers = []
+        for _ in range(copies):
+            lin = nn.Linear(k, n, bias=True, device=dev)
+            with torch.no_grad():
+                lin.weight.copy_(torch.randn(n, k, device=dev, generator=g) * 0.02)
+            layers.append(lin.to_quantized(bits=bits))
+            del lin
+        xs = [torch.randn(m, k, device=dev, generator=g).to(torch.bfloat16) for _ in range(copies)]
+        ys = [torch.empty(m, n, device=dev, dtype=torch.bfloat16) for _ in range(copies)]
+
+        def timed_together(fns, reps=40, chunks=7):
+            """Per function (median, worst) microseconds per call. The functions take turns, one run of `reps`
+            calls each per round, so that clock drift under the power cap falls on all of them alike."""
+            for fn in fns:
+                for i in range(max(3, args.warmup, copies)):
+                    fn(i % copies)
+            per = [[] for _ in fns]
+            for _ in range(chunks):
+                for j, fn in enumerate(fns):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    torch.cuda.synchronize()
+                    e0.record()
+                    for i in range(reps):
+                        fn(i % copies)
+                    e1.record()
+                    torch.cuda.synchronize()
+                    per[j].append(e0.elapsed_time(e1) * 1e3 / reps)
+            return [(sorted(v)[len(v) // 2], max(v)) for v in per]
+
+        for ranks in ((16,), (64,), (128,), (16, 16, 32)):
+            wrapped = []
+            for q in layers:
+                adapters = [LoRALinear.from_linear(q, r=r, scale=0.8) for r in ranks]
+                wrapped.append(adapters[0] if len(adapters) == 1 else FusedLoRALinear(q, adapters))
+
+            def library(i):
+                y = layers[i](xs[i], out=ys[i])
+                w = wrapped[i]
+                for l in ([w] if isinstance(w, LoRALinear) else w.loras):
+                    _low_rank_add(y, xs[i], l.lora_A.data, l.lora_B.data, l.scale)
+
+            (base_us, base_w), (fused_us, fused_w), (library_us, library_w) = timed_together(
+                [lambda i: layers[i](xs[i], out=ys[i]), lambda i: wrapped[i](xs[i], out=ys[i]), library])
+            rows.append({"bits": bits, "M": m, "N": n, "K": k, "ranks": list(ranks), "base_us": round(base_us, 1),
+                         "fused_us": round(fused_us, 1), "library_us": round(library_us, 1),
+                         "worst_chunk_us": [round(base_w, 1), round(fused_w, 1), round(library_w, 1)],
+                         "fused_over_base": round(fused_us / base_us, 3),
+                         "library_over_base": round(library_us / base_us, 3)})
+        del layers, xs, ys
+    return rows
+
+
 def run_sweep(args, dev):
     """Single quantized linears: bits x (N, K) x M. Every shape cycles through enough weight/activation copies
     that consecutive launches never find their operands in L2."""
@@ -378,7 +444,7 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="flux", choices=["flux", "zimage", "qwen", "sweep"])
+    ap.add_argument("--workload", default="flux", choices=["flux", "zimage", "qwen", "sweep", "lora"])
     ap.add_argument("--small", action="store_true", help="flux at reduced depth for profiler captures (not a bench value)")
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (default: the workload's own)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -389,7 +455,7 @@ def main():
                     help="qwen: issue the step's launches one by one instead of replaying them as a CUDA graph")
     args = ap.parse_args()
 
-    if args.workload == "sweep":
+    if args.workload in ("sweep", "lora"):
         spec = None
     else:
         spec = SPECS[args.workload](args)
@@ -411,6 +477,22 @@ def main():
         raise RuntimeError("bench.py needs a CUDA device: there is no CPU path")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+
+    if args.workload == "lora":
+        if rank == 0:
+            sampler = ClockSampler(local)
+            sampler.start()
+            rows = run_lora(args, dev)
+            clocks = sampler.stop()
+            print(json.dumps({
+                "metric": "lora_over_qlinear_time_ratio", "value": rows[0]["fused_over_base"],
+                "unit": "time of the rank-16 wrapped W4 layer / time of the frozen layer", "n_gpus": 1, "steps": 1,
+                "warmup": max(3, args.warmup), "higher_is_better": False, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": "LoRA adapters over one quantized linear, M 4096 N 12288 K 3072, group 64",
+                           "l2_policy": "four operand sets rotated (0.6 GB between reuses)",
+                           "device_status": ops.poll_device_status()},
+                "clocks": clocks, "lora": rows}), flush=True)
+        return
 
     if spec is None:   # single-GPU table of quantized linears
         if rank == 0:
