@@ -71,6 +71,24 @@ def test_validation_of_the_later_entry_points(lib_built):
     assert lib.mfx_qlinear_ex(a, None) == -1          # N = 24 is not a multiple of 16
     a.epilogue = 6
     assert lib.mfx_qlinear_ex(a, None) == -1          # unknown epilogue
+    # low-rank term of the quantized matmul
+    a.epilogue, a.N, a.y_row_stride = _lib.EPI_NONE, 64, 64
+    a.lora_r = 8
+    assert lib.mfx_qlinear_ex(a, None) == -7          # rank given without the two operands
+    a.lora_t = a.lora_b = 1024
+    a.lora_ld, a.lora_t_row_stride = 48, 48
+    assert lib.mfx_qlinear_ex(a, None) == -1          # row length not a multiple of 64
+    a.lora_ld, a.lora_t_row_stride = 64, 64
+    a.lora_r = 65
+    assert lib.mfx_qlinear_ex(a, None) == -1          # rank beyond the row length
+    a.lora_r, a.lora_ld, a.lora_t_row_stride = 8, 2048, 2048
+    assert lib.mfx_qlinear_ex(a, None) == -1          # more columns than the kernel takes
+    a.lora_ld, a.lora_t_row_stride, a.lora_b = 64, 64, 1032
+    assert lib.mfx_qlinear_ex(a, None) == -2          # operand not 16-byte aligned
+    a.lora_b, a.lora_t_row_stride = 1024, 32
+    assert lib.mfx_qlinear_ex(a, None) == -2          # rows of t shorter than the row length
+    a.lora_r = -1
+    assert lib.mfx_qlinear_ex(a, None) == -1
     p = _lib.PostPreNormArgs()
     assert lib.mfx_post_pre_norm(p, None) == -7
     assert lib.mfx_post_pre_norm(None, None) == -7
