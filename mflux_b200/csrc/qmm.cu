@@ -172,7 +172,8 @@ __device__ __noinline__ float gelu_tanh(float v) {
 }
 __device__ __forceinline__ float silu(float v) { return v / (1.0f + __expf(-v)); }
 
-template <int BITS, uint32_t WF, int ST, int SD, typename OUT, int EPI, int NUM_DQ_WARPS>
+// EXT compiles the low-rank extension stages in; without it the loops below are the plain quantized matmul.
+template <int BITS, uint32_t WF, int ST, int SD, typename OUT, int EPI, int NUM_DQ_WARPS, bool EXT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((FIXED_WARPS + NUM_DQ_WARPS) * 32, 1)
 qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
            const __grid_constant__ CUtensorMap tmap_sb, const __grid_constant__ CUtensorMap tmap_t,
@@ -205,7 +206,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
   // An extension stage moves as many bytes through the codes' staging buffer as a quantized one: per group
   // 128 rows x EXT_KG dense bf16 values, 16 (4-bit codes) or 32 (8-bit codes) k-values of the low-rank term.
   constexpr int EXT_KG = 4 * BITS;
-  const int num_all = num_st + p.num_ext;
+  const int num_all = EXT ? num_st + p.num_ext : num_st;
   const uint32_t rank = cluster_ctarank();      // 0 = leader of the pair
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
@@ -258,7 +259,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         if (lane == 0) {
           if (rank == 0) mbar_arrive_expect_tx(x_full(st), 2 * L::X_STAGE);
           mbar_arrive_expect_tx(w_full(st), L::WQ_STAGE + L::SB_STAGE);
-          if (s < num_st) {
+          if (!EXT || s < num_st) {
 #pragma unroll
             for (int g = 0; g < GPS; ++g) {
               const int kb = s * GPS + g;  // beyond K on a ragged last stage: the loads return zeros
@@ -311,7 +312,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
           }
           tc_fence_after();
           if (lane == 0) {
-            if (s < num_st) {
+            if (!EXT || s < num_st) {
 #pragma unroll
               for (int g = 0; g < GPS; ++g) {
                 const uint64_t adesc = smem_desc_sw128(x_s + st * L::X_STAGE + g * X_TILE_BYTES);
@@ -391,7 +392,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
           ok = false;
           break;
         }
-        if (s >= num_st) {
+        if (EXT && s >= num_st) {
           // extension stage: the staged bytes are bf16 values already; chunk c of the row goes to chunk c of the
           // B tile row (the tensor cores read no further than EXT_KG k-values of these stages)
           const uint8_t* esrc = rd_base + st * L::WQ_STAGE;
@@ -579,7 +580,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
 
 MFX_DEFINE_STATUS_READER(read_status)
 
-template <int BITS, uint32_t WF, int ST, int SD, typename OUT, int EPI>
+template <int BITS, uint32_t WF, int ST, int SD, typename OUT, int EPI, bool EXT>
 int launch_epi(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tsb, const CUtensorMap& tt,
                const CUtensorMap& tlb, const Params& p, int grid, cudaStream_t st) {
   using L = Smem<BITS, ST, SD>;
@@ -587,7 +588,7 @@ int launch_epi(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& 
   // arithmetic, five instructions per pair) and draw less power than sixteen
   constexpr int NDQ = 8;
   constexpr int NUM_THREADS = (FIXED_WARPS + NDQ) * 32;
-  auto kern = qmm_kernel<BITS, WF, ST, SD, OUT, EPI, NDQ>;
+  auto kern = qmm_kernel<BITS, WF, ST, SD, OUT, EPI, NDQ, EXT>;
   static bool configured = false;  // attribute is per function; set once per process and device reuse is fine
   static int configured_dev = -1;
   int dev = 0;
@@ -602,17 +603,24 @@ int launch_epi(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& 
   return MFX_OK;
 }
 
+template <int BITS, uint32_t WF, int ST, int SD, typename OUT, bool EXT>
+int launch_ext(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tsb, const CUtensorMap& tt,
+           const CUtensorMap& tlb, const Params& p, int grid, cudaStream_t st) {
+  switch (p.epilogue) {
+    case MFX_EPI_GELU_ERF: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_GELU_ERF, EXT>(tx, tw, tsb, tt, tlb, p, grid, st);
+    case MFX_EPI_GELU_TANH: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_GELU_TANH, EXT>(tx, tw, tsb, tt, tlb, p, grid, st);
+    case MFX_EPI_GATE_RESIDUAL: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_GATE_RESIDUAL, EXT>(tx, tw, tsb, tt, tlb, p, grid, st);
+    case MFX_EPI_SILU: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_SILU, EXT>(tx, tw, tsb, tt, tlb, p, grid, st);
+    case MFX_EPI_SWIGLU: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_SWIGLU, EXT>(tx, tw, tsb, tt, tlb, p, grid, st);
+    default: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_NONE, EXT>(tx, tw, tsb, tt, tlb, p, grid, st);
+  }
+}
+
 template <int BITS, uint32_t WF, int ST, int SD, typename OUT>
 int launch(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tsb, const CUtensorMap& tt,
            const CUtensorMap& tlb, const Params& p, int grid, cudaStream_t st) {
-  switch (p.epilogue) {
-    case MFX_EPI_GELU_ERF: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_GELU_ERF>(tx, tw, tsb, tt, tlb, p, grid, st);
-    case MFX_EPI_GELU_TANH: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_GELU_TANH>(tx, tw, tsb, tt, tlb, p, grid, st);
-    case MFX_EPI_GATE_RESIDUAL: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_GATE_RESIDUAL>(tx, tw, tsb, tt, tlb, p, grid, st);
-    case MFX_EPI_SILU: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_SILU>(tx, tw, tsb, tt, tlb, p, grid, st);
-    case MFX_EPI_SWIGLU: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_SWIGLU>(tx, tw, tsb, tt, tlb, p, grid, st);
-    default: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_NONE>(tx, tw, tsb, tt, tlb, p, grid, st);
-  }
+  return p.num_ext > 0 ? launch_ext<BITS, WF, ST, SD, OUT, true>(tx, tw, tsb, tt, tlb, p, grid, st)
+                       : launch_ext<BITS, WF, ST, SD, OUT, false>(tx, tw, tsb, tt, tlb, p, grid, st);
 }
 
 int sm_count() {
