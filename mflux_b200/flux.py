@@ -152,11 +152,33 @@ class SingleTransformerBlock(nn.Module):
 
 
 class FusedRows:
-    """Row-concatenation of several QuantizedLinear layers run as one matmul (same K, bits)."""
+    """Row-concatenation of several QuantizedLinear layers run as one matmul (same K, bits). Layers wrapped with
+    LoRA adapters keep them: the adapters of all layers become one low-rank term of that matmul, each adapter
+    acting on its own layer's block of output rows."""
 
     def __init__(self, layers):
-        self.layers = list(layers)
+        from .lora import _FusedTerms, split_wrapped
+
+        parts = [split_wrapped(l) for l in layers]
+        if any(p is None for p in parts):
+            raise ValueError("FusedRows needs quantized layers (bare or LoRA-wrapped)")
+        self.layers = [p[0] for p in parts]
+        self.groups, row = [], 0
+        for base, adapters in parts:
+            if adapters:
+                self.groups.append((row, adapters))
+            row += base.weight.shape[0]
+        self.rows = row
+        self.terms = _FusedTerms() if self.groups else None
         self.blob = None
+
+    @staticmethod
+    def accepts(layers) -> bool:
+        from .lora import MAX_FUSED_COLUMNS, split_wrapped
+
+        parts = [split_wrapped(l) for l in layers]
+        return (all(p is not None for p in parts)
+                and sum(a.lora_A.shape[1] for _, ads in parts for a in ads) <= MAX_FUSED_COLUMNS)
 
     def __call__(self, x, out):
         l0 = self.layers[0]
@@ -168,8 +190,13 @@ class FusedRows:
             self.wshape = w.shape
             self.blob = ops.prepare_qlinear(w, s, b, l0.bits, l0.group_size)
             self.wq_stub = torch.empty((w.shape[0], w.shape[1]), dtype=torch.uint32, device="meta")
-        return ops.qlinear(x, self.wq_stub, None, None, self.bias, bits=l0.bits, group_size=l0.group_size, out=out,
-                           prepared=self.blob)
+        if self.terms is None:
+            return ops.qlinear(x, self.wq_stub, None, None, self.bias, bits=l0.bits, group_size=l0.group_size,
+                               out=out, prepared=self.blob)
+        a_cat, b_rows, rank = self.terms.get(None, self.groups, self.rows)   # rows of bare layers stay zero
+        xb = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+        return ops.qlinear(xb, self.wq_stub, None, None, self.bias, bits=l0.bits, group_size=l0.group_size, out=out,
+                           prepared=self.blob, lora_t=torch.matmul(xb, a_cat), lora_b=b_rows, lora_r=rank)
 
 
 def _call(layer, x, **kw):
@@ -219,7 +246,7 @@ class Transformer(nn.Module):
     def _fuse(self, key, layers):
         f = self._fused.get(key)
         if f is None:
-            if all(isinstance(l, nn.QuantizedLinear) for l in layers):
+            if FusedRows.accepts(layers):
                 f = FusedRows(layers)
             else:
                 f = lambda x, out, ls=layers: out.copy_(torch.cat([l(x) for l in ls], dim=-1))  # noqa: E731

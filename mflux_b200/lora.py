@@ -40,30 +40,52 @@ MAX_FUSED_COLUMNS = 1024   # the kernel's limit on the row length of the low-ran
 
 
 class _FusedTerms:
-    """Caches [A_1 | A_2 | ...] ([K, ld]) and the rows scale_i * B_i[:, n] ([N, ld]) of a list of adapters,
-    zero-padded to ld = a multiple of 64 columns; rebuilt when an adapter's tensors or scale change."""
+    """Caches the two dense operands of the kernel's low-rank term for groups of adapters, each group acting on
+    its own block of output rows: a_cat = [A_1 | A_2 | ...] ([K, ld], all adapters of all groups side by side) and
+    b_rows ([N, ld]) whose row n holds scale_i * B_i[:, n - row0] in adapter i's columns when i belongs to the group
+    covering row n, zeros elsewhere. ld is the column count padded to a multiple of 64. A single wrapped layer is
+    one group over all rows; row-concatenated layers (fused q/k/v) are one group per layer. Rebuilt when an
+    adapter's tensors or scale change."""
 
     def __init__(self):
         self.key, self.a_cat, self.b_rows, self.rank = None, None, None, 0
 
-    def get(self, adapters):
+    def get(self, adapters, groups=None, n_rows=None):
+        """`groups`: list of (first row, adapters of that block); default one block of all `adapters` from row 0.
+        `n_rows`: rows of b_rows when blocks without adapters follow the last group."""
+        if groups is None:
+            groups = [(0, list(adapters))]
+        flat = [l for _, ls in groups for l in ls]
         key = tuple((l.lora_A.data_ptr(), l.lora_A._version, l.lora_B.data_ptr(), l.lora_B._version, float(l.scale))
-                    for l in adapters)
+                    for l in flat) + tuple(r0 for r0, _ in groups)
         if key != self.key:
-            rank = sum(l.lora_A.shape[1] for l in adapters)
+            rank = sum(l.lora_A.shape[1] for l in flat)
             ld = -(-rank // 64) * 64
-            k, n = adapters[0].lora_A.shape[0], adapters[0].lora_B.shape[1]
-            dev = adapters[0].lora_A.device
+            k = flat[0].lora_A.shape[0]
+            n = n_rows or max(r0 + ls[0].lora_B.shape[1] for r0, ls in groups if ls)
+            dev = flat[0].lora_A.device
             a_cat = torch.zeros(k, ld, dtype=torch.bfloat16, device=dev)
             b_rows = torch.zeros(n, ld, dtype=torch.bfloat16, device=dev)
             col = 0
-            for l in adapters:
-                r = l.lora_A.shape[1]
-                a_cat[:, col:col + r] = l.lora_A.data
-                b_rows[:, col:col + r] = (float(l.scale) * l.lora_B.data.float()).t()
-                col += r
+            for r0, ls in groups:
+                for l in ls:
+                    r, rows = l.lora_A.shape[1], l.lora_B.shape[1]
+                    a_cat[:, col:col + r] = l.lora_A.data
+                    b_rows[r0:r0 + rows, col:col + r] = (float(l.scale) * l.lora_B.data.float()).t()
+                    col += r
             self.key, self.a_cat, self.b_rows, self.rank = key, a_cat, b_rows, rank
         return self.a_cat, self.b_rows, self.rank
+
+
+def split_wrapped(layer):
+    """(quantized base, list of adapters) of a QuantizedLinear or of a LoRA wrapper over one; None otherwise."""
+    if isinstance(layer, nn.QuantizedLinear):
+        return layer, []
+    if isinstance(layer, LoRALinear) and isinstance(layer.linear, nn.QuantizedLinear):
+        return layer.linear, [layer]
+    if isinstance(layer, FusedLoRALinear) and isinstance(layer.base_linear, nn.QuantizedLinear):
+        return layer.base_linear, list(layer.loras)
+    return None
 
 
 def _fusable(base, adapters, x) -> bool:

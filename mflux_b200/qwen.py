@@ -132,7 +132,7 @@ class QwenTransformer(nn.Module):
     def _fuse(self, key, layers):
         f = self._fused.get(key)
         if f is None:
-            if all(isinstance(l, nn.QuantizedLinear) for l in layers):
+            if FusedRows.accepts(layers):
                 f = FusedRows(layers)
             else:
                 f = lambda x, out, ls=layers: out.copy_(torch.cat([l(x) for l in ls], dim=-1))  # noqa: E731

@@ -176,7 +176,7 @@ class ZImageTransformer(nn.Module):
         if f is None:
             a = blk.attention
             layers = [a.to_q, a.to_k, a.to_v]
-            if all(isinstance(l, nn.QuantizedLinear) for l in layers):
+            if FusedRows.accepts(layers):
                 f = FusedRows(layers)
             else:
                 f = lambda x, out, ls=layers: out.copy_(torch.cat([l(x) for l in ls], dim=-1))  # noqa: E731

@@ -196,3 +196,48 @@ def test_wrappers_take_the_fused_path_and_match_the_library_path(lib_built):
     assert rel_l2(y0, q(x, out_dtype=torch.float32).cpu().numpy()) <= 1e-6
     dense = LoRALinear.from_linear(lin, r=8)
     assert not dense.fuses_epilogue
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_row_fused_layers_keep_their_adapters(lib_built, bits):
+    """q/k/v run as one matmul: a wrapped q, a bare k and a doubly wrapped v give what the three layers give one
+    by one, and changing an adapter's scale afterwards is picked up."""
+    from mflux_b200 import nn
+    from mflux_b200.flux import FusedRows
+    from mflux_b200.lora import FusedLoRALinear, LoRALinear
+
+    g = torch.Generator(device="cpu").manual_seed(33 + bits)
+    d = 256
+    base = []
+    for _ in range(3):
+        lin = nn.Linear(d, d, bias=True, device="cuda")
+        with torch.no_grad():
+            lin.weight.copy_(torch.randn(d, d, generator=g) * 0.05)
+            lin.bias.copy_(torch.randn(d, generator=g) * 0.05)
+        base.append(lin.to_quantized(bits=bits))
+
+    def wrap(q, r, scale):
+        l = LoRALinear.from_linear(q, r=r, scale=scale)
+        a, b = _adapter(g, d, d, r)
+        l.lora_A.data, l.lora_B.data = a.to(torch.bfloat16), b.to(torch.bfloat16)
+        return l
+
+    wq = wrap(base[0], 8, 0.9)
+    wv = FusedLoRALinear(base[2], [wrap(base[2], 16, -0.7), wrap(base[2], 4, 1.5)])
+    layers = [wq, base[1], wv]
+    assert FusedRows.accepts(layers) and not FusedRows.accepts([wq, torch.nn.Linear(d, d)])
+    fused = FusedRows(layers)
+    x = torch.randn(2, 90, d, generator=g).to(torch.bfloat16).cuda()
+    out = torch.empty(2, 90, 3 * d, device="cuda", dtype=torch.bfloat16)
+    fused(x, out)
+    want = torch.cat([l(x) for l in layers], dim=-1)
+    torch.cuda.synchronize()
+    assert rel_l2(out, want.float().cpu().numpy()) <= 2e-3
+    ref = torch.cat([oflux.lin(l, x.cpu()) for l in layers], dim=-1)
+    assert rel_l2(out, ref.numpy()) <= TOL
+    # k carries no adapter: its block equals the bare layer bit for bit; q's differs from its bare layer
+    assert torch.equal(out[..., d:2 * d], base[1](x))
+    assert rel_l2(out[..., :d], base[0](x).float().cpu().numpy()) > 0.02
+    wq.scale = 0.0
+    fused(x, out)
+    assert rel_l2(out[..., :d], base[0](x).float().cpu().numpy()) <= 1e-6
