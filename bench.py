@@ -168,6 +168,28 @@ def flux_spec(args):
         from mflux_b200.schedulers import LinearScheduler
 
         model = Transformer(cfg, bits=4, device=dev, seed=1234)  # same weights on every rank (replicated)
+        if args.lora_rank:
+            # one adapter on every attention projection and feed-forward linear of every block (the modulation
+            # linears stay bare), random A and B: the usual target set of a LoRA file for this model
+            from mflux_b200 import nn as mnn
+            from mflux_b200.lora import apply_lora
+
+            ga = torch.Generator(device=dev).manual_seed(77)
+            adapters = {}
+            for name, mod in list(model.named_modules()):
+                if (not isinstance(mod, mnn.QuantizedLinear) or "blocks." not in name
+                        or ".norm" in name):   # norm*.linear are the modulation linears
+                    continue
+                n_out, k_in = mod.output_dims, mod.input_dims
+                a = (torch.randn(k_in, args.lora_rank, device=dev, generator=ga) * k_in ** -0.5).to(torch.bfloat16)
+                b = (torch.randn(args.lora_rank, n_out, device=dev, generator=ga) * 0.02).to(torch.bfloat16)
+                adapters[name] = [(a, b, 1.0)]
+            apply_lora(model, adapters)
+            if args.lora_library:   # the same adapters through two library GEMMs per layer, for comparison
+                import mflux_b200.lora as mlora
+
+                mlora.MAX_FUSED_COLUMNS = 0
+            flux_spec.adapters = len(adapters)
         g = torch.Generator(device="cpu").manual_seed(100 + rank)  # every rank has its own batch of images
         lat_h = torch.randn(batch, si, cfg.in_channels, generator=g).pin_memory()
         ctx_h = torch.randn(batch, st, cfg.context_dim, generator=g).to(torch.bfloat16).pin_memory()
@@ -189,7 +211,10 @@ def flux_spec(args):
         "unit": "steps/s (one step = 16 images x 4608 tokens through 19+38 blocks)",
         "workload": (f"FLUX.1-shaped MMDiT {cfg.num_joint}+{cfg.num_single} blocks, hidden {cfg.hidden}, "
                      f"{cfg.heads}x128 heads, W4 g64, batch {batch}, {si} image + {st} text tokens, "
-                     f"guidance-embedded, CFG-free"),
+                     f"guidance-embedded, CFG-free"
+                     + (f", rank-{args.lora_rank} LoRA adapter on every attention and feed-forward linear ("
+                        + ("library GEMMs" if args.lora_library else "inside the quantized matmul") + ")"
+                        if args.lora_rank else "")),
         "scaling": "weak", "lin": lin, "attn": attn, "per_gpu_batch": batch, "build": build,
         "l2_policy": "inputs larger than L2 (6.7 GB of packed weights stream every step)",
     }
@@ -451,6 +476,10 @@ def main():
     ap.add_argument("--qwen-parallel", default="cfg+tp", choices=["cfg+tp", "tp"],
                     help="qwen on N > 1 GPUs: split the two guidance branches over the halves of the ranks and use "
                          "tensor parallelism inside each half (default), or tensor parallelism over all ranks")
+    ap.add_argument("--lora-rank", type=int, default=0,
+                    help="flux: wrap every attention / feed-forward linear with one LoRA adapter of this rank")
+    ap.add_argument("--lora-library", action="store_true",
+                    help="with --lora-rank: run the adapters as library GEMMs instead of inside the quantized matmul")
     ap.add_argument("--no-cuda-graph", action="store_true",
                     help="qwen: issue the step's launches one by one instead of replaying them as a CUDA graph")
     args = ap.parse_args()
