@@ -349,7 +349,10 @@ def run_lora(args, dev):
     rows = []
     g = torch.Generator(device=dev).manual_seed(0)
     copies = 4
-    for bits in (4, 8):
+    # --small: one width, one rank, a handful of launches (the case a profiler capture runs)
+    all_bits = (4,) if args.small else (4, 8)
+    all_ranks = ((64,),) if args.small else ((16,), (64,), (128,), (16, 16, 32))
+    for bits in all_bits:
         layers = []
         for _ in range(copies):
             lin = nn.Linear(k, n, bias=True, device=dev)
@@ -360,7 +363,7 @@ def run_lora(args, dev):
         xs = [torch.randn(m, k, device=dev, generator=g).to(torch.bfloat16) for _ in range(copies)]
         ys = [torch.empty(m, n, device=dev, dtype=torch.bfloat16) for _ in range(copies)]
 
-        def timed_together(fns, reps=40, chunks=7):
+        def timed_together(fns, reps=4 if args.small else 40, chunks=1 if args.small else 7):
             """Per function (median, worst) microseconds per call. The functions take turns, one run of `reps`
             calls each per round, so that clock drift under the power cap falls on all of them alike."""
             for fn in fns:
@@ -379,7 +382,7 @@ def run_lora(args, dev):
                     per[j].append(e0.elapsed_time(e1) * 1e3 / reps)
             return [(sorted(v)[len(v) // 2], max(v)) for v in per]
 
-        for ranks in ((16,), (64,), (128,), (16, 16, 32)):
+        for ranks in all_ranks:
             wrapped = []
             for q in layers:
                 adapters = [LoRALinear.from_linear(q, r=r, scale=0.8) for r in ranks]
@@ -470,7 +473,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="flux", choices=["flux", "zimage", "qwen", "sweep", "lora"])
-    ap.add_argument("--small", action="store_true", help="flux at reduced depth for profiler captures (not a bench value)")
+    ap.add_argument("--small", action="store_true", help="flux at reduced depth, lora with one case and few launches: for profiler captures (not a bench value)")
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (default: the workload's own)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--qwen-parallel", default="cfg+tp", choices=["cfg+tp", "tp"],
