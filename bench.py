@@ -518,7 +518,7 @@ def main():
             clocks = sampler.stop()
             print(json.dumps({
                 "metric": "lora_over_qlinear_time_ratio", "value": rows[0]["fused_over_base"],
-                "unit": "time of the rank-16 wrapped W4 layer / time of the frozen layer", "n_gpus": 1, "steps": 1,
+                "unit": "time of the first wrapped case (4 bits, rank 16; rank 64 with --small) / time of the frozen layer", "n_gpus": 1, "steps": 1,
                 "warmup": max(3, args.warmup), "higher_is_better": False, "dtype": "bf16", "data": "synthetic",
                 "config": {"workload": "LoRA adapters over one quantized linear, M 4096 N 12288 K 3072, group 64",
                            "l2_policy": "four operand sets rotated (0.6 GB between reuses)",
