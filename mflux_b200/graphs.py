@@ -1,9 +1,10 @@
 """CUDA-graph replay of a denoiser evaluation.
 
-A tensor-parallel step is a few thousand short launches and collectives; issued one by one from Python the host
-cannot keep eight GPUs fed. `CapturedStep` records the launches of one call (this library's kernels, torch's own
-and NCCL's collectives alike -- all of them are stream work) into a CUDA graph and replays it with new inputs
-copied into the recorded input buffers. Everything that changes between denoising steps therefore has to arrive
+A tensor-parallel step is a few thousand short launches and collectives. `CapturedStep` records the launches of
+one call (this library's kernels, torch's own and NCCL's collectives alike -- all of them are stream work) into a
+CUDA graph and replays it with new inputs copied into the recorded input buffers, which takes the per-launch host
+work out of the step. Measured on the Qwen-Image-shaped step the gain is small, 2.5 % on two and 1.5 % on four
+tensor-parallel B200s: those steps are bound by the GPUs, not by the host; eight ranks were not measured. Everything that changes between denoising steps therefore has to arrive
 as a tensor (the noise level is a one-element tensor, not a Python float); shapes, guidance scale and image size
 are part of the recorded graph, one graph per distinct set of input shapes.
 
