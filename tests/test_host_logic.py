@@ -215,3 +215,47 @@ def test_tensor_parallel_shards_are_slices_of_the_full_quantization():
                                   full_b[:, r * (k // 64) // tp:(r + 1) * (k // 64) // tp], None, 64, bits)
                     for r in range(tp))
         np.testing.assert_allclose(y_sum, y_full, rtol=1e-4, atol=1e-4)
+
+
+def test_low_rank_operands_of_row_fused_layers():
+    """The two dense operands handed to the matmul kernel for adapters on row-concatenated layers: every adapter
+    gets its own columns, acts only on its layer's block of output rows, scales are folded into the second
+    operand, columns are padded with zeros to a multiple of 64, and a change of scale rebuilds them."""
+    import torch
+
+    from mflux_b200.lora import LoRALinear, _FusedTerms
+
+    g = torch.Generator().manual_seed(4)
+    k, n = 96, 40
+
+    def adapter(r, scale):
+        l = LoRALinear(k, n, r=r, scale=scale, device="cpu")
+        l.lora_A.data = torch.randn(k, r, generator=g).to(torch.bfloat16)
+        l.lora_B.data = torch.randn(r, n, generator=g).to(torch.bfloat16)
+        return l
+
+    q1, v1, v2 = adapter(8, 0.5), adapter(16, -1.25), adapter(4, 2.0)
+    terms = _FusedTerms()
+    groups = [(0, [q1]), (2 * n, [v1, v2])]            # rows: q | k (bare) | v | one more bare layer
+    a_cat, b_rows, rank = terms.get(None, groups, 4 * n)
+    assert rank == 28 and a_cat.shape == (k, 64) and b_rows.shape == (4 * n, 64)
+    assert (a_cat[:, 28:] == 0).all() and (b_rows[:, 28:] == 0).all()
+    assert (b_rows[n:2 * n] == 0).all() and (b_rows[3 * n:] == 0).all()      # bare layers: no term
+    assert (b_rows[:n, 8:] == 0).all() and (b_rows[2 * n:3 * n, :8] == 0).all()   # blocks do not leak
+    x = torch.randn(7, k, generator=g).to(torch.bfloat16)
+    got = (x.float() @ a_cat.float()) @ b_rows.float().T
+    want = torch.zeros(7, 4 * n)
+    want[:, :n] = 0.5 * (x.float() @ q1.lora_A.float()) @ q1.lora_B.float()
+    for l in (v1, v2):
+        want[:, 2 * n:3 * n] += l.scale * (x.float() @ l.lora_A.float()) @ l.lora_B.float()
+    # scale * B is rounded to bf16 (2^-9 relative per element): compare in relative L2, not element by element
+    assert float((got - want).norm() / want.norm()) <= 5e-3
+    same = terms.get(None, groups, 4 * n)
+    assert same[1] is b_rows                                              # cached
+    v2.scale = 0.0
+    _, b2, _ = terms.get(None, groups, 4 * n)
+    assert b2 is not b_rows and (b2[2 * n:3 * n, 24:28] == 0).all()
+    # a single wrapped layer is one block from row 0
+    a1, b1, r1 = _FusedTerms().get([q1])
+    assert r1 == 8 and b1.shape == (n, 64)
+    torch.testing.assert_close(b1[:, :8].float(), (0.5 * q1.lora_B.float()).T.to(torch.bfloat16).float())
