@@ -166,7 +166,7 @@ class FusedRows:
         self.groups, row = [], 0
         for base, adapters in parts:
             if adapters:
-                self.groups.append((row, adapters))
+                self.groups.append((row, 1, adapters))
             row += base.weight.shape[0]
         self.rows = row
         self.terms = _FusedTerms() if self.groups else None

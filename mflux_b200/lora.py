@@ -51,27 +51,29 @@ class _FusedTerms:
         self.key, self.a_cat, self.b_rows, self.rank = None, None, None, 0
 
     def get(self, adapters, groups=None, n_rows=None):
-        """`groups`: list of (first row, adapters of that block); default one block of all `adapters` from row 0.
-        `n_rows`: rows of b_rows when blocks without adapters follow the last group."""
+        """`groups`: list of (first row, adapters of that block) or (first row, row step, adapters) -- a step of 2
+        addresses every other row (two layers whose rows are interleaved); default one block of all `adapters`
+        from row 0. `n_rows`: rows of b_rows when rows without adapters follow the last group."""
         if groups is None:
-            groups = [(0, list(adapters))]
-        flat = [l for _, ls in groups for l in ls]
+            groups = [(0, 1, list(adapters))]
+        groups = [g if len(g) == 3 else (g[0], 1, g[1]) for g in groups]
+        flat = [l for _, _, ls in groups for l in ls]
         key = tuple((l.lora_A.data_ptr(), l.lora_A._version, l.lora_B.data_ptr(), l.lora_B._version, float(l.scale))
-                    for l in flat) + tuple(r0 for r0, _ in groups)
+                    for l in flat) + tuple((r0, step) for r0, step, _ in groups)
         if key != self.key:
             rank = sum(l.lora_A.shape[1] for l in flat)
             ld = -(-rank // 64) * 64
             k = flat[0].lora_A.shape[0]
-            n = n_rows or max(r0 + ls[0].lora_B.shape[1] for r0, ls in groups if ls)
+            n = n_rows or max(r0 + step * (ls[0].lora_B.shape[1] - 1) + 1 for r0, step, ls in groups if ls)
             dev = flat[0].lora_A.device
             a_cat = torch.zeros(k, ld, dtype=torch.bfloat16, device=dev)
             b_rows = torch.zeros(n, ld, dtype=torch.bfloat16, device=dev)
             col = 0
-            for r0, ls in groups:
+            for r0, step, ls in groups:
                 for l in ls:
                     r, rows = l.lora_A.shape[1], l.lora_B.shape[1]
                     a_cat[:, col:col + r] = l.lora_A.data
-                    b_rows[r0:r0 + rows, col:col + r] = (float(l.scale) * l.lora_B.data.float()).t()
+                    b_rows[r0:r0 + step * rows:step, col:col + r] = (float(l.scale) * l.lora_B.data.float()).t()
                     col += r
             self.key, self.a_cat, self.b_rows, self.rank = key, a_cat, b_rows, rank
         return self.a_cat, self.b_rows, self.rank

@@ -66,11 +66,25 @@ class ZImageConfig:
 class FusedSwiGLU:
     """w1 and w3 of a FeedForward as one quantized matmul: row 2j of the fused weight is w1's row j, row 2j+1
     is w3's row j, and the matmul epilogue reduces each (gate, up) column pair to silu(gate) * up. Interleaving
-    whole rows keeps every packed code, scale and bias of the two layers unchanged."""
+    whole rows keeps every packed code, scale and bias of the two layers unchanged. LoRA-wrapped layers keep
+    their adapters: w1's act on the even rows of the fused product, w3's on the odd rows, as one low-rank term of
+    the same matmul (added before the epilogue)."""
 
     def __init__(self, w1, w3):
-        self.w1, self.w3 = w1, w3
+        from .lora import _FusedTerms, split_wrapped
+
+        (self.w1, ad1), (self.w3, ad3) = split_wrapped(w1), split_wrapped(w3)
+        self.groups = [(r0, 2, ads) for r0, ads in ((0, ad1), (1, ad3)) if ads]
+        self.terms = _FusedTerms() if self.groups else None
         self.blob = None
+
+    @staticmethod
+    def accepts(w1, w3) -> bool:
+        from .lora import MAX_FUSED_COLUMNS, split_wrapped
+
+        parts = [split_wrapped(w1), split_wrapped(w3)]
+        return (all(p is not None for p in parts)
+                and sum(a.lora_A.shape[1] for _, ads in parts for a in ads) <= MAX_FUSED_COLUMNS)
 
     def __call__(self, x, out):
         w1 = self.w1
@@ -83,8 +97,14 @@ class FusedSwiGLU:
             self.bias = inter(w1.bias.data, self.w3.bias.data) if w1.bias is not None else None
             self.blob = ops.prepare_qlinear(w, s, b, w1.bits, w1.group_size)
             self.wq_stub = torch.empty((w.shape[0], w.shape[1]), dtype=torch.uint32, device="meta")
-        return ops.qlinear(x, self.wq_stub, None, None, self.bias, bits=w1.bits, group_size=w1.group_size,
-                           epilogue="swiglu", out=out, prepared=self.blob)
+        if self.terms is None:
+            return ops.qlinear(x, self.wq_stub, None, None, self.bias, bits=w1.bits, group_size=w1.group_size,
+                               epilogue="swiglu", out=out, prepared=self.blob)
+        a_cat, b_rows, rank = self.terms.get(None, self.groups, self.wq_stub.shape[0])
+        xb = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+        return ops.qlinear(xb, self.wq_stub, None, None, self.bias, bits=w1.bits, group_size=w1.group_size,
+                           epilogue="swiglu", out=out, prepared=self.blob, lora_t=torch.matmul(xb, a_cat),
+                           lora_b=b_rows, lora_r=rank)
 
 
 class ZImageAttention(nn.Module):
@@ -187,7 +207,7 @@ class ZImageTransformer(nn.Module):
         f = self._fused.get(("ffn", id(blk)))
         if f is None:
             ff = blk.feed_forward
-            if isinstance(ff.w1, nn.QuantizedLinear) and isinstance(ff.w3, nn.QuantizedLinear):
+            if FusedSwiGLU.accepts(ff.w1, ff.w3):
                 f = FusedSwiGLU(ff.w1, ff.w3)
             else:
                 f = lambda x, out, ff=ff: out.copy_(torch.nn.functional.silu(ff.w1(x).float()) * ff.w3(x).float())  # noqa: E731

@@ -181,3 +181,41 @@ def test_norm_gate_residual_with_following_pre_norm(lib_built, scaled):
     assert torch.equal(res_a, res_b)
     assert rel_l2(nb[:, lo:hi], ref.float().cpu().numpy()) <= 1e-3
     assert (nb[:, :lo] == 0).all() and (nb[:, hi:] == 0).all()
+
+
+def test_step_with_adapters_on_fused_projections(lib_built):
+    """Adapters on q / v (row-fused projection), on the gate and up projections (interleaved SwiGLU matmul) and on
+    the down projection: the step matches the oracle, which adds every adapter's term layer by layer, and the
+    fused paths are the ones that ran."""
+    from mflux_b200.flux import FusedRows
+    from mflux_b200.lora import apply_lora
+    from mflux_b200.zimage import FusedSwiGLU, ZImageTransformer
+
+    cfg = _small_cfg(n_layers=1, n_refiner_layers=0)
+    model = ZImageTransformer(cfg, bits=4, device="cuda", seed=5)
+    g = torch.Generator(device="cpu").manual_seed(12)
+
+    def ad(i, o, r, scale):
+        return ((torch.randn(i, r, generator=g) * i ** -0.5).cuda(), (torch.randn(r, o, generator=g) * 0.1).cuda(), scale)
+
+    d, h = cfg.dim, cfg.ffn_hidden
+    apply_lora(model, {
+        "layers.0.attention.to_q": [ad(d, d, 8, 1.0)],
+        "layers.0.attention.to_v": [ad(d, d, 4, -0.8), ad(d, d, 16, 0.6)],
+        "layers.0.feed_forward.w1": [ad(d, h, 8, 1.2)],
+        "layers.0.feed_forward.w3": [ad(d, h, 24, -0.9)],
+        "layers.0.feed_forward.w2": [ad(h, d, 8, 1.0)],
+    })
+    lat = torch.randn(2, cfg.in_channels, 1, 16, 16, generator=g).to(torch.bfloat16)
+    cap = torch.randn(2, 32, cfg.cap_feat_dim, generator=g).to(torch.bfloat16)
+    t = torch.tensor([0.3, 0.8])
+    out = model(lat.cuda(), t.cuda(), cap.cuda())
+    torch.cuda.synchronize()
+    ref = oz.forward(model, lat, t, cap)
+    assert rel_l2(out, ref.numpy()) <= TOL
+    fused = list(model._fused.values())
+    assert any(isinstance(f, FusedRows) and f.terms is not None for f in fused)
+    assert any(isinstance(f, FusedSwiGLU) and f.terms is not None for f in fused)
+    # and the adapters matter: the bare model gives something else
+    bare = ZImageTransformer(cfg, bits=4, device="cuda", seed=5)
+    assert rel_l2(bare(lat.cuda(), t.cuda(), cap.cuda()), ref.numpy()) > 2 * TOL

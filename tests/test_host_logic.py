@@ -255,6 +255,12 @@ def test_low_rank_operands_of_row_fused_layers():
     v2.scale = 0.0
     _, b2, _ = terms.get(None, groups, 4 * n)
     assert b2 is not b_rows and (b2[2 * n:3 * n, 24:28] == 0).all()
+    # two layers whose rows are interleaved (gate / up of a fused SwiGLU): step 2 from row 0 and from row 1
+    _, bi, ri = _FusedTerms().get(None, [(0, 2, [q1]), (1, 2, [v1])], 2 * n)
+    assert ri == 24 and bi.shape == (2 * n, 64)
+    assert (bi[0::2, 8:] == 0).all() and (bi[1::2, :8] == 0).all()
+    torch.testing.assert_close(bi[0::2, :8].float(), (0.5 * q1.lora_B.float()).T.to(torch.bfloat16).float())
+    torch.testing.assert_close(bi[1::2, 8:24].float(), (-1.25 * v1.lora_B.float()).T.to(torch.bfloat16).float())
     # a single wrapped layer is one block from row 0
     a1, b1, r1 = _FusedTerms().get([q1])
     assert r1 == 8 and b1.shape == (n, 64)
