@@ -265,3 +265,19 @@ def test_low_rank_operands_of_row_fused_layers():
     a1, b1, r1 = _FusedTerms().get([q1])
     assert r1 == 8 and b1.shape == (n, 64)
     torch.testing.assert_close(b1[:, :8].float(), (0.5 * q1.lora_B.float()).T.to(torch.bfloat16).float())
+
+
+def test_captured_step_refuses_host_tensors():
+    """Graph replay is a device feature: a step called with host tensors fails before anything is recorded."""
+    import pytest
+    import torch
+
+    from mflux_b200.graphs import CapturedStep
+
+    step = CapturedStep(lambda a: a + 1)
+    with pytest.raises(ValueError):
+        step(torch.zeros(4))
+    with pytest.raises(ValueError):
+        step()
+    assert step.captured_shapes == []
+    step.release()   # nothing recorded: a no-op
