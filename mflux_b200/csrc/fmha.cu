@@ -471,15 +471,8 @@ int mfx_fmha(const void* q, const void* k, const void* v, int64_t qkv_row_stride
   p.out = static_cast<__nv_bfloat16*>(out);
   p.out_row_stride = out_row_stride;
   p.out_batch_stride = out_batch_stride;
-  static bool configured = false;
-  static int configured_dev = -1;
-  int dev = 0;
-  MFX_CUDA_TRY(cudaGetDevice(&dev));
-  if (!configured || configured_dev != dev) {
-    MFX_CUDA_TRY(cudaFuncSetAttribute(fmha_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DYN_BYTES));
-    configured = true;
-    configured_dev = dev;
-  }
+  static SmemConfigured configured;
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(fmha_kernel), DYN_BYTES, configured)) return rc;
   dim3 grid(static_cast<unsigned>((seq + BQ - 1) / BQ), static_cast<unsigned>(heads), static_cast<unsigned>(batch));
   fmha_kernel<<<grid, NUM_THREADS, DYN_BYTES, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
   MFX_CUDA_TRY(cudaGetLastError());

@@ -27,6 +27,17 @@ inline size_t dtype_size(int dt) { return dt == MFX_F32 ? 4 : 2; }
 inline bool valid_dtype(int dt) { return dt == MFX_F32 || dt == MFX_BF16 || dt == MFX_F16; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Number of SMs of the current device (looked up once per device; 148 if the query fails).
+int device_sm_count();
+
+// Per-kernel record of the devices on which its dynamic shared-memory limit has been raised. The attribute belongs
+// to (function, device), so every device needs the call once; a mutex makes concurrent host threads safe.
+struct SmemConfigured {
+  bool done[64] = {};
+};
+// cudaFuncSetAttribute(func, MaxDynamicSharedMemorySize, bytes) on the current device unless `rec` says it was done.
+int ensure_dynamic_smem(const void* func, int bytes, SmemConfigured& rec);
+
 // Encodes a tiled tensor map of `rank` dims (innermost first). strides_bytes[i] is the byte stride
 // of dim i+1 (rank-1 entries, multiples of 16). Returns MFX_OK or an error status.
 int encode_tmap(CUtensorMap* out, CUtensorMapDataType dt, int rank, const void* base, const uint64_t* dims,

@@ -93,35 +93,25 @@ __device__ __forceinline__ float load_scalar(const void* p, int dtype, int64_t i
 
 // d = (a - magic) * s + b on packed 16-bit pairs: the subtraction is exact (small integers),
 // the fma rounds once.
-template <uint32_t WF>
 __device__ __forceinline__ uint32_t sub_fma(uint32_t a, uint32_t magic, uint32_t s, uint32_t b) {
   uint32_t d;
-  if (WF == FMT_BF16) {
-    asm("{\n\t.reg .b32 t;\n\t"
-        "sub.rn.bf16x2 t, %1, %2;\n\t"
-        "fma.rn.bf16x2 %0, t, %3, %4;\n\t}"
-        : "=r"(d)
-        : "r"(a), "r"(magic), "r"(s), "r"(b));
-  } else {
-    asm("{\n\t.reg .b32 t;\n\t"
-        "sub.rn.f16x2 t, %1, %2;\n\t"
-        "fma.rn.f16x2 %0, t, %3, %4;\n\t}"
-        : "=r"(d)
-        : "r"(a), "r"(magic), "r"(s), "r"(b));
-  }
+  asm("{\n\t.reg .b32 t;\n\t"
+      "sub.rn.bf16x2 t, %1, %2;\n\t"
+      "fma.rn.bf16x2 %0, t, %3, %4;\n\t}"
+      : "=r"(d)
+      : "r"(a), "r"(magic), "r"(s), "r"(b));
   return d;
 }
 
 // 8 four-bit codes of one prepared uint32 (nibble order e0,e2,e4,e6,e1,e3,e5,e7) -> 8 values in K order:
 // nibble j lands in the low half and nibble 4+j in the high half of one masked word.
-template <uint32_t WF>
 __device__ __forceinline__ uint4 dequant_w4(uint32_t q, uint32_t s2, uint32_t b2) {
-  constexpr uint32_t MAGIC = (WF == FMT_BF16) ? 0x43004300u : 0x64006400u;  // 128.0 | 1024.0: ulp 1
+  constexpr uint32_t MAGIC = 0x43004300u;  // bf16 128.0 twice: ulp 1 up to 255
   uint4 r;
-  r.x = sub_fma<WF>((q & 0x000F000Fu) | MAGIC, MAGIC, s2, b2);          // (e0, e1)
-  r.y = sub_fma<WF>(((q >> 4) & 0x000F000Fu) | MAGIC, MAGIC, s2, b2);   // (e2, e3)
-  r.z = sub_fma<WF>(((q >> 8) & 0x000F000Fu) | MAGIC, MAGIC, s2, b2);   // (e4, e5)
-  r.w = sub_fma<WF>(((q >> 12) & 0x000F000Fu) | MAGIC, MAGIC, s2, b2);  // (e6, e7)
+  r.x = sub_fma((q & 0x000F000Fu) | MAGIC, MAGIC, s2, b2);          // (e0, e1)
+  r.y = sub_fma(((q >> 4) & 0x000F000Fu) | MAGIC, MAGIC, s2, b2);   // (e2, e3)
+  r.z = sub_fma(((q >> 8) & 0x000F000Fu) | MAGIC, MAGIC, s2, b2);   // (e4, e5)
+  r.w = sub_fma(((q >> 12) & 0x000F000Fu) | MAGIC, MAGIC, s2, b2);  // (e6, e7)
   return r;
 }
 
@@ -431,7 +421,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             const uint32_t wds[4] = {pk.x, pk.y, pk.z, pk.w};
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-              *reinterpret_cast<uint4*>(dst + wr_off[h * 4 + j]) = dequant_w4<WF>(wds[j], s2, b2);
+              *reinterpret_cast<uint4*>(dst + wr_off[h * 4 + j]) = dequant_w4(wds[j], s2, b2);
           } else {          // 4 words x 4 codes -> 2 output chunks
             const uint32_t sf = sbv << 16, bf = sbv & 0xFFFF0000u;   // scale and bias as float32 bit patterns
             uint64_t sc2, bi2;
@@ -589,15 +579,8 @@ int launch_epi(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& 
   constexpr int NDQ = 8;
   constexpr int NUM_THREADS = (FIXED_WARPS + NDQ) * 32;
   auto kern = qmm_kernel<BITS, WF, ST, SD, OUT, EPI, NDQ, EXT>;
-  static bool configured = false;  // attribute is per function; set once per process and device reuse is fine
-  static int configured_dev = -1;
-  int dev = 0;
-  MFX_CUDA_TRY(cudaGetDevice(&dev));
-  if (!configured || configured_dev != dev) {
-    MFX_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
-    configured = true;
-    configured_dev = dev;
-  }
+  static SmemConfigured configured;  // one record per instantiation of the kernel
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), L::DYN_BYTES, configured)) return rc;
   kern<<<grid, NUM_THREADS, L::DYN_BYTES, st>>>(tx, tw, tsb, tt, tlb, p);
   MFX_CUDA_TRY(cudaGetLastError());
   return MFX_OK;
@@ -621,18 +604,6 @@ int launch(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tsb,
            const CUtensorMap& tlb, const Params& p, int grid, cudaStream_t st) {
   return p.num_ext > 0 ? launch_ext<BITS, WF, ST, SD, OUT, true>(tx, tw, tsb, tt, tlb, p, grid, st)
                        : launch_ext<BITS, WF, ST, SD, OUT, false>(tx, tw, tsb, tt, tlb, p, grid, st);
-}
-
-int sm_count() {
-  static int cached[64];
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-  if (cached[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    cached[dev] = n;
-  }
-  return cached[dev];
 }
 
 // sb[g * N + n] = bf16(scales[n, g]) | bf16(biases[n, g]) << 16
@@ -859,7 +830,7 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
   p.y = a.y;
   p.y_row_stride = a.y_row_stride;
   p.y_batch_stride = a.y_batch_stride;
-  const int pairs = sm_count() / 2;
+  const int pairs = device_sm_count() / 2;
   const int grid = 2 * (p.total_tiles < pairs ? p.total_tiles : pairs);
   const bool f32 = a.y_dtype == MFX_F32;
   if (a.bits == 4) {

@@ -193,16 +193,6 @@ __global__ void __launch_bounds__(THREADS) qmv_kernel(const Params p) {
   }
 }
 
-int sm_count_cached() {
-  static int cached = 0;
-  if (cached == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    if (cudaDeviceGetAttribute(&cached, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) cached = 148;
-  }
-  return cached;
-}
-
 bool eligible(const mfx_qlinear_args& a) {
   return a.batch == 1 && a.rows <= 16 && (a.epilogue == MFX_EPI_NONE || a.epilogue == MFX_EPI_SILU);
 }
@@ -223,7 +213,7 @@ int run(const mfx_qlinear_args& a, const void* prepared, size_t codes_bytes, cud
   p.y_dtype = a.y_dtype;
   p.y_row_stride = a.y_row_stride;
   // 32 rows per block while that still gives every SM two blocks, else 8 rows per block
-  const bool wide = (a.N + 31) / 32 >= 2 * sm_count_cached();
+  const bool wide = (a.N + 31) / 32 >= 2 * device_sm_count();
   const unsigned blocks = static_cast<unsigned>(wide ? (a.N + 31) / 32 : (a.N + 7) / 8);
   if (a.bits == 4) {
     if (wide) qmv_kernel<4, 4><<<blocks, THREADS, 0, st>>>(p);

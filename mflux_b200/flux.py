@@ -244,13 +244,14 @@ class Transformer(nn.Module):
 
     # ------------------------------------------------------------------ helpers
     def _fuse(self, key, layers):
-        f = self._fused.get(key)
+        fused = nn.fused_cache(self)
+        f = fused.get(key)
         if f is None:
             if FusedRows.accepts(layers):
                 f = FusedRows(layers)
             else:
                 f = lambda x, out, ls=layers: out.copy_(torch.cat([l(x) for l in ls], dim=-1))  # noqa: E731
-            self._fused[key] = f
+            fused[key] = f
         return f
 
     def _workspace(self, b, s, device):

@@ -199,6 +199,5 @@ def apply_lora(model: torch.nn.Module, adapters: dict[str, list[tuple[torch.Tens
             parent[int(name)] = new
         else:
             setattr(parent, name, new)
-    if hasattr(model, "_fused"):
-        model._fused = {}
+    nn.bump_weights_epoch()   # row-fused blobs and recorded graphs built from the bare layers are stale now
     return model

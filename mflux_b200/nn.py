@@ -16,6 +16,28 @@ import torch
 from . import ops
 
 
+# Bumped by everything that replaces weights or modules (Module.update, quantize, the LoRA appliers). Caches that
+# are derived from several layers' weights (row-fused q/k/v blobs, recorded CUDA graphs) remember the value they
+# were built under and are dropped when it has moved on; per-layer prepared blobs are keyed on their own tensors.
+_WEIGHTS_EPOCH = [0]
+
+
+def weights_epoch() -> int:
+    return _WEIGHTS_EPOCH[0]
+
+
+def bump_weights_epoch() -> None:
+    _WEIGHTS_EPOCH[0] += 1
+
+
+def fused_cache(owner) -> dict:
+    """`owner._fused`, emptied first if any weight in the process changed since it was last used."""
+    if getattr(owner, "_fused_epoch", None) != _WEIGHTS_EPOCH[0]:
+        owner._fused = {}
+        owner._fused_epoch = _WEIGHTS_EPOCH[0]
+    return owner._fused
+
+
 class Module(torch.nn.Module):
     """torch.nn.Module with the two mlx.nn.Module helpers the reference calls on the hot path."""
 
@@ -38,6 +60,7 @@ class Module(torch.nn.Module):
             mod = self.get_submodule(key.rsplit(".", 1)[0]) if "." in key else self
             if isinstance(mod, QuantizedLinear):
                 mod._prepared = None
+        bump_weights_epoch()
         if strict:
             missing = set(own) - set(flat)
             if missing:
@@ -170,4 +193,5 @@ def quantize(model: torch.nn.Module, group_size: int = 64, bits: int = 4,
             parent[int(name)] = q
         else:
             setattr(parent, name, q)
+    bump_weights_epoch()
     return model

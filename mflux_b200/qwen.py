@@ -36,6 +36,18 @@ class QwenConfig:
     in_channels: int = 64
     joint_attention_dim: int = 3584
     mlp_ratio: int = 4
+    # sigma schedule of the reference's "qwen-image" ModelConfig (models/common/config/model_config.py:505-520):
+    # a flatter resolution shift than FLUX and a last sigma stretched to 0.02
+    sigma_base_shift: float = 0.5
+    sigma_max_shift: float = 0.9
+    sigma_base_seq_len: int = 256
+    sigma_max_seq_len: int = 8192
+    sigma_shift_terminal: float | None = 0.02
+
+    def scheduler(self, num_inference_steps: int, width: int, height: int) -> LinearScheduler:
+        return LinearScheduler(num_inference_steps, width, height, True, base_shift=self.sigma_base_shift,
+                               max_shift=self.sigma_max_shift, base_seq_len=self.sigma_base_seq_len,
+                               max_seq_len=self.sigma_max_seq_len, shift_terminal=self.sigma_shift_terminal)
 
     def __post_init__(self):
         if self.hidden != self.heads * 128:
@@ -130,13 +142,14 @@ class QwenTransformer(nn.Module):
 
     # ------------------------------------------------------------------ helpers
     def _fuse(self, key, layers):
-        f = self._fused.get(key)
+        fused = nn.fused_cache(self)
+        f = fused.get(key)
         if f is None:
             if FusedRows.accepts(layers):
                 f = FusedRows(layers)
             else:
                 f = lambda x, out, ls=layers: out.copy_(torch.cat([l(x) for l in ls], dim=-1))  # noqa: E731
-            self._fused[key] = f
+            fused[key] = f
         return f
 
     def _workspace(self, b, s, device):
@@ -296,7 +309,7 @@ class QwenImage:
         self.bits = bits
         self.model_config = model_config or QwenConfig()
         self.cfg_rank, self.cfg_group = cfg_rank, cfg_group
-        self.cuda_graph, self._captured = cuda_graph, {}
+        self.cuda_graph, self._captured, self._captured_epoch = cuda_graph, {}, nn.weights_epoch()
         self.transformer = QwenTransformer(self.model_config, bits=bits, device=device, seed=seed, tp_rank=tp_rank,
                                            tp_world=tp_world, tp_group=tp_group)
 
@@ -347,6 +360,10 @@ class QwenImage:
             return run(latents, prompt_embeds, negative_prompt_embeds, sigma)
         from .graphs import CapturedStep
 
+        if self._captured and self._captured_epoch != nn.weights_epoch():
+            self.release_graphs()   # recorded launches point at the prepared blobs of replaced weights
+        self._captured_epoch = nn.weights_epoch()
+
         key = (float(guidance), height, width)
         step = self._captured.get(key)
         if step is None:
@@ -370,7 +387,7 @@ class QwenImage:
         """Returns the final latents [B, (H/16)(W/16), C] (f32); prompt embeddings stand in for the text encoder."""
         dev = prompt_embeds.device
         b = prompt_embeds.shape[0]
-        sched = LinearScheduler(num_inference_steps, width, height, True)
+        sched = self.model_config.scheduler(num_inference_steps, width, height)
         if latents is None:
             g = torch.Generator(device=dev).manual_seed(seed)
             latents = torch.randn(b, (height // 16) * (width // 16), self.model_config.in_channels, device=dev,

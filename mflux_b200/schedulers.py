@@ -56,7 +56,7 @@ class FlowMatchEulerDiscreteScheduler:
         self.shift_terminal = shift_terminal
         n, nt = num_inference_steps, num_train_timesteps
         sigma_min, sigma_max = 1.0 / nt, 1.0
-        t_lin = [sigma_max * nt - i * (sigma_max - sigma_min) * nt / (n - 1) for i in range(n)]
+        t_lin = [sigma_max * nt - i * (sigma_max - sigma_min) * nt / max(n - 1, 1) for i in range(n)]
         shifted = [self._time_shift(1.0, 1.0, t / nt) for t in t_lin]
         one_minus = [1.0 - s for s in shifted]
         scale = one_minus[-1] / (1.0 - shift_terminal)

@@ -26,7 +26,7 @@ import torch
 
 from . import nn, ops, resolution
 from .flux import FusedRows, RMSNorm, _call, _Ctx
-from .schedulers import LinearScheduler
+from .schedulers import FlowMatchEulerDiscreteScheduler, LinearScheduler
 
 
 @dataclass
@@ -45,6 +45,10 @@ class ZImageConfig:
     axes_dims: tuple = (32, 48, 48)
     axes_lens: tuple = (1024, 512, 512)
     ffn_hidden: int = field(default=0)
+    # False = the Turbo checkpoint (guidance forced to 0, linear schedule); True = the base model, which runs with
+    # a negative prompt on the flow-match schedule (models/common/config/model_config.py:580-603)
+    supports_guidance: bool = False
+    requires_sigma_shift: bool = True
 
     def __post_init__(self):
         if self.dim != self.n_heads * 128:
@@ -192,7 +196,8 @@ class ZImageTransformer(nn.Module):
 
     # ------------------------------------------------------------------ helpers
     def _qkv(self, blk):
-        f = self._fused.get(("qkv", id(blk)))
+        fused = nn.fused_cache(self)
+        f = fused.get(("qkv", id(blk)))
         if f is None:
             a = blk.attention
             layers = [a.to_q, a.to_k, a.to_v]
@@ -200,18 +205,19 @@ class ZImageTransformer(nn.Module):
                 f = FusedRows(layers)
             else:
                 f = lambda x, out, ls=layers: out.copy_(torch.cat([l(x) for l in ls], dim=-1))  # noqa: E731
-            self._fused[("qkv", id(blk))] = f
+            fused[("qkv", id(blk))] = f
         return f
 
     def _swiglu(self, blk):
-        f = self._fused.get(("ffn", id(blk)))
+        fused = nn.fused_cache(self)
+        f = fused.get(("ffn", id(blk)))
         if f is None:
             ff = blk.feed_forward
             if FusedSwiGLU.accepts(ff.w1, ff.w3):
                 f = FusedSwiGLU(ff.w1, ff.w3)
             else:
                 f = lambda x, out, ff=ff: out.copy_(torch.nn.functional.silu(ff.w1(x).float()) * ff.w3(x).float())  # noqa: E731
-            self._fused[("ffn", id(blk))] = f
+            fused[("ffn", id(blk))] = f
         return f
 
     def _workspace(self, b, s, device):
@@ -397,6 +403,22 @@ class ZImage:
         if hasattr(self.transformer, "_fused"):
             self.transformer._fused = {}
 
+    def make_scheduler(self, num_inference_steps: int, width: int, height: int, scheduler: str | None = None):
+        """The schedule Config.scheduler builds for this model (models/common/config/config.py:146-164): by name,
+        defaulting to "flow_match_euler_discrete" with guidance support and "linear" without; a scheduler that
+        has set_image_seq_len gets the image sequence length when the model wants its sigmas shifted."""
+        cfg = self.model_config
+        if scheduler is None:
+            scheduler = "flow_match_euler_discrete" if cfg.supports_guidance else "linear"
+        if scheduler == "linear":
+            return LinearScheduler(num_inference_steps, width, height, cfg.requires_sigma_shift)
+        if scheduler == "flow_match_euler_discrete":
+            sched = FlowMatchEulerDiscreteScheduler(num_inference_steps)
+            if cfg.requires_sigma_shift:
+                sched.set_image_seq_len((height // 16) * (width // 16))
+            return sched
+        raise NotImplementedError(f"The scheduler {scheduler!r} is not implemented.")
+
     def denoise_step(self, latents, cap_feats, negative_cap_feats, sigma, dt, guidance):
         b = latents.shape[0]
         t = torch.full((b,), 1.0 - sigma, device=latents.device)
@@ -410,11 +432,16 @@ class ZImage:
 
     def generate_image(self, seed: int, cap_feats: torch.Tensor, negative_cap_feats: torch.Tensor | None = None,
                        num_inference_steps: int = 9, height: int = 1024, width: int = 1024, guidance: float = 0.0,
-                       latents: torch.Tensor | None = None) -> torch.Tensor:
-        """Returns the final latents [B, C, 1, H/8, W/8] (f32); caption features stand in for the text encoder."""
+                       latents: torch.Tensor | None = None, scheduler: str | None = None) -> torch.Tensor:
+        """Returns the final latents [B, C, 1, H/8, W/8] (f32); caption features stand in for the text encoder.
+
+        As in the reference (variants/z_image.py:60-66) a model without guidance support runs with guidance 0 on
+        the linear schedule, one with it on the flow-match schedule unless `scheduler` names the other."""
         dev = cap_feats.device
         b = cap_feats.shape[0]
-        sched = LinearScheduler(num_inference_steps, width, height, True)
+        if not self.model_config.supports_guidance:
+            guidance = 0.0
+        sched = self.make_scheduler(num_inference_steps, width, height, scheduler)
         if latents is None:
             g = torch.Generator(device=dev).manual_seed(seed)
             latents = torch.randn(b, self.model_config.in_channels, 1, height // 8, width // 8, device=dev, generator=g)

@@ -281,3 +281,68 @@ def test_captured_step_refuses_host_tensors():
         step()
     assert step.captured_shapes == []
     step.release()   # nothing recorded: a no-op
+
+
+def test_qwen_sigma_schedule_uses_the_qwen_image_config():
+    """The reference's "qwen-image" ModelConfig (models/common/config/model_config.py:505-520) shifts with
+    max_shift 0.9 over max_seq_len 8192 and stretches the last sigma to 0.02; LinearScheduler._get_sigmas
+    (linear_scheduler.py:25-48) applies all three. Values below are that formula evaluated in float64."""
+    from mflux_b200.qwen import QwenConfig
+
+    n, w, h = 20, 1328, 1328
+    s = QwenConfig().scheduler(n, w, h)
+    m = (0.9 - 0.5) / (8192 - 256)
+    mu = m * w * h / 256 + (0.5 - m * 256)
+    lin = np.linspace(1.0, 1.0 / n, n)
+    shifted = np.exp(mu) / (np.exp(mu) + (1.0 / lin - 1.0))
+    one_minus = 1.0 - shifted
+    want = 1.0 - one_minus / (one_minus[-1] / (1.0 - 0.02))
+    assert s.sigmas.shape == (n + 1,) and s.sigmas[-1] == 0.0
+    np.testing.assert_allclose(s.sigmas[:-1], want, rtol=2e-5)
+    assert abs(float(s.sigmas[-2]) - 0.02) < 1e-6          # terminal stretch
+    assert abs(mu - 0.8343) < 1e-3                           # not the FLUX shift (about 1.6 at this size)
+    flux_like = LinearScheduler(n, w, h, True)
+    assert not np.allclose(flux_like.sigmas, s.sigmas, atol=1e-3)
+
+
+def test_zimage_scheduler_choice_follows_guidance_support():
+    """variants/z_image.py:60-66: guidance support picks flow_match_euler_discrete, Turbo (no guidance) linear;
+    Config.scheduler (config.py:146-164) hands the flow-match schedule the image sequence length."""
+    from mflux_b200.schedulers import FlowMatchEulerDiscreteScheduler
+    from mflux_b200.zimage import ZImage, ZImageConfig
+
+    pick = ZImage.make_scheduler
+    turbo = type("P", (), {"model_config": ZImageConfig(supports_guidance=False)})()
+    base = type("P", (), {"model_config": ZImageConfig(supports_guidance=True)})()
+    assert isinstance(pick(turbo, 9, 1024, 1024), LinearScheduler)
+    fm = pick(base, 9, 1024, 1024)
+    assert isinstance(fm, FlowMatchEulerDiscreteScheduler)
+    want = FlowMatchEulerDiscreteScheduler(9)
+    want.set_image_seq_len(64 * 64)
+    np.testing.assert_array_equal(fm.sigmas, want.sigmas)
+    assert isinstance(pick(base, 9, 1024, 1024, "linear"), LinearScheduler)
+    assert isinstance(pick(turbo, 9, 1024, 1024, "flow_match_euler_discrete"), FlowMatchEulerDiscreteScheduler)
+    with pytest.raises(NotImplementedError):
+        pick(base, 9, 1024, 1024, "ddim")
+
+
+def test_weight_updates_invalidate_derived_caches():
+    """Module.update and nn.quantize move the weights epoch, which empties every cache built from several layers'
+    weights (row-fused blobs) the next time it is consulted."""
+    import torch
+
+    from mflux_b200 import nn
+
+    class Owner:
+        pass
+
+    o = Owner()
+    nn.fused_cache(o)["k"] = "blob"
+    assert nn.fused_cache(o) == {"k": "blob"}
+    m = nn.Module()
+    m.lin = torch.nn.Linear(2, 2)
+    m.update({"lin": {"weight": torch.zeros(2, 2)}}, strict=False)
+    assert nn.fused_cache(o) == {}
+    nn.fused_cache(o)["k"] = "blob"
+    nn.quantize(torch.nn.Sequential(), class_predicate=lambda p, mod: False)
+    assert nn.fused_cache(o) == {}
