@@ -32,11 +32,23 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-# Mean DRAM bytes (read + write) per quantized-matmul launch of the full flux step, from an ncu capture of
-# dram__bytes_read.sum + dram__bytes_write.sum on the reduced-depth model at the same per-GPU batch, weighted by
-# the block counts of the full model (every block of one kind launches the same shapes): 573 GB over 352 launches,
-# 1.13x the algorithmic bytes.
-QMM_TRAFFIC_PER_LAUNCH = 1.629e9
+TRAFFIC_RECORD = ROOT / "profiles" / "qmm_flux_step_dram_traffic.json"
+
+
+def recorded_traffic():
+    """Mean DRAM bytes (read + write) per quantized-matmul launch of the full flux step, from the committed record
+    of an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum on the reduced-depth model at the same per-GPU
+    batch, weighted by the block counts of the full model). The record names the command that made it and the
+    SHA-256 of the kernel source it was taken on; it is reported only while that source is unchanged."""
+    import hashlib
+
+    if not TRAFFIC_RECORD.exists():
+        return None
+    rec = json.loads(TRAFFIC_RECORD.read_text())
+    src = ROOT / "mflux_b200" / "csrc" / "qmm.cu"
+    if hashlib.sha256(src.read_bytes()).hexdigest() != rec.get("qmm_cu_sha256"):
+        return None
+    return rec.get("dram_bytes_per_launch")
 
 
 def step_flops(cfg, batch, si, st):
@@ -96,14 +108,32 @@ def measured_peaks():
     return 1400.0, "fallback (sustained)", 1590.0
 
 
+def blas_threads(cores: int) -> int:
+    """Gives the BLAS behind NumPy `cores` threads (a launcher may have exported OMP_NUM_THREADS=1) and returns
+    the number it reports afterwards."""
+    try:
+        from threadpoolctl import threadpool_info, threadpool_limits
+
+        threadpool_limits(limits=cores)
+        return max((int(p.get("num_threads", 1)) for p in threadpool_info()), default=1)
+    except Exception:
+        return int(os.environ.get("OMP_NUM_THREADS", "1") or 1)
+
+
+def measured_hbm():
+    f = ROOT / "MEASURED_PEAKS.json"
+    return json.loads(f.read_text()).get("hbm_gbs", 6650.0) if f.exists() else 6650.0
+
+
 def cpu_sample(seconds_target: float = 12.0):
     """Times the CPU oracle (dequantize + float32 matmul on all host cores) on a bounded sample: quantized
-    linears of the step's dominant shape. Returns (TFLOP/s, description, cores)."""
+    linears of the step's dominant shape. Returns (TFLOP/s, description, cores, BLAS threads)."""
     import numpy as np
 
     from oracle import quant
 
     cores = os.cpu_count() or 1
+    threads = blas_threads(cores)
     m, n, k = 2048, 3072, 3072
     rng = np.random.default_rng(0)
     w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
@@ -119,7 +149,7 @@ def cpu_sample(seconds_target: float = 12.0):
     dt = (time.perf_counter() - t0) / reps
     desc = (f"{reps} x quantized linear M={m} N={n} K={k} W4 g64 (dequantize + float32 GEMM, numpy/OpenBLAS), "
             f"scaled to a step by algorithmic flops")
-    return 2.0 * m * n * k / dt / 1e12, desc, cores
+    return 2.0 * m * n * k / dt / 1e12, desc, cores, threads
 
 
 def run_reference(args, spec):
@@ -128,9 +158,9 @@ def run_reference(args, spec):
         return
     flops = spec["lin"] + spec["attn"]
     vals = []
-    desc, cores = "", 1
+    desc, cores, threads = "", 1, 1
     for i in range(args.warmup + args.steps):
-        tf, desc, cores = cpu_sample(seconds_target=max(2.0, 20.0 / max(1, args.steps + args.warmup)))
+        tf, desc, cores, threads = cpu_sample(seconds_target=max(2.0, 20.0 / max(1, args.steps + args.warmup)))
         if i >= args.warmup:
             vals.append(tf)
     tflops = sum(vals) / len(vals)
@@ -139,9 +169,11 @@ def run_reference(args, spec):
         "impl": "reference", "metric": spec["metric"], "value": value, "unit": spec["unit"], "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / value, "higher_is_better": True,
         "scaling": spec["scaling"], "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": spec["workload"], "note": "CPU oracle port of the MLX arithmetic; "
-                   "MLX itself is not installable offline"},
-        "cpu_baseline": {"value": value, "unit": spec["unit"], "cores": cores, "kind": "port", "sample": desc},
+        "config": {"workload": spec["workload"], "note": "CPU oracle port of the MLX arithmetic (MLX itself is not "
+                   "installable offline); every step times the bounded sample below, value and ms_per_step are "
+                   "that sample's rate extrapolated to a whole step by algorithmic flops, not a step that ran"},
+        "cpu_baseline": {"value": value, "unit": spec["unit"], "cores": cores, "threads": threads, "kind": "port",
+                         "sample": desc},
         "e2e": {"value": value, "unit": spec["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -486,6 +518,11 @@ def main():
     ap.add_argument("--no-cuda-graph", action="store_true",
                     help="qwen: issue the step's launches one by one instead of replaying them as a CUDA graph")
     args = ap.parse_args()
+    if args.impl == "reference":
+        # torch.distributed.run exports OMP_NUM_THREADS=1 to its workers; the CPU arm is meant to use every core,
+        # at every N, so say so before NumPy's BLAS is loaded
+        for var in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+            os.environ[var] = str(os.cpu_count() or 1)
 
     if args.workload in ("sweep", "lora"):
         spec = None
@@ -561,7 +598,7 @@ def main():
 
     sampler = ClockSampler(local)
     sampler.start()
-    ops.QLINEAR_TRACE = []
+    ops.TRACE = {}
     launches0 = ops.LAUNCHES[0]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -571,7 +608,7 @@ def main():
     e1.record()
     barrier()
     launches = ops.LAUNCHES[0] - launches0
-    trace, ops.QLINEAR_TRACE = ops.QLINEAR_TRACE, None
+    trace, ops.TRACE = ops.TRACE, None
     ms = e0.elapsed_time(e1)
 
     # end to end through the public call with host buffers: pinned H2D of the step's inputs, D2H of its result
@@ -587,13 +624,13 @@ def main():
     clocks = sampler.stop()
     trace_steps = args.steps
     if not trace and hasattr(step, "eager"):
-        # a replayed graph has no per-launch events: time the quantized linears on launch-by-launch passes
+        # a replayed graph has no per-launch events: time the kernels on launch-by-launch passes
         trace_steps = min(2, args.steps)
-        ops.QLINEAR_TRACE = []
+        ops.TRACE = {}
         for i in range(trace_steps):
             step.eager(i, *dev_in)
         barrier()
-        trace, ops.QLINEAR_TRACE = ops.QLINEAR_TRACE, None
+        trace, ops.TRACE = ops.TRACE, None
     status = ops.poll_device_status()
 
     times = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
@@ -605,13 +642,24 @@ def main():
         units = world if spec["scaling"] == "weak" else 1   # weak: every rank finishes its own steps
         value = units * args.steps / (ms / 1e3)
         e2e_value = units * args.steps / (ms_e2e / 1e3)
-        q_flops = sum(t[0] for t in trace)
-        q_ms = sum(t[1].elapsed_time(t[2]) for t in trace)
+        def totals(kind):
+            rows = trace.get(kind, [])
+            return (sum(t[0] for t in rows), sum(t[1] for t in rows), sum(t[2].elapsed_time(t[3]) for t in rows),
+                    len(rows))
+
+        q_flops, _, q_ms, q_n = totals("qlinear")
+        a_flops, _, a_ms, a_n = totals("fmha")
+        _, g_bytes, g_ms, g_n = totals("glue")
         peak, peak_kind, burst = measured_peaks()
         achieved = q_flops / (q_ms / 1e3) / 1e12 if q_ms > 0 else 0.0
+        a_achieved = a_flops / (a_ms / 1e3) / 1e12 if a_ms > 0 else 0.0
+        g_achieved = g_bytes / (g_ms / 1e3) / 1e9 if g_ms > 0 else 0.0
+        hbm = measured_hbm()
+        sm_mhz = clocks.get("sm_mhz")
+        step_ms = ms / args.steps
         flops = spec["lin"] + spec["attn"]
-        traffic = QMM_TRAFFIC_PER_LAUNCH if (args.workload == "flux" and not args.small and
-                                             spec["per_gpu_batch"] == 16) else None
+        traffic = recorded_traffic() if (args.workload == "flux" and not args.small and
+                                         spec["per_gpu_batch"] == 16) else None
         line = {
             "metric": spec["metric"], "value": value, "unit": spec["unit"], "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
@@ -626,15 +674,29 @@ def main():
             "clocks": clocks,
             "roofline": {"bound": "tensor", "kernel": "qmm_kernel (quantized linear)", "achieved": achieved,
                          "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak if peak else None,
-                         "peak_kind": peak_kind, "burst_peak": burst, "launches": len(trace),
-                         "share_of_step_time": (q_ms / trace_steps) / (ms / args.steps) if ms > 0 else None, "traffic": traffic,
-                         "traffic_unit": "DRAM bytes per launch, mean over the step's launches (ncu)"},
+                         "peak_kind": peak_kind, "burst_peak": burst,
+                         "frac_of_burst": achieved / burst if burst else None,
+                         "tflops_per_sm_mhz": achieved / sm_mhz if sm_mhz else None, "launches": q_n,
+                         "share_of_step_time": (q_ms / trace_steps) / step_ms if ms > 0 else None, "traffic": traffic,
+                         "traffic_unit": "DRAM bytes per launch, mean over the step's launches (ncu record under "
+                                         "profiles/, null when the kernel source changed since the capture)"},
+            "roofline_attention": {"bound": "tensor", "kernel": "fmha_kernel (flash attention, head dim 128)",
+                                   "achieved": a_achieved, "peak": peak, "unit": "TFLOP/s",
+                                   "frac": a_achieved / peak if peak else None, "peak_kind": peak_kind,
+                                   "burst_peak": burst, "frac_of_burst": a_achieved / burst if burst else None,
+                                   "launches": a_n,
+                                   "share_of_step_time": (a_ms / trace_steps) / step_ms if ms > 0 else None},
+            "roofline_glue": {"bound": "hbm", "kernel": "norm / modulate / qk-norm + RoPE / gated-residual kernels",
+                              "achieved": g_achieved, "peak": hbm, "unit": "GB/s",
+                              "frac": g_achieved / hbm if hbm else None, "peak_kind": "measured copy bandwidth",
+                              "launches": g_n,
+                              "share_of_step_time": (g_ms / trace_steps) / step_ms if ms > 0 else None},
             "step_tflops": flops / 1e12 * args.steps / (ms / 1e3) / (world if spec["scaling"] == "strong" else 1),
         }
         if not args.no_cpu_baseline and world == 1:
-            tf, desc, cores = cpu_sample()
-            line["cpu_baseline"] = {"value": tf * 1e12 / flops, "unit": spec["unit"], "cores": cores, "kind": "port",
-                                    "sample": desc}
+            tf, desc, cores, threads = cpu_sample()
+            line["cpu_baseline"] = {"value": tf * 1e12 / flops, "unit": spec["unit"], "cores": cores,
+                                    "threads": threads, "kind": "port", "sample": desc}
         print(json.dumps(line), flush=True)
     getattr(step, "release", lambda: None)()
     if world > 1:

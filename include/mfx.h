@@ -208,6 +208,18 @@ int mfx_fmha(const void* q, const void* k, const void* v, int64_t qkv_row_stride
              int64_t seq, int64_t batch, int heads, float scale, void* out, int64_t out_row_stride,
              int64_t out_batch_stride, void* stream);
 
+/* mfx_fmha with an additive bias per key: softmax(Q K^T * scale + key_bias[sample, key]) V, the bias shared by
+ * all heads and queries of a sample. Replaces scaled_dot_product_attention(..., mask=additive) where the mask is
+ * the [B, 1, 1, S] key-padding mask built by AttentionUtils.convert_key_padding_mask_to_additive_mask
+ * (attention_utils.py:55-72) and QwenAttention._convert_mask_for_qwen
+ * (src/mflux/models/qwen/model/qwen_transformer/qwen_attention.py:117-135): 0 on real keys, -1e9 on padded text
+ * keys. key_bias is f32 [batch, seq] with bias_batch_stride elements between samples (16-byte aligned, stride a
+ * multiple of 4). Any finite values are accepted; a row whose keys all carry -1e9 yields the mean of V. */
+int mfx_fmha_bias(const void* q, const void* k, const void* v, int64_t qkv_row_stride, int64_t qkv_batch_stride,
+                  int64_t seq, int64_t batch, int heads, float scale, const float* key_bias,
+                  int64_t bias_batch_stride, void* out, int64_t out_row_stride, int64_t out_batch_stride,
+                  void* stream);
+
 /* out = act(a + b + c) elementwise (b, c nullable; act 0 = identity, 1 = SiLU, 2 = tanh): the conditioning-vector
  * arithmetic of time_text_embed.py:25-31, the nn.silu in front of every AdaLN linear and the mx.tanh on the
  * Z-Image gates (z_image_transformer/transformer_block.py:26-27). */

@@ -164,6 +164,11 @@ SIGNATURES = {
         [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, ctypes.c_float, c_void_p, c_int64,
          c_int64, c_void_p],
     ),
+    "mfx_fmha_bias": (
+        c_int,
+        [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, ctypes.c_float, c_void_p, c_int64,
+         c_void_p, c_int64, c_int64, c_void_p],
+    ),
     "mfx_vec_sum_act": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int64, c_void_p]),
     "mfx_gate_residual": (
         c_int,

@@ -63,6 +63,8 @@ constexpr int DYN_BYTES = OFF_XCH + XCH_BYTES + 1024;
 struct Params {
   int seq, batch, heads;
   float scale_log2;  // scale * log2(e)
+  const float* key_bias;        // optional additive bias per (sample, key), added to the scaled scores
+  int64_t bias_batch_stride;
   __nv_bfloat16* out;
   int64_t out_row_stride, out_batch_stride;
 };
@@ -168,6 +170,9 @@ __device__ __forceinline__ void exp_chunk(const uint32_t (&s)[32], uint64_t scal
   }
 }
 
+// HAS_BIAS adds a per-key additive bias (a key-padding mask) to the scaled scores before the row maximum; the
+// variant without it is the plain kernel, instruction for instruction.
+template <bool HAS_BIAS>
 __global__ void __launch_bounds__(NUM_THREADS, CTAS_PER_SM)
 fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
             const __grid_constant__ CUtensorMap tmap_v, const Params p) {
@@ -317,6 +322,30 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       uint32_t sA[32];
       tmem_ld_32x32(t_s, sA);
       tmem_ld_fence(sA);
+      if constexpr (HAS_BIAS) {
+        // scores become s * scale * log2(e) + bias * log2(e) here; everything after works on them with scale 1.
+        // All threads of the warp read the same 32 bias values (one transaction per load).
+        constexpr float LOG2E = 1.4426950408889634f;
+        const int k0 = j * BKV + pt * 32;
+        const float* bp = p.key_bias + b * p.bias_batch_stride + k0;
+        if (!tail) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 bv = __ldg(reinterpret_cast<const float4*>(bp) + i);
+            sA[4 * i + 0] = __float_as_uint(fmaf(__uint_as_float(sA[4 * i + 0]), p.scale_log2, bv.x * LOG2E));
+            sA[4 * i + 1] = __float_as_uint(fmaf(__uint_as_float(sA[4 * i + 1]), p.scale_log2, bv.y * LOG2E));
+            sA[4 * i + 2] = __float_as_uint(fmaf(__uint_as_float(sA[4 * i + 2]), p.scale_log2, bv.z * LOG2E));
+            sA[4 * i + 3] = __float_as_uint(fmaf(__uint_as_float(sA[4 * i + 3]), p.scale_log2, bv.w * LOG2E));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float bv = i < keys_here ? __ldg(bp + i) : 0.f;
+            sA[i] = __float_as_uint(fmaf(__uint_as_float(sA[i]), p.scale_log2, bv * LOG2E));
+          }
+        }
+      }
+      const float sc = HAS_BIAS ? 1.0f : p.scale_log2;
       float m_mine;
       if (!tail) {
         m_mine = max_chunk(sA, -INFINITY);
@@ -333,7 +362,7 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       float m_all = m_mine;
 #pragma unroll
       for (int o = 0; o < PARTS; ++o) m_all = fmaxf(m_all, xch[st * XCH_FLOATS + xch_row + 32 * o]);
-      const float m_tile = m_all * p.scale_log2;
+      const float m_tile = m_all * sc;
       // grow the reference maximum only when it would change the exponent range by more than 2^8; both warps
       // of a quarter see the same maxima and take the same branch, each rescaling its own half of O
       const bool grow = m_tile > m_ref + 8.0f;
@@ -365,13 +394,13 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       uint64_t l2 = pack2(0.f, 0.f);
       uint32_t pk[16];
       if (!tail) {
-        exp_chunk(sA, pack2(p.scale_log2, p.scale_log2), pack2(-m_ref, -m_ref), l2, pk);
+        exp_chunk(sA, pack2(sc, sc), pack2(-m_ref, -m_ref), l2, pk);
       } else {
         float l0 = 0.f, l1 = 0.f;
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float p0 = ex2(fmaf(__uint_as_float(sA[2 * i]), p.scale_log2, -m_ref));
-          float p1 = ex2(fmaf(__uint_as_float(sA[2 * i + 1]), p.scale_log2, -m_ref));
+          float p0 = ex2(fmaf(__uint_as_float(sA[2 * i]), sc, -m_ref));
+          float p1 = ex2(fmaf(__uint_as_float(sA[2 * i + 1]), sc, -m_ref));
           if (2 * i >= keys_here) p0 = 0.f;
           if (2 * i + 1 >= keys_here) p1 = 0.f;
           l0 += p0;
@@ -436,19 +465,23 @@ MFX_DEFINE_STATUS_READER(read_status)
 }  // namespace fmha
 }  // namespace mfx
 
-extern "C" {
+namespace mfx {
+namespace fmha {
 
-int mfx_fmha(const void* q, const void* k, const void* v, int64_t qkv_row_stride, int64_t qkv_batch_stride,
-             int64_t seq, int64_t batch, int heads, float scale, void* out, int64_t out_row_stride,
-             int64_t out_batch_stride, void* stream) {
-  using namespace mfx;
-  using namespace mfx::fmha;
+int run(const void* q, const void* k, const void* v, int64_t qkv_row_stride, int64_t qkv_batch_stride, int64_t seq,
+        int64_t batch, int heads, float scale, const float* key_bias, int64_t bias_batch_stride, void* out,
+        int64_t out_row_stride, int64_t out_batch_stride, cudaStream_t stream) {
   if (!q || !k || !v || !out) return MFX_ERR_NULL;
   if (seq <= 0 || batch <= 0 || heads <= 0) return MFX_ERR_SHAPE;
   if (seq > (1 << 24) || batch > 65535 || heads > 65535) return MFX_ERR_TOO_LARGE;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || (qkv_row_stride * 2) % 16 != 0 ||
       (qkv_batch_stride * 2) % 16 != 0 || (out_row_stride * 2) % 16 != 0 || (out_batch_stride * 2) % 16 != 0)
     return MFX_ERR_ALIGN;
+  if (key_bias) {
+    // the kernel reads the bias of 32 consecutive keys as eight 16-byte vectors
+    if (!aligned16(key_bias) || (bias_batch_stride * 4) % 16 != 0) return MFX_ERR_ALIGN;
+    if (batch > 1 && bias_batch_stride < seq) return MFX_ERR_SHAPE;
+  }
   if (int rc = check_arch()) return rc;
   CUtensorMap tq, tk, tv;
   const uint64_t dims[4] = {HD, static_cast<uint64_t>(heads), static_cast<uint64_t>(seq),
@@ -468,15 +501,46 @@ int mfx_fmha(const void* q, const void* k, const void* v, int64_t qkv_row_stride
   p.batch = static_cast<int>(batch);
   p.heads = heads;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.key_bias = key_bias;
+  p.bias_batch_stride = batch > 1 ? bias_batch_stride : 0;
   p.out = static_cast<__nv_bfloat16*>(out);
   p.out_row_stride = out_row_stride;
   p.out_batch_stride = out_batch_stride;
-  static SmemConfigured configured;
-  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(fmha_kernel), DYN_BYTES, configured)) return rc;
   dim3 grid(static_cast<unsigned>((seq + BQ - 1) / BQ), static_cast<unsigned>(heads), static_cast<unsigned>(batch));
-  fmha_kernel<<<grid, NUM_THREADS, DYN_BYTES, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
+  if (key_bias) {
+    static SmemConfigured configured;
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(fmha_kernel<true>), DYN_BYTES, configured))
+      return rc;
+    fmha_kernel<true><<<grid, NUM_THREADS, DYN_BYTES, stream>>>(tq, tk, tv, p);
+  } else {
+    static SmemConfigured configured;
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(fmha_kernel<false>), DYN_BYTES, configured))
+      return rc;
+    fmha_kernel<false><<<grid, NUM_THREADS, DYN_BYTES, stream>>>(tq, tk, tv, p);
+  }
   MFX_CUDA_TRY(cudaGetLastError());
   return MFX_OK;
+}
+
+}  // namespace fmha
+}  // namespace mfx
+
+extern "C" {
+
+int mfx_fmha(const void* q, const void* k, const void* v, int64_t qkv_row_stride, int64_t qkv_batch_stride,
+             int64_t seq, int64_t batch, int heads, float scale, void* out, int64_t out_row_stride,
+             int64_t out_batch_stride, void* stream) {
+  return mfx::fmha::run(q, k, v, qkv_row_stride, qkv_batch_stride, seq, batch, heads, scale, nullptr, 0, out,
+                        out_row_stride, out_batch_stride, static_cast<cudaStream_t>(stream));
+}
+
+int mfx_fmha_bias(const void* q, const void* k, const void* v, int64_t qkv_row_stride, int64_t qkv_batch_stride,
+                  int64_t seq, int64_t batch, int heads, float scale, const float* key_bias,
+                  int64_t bias_batch_stride, void* out, int64_t out_row_stride, int64_t out_batch_stride,
+                  void* stream) {
+  if (!key_bias) return MFX_ERR_NULL;
+  return mfx::fmha::run(q, k, v, qkv_row_stride, qkv_batch_stride, seq, batch, heads, scale, key_bias,
+                        bias_batch_stride, out, out_row_stride, out_batch_stride, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -241,6 +241,7 @@ class Transformer(nn.Module):
         self._fused = {}
         self._buffers_for = None
         self._rope = {}
+        self.trace = None   # a dict here receives a copy of the residual stream after every block (parity tests)
 
     # ------------------------------------------------------------------ helpers
     def _fuse(self, key, layers):
@@ -348,6 +349,8 @@ class Transformer(nn.Module):
             _call(blk.ff_context.linear1, n_txt, epilogue="gelu_approx", out=ffb[:, :st])
             _call(blk.ff_context.linear2, ffb[:, :st], epilogue="gate_residual", gate=mod_t[:, 5 * d:6 * d],
                   residual=x_txt, out=x_txt)
+            if self.trace is not None:
+                self.trace[f"joint{i}"] = xs.clone()
 
         for i, blk in enumerate(self.single_transformer_blocks):
             a = blk.attn
@@ -359,6 +362,8 @@ class Transformer(nn.Module):
             ops.fmha(qkv, heads, out=attn)
             _call(blk.proj_mlp, nbuf, epilogue="gelu_approx", out=ffb)
             _call(blk.proj_out, cat, epilogue="gate_residual", gate=mod[:, 2 * d:3 * d], residual=xs, out=xs)
+            if self.trace is not None:
+                self.trace[f"single{i}"] = xs.clone()
 
         mod = _call(self.norm_out.linear, sv)               # [B, 2D]: scale, shift
         ops.norm_modulate(x_img, mod[:, d:2 * d], mod[:, 0:d], out=n_img)

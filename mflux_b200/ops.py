@@ -22,8 +22,23 @@ _EPI = {None: EPI_NONE, "none": EPI_NONE, "gelu": EPI_GELU_ERF, "gelu_erf": EPI_
 
 # Kernel launches issued through this module since import (bench.py reports the count of a timed region).
 LAUNCHES = [0]
-# When set to a list, qlinear appends (flops, start_event, end_event) for every launch (bench.py's roofline leg).
-QLINEAR_TRACE = None
+# When set to a dict, the traced operations append (flops, bytes, start_event, end_event) per launch under their
+# kind ("qlinear", "fmha", "glue"): bench.py's roofline legs read the events after the timed region. `flops` and
+# `bytes` are the algorithmic work of the launch (2 M N K; 4 B H S^2 128; one read and one write of the rows).
+TRACE = None
+_trace_open = []
+
+
+def _trace_begin():
+    e0 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    _trace_open.append(e0)
+
+
+def _trace_end(kind: str, flops: float, nbytes: float):
+    e1 = torch.cuda.Event(enable_timing=True)
+    e1.record()
+    TRACE.setdefault(kind, []).append((flops, nbytes, _trace_open.pop(), e1))
 
 
 def _dt(t: torch.Tensor) -> int:
@@ -216,15 +231,14 @@ def qlinear(x: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, biases: tor
             raise ValueError("lora_t must be [.., rows, ld] like x and lora_b a dense [N, ld]")
         a.lora_t, a.lora_t_row_stride, a.lora_t_batch_stride = tv.data_ptr(), t_rs, t_bs
         a.lora_b, a.lora_ld, a.lora_r = lora_b.data_ptr(), ld, int(lora_r)
-    trace = QLINEAR_TRACE
-    if trace is not None:
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
+    if TRACE is not None:
+        _trace_begin()
     rc = lib.mfx_qlinear_ex(byref(a), _stream())
     _lib.check(rc, "mfx_qlinear_ex")
-    if trace is not None:
-        e1.record()
-        trace.append((2.0 * rows * batch * n * k, e0, e1))
+    if TRACE is not None:
+        m = rows * batch
+        _trace_end("qlinear", 2.0 * m * n * k, n * k * bits / 8 + 4.0 * n * (k // group_size) + 2.0 * m * k
+                   + ov.element_size() * m * n_out)
     LAUNCHES[0] += 1 if prepared is not None else 3
     return ret
 
@@ -269,7 +283,11 @@ def norm_modulate(x: torch.Tensor, shift: torch.Tensor | None = None, scale: tor
         a.weight, a.weight_dtype = weight.data_ptr(), _dt(weight)
     a.eps, a.rms = eps, int(rms)
     a.y, a.y_row_stride, a.y_batch_stride = ov.data_ptr(), o_rs, o_bs
+    if TRACE is not None:
+        _trace_begin()
     _lib.check(lib.mfx_norm_modulate(byref(a), _stream()), "mfx_norm_modulate")
+    if TRACE is not None:
+        _trace_end("glue", 0.0, float(rows * batch * d * (xv.element_size() + 2)))
     LAUNCHES[0] += 1
     return ret
 
@@ -295,18 +313,25 @@ def qknorm_rope(qkv: torch.Tensor, heads: int, q_weight_a: torch.Tensor, k_weigh
     cos_sin = cos_sin.contiguous()
     if cos_sin.dtype != torch.float32 or tuple(cos_sin.shape) != (seq, 64, 2):
         raise ValueError("cos_sin must be f32 [seq, 64, 2]")
+    if TRACE is not None:
+        _trace_begin()
     rc = lib.mfx_qknorm_rope(_ptr(qkv), qkv.stride(1), qkv.stride(0), seq, batch, heads, split, _ptr(ws[0]),
                              _ptr(ws[1]), _ptr(ws[2]), _ptr(ws[3]), _dt(ws[0]), _ptr(cos_sin), eps, _stream())
     _lib.check(rc, "mfx_qknorm_rope")
+    if TRACE is not None:   # q and k sections read and written once
+        _trace_end("glue", 0.0, float(2 * 2 * batch * seq * heads * 128 * 2))
     LAUNCHES[0] += 1
     return qkv
 
 
-def fmha(qkv: torch.Tensor, heads: int, scale: float | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
-    """softmax(Q K^T * scale) V for head dim 128 on the fused buffer qkv [batch, seq, 3*heads*128] (bf16).
+def fmha(qkv: torch.Tensor, heads: int, scale: float | None = None, out: torch.Tensor | None = None,
+         key_bias: torch.Tensor | None = None) -> torch.Tensor:
+    """softmax(Q K^T * scale [+ key_bias]) V for head dim 128 on the fused buffer qkv [batch, seq, 3*heads*128]
+    (bf16).
 
     Returns (or fills the strided view `out`) bf16 [batch, seq, heads*128], the layout the reference
-    hands to the output projection.
+    hands to the output projection. `key_bias` is an optional float32 [batch, seq] additive bias per key (the
+    reference's key-padding mask: 0 on real keys, -1e9 on padded ones), shared by all heads and queries.
     """
     lib = _lib.load()
     _cuda(qkv, "qkv")
@@ -322,10 +347,23 @@ def fmha(qkv: torch.Tensor, heads: int, scale: float | None = None, out: torch.T
         raise ValueError("out must be a bf16 [batch, seq, heads*128] view with a dense last dim")
     es = qkv.element_size()
     base = qkv.data_ptr()
-    rc = lib.mfx_fmha(c_void_p(base), c_void_p(base + hd * es), c_void_p(base + 2 * hd * es), qkv.stride(1),
-                      qkv.stride(0), seq, batch, heads, float(scale if scale is not None else 128 ** -0.5),
-                      _ptr(out), out.stride(1), out.stride(0), _stream())
-    _lib.check(rc, "mfx_fmha")
+    sc = float(scale if scale is not None else 128 ** -0.5)
+    if TRACE is not None:
+        _trace_begin()
+    if key_bias is None:
+        rc = lib.mfx_fmha(c_void_p(base), c_void_p(base + hd * es), c_void_p(base + 2 * hd * es), qkv.stride(1),
+                          qkv.stride(0), seq, batch, heads, sc, _ptr(out), out.stride(1), out.stride(0), _stream())
+        _lib.check(rc, "mfx_fmha")
+    else:
+        _cuda(key_bias, "key_bias")
+        if key_bias.dtype != torch.float32 or tuple(key_bias.shape) != (batch, seq) or key_bias.stride(1) != 1:
+            raise ValueError("key_bias must be a float32 [batch, seq] tensor with a dense last dim")
+        rc = lib.mfx_fmha_bias(c_void_p(base), c_void_p(base + hd * es), c_void_p(base + 2 * hd * es), qkv.stride(1),
+                               qkv.stride(0), seq, batch, heads, sc, _ptr(key_bias), key_bias.stride(0), _ptr(out),
+                               out.stride(1), out.stride(0), _stream())
+        _lib.check(rc, "mfx_fmha_bias")
+    if TRACE is not None:
+        _trace_end("fmha", 4.0 * batch * heads * seq * seq * 128, 0.0)
     LAUNCHES[0] += 1
     return out
 
@@ -416,10 +454,14 @@ def gate_residual(y: torch.Tensor, gate: torch.Tensor, residual: torch.Tensor, b
         raise ValueError("residual and out must share their strides")
     gate = gate.reshape(b, d) if gate.stride(-1) == 1 else gate.reshape(b, d).contiguous()
     bias_c = None if bias is None else bias.contiguous()
+    if TRACE is not None:
+        _trace_begin()
     rc = lib.mfx_gate_residual(_ptr(y), _dt(y), _ptr(bias_c), 0 if bias_c is None else _dt(bias_c), _ptr(gate),
                                _dt(gate), gate.stride(0), _ptr(residual), _ptr(out), residual.stride(1),
                                residual.stride(0) if b > 1 else r * residual.stride(1), b, r, d, _stream())
     _lib.check(rc, "mfx_gate_residual")
+    if TRACE is not None:
+        _trace_end("glue", 0.0, float(b * r * d * (y.element_size() + 8)))
     LAUNCHES[0] += 1
     return out
 
@@ -487,6 +529,10 @@ def norm_gate_residual(y: torch.Tensor, weight: torch.Tensor, residual: torch.Te
                 raise ValueError("next_scale must be [batch, D]")
             a.next_scale, a.next_scale_dtype = next_scale.data_ptr(), _dt(next_scale)
             a.next_scale_batch_stride = next_scale.stride(0)
+    if TRACE is not None:
+        _trace_begin()
     _lib.check(lib.mfx_post_pre_norm(byref(a), _stream()), "mfx_post_pre_norm")
+    if TRACE is not None:
+        _trace_end("glue", 0.0, float(rows * batch * d * (yv.element_size() + 8 + (2 if next_out is not None else 0))))
     LAUNCHES[0] += 1
     return residual

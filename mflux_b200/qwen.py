@@ -139,6 +139,7 @@ class QwenTransformer(nn.Module):
         self.proj_out = ctx.linear(d, cfg.in_channels)
         self._fused, self._rope, self._buffers_for = {}, {}, None
         self._partials, self.tp_chunks, self.tp_chunk_min_rows = {}, 4, 512
+        self.trace = None   # a dict here receives copies of the two residual streams after every block (parity tests)
 
     # ------------------------------------------------------------------ helpers
     def _fuse(self, key, layers):
@@ -240,9 +241,13 @@ class QwenTransformer(nn.Module):
 
     # ------------------------------------------------------------------ forward
     def forward(self, hidden_states: torch.Tensor, encoder_hidden_states: torch.Tensor, timestep: torch.Tensor,
-                height: int, width: int) -> torch.Tensor:
+                height: int, width: int, encoder_hidden_states_mask: torch.Tensor | None = None) -> torch.Tensor:
         """latents [B, Si, C] + text states [B, St, joint_dim] + sigma [B] -> predicted noise [B, Si, C] (bf16).
-        The text mask of the reference is all ones here (it drops an all-ones mask, qwen_attention.py:131-132)."""
+
+        `encoder_hidden_states_mask` [B, St] (1 = real token, 0 = padding) is the reference's text mask
+        (qwen_transformer.py:37-72 passes it down to qwen_attention.py:117-135): padded text keys get an additive
+        -1e9 in every block's attention, image keys 0. None means all ones, which the reference drops as well
+        (:131-132); a caller that knows its mask is all ones should pass None, the masked kernel does more work."""
         cfg = self.cfg
         d, heads = cfg.hidden, cfg.heads // self.tp_world
         b, si, _ = hidden_states.shape
@@ -257,6 +262,10 @@ class QwenTransformer(nn.Module):
         x_img, x_txt = self.x_img, self.x_txt
         n_img, n_txt = nbuf[:, st:], nbuf[:, :st]
         cos_sin = self.rope_table(height, width, st, dev)
+        key_bias = None
+        if encoder_hidden_states_mask is not None:
+            key_bias = torch.zeros(b, st + si, dtype=torch.float32, device=dev)
+            key_bias[:, :st] = (1.0 - encoder_hidden_states_mask.to(dev, torch.float32)) * -1e9
 
         _call(self.img_in, hidden_states.to(torch.bfloat16), out=x_img)
         tn = ops.norm_modulate(encoder_hidden_states.to(torch.bfloat16), weight=self.txt_norm.weight.data,
@@ -275,7 +284,7 @@ class QwenTransformer(nn.Module):
             self._fuse(("a", i), [a.add_q_proj, a.add_k_proj, a.add_v_proj])(n_txt, qkv[:, :st])
             ops.qknorm_rope(qkv, heads, a.norm_added_q.weight.data, a.norm_added_k.weight.data, a.norm_q.weight.data,
                             a.norm_k.weight.data, st, cos_sin, a.norm_q.eps)
-            ops.fmha(qkv, heads, out=attn)
+            ops.fmha(qkv, heads, out=attn, key_bias=key_bias)
             self._row_parallel(a.attn_to_out[0], attn[:, st:], mi[:, 2 * d:3 * d], x_img)
             self._row_parallel(a.to_add_out, attn[:, :st], mt[:, 2 * d:3 * d], x_txt)
             ops.norm_modulate(x_img, mi[:, 3 * d:4 * d], mi[:, 4 * d:5 * d], out=n_img)
@@ -284,6 +293,8 @@ class QwenTransformer(nn.Module):
             self._row_parallel(blk.img_ff.mlp_out, ffb[:, st:], mi[:, 5 * d:6 * d], x_img)
             _call(blk.txt_ff.mlp_in, n_txt, epilogue="gelu_approx", out=ffb[:, :st])
             self._row_parallel(blk.txt_ff.mlp_out, ffb[:, :st], mt[:, 5 * d:6 * d], x_txt)
+            if self.trace is not None:
+                self.trace[f"block{i}"] = (x_txt.clone(), x_img.clone())
 
         mod = _call(self.norm_out.linear, sv)   # [B, 2D]: scale, shift (ada_layer_norm_continuous.py:16-19)
         ops.norm_modulate(x_img, mod[:, d:2 * d], mod[:, 0:d], out=n_img)
@@ -329,19 +340,46 @@ class QwenImage:
             self.transformer._fused = {}
         self.release_graphs()   # recorded graphs hold the prepared weights of the old parameters
 
-    def predict_noise(self, latents, prompt_embeds, negative_prompt_embeds, sigma, height, width):
+    @staticmethod
+    def _pad_pair(pos, neg, pos_mask, neg_mask):
+        """Text states of the two guidance branches as one batch. The reference evaluates the branches one after
+        the other, each at its own token count (qwen_image.py:105-118); batched, the shorter one is padded with
+        zero rows that the key mask removes from every attention, which leaves its real rows unchanged."""
+        lp, ln = pos.shape[1], neg.shape[1]
+        if lp == ln and pos_mask is None and neg_mask is None:
+            return torch.cat([pos, neg]), None
+        lt = max(lp, ln)
+
+        def grow(t, m):
+            if m is None:
+                m = torch.ones(t.shape[0], t.shape[1], dtype=torch.float32, device=t.device)
+            m = m.to(t.device, torch.float32)
+            if t.shape[1] < lt:
+                t = torch.cat([t, t.new_zeros(t.shape[0], lt - t.shape[1], t.shape[2])], dim=1)
+                m = torch.cat([m, m.new_zeros(m.shape[0], lt - m.shape[1])], dim=1)
+            return t, m
+
+        (pos, pm), (neg, nm) = grow(pos, pos_mask), grow(neg, neg_mask)
+        return torch.cat([pos, neg]), torch.cat([pm, nm])
+
+    def predict_noise(self, latents, prompt_embeds, negative_prompt_embeds, sigma, height, width,
+                      prompt_mask=None, negative_prompt_mask=None):
         """(noise for the prompt, noise for the negative prompt), each [B, Si, C]. `sigma` is a number or a
-        one-element tensor on the device."""
+        one-element tensor on the device. The two prompts may differ in token count; `prompt_mask` /
+        `negative_prompt_mask` [B, St] (1 = real token) are the reference's text masks."""
         b = latents.shape[0]
         if not torch.is_tensor(sigma):
             sigma = torch.full((1,), sigma, device=latents.device)
         sigma = sigma.reshape(1).float()
         if self.cfg_group is None:
-            both = self.transformer(torch.cat([latents, latents]), torch.cat([prompt_embeds, negative_prompt_embeds]),
-                                    sigma.expand(2 * b), height, width)
+            embeds, mask = self._pad_pair(prompt_embeds, negative_prompt_embeds, prompt_mask, negative_prompt_mask)
+            both = self.transformer(torch.cat([latents, latents]), embeds, sigma.expand(2 * b), height, width,
+                                    encoder_hidden_states_mask=mask)
             return both[:b], both[b:]
         mine = self.transformer(latents, prompt_embeds if self.cfg_rank == 0 else negative_prompt_embeds,
-                                sigma.expand(b), height, width).contiguous()
+                                sigma.expand(b), height, width,
+                                encoder_hidden_states_mask=prompt_mask if self.cfg_rank == 0 else negative_prompt_mask
+                                ).contiguous()
         parts = torch.empty(2, *mine.shape, dtype=mine.dtype, device=mine.device)
         dist.all_gather_into_tensor(parts, mine, group=self.cfg_group)
         return parts[0], parts[1]

@@ -193,6 +193,7 @@ class ZImageTransformer(nn.Module):
         self.context_refiner = torch.nn.ModuleList([ZImageContextBlock(ctx, cfg) for _ in range(cfg.n_refiner_layers)])
         self.layers = torch.nn.ModuleList([ZImageTransformerBlock(ctx, cfg) for _ in range(cfg.n_layers)])
         self._fused, self._rope, self._buffers_for = {}, {}, None
+        self.trace = None   # a dict here receives a copy of the unified stream after every main layer (parity tests)
 
     # ------------------------------------------------------------------ helpers
     def _qkv(self, blk):
@@ -299,7 +300,7 @@ class ZImageTransformer(nn.Module):
         return (mod[:, 0:d], ops.vec_sum_act(mod[:, d:2 * d], act="tanh"), mod[:, 2 * d:3 * d],
                 ops.vec_sum_act(mod[:, 3 * d:4 * d], act="tanh"))
 
-    def _run_blocks(self, blocks, lo, hi, cos_sin, t_emb):
+    def _run_blocks(self, blocks, lo, hi, cos_sin, t_emb, tag=None):
         """A run of blocks on rows lo:hi of the stream. Every post-norm + gated residual also writes the pre-norm
         of whatever comes next on the same rows (this block's FFN, or the next block's attention), so the stream is
         read once per sub-layer instead of twice."""
@@ -329,6 +330,8 @@ class ZImageTransformer(nn.Module):
                                        next_out=nbuf)
             else:
                 ops.norm_gate_residual(ybuf, blk.ffn_norm2.weight.data, xs, gate_mlp, eps)
+            if tag is not None and self.trace is not None:
+                self.trace[f"{tag}{i}"] = xs.clone()
 
     # ------------------------------------------------------------------ forward
     def forward(self, x: torch.Tensor, timestep: torch.Tensor, cap_feats: torch.Tensor) -> torch.Tensor:
@@ -364,7 +367,7 @@ class ZImageTransformer(nn.Module):
             xs[:, si + n_cap:] = self.cap_pad_token.data.float()
         self._run_blocks(list(self.context_refiner), si, si + sc, cs_cap, None)
 
-        self._run_blocks(list(self.layers), 0, si + sc, cs_all, t_emb)
+        self._run_blocks(list(self.layers), 0, si + sc, cs_all, t_emb, tag="layer")
 
         fl = self.all_final_layer[cfg.key]
         scale = _call(fl.adaLN_modulation[0], ops.vec_sum_act(t_emb, act="silu"))

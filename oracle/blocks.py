@@ -60,12 +60,33 @@ def apply_rope(x, cos_sin):
     return torch.stack([o0, o1], dim=-1).reshape(x.shape)
 
 
-def sdpa(q, k, v, scale=None):
-    """mx.fast.scaled_dot_product_attention without mask (attention_utils.py:48-52), float32."""
+def additive_key_mask(mask, joint_seq_len, txt_seq_len):
+    """AttentionUtils.convert_key_padding_mask_to_additive_mask (attention_utils.py:55-72) and
+    QwenAttention._convert_mask_for_qwen (qwen_attention.py:117-135): a [B, St] keep-mask over the text keys
+    becomes a [B, S] additive bias, 0 on kept and image keys and -1e9 on padded text keys (text keys first)."""
+    m = mask.float()
+    joint = torch.cat([m, torch.ones(m.shape[0], joint_seq_len - txt_seq_len)], dim=1)
+    return (1.0 - joint) * (-1e9)
+
+
+def sdpa(q, k, v, scale=None, mask=None):
+    """mx.fast.scaled_dot_product_attention (attention_utils.py:48-52), float32, on [B, H, S, 128]; `mask` is an
+    additive bias per key, [B, S], broadcast over heads and queries as the reference's [B, 1, 1, S] mask is.
+    Large problems go head by head so that the score matrix of one head is all that is ever held."""
     q, k, v = q.float(), k.float(), v.float()
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
-    p = torch.softmax(q @ k.transpose(-1, -2) * scale, dim=-1)
-    return p @ v
+    bias = None if mask is None else mask.float()[:, None, None, :]
+    if q.shape[0] * q.shape[1] * q.shape[2] * k.shape[2] <= (1 << 27):
+        s = q @ k.transpose(-1, -2) * scale
+        return torch.softmax(s if bias is None else s + bias, dim=-1) @ v
+    out = torch.empty(q.shape[:-1] + (v.shape[-1],), dtype=torch.float32)
+    for b in range(q.shape[0]):
+        for h in range(q.shape[1]):
+            s = q[b, h] @ k[b, h].T * scale
+            if bias is not None:
+                s = s + bias[b, 0]
+            out[b, h] = torch.softmax(s, dim=-1) @ v[b, h]
+    return out
 
 
 def heads_first(x, heads):

@@ -17,7 +17,7 @@ Two quantizer modes are restated:
          scale to edge / rint(edge / scale) so that 0.0 is exactly representable; bias = edge
          (or 0 with the unsnapped scale when rint(edge/scale) == 0). All in float32; scales and
          biases are stored in the dtype of w.
-  "doc"  the formula in MLX's documentation and in this project's brief: scale = (max - min) /
+  "doc"  the formula in MLX's documentation: scale = (max - min) /
          (2^bits - 1), bias = min.
 Codes: q = clip(rint((w - bias) / scale), 0, 2^bits - 1) with the float32 (unrounded) scale and
 bias, round-half-to-even, packed little-end first into uint32 (element j of a word in bits

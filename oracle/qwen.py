@@ -64,7 +64,9 @@ def rope(x, cs):
     return torch.stack([xr * c - xi * s, xr * s + xi * c], dim=-1).reshape(x.shape)
 
 
-def forward(model, hidden_states, encoder_hidden_states, timestep, height, width):
+def forward(model, hidden_states, encoder_hidden_states, timestep, height, width, collect=None, mask=None):
+    """Predicted noise [B, Si, C] in float32. `mask` [B, St] (1 = real token, 0 = padding) is the reference's
+    encoder_hidden_states_mask; `collect` (a dict) receives the two streams after every block."""
     cfg = model.cfg
     d, heads = cfg.hidden, cfg.heads
     hs = lin(model.img_in, hidden_states.float().cpu())
@@ -74,7 +76,10 @@ def forward(model, hidden_states, encoder_hidden_states, timestep, height, width
     sv = silu(temb)
     b, st = enc.shape[0], enc.shape[1]
     img_cs, txt_cs = rope_tables(height // 16, width // 16, st)
-    for blk in model.transformer_blocks:
+    key_bias = None
+    if mask is not None and not bool((mask.float() >= 0.999).all()):   # qwen_attention.py:131-132
+        key_bias = blocks.additive_key_mask(mask.cpu(), st + hs.shape[1], st)
+    for i, blk in enumerate(model.transformer_blocks):
         a = blk.attn
         mi, mt = lin(blk.img_mod_linear, sv), lin(blk.txt_mod_linear, sv)
         ch = lambda m, j: m[:, j * d:(j + 1) * d]  # noqa: E731
@@ -87,7 +92,7 @@ def forward(model, hidden_states, encoder_hidden_states, timestep, height, width
         tq, tk = rms(tq, a.norm_added_q.weight, a.norm_added_q.eps), rms(tk, a.norm_added_k.weight, a.norm_added_k.eps)
         iq, ik, tq, tk = rope(iq, img_cs), rope(ik, img_cs), rope(tq, txt_cs), rope(tk, txt_cs)
         q, k, v = torch.cat([tq, iq], 1), torch.cat([tk, ik], 1), torch.cat([tv, iv], 1)
-        o = blocks.sdpa(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3))
+        o = blocks.sdpa(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3), mask=key_bias)
         o = o.permute(0, 2, 1, 3).reshape(b, -1, d)
         hs = hs + ch(mi, 2)[:, None] * lin(a.attn_to_out[0], o[:, st:])
         enc = enc + ch(mt, 2)[:, None] * lin(a.to_add_out, o[:, :st])
@@ -95,6 +100,8 @@ def forward(model, hidden_states, encoder_hidden_states, timestep, height, width
             lin(blk.img_ff.mlp_in, blocks.modulate(hs, ch(mi, 3), ch(mi, 4))), approx=True))
         enc = enc + ch(mt, 5)[:, None] * lin(blk.txt_ff.mlp_out, blocks.gelu(
             lin(blk.txt_ff.mlp_in, blocks.modulate(enc, ch(mt, 3), ch(mt, 4))), approx=True))
+        if collect is not None:
+            collect[f"block{i}"] = (enc, hs)
     m = lin(model.norm_out.linear, sv)
     x = blocks.layer_norm(hs) * (1 + m[:, :d])[:, None] + m[:, d:2 * d][:, None]
     return lin(model.proj_out, x)

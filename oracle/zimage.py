@@ -118,7 +118,7 @@ def block(blk, x, freqs, t_emb, heads):
     return x + gate_mlp * rms(ffn_out, blk.ffn_norm2)
 
 
-def forward_one(model, image, timestep, cap_feats):
+def forward_one(model, image, timestep, cap_feats, collect=None):
     """ZImageTransformer.__call__ for one sample: image [C, F, H, W], timestep scalar tensor, cap_feats [L, Dc]."""
     cfg = model.cfg
     heads = cfg.n_heads
@@ -142,13 +142,18 @@ def forward_one(model, image, timestep, cap_feats):
     x_len = x_emb.shape[1]
     unified = torch.cat([x_emb, cap_emb], dim=1)
     freqs = torch.cat([x_freqs, cap_freqs], dim=0)
-    for layer in model.layers:
+    for i, layer in enumerate(model.layers):
         unified = block(layer, unified, freqs, t_emb, heads)
+        if collect is not None:
+            collect.setdefault(f"layer{i}", []).append(unified[0])
     fl = model.all_final_layer[cfg.key]
     scale = 1.0 + lin(fl.adaLN_modulation[0], silu(t_emb))
     unified = lin(fl.linear, blocks.layer_norm(unified, 1e-6) * scale[:, None])
     return -unpatchify(unified[0, :x_len], size, cfg.in_channels, cfg.patch_size, cfg.f_patch_size)
 
 
-def forward(model, images, timesteps, cap_feats):
-    return torch.stack([forward_one(model, images[i], timesteps[i], cap_feats[i]) for i in range(images.shape[0])])
+def forward(model, images, timesteps, cap_feats, collect=None):
+    """All samples, one at a time as the reference runs them. `collect` (a dict) receives, per main layer, the list
+    of the samples' unified streams [image tokens, then caption tokens] after that layer."""
+    return torch.stack([forward_one(model, images[i], timesteps[i], cap_feats[i], collect)
+                        for i in range(images.shape[0])])

@@ -122,3 +122,45 @@ def test_tensor_parallel_matches_single_gpu(lib_built, tmp_path):
     assert cfg_err <= 2e-3, cfg_err
     graph_err = float((tmp_path / "graph_err.txt").read_text())
     assert graph_err <= 1e-5, graph_err
+
+
+def test_masked_step_matches_oracle(lib_built):
+    """encoder_hidden_states_mask (qwen_attention.py:117-135): padded text keys are removed from every block's
+    attention. rel-L2 <= 1e-2 against the float32 oracle run with the same mask."""
+    from mflux_b200.qwen import QwenConfig, QwenTransformer
+
+    cfg = QwenConfig(hidden=256, heads=2, num_layers=2, joint_attention_dim=192)
+    model = QwenTransformer(cfg, bits=4, device="cuda", seed=5)
+    b, height, width, txt = 2, 128, 128, 40
+    lat, ctx = _inputs(cfg, b, height, width, txt, 7)
+    mask = torch.ones(b, txt)
+    mask[1, 25:] = 0.0
+    sigma = torch.tensor([0.6, 0.6])
+    out = model(lat.cuda(), ctx.cuda(), sigma.cuda(), height, width, encoder_hidden_states_mask=mask.cuda())
+    torch.cuda.synchronize()
+    ref = oq.forward(model, lat.to(torch.bfloat16), ctx, sigma, height, width, mask=mask)
+    assert rel_l2(out, ref.numpy()) <= TOL
+    unmasked = oq.forward(model, lat.to(torch.bfloat16), ctx, sigma, height, width)
+    assert rel_l2(ref[1].numpy(), unmasked[1].numpy()) > 1e-3   # the mask matters for the padded sample
+
+
+def test_prompt_pair_of_different_lengths_equals_separate_evaluations(lib_built):
+    """The reference runs the prompt and the negative prompt one after the other, each at its own token count
+    (variants/txt2img/qwen_image.py:105-118). Batched with padding + key mask the two predictions must equal the
+    separate evaluations (same kernels, other batch size: within bf16 rounding noise, far below 1e-2)."""
+    from mflux_b200.qwen import QwenConfig, QwenImage
+
+    cfg = QwenConfig(hidden=256, heads=2, num_layers=2, joint_attention_dim=192)
+    pipe = QwenImage(quantize=4, model_config=cfg, seed=6)
+    height = width = 128
+    lat, pos = _inputs(cfg, 1, height, width, 48, 11)
+    _, neg = _inputs(cfg, 1, height, width, 20, 12)
+    n_pos, n_neg = pipe.predict_noise(lat.cuda(), pos.cuda(), neg.cuda(), 0.7, height, width)
+    torch.cuda.synchronize()
+    sig = torch.tensor([0.7])
+    alone_pos = pipe.transformer(lat.cuda(), pos.cuda(), sig.cuda(), height, width).float().cpu()
+    alone_neg = pipe.transformer(lat.cuda(), neg.cuda(), sig.cuda(), height, width).float().cpu()
+    assert rel_l2(n_pos, alone_pos.numpy()) <= 2e-3
+    assert rel_l2(n_neg, alone_neg.numpy()) <= 2e-3
+    ref_neg = oq.forward(pipe.transformer, lat.to(torch.bfloat16), neg, sig, height, width)
+    assert rel_l2(n_neg, ref_neg.numpy()) <= TOL

@@ -3,14 +3,17 @@
 Some callers cannot allocate device memory when they call into the library (all of HBM already belongs
 to their own allocator, or an allocation's implicit synchronisation is not acceptable where they call
 from), so they cannot supply the workspace mfx_qlinear wants. This entry point keeps that scratch in a
-fixed array inside the library instead. The test calls it through the C ABI twice in a row, with two
+fixed array inside the library instead. The test calls it through the C ABI several times in a row, with
 different weights, and compares each result with what the workspace-taking entry point returns for the same
-inputs: the kernels are the same, so the outputs must be identical, and the second call must not see
-anything of the first. It also checks the documented size limit.
+inputs (the kernels are the same, so the outputs must be identical, and a call must not see anything of the
+one before) and with the float32 CPU oracle (rel-L2 <= 1e-2, the tolerance of the other quantized-linear
+tests). The cases cover both kernels behind the entry point: the tensor-core kernel (more than 16 rows) and the
+weight-streaming kernel (at most 16 rows). It also checks the documented size limit.
 """
 import pytest
 import torch
 
+from oracle import quant
 from oracle.quant import rel_l2
 
 pytestmark = pytest.mark.gpu
@@ -24,10 +27,11 @@ def _case(m, n, k, bits, seed):
     return w, x, b
 
 
-def test_static_scratch_matches_workspace_entry_point_twice(lib_built):
+def test_static_scratch_matches_workspace_entry_point_and_oracle(lib_built):
     from mflux_b200 import ops
 
-    for call, (m, n, k, bits) in enumerate([(300, 1024, 512, 4), (129, 520, 1024, 8)]):
+    cases = [(300, 1024, 512, 4), (129, 520, 1024, 8), (16, 768, 512, 4), (1, 264, 256, 8), (300, 1024, 512, 4)]
+    for call, (m, n, k, bits) in enumerate(cases):
         w, x, b = _case(m, n, k, bits, 40 + call)
         wq, s, bi = ops.quantize_affine(w.cuda(), 64, bits)
         want = ops.qlinear_plain(x.cuda(), wq, s, bi, b.cuda(), bits=bits, static_scratch=False)
@@ -35,8 +39,9 @@ def test_static_scratch_matches_workspace_entry_point_twice(lib_built):
         torch.cuda.synchronize()
         assert ops.poll_device_status() == 0
         assert torch.isfinite(got.float()).all()
-        assert rel_l2(got, want.float().cpu().numpy()) <= 1e-2  # the tolerance of the other GPU tests
-        assert torch.equal(got, want)  # same kernels, same inputs: in fact bit-identical
+        assert torch.equal(got, want)  # same kernels, same inputs: bit-identical
+        ref = quant.qlinear(x, wq.cpu().numpy(), s.float().cpu().numpy(), bi.float().cpu().numpy(), b, 64, bits)
+        assert rel_l2(got, ref) <= 1e-2
 
 
 def test_static_scratch_rejects_weights_beyond_its_limit(lib_built):
