@@ -28,7 +28,7 @@ typedef enum mfx_status {
   MFX_OK = 0,
   MFX_ERR_SHAPE = -1,            /* a size is zero/negative or violates a divisibility rule */
   MFX_ERR_ALIGN = -2,            /* a pointer or stride is not 16-byte aligned where required */
-  MFX_ERR_UNSUPPORTED_BITS = -3, /* bits not in {4, 8} or group size != 64 */
+  MFX_ERR_UNSUPPORTED_BITS = -3, /* bits not in {3, 4, 5, 6, 8} or group size != 64 */
   MFX_ERR_DTYPE = -4,            /* dtype code not accepted by this entry point */
   MFX_ERR_ARCH = -5,             /* current device is not compute capability 10.x */
   MFX_ERR_CUDA = -6,             /* a CUDA runtime/driver call failed (see mfx_last_cuda_error) */
@@ -68,7 +68,10 @@ int mfx_poll_device_status(int* status_out, void* stream);
 
 /* Replaces mx.quantize(w, group_size=64, bits) as reached through mlx.nn.quantize from
  * src/mflux/models/common/weights/loading/weight_applier.py:93-103.
- * w [N, K] row-major (w_dtype) -> wq uint32 [N, K*bits/32], scales/biases [N, K/64] in w_dtype. */
+ * w [N, K] row-major (w_dtype) -> wq uint32 [N, K*bits/32], scales/biases [N, K/64] in w_dtype.
+ * bits is 3, 4, 5, 6 or 8 (the widths of src/mflux/cli/defaults/defaults.py:63). Code j of a row occupies bits
+ * [j*bits, (j+1)*bits) of the row's little-end-first bit stream: 8 or 4 codes per uint32 at 4 / 8 bits, codes
+ * straddling byte and word boundaries at 3, 5 and 6 bits (8 codes in 3 or 5 bytes, 4 codes in 3 bytes). */
 int mfx_quantize_affine(const void* w, int w_dtype, int64_t N, int64_t K, int bits, int group_size, int qmode,
                         uint32_t* wq, void* scales, void* biases, void* stream);
 
@@ -82,7 +85,11 @@ int mfx_dequantize_affine(const uint32_t* wq, const void* scales, const void* bi
  *  (a) the codes of each uint32 are interleaved so that one mask yields two neighbouring values
  *      (4 bits: nibble order e0,e2,e4,e6,e1,e3,e5,e7; 8 bits: byte order e0,e2,e1,e3), and
  *  (b) scales and biases are transposed and paired: sb[g*N + n] = bf16(scales[n,g]) | bf16(biases[n,g]) << 16.
- * The blob is [interleaved codes, N*K*bits/8 bytes, padded to 256][sb, (K/64)*N*4 bytes]. It has no
+ * Codes of 3 bits are widened to 4 and codes of 5 or 6 bits to 8 on the way, so the matmul kernels unpack two
+ * widths only (kb = 4 or 8); the matmul is bound by the tensor cores at every width, so the wider stream costs no time.
+ * Scales and biases are carried as bf16 whatever sb_dtype is: f16 / f32 scales lose mantissa bits here (each
+ * dequantized weight moves by at most 2^-9 of scale and bias), which MLX's quantized_matmul does not do.
+ * The blob is [interleaved codes, N*K*kb/8 bytes, padded to 256][sb, (K/64)*N*4 bytes]. It has no
  * counterpart in the reference (MLX consumes its own [N, K*bits/32] / [N, K/64] arrays directly); a
  * caller that keeps weights resident prepares once per weight and passes `prepared` afterwards. */
 size_t mfx_qlinear_prepared_bytes(int64_t N, int64_t K, int bits, int group_size); /* 0 on bad arguments */

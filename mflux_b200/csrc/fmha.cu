@@ -479,7 +479,7 @@ int run(const void* q, const void* k, const void* v, int64_t qkv_row_stride, int
     return MFX_ERR_ALIGN;
   if (key_bias) {
     // the kernel reads the bias of 32 consecutive keys as eight 16-byte vectors
-    if (!aligned16(key_bias) || (bias_batch_stride * 4) % 16 != 0) return MFX_ERR_ALIGN;
+    if (!aligned16(key_bias) || (batch > 1 && (bias_batch_stride * 4) % 16 != 0)) return MFX_ERR_ALIGN;
     if (batch > 1 && bias_batch_stride < seq) return MFX_ERR_SHAPE;
   }
   if (int rc = check_arch()) return rc;

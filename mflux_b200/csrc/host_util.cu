@@ -120,7 +120,7 @@ const char* mfx_status_str(int status) {
     case MFX_OK: return "ok";
     case MFX_ERR_SHAPE: return "bad shape (zero/negative size or divisibility rule violated)";
     case MFX_ERR_ALIGN: return "pointer or stride not 16-byte aligned";
-    case MFX_ERR_UNSUPPORTED_BITS: return "unsupported bits/group size (bits must be 4 or 8, group 64)";
+    case MFX_ERR_UNSUPPORTED_BITS: return "unsupported bits/group size (bits must be 3, 4, 5, 6 or 8, group 64)";
     case MFX_ERR_DTYPE: return "unsupported dtype for this entry point";
     case MFX_ERR_ARCH: return "device is not sm_100 (compute capability 10.x)";
     case MFX_ERR_CUDA: return "CUDA call failed";

@@ -25,6 +25,11 @@ int check_arch();  // MFX_OK when the current device is compute capability 10.x
 
 inline size_t dtype_size(int dt) { return dt == MFX_F32 ? 4 : 2; }
 inline bool valid_dtype(int dt) { return dt == MFX_F32 || dt == MFX_BF16 || dt == MFX_F16; }
+// Code widths of the affine quantizer (the ones the reference's CLI offers).
+inline bool valid_bits(int bits) { return bits == 3 || bits == 4 || bits == 5 || bits == 6 || bits == 8; }
+// Width the matmul kernels unpack: 3-bit codes are widened to 4 bits, 5- and 6-bit codes to 8 bits when a weight
+// is prepared, so that one dequantizer per kernel width serves all of them.
+inline int kernel_bits(int bits) { return bits <= 4 ? 4 : 8; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Number of SMs of the current device (looked up once per device; 148 if the query fails).

@@ -659,34 +659,77 @@ __global__ void __launch_bounds__(256) interleave_codes_kernel(const uint4* __re
   out[i] = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// Codes of SRC_BITS (3, 5 or 6) bits, packed as a little-end-first bit stream, widened to the kernel's 4- or 8-bit
+// codes and interleaved like interleave_codes_kernel does. One thread writes 16 bytes: 32 (4-bit) or 16 (8-bit)
+// codes, whose source is 12, 10 or 12 bytes of the stream.
+template <int SRC_BITS>
+__global__ void __launch_bounds__(256) widen_codes_kernel(const uint8_t* __restrict__ in, uint4* __restrict__ out,
+                                                          int64_t n_vec) {
+  constexpr int KB = SRC_BITS <= 4 ? 4 : 8;
+  constexpr int CODES = 128 / KB;                 // codes per 16-byte vector
+  constexpr int SRC_BYTES = CODES * SRC_BITS / 8;
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n_vec) return;
+  const uint8_t* src = in + i * SRC_BYTES;
+  uint32_t w[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    // the 8 (or 4) codes of output word j start at bit j * (32 / KB) * SRC_BITS of this thread's stream
+    constexpr int PER_WORD = 32 / KB;
+    const int bit0 = j * PER_WORD * SRC_BITS;
+    unsigned long long stream = 0;
+#pragma unroll
+    for (int b = 0; b < (PER_WORD * SRC_BITS + 7) / 8 + 1; ++b) {
+      const int byte = bit0 / 8 + b;
+      if (byte < SRC_BYTES) stream |= static_cast<unsigned long long>(__ldg(src + byte)) << (8 * b);
+    }
+    stream >>= (bit0 & 7);
+    uint32_t r = 0;
+#pragma unroll
+    for (int e = 0; e < PER_WORD; ++e) {
+      const uint32_t code = static_cast<uint32_t>(stream >> (SRC_BITS * e)) & ((1u << SRC_BITS) - 1u);
+      int pos;
+      if (KB == 4) pos = (e & 1) ? 4 + (e >> 1) : (e >> 1);   // nibbles e0,e2,e4,e6,e1,e3,e5,e7
+      else pos = (e == 1) ? 2 : (e == 2) ? 1 : e;             // bytes e0,e2,e1,e3
+      r |= code << (KB * pos);
+    }
+    w[j] = r;
+  }
+  out[i] = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 size_t codes_bytes_padded(int64_t N, int64_t K, int bits) {
-  const size_t raw = static_cast<size_t>(N) * static_cast<size_t>(K) * bits / 8;
+  const size_t raw = static_cast<size_t>(N) * static_cast<size_t>(K) * kernel_bits(bits) / 8;
   return (raw + 255) & ~static_cast<size_t>(255);
 }
 
 size_t prepared_bytes(int64_t N, int64_t K, int bits, int group_size) {
-  if (N <= 0 || K <= 0 || group_size != 64 || K % 64 != 0 || (bits != 4 && bits != 8)) return 0;
+  if (N <= 0 || K <= 0 || group_size != 64 || K % 64 != 0 || !valid_bits(bits)) return 0;
   return codes_bytes_padded(N, K, bits) + static_cast<size_t>(N) * static_cast<size_t>(K / 64) * 4;
 }
 
 int prepare(const uint32_t* wq, const void* scales, const void* biases, int sb_dtype, int64_t N, int64_t K,
             int bits, int group_size, void* prepared, size_t bytes, cudaStream_t st) {
   if (!wq || !scales || !biases || !prepared) return MFX_ERR_NULL;
-  if ((bits != 4 && bits != 8) || group_size != 64) return MFX_ERR_UNSUPPORTED_BITS;
+  if (!valid_bits(bits) || group_size != 64) return MFX_ERR_UNSUPPORTED_BITS;
   if (N <= 0 || K <= 0 || K % 64 != 0) return MFX_ERR_SHAPE;
   if (N > (1 << 30) || K > (1 << 30)) return MFX_ERR_TOO_LARGE;
   if (!valid_dtype(sb_dtype)) return MFX_ERR_DTYPE;
   if (bytes < prepared_bytes(N, K, bits, group_size)) return MFX_ERR_SHAPE;
   if (!aligned16(wq) || (reinterpret_cast<uintptr_t>(prepared) & 255u) != 0) return MFX_ERR_ALIGN;
   if (int rc = check_arch()) return rc;
-  const int64_t n_vec = N * K * bits / 8 / 16;  // K % 64 == 0 makes every row a whole number of 16-byte vectors
+  // K % 64 == 0 makes every row a whole number of 16-byte vectors of kernel-width codes
+  const int64_t n_vec = N * K * kernel_bits(bits) / 8 / 16;
   const unsigned blocks = static_cast<unsigned>((n_vec + 255) / 256);
-  if (bits == 4)
-    interleave_codes_kernel<4><<<blocks, 256, 0, st>>>(reinterpret_cast<const uint4*>(wq),
-                                                       static_cast<uint4*>(prepared), n_vec);
-  else
-    interleave_codes_kernel<8><<<blocks, 256, 0, st>>>(reinterpret_cast<const uint4*>(wq),
-                                                       static_cast<uint4*>(prepared), n_vec);
+  uint4* dst = static_cast<uint4*>(prepared);
+  const uint8_t* stream = reinterpret_cast<const uint8_t*>(wq);
+  switch (bits) {
+    case 4: interleave_codes_kernel<4><<<blocks, 256, 0, st>>>(reinterpret_cast<const uint4*>(wq), dst, n_vec); break;
+    case 8: interleave_codes_kernel<8><<<blocks, 256, 0, st>>>(reinterpret_cast<const uint4*>(wq), dst, n_vec); break;
+    case 3: widen_codes_kernel<3><<<blocks, 256, 0, st>>>(stream, dst, n_vec); break;
+    case 5: widen_codes_kernel<5><<<blocks, 256, 0, st>>>(stream, dst, n_vec); break;
+    default: widen_codes_kernel<6><<<blocks, 256, 0, st>>>(stream, dst, n_vec); break;
+  }
   MFX_CUDA_TRY(cudaGetLastError());
   const int G = static_cast<int>(K / 64);
   uint32_t* sb = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(prepared) + codes_bytes_padded(N, K, bits));
@@ -698,7 +741,8 @@ int prepare(const uint32_t* wq, const void* scales, const void* biases, int sb_d
 
 int run(const mfx_qlinear_args& a, cudaStream_t st) {
   if (!a.x || !a.y) return MFX_ERR_NULL;
-  if ((a.bits != 4 && a.bits != 8) || a.group_size != 64) return MFX_ERR_UNSUPPORTED_BITS;
+  if (!valid_bits(a.bits) || a.group_size != 64) return MFX_ERR_UNSUPPORTED_BITS;
+  const int kb = kernel_bits(a.bits);   // width of the prepared codes: 4 (from 3 or 4) or 8 (from 5, 6 or 8)
   if (a.rows <= 0 || a.batch <= 0 || a.N <= 0 || a.K <= 0) return MFX_ERR_SHAPE;
   if (a.K % 64 != 0 || a.N % 8 != 0) return MFX_ERR_SHAPE;
   if (a.rows > (1 << 30) || a.N > (1 << 30) || a.K > (1 << 30) || a.batch > (1 << 20)) return MFX_ERR_TOO_LARGE;
@@ -760,12 +804,12 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
       return rc;
   }
   {
-    const uint64_t words_per_row = static_cast<uint64_t>(a.K) * a.bits / 32;
+    const uint64_t words_per_row = static_cast<uint64_t>(a.K) * kb / 32;
     const uint64_t dims[2] = {words_per_row, static_cast<uint64_t>(a.N)};
     const uint64_t strides[1] = {words_per_row * 4};
-    const uint32_t box[2] = {static_cast<uint32_t>(BK * a.bits / 32), BN_HALF};  // each CTA of a pair: 128 weight rows
+    const uint32_t box[2] = {static_cast<uint32_t>(BK * kb / 32), BN_HALF};  // each CTA of a pair: 128 weight rows
     if (int rc = encode_tmap(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, codes, dims, strides, box,
-                             a.bits == 4 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B))
+                             kb == 4 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B))
       return rc;
   }
   {
@@ -789,9 +833,9 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
     // the dense tile takes the place of the packed codes in shared memory: same bytes per row (32 or 64), same swizzle
     const uint64_t bdims[2] = {static_cast<uint64_t>(a.lora_ld), static_cast<uint64_t>(a.N)};
     const uint64_t bstrides[1] = {static_cast<uint64_t>(a.lora_ld) * 2};
-    const uint32_t bbox[2] = {static_cast<uint32_t>(4 * a.bits), BN_HALF};
+    const uint32_t bbox[2] = {static_cast<uint32_t>(4 * kb), BN_HALF};
     if (int rc = encode_tmap(&tlb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.lora_b, bdims, bstrides, bbox,
-                             a.bits == 4 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B))
+                             kb == 4 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B))
       return rc;
   } else {
     tt = tx;   // never read: the kernel runs no extension stage
@@ -799,7 +843,7 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
   }
   Params p;
   p.ext_r = low_rank ? static_cast<int>((a.lora_r + 15) / 16 * 16) : 0;
-  p.num_ext = low_rank ? (p.ext_r + GPS * 4 * a.bits - 1) / (GPS * 4 * a.bits) : 0;
+  p.num_ext = low_rank ? (p.ext_r + GPS * 4 * kb - 1) / (GPS * 4 * kb) : 0;
   p.rows = static_cast<int>(a.rows);
   p.batch = static_cast<int>(a.batch);
   p.N = static_cast<int>(a.N);
@@ -813,7 +857,7 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
   {
     // bands of weight rows that stay L2-resident while every activation tile passes over them: 32 MB leaves room
     // for the activation and output tiles in flight even if each die's half of the L2 keeps its own copy
-    const int64_t n_tile_bytes = static_cast<int64_t>(BN) * (a.K * a.bits / 8 + a.K / 64 * 4);
+    const int64_t n_tile_bytes = static_cast<int64_t>(BN) * (a.K * kb / 8 + a.K / 64 * 4);
     const int64_t bands = (n_tile_bytes * p.tiles_n + (32ll << 20) - 1) / (32ll << 20);
     p.band_n = static_cast<int>((p.tiles_n + bands - 1) / bands);
     if (p.band_n < 1) p.band_n = 1;
@@ -833,7 +877,7 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
   const int pairs = device_sm_count() / 2;
   const int grid = 2 * (p.total_tiles < pairs ? p.total_tiles : pairs);
   const bool f32 = a.y_dtype == MFX_F32;
-  if (a.bits == 4) {
+  if (kb == 4) {
     return f32 ? launch<4, FMT_BF16, 3, 3, float>(tx, tw, tsb, tt, tlb, p, grid, st)
                : launch<4, FMT_BF16, 3, 3, __nv_bfloat16>(tx, tw, tsb, tt, tlb, p, grid, st);
   }
@@ -923,7 +967,7 @@ int mfx_qlinear_static_scratch(const void* x, int64_t M, int64_t K, int64_t ldx,
                                void* stream) {
   const size_t need = mfx::qmm::prepared_bytes(N, K, bits, group_size);
   if (need == 0) {
-    if ((bits != 4 && bits != 8) || group_size != 64) return MFX_ERR_UNSUPPORTED_BITS;
+    if (!mfx::valid_bits(bits) || group_size != 64) return MFX_ERR_UNSUPPORTED_BITS;
     return MFX_ERR_SHAPE;
   }
   if (need > static_cast<size_t>(MFX_STATIC_SCRATCH_BYTES)) {

@@ -215,7 +215,7 @@ int run(const mfx_qlinear_args& a, const void* prepared, size_t codes_bytes, cud
   // 32 rows per block while that still gives every SM two blocks, else 8 rows per block
   const bool wide = (a.N + 31) / 32 >= 2 * device_sm_count();
   const unsigned blocks = static_cast<unsigned>(wide ? (a.N + 31) / 32 : (a.N + 7) / 8);
-  if (a.bits == 4) {
+  if (kernel_bits(a.bits) == 4) {
     if (wide) qmv_kernel<4, 4><<<blocks, THREADS, 0, st>>>(p);
     else qmv_kernel<4, 1><<<blocks, THREADS, 0, st>>>(p);
   } else {

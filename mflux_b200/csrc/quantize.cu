@@ -2,7 +2,10 @@
 //
 // Semantics follow mx.quantize(w, group_size=64, bits) as reached from the reference through
 // mlx.nn.quantize (src/mflux/models/common/weights/loading/weight_applier.py:93-103): groups of 64
-// along the input dimension, float32 arithmetic, codes packed little-end first into uint32.
+// along the input dimension, float32 arithmetic, codes packed little-end first: code j of a row occupies
+// bits [j*bits, (j+1)*bits) of the row's bit stream, which for 4 and 8 bits is "8 / 4 codes per uint32" and for
+// 3, 5 and 6 bits (the other widths the reference's CLI offers, src/mflux/cli/defaults/defaults.py:63) lets
+// codes straddle byte and word boundaries (8 codes in 3 or 5 bytes, 4 codes in 3 bytes).
 // Eight lanes own one group (8 values each); min/max go through warp shuffles.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -101,11 +104,19 @@ __global__ void __launch_bounds__(256) quantize_kernel(const T* __restrict__ w, 
 #pragma unroll
     for (int i = 0; i < 8; ++i) word |= codes[i] << (4 * i);
     wq[g * 8 + sub] = word;
-  } else {
+  } else if (BITS == 8) {
     uint2 words;
     words.x = codes[0] | (codes[1] << 8) | (codes[2] << 16) | (codes[3] << 24);
     words.y = codes[4] | (codes[5] << 8) | (codes[6] << 16) | (codes[7] << 24);
     reinterpret_cast<uint2*>(wq)[g * 8 + sub] = words;
+  } else {
+    // 8 codes = BITS bytes of the bit stream, starting at byte (8 * thread) * BITS / 8 of the tensor
+    unsigned long long stream = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) stream |= static_cast<unsigned long long>(codes[i]) << (BITS * i);
+    uint8_t* dst = reinterpret_cast<uint8_t*>(wq) + (g * 8 + sub) * BITS;
+#pragma unroll
+    for (int i = 0; i < BITS; ++i) dst[i] = static_cast<uint8_t>(stream >> (8 * i));
   }
   if (sub == 0) {
     scales[g] = from_f32<T>(scale);
@@ -129,13 +140,20 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const uint32_t* __restr
     const uint32_t word = __ldg(wq + tid);
 #pragma unroll
     for (int i = 0; i < 8; ++i) codes[i] = (word >> (4 * i)) & 0xF;
-  } else {
+  } else if (BITS == 8) {
     const uint2 words = __ldg(reinterpret_cast<const uint2*>(wq) + tid);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       codes[i] = (words.x >> (8 * i)) & 0xFF;
       codes[4 + i] = (words.y >> (8 * i)) & 0xFF;
     }
+  } else {
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(wq) + tid * BITS;
+    unsigned long long stream = 0;
+#pragma unroll
+    for (int i = 0; i < BITS; ++i) stream |= static_cast<unsigned long long>(__ldg(src + i)) << (8 * i);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) codes[i] = static_cast<uint32_t>(stream >> (BITS * i)) & ((1u << BITS) - 1u);
   }
   OUT res[8];
 #pragma unroll
@@ -158,14 +176,22 @@ int launch_quantize(const void* w, int64_t n_groups, int bits, int qmode, uint32
   const T* wp = static_cast<const T*>(w);
   T* sp = static_cast<T*>(scales);
   T* bp = static_cast<T*>(biases);
-  if (bits == 4 && qmode == MFX_QMODE_MLX)
-    quantize_kernel<T, 4, MFX_QMODE_MLX><<<blocks, 256, 0, st>>>(wp, n_groups, wq, sp, bp);
-  else if (bits == 4)
-    quantize_kernel<T, 4, MFX_QMODE_DOC><<<blocks, 256, 0, st>>>(wp, n_groups, wq, sp, bp);
-  else if (qmode == MFX_QMODE_MLX)
-    quantize_kernel<T, 8, MFX_QMODE_MLX><<<blocks, 256, 0, st>>>(wp, n_groups, wq, sp, bp);
-  else
-    quantize_kernel<T, 8, MFX_QMODE_DOC><<<blocks, 256, 0, st>>>(wp, n_groups, wq, sp, bp);
+#define MFX_QUANT_CASE(B)                                                                        \
+  case B:                                                                                       \
+    if (qmode == MFX_QMODE_MLX)                                                                 \
+      quantize_kernel<T, B, MFX_QMODE_MLX><<<blocks, 256, 0, st>>>(wp, n_groups, wq, sp, bp);   \
+    else                                                                                        \
+      quantize_kernel<T, B, MFX_QMODE_DOC><<<blocks, 256, 0, st>>>(wp, n_groups, wq, sp, bp);   \
+    break;
+  switch (bits) {
+    MFX_QUANT_CASE(3)
+    MFX_QUANT_CASE(4)
+    MFX_QUANT_CASE(5)
+    MFX_QUANT_CASE(6)
+    MFX_QUANT_CASE(8)
+    default: return MFX_ERR_UNSUPPORTED_BITS;
+  }
+#undef MFX_QUANT_CASE
   MFX_CUDA_TRY(cudaGetLastError());
   return MFX_OK;
 }
@@ -177,10 +203,14 @@ int launch_dequantize(const uint32_t* wq, const void* scales, const void* biases
   const SB* sp = static_cast<const SB*>(scales);
   const SB* bp = static_cast<const SB*>(biases);
   OUT* op = static_cast<OUT*>(out);
-  if (bits == 4)
-    dequantize_kernel<SB, OUT, 4><<<blocks, 256, 0, st>>>(wq, sp, bp, n_chunks, op);
-  else
-    dequantize_kernel<SB, OUT, 8><<<blocks, 256, 0, st>>>(wq, sp, bp, n_chunks, op);
+  switch (bits) {
+    case 3: dequantize_kernel<SB, OUT, 3><<<blocks, 256, 0, st>>>(wq, sp, bp, n_chunks, op); break;
+    case 4: dequantize_kernel<SB, OUT, 4><<<blocks, 256, 0, st>>>(wq, sp, bp, n_chunks, op); break;
+    case 5: dequantize_kernel<SB, OUT, 5><<<blocks, 256, 0, st>>>(wq, sp, bp, n_chunks, op); break;
+    case 6: dequantize_kernel<SB, OUT, 6><<<blocks, 256, 0, st>>>(wq, sp, bp, n_chunks, op); break;
+    case 8: dequantize_kernel<SB, OUT, 8><<<blocks, 256, 0, st>>>(wq, sp, bp, n_chunks, op); break;
+    default: return MFX_ERR_UNSUPPORTED_BITS;
+  }
   MFX_CUDA_TRY(cudaGetLastError());
   return MFX_OK;
 }
@@ -205,7 +235,7 @@ int mfx_quantize_affine(const void* w, int w_dtype, int64_t N, int64_t K, int bi
                         uint32_t* wq, void* scales, void* biases, void* stream) {
   using namespace mfx;
   if (!w || !wq || !scales || !biases) return MFX_ERR_NULL;
-  if ((bits != 4 && bits != 8) || group_size != 64) return MFX_ERR_UNSUPPORTED_BITS;
+  if (!valid_bits(bits) || group_size != 64) return MFX_ERR_UNSUPPORTED_BITS;
   if (qmode != MFX_QMODE_MLX && qmode != MFX_QMODE_DOC) return MFX_ERR_SHAPE;
   if (N <= 0 || K <= 0 || K % 64 != 0) return MFX_ERR_SHAPE;
   if (!valid_dtype(w_dtype)) return MFX_ERR_DTYPE;
@@ -224,7 +254,7 @@ int mfx_dequantize_affine(const uint32_t* wq, const void* scales, const void* bi
                           int64_t K, int bits, int group_size, void* out, int out_dtype, void* stream) {
   using namespace mfx;
   if (!wq || !scales || !biases || !out) return MFX_ERR_NULL;
-  if ((bits != 4 && bits != 8) || group_size != 64) return MFX_ERR_UNSUPPORTED_BITS;
+  if (!valid_bits(bits) || group_size != 64) return MFX_ERR_UNSUPPORTED_BITS;
   if (N <= 0 || K <= 0 || K % 64 != 0) return MFX_ERR_SHAPE;
   if (!valid_dtype(sb_dtype) || !valid_dtype(out_dtype)) return MFX_ERR_DTYPE;
   if (!aligned16(wq) || !aligned16(out)) return MFX_ERR_ALIGN;

@@ -110,8 +110,8 @@ class QuantizedLinear(Module):
     def __init__(self, input_dims: int, output_dims: int, bias: bool = True, group_size: int = 64, bits: int = 4,
                  device=None, dtype: torch.dtype = torch.bfloat16):
         super().__init__()
-        if bits not in (4, 8):
-            raise ValueError(f"bits={bits} is not supported (only 4 and 8; the reference's 3/5/6 are not built)")
+        if bits not in ops.BITS:
+            raise ValueError(f"bits={bits} is not supported (supported: {ops.BITS})")
         if group_size != 64:
             raise ValueError("group_size must be 64")
         if input_dims % group_size != 0:

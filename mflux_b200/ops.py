@@ -20,6 +20,9 @@ _EPI = {None: EPI_NONE, "none": EPI_NONE, "gelu": EPI_GELU_ERF, "gelu_erf": EPI_
         "silu": EPI_SILU, "swiglu": EPI_SWIGLU}
 
 
+# Code widths of the affine quantizer: the ones the reference's CLI offers (src/mflux/cli/defaults/defaults.py:63).
+BITS = (3, 4, 5, 6, 8)
+
 # Kernel launches issued through this module since import (bench.py reports the count of a timed region).
 LAUNCHES = [0]
 # When set to a dict, the traced operations append (flops, bytes, start_event, end_event) per launch under their
@@ -73,16 +76,17 @@ def poll_device_status() -> int:
 
 
 def quantize_affine(w: torch.Tensor, group_size: int = 64, bits: int = 4, mode: str = "mlx"):
-    """mx.quantize(w, group_size, bits): W[N, K] -> (uint32 [N, K*bits/32], scales, biases [N, K/64])."""
+    """mx.quantize(w, group_size, bits): W[N, K] -> (uint32 [N, K*bits/32], scales, biases [N, K/64]).
+    bits is 3, 4, 5, 6 or 8; code j of a row sits at bits [j*bits, (j+1)*bits) of the row's bit stream."""
     lib = _lib.load()
     _cuda(w, "w")
     if w.dim() != 2:
         raise ValueError("w must be [N, K]")
     w = w.contiguous()
     n, k = w.shape
-    if bits not in (4, 8) or group_size != 64 or k % 64 != 0:
+    if bits not in BITS or group_size != 64 or k % 64 != 0:
         # validated again by the library; shapes of the outputs need it here
-        _lib.check(-3 if (bits not in (4, 8) or group_size != 64) else -1, "quantize_affine")
+        _lib.check(-3 if (bits not in BITS or group_size != 64) else -1, "quantize_affine")
     wq = torch.empty((n, k * bits // 32), dtype=torch.uint32, device=w.device)
     scales = torch.empty((n, k // group_size), dtype=w.dtype, device=w.device)
     biases = torch.empty_like(scales)
@@ -123,7 +127,7 @@ def prepare_qlinear(wq: torch.Tensor, scales: torch.Tensor, biases: torch.Tensor
     k = wq.shape[1] * 32 // bits
     nbytes = lib.mfx_qlinear_prepared_bytes(n, k, bits, group_size)
     if nbytes == 0:
-        _lib.check(-3 if (bits not in (4, 8) or group_size != 64) else -1, "prepare_qlinear")
+        _lib.check(-3 if (bits not in BITS or group_size != 64) else -1, "prepare_qlinear")
     blob = torch.empty(nbytes, dtype=torch.uint8, device=wq.device)
     rc = lib.mfx_qlinear_prepare(_ptr(wq), _ptr(scales), _ptr(biases), _dt(scales), n, k, bits, group_size,
                                  _ptr(blob), nbytes, _stream())
@@ -358,6 +362,11 @@ def fmha(qkv: torch.Tensor, heads: int, scale: float | None = None, out: torch.T
         _cuda(key_bias, "key_bias")
         if key_bias.dtype != torch.float32 or tuple(key_bias.shape) != (batch, seq) or key_bias.stride(1) != 1:
             raise ValueError("key_bias must be a float32 [batch, seq] tensor with a dense last dim")
+        if batch > 1 and key_bias.stride(0) % 4 != 0:
+            # every sample's row has to start on a 16-byte boundary: copy into rows padded to a multiple of 4
+            padded = torch.zeros(batch, (seq + 3) // 4 * 4, dtype=torch.float32, device=key_bias.device)
+            padded[:, :seq] = key_bias
+            key_bias = padded[:, :seq]
         rc = lib.mfx_fmha_bias(c_void_p(base), c_void_p(base + hd * es), c_void_p(base + 2 * hd * es), qkv.stride(1),
                                qkv.stride(0), seq, batch, heads, sc, _ptr(key_bias), key_bias.stride(0), _ptr(out),
                                out.stride(1), out.stride(0), _stream())

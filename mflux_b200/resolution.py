@@ -7,7 +7,7 @@ stored bits; any/any -> the stored bits win, with a warning when they differ.
 """
 from __future__ import annotations
 
-SUPPORTED_BITS = (4, 8)
+SUPPORTED_BITS = (3, 4, 5, 6, 8)
 
 
 def resolve(stored: int | None, requested: int | None) -> tuple[int | None, str | None]:
@@ -24,6 +24,6 @@ def resolve(stored: int | None, requested: int | None) -> tuple[int | None, str 
 
 
 def check_supported(bits: int | None) -> None:
-    """The reference's CLI accepts 3, 4, 5, 6, 8 (cli/defaults/defaults.py:63); this build implements 4 and 8."""
+    """The widths the reference's CLI accepts (cli/defaults/defaults.py:63): 3, 4, 5, 6, 8."""
     if bits is not None and bits not in SUPPORTED_BITS:
         raise ValueError(f"quantize={bits} is not implemented on this backend (supported: {SUPPORTED_BITS})")

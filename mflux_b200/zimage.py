@@ -331,7 +331,7 @@ class ZImageTransformer(nn.Module):
             else:
                 ops.norm_gate_residual(ybuf, blk.ffn_norm2.weight.data, xs, gate_mlp, eps)
             if tag is not None and self.trace is not None:
-                self.trace[f"{tag}{i}"] = xs.clone()
+                self.trace[f"{tag}{i}"] = xs.clone()   # rows lo:hi of the stream
 
     # ------------------------------------------------------------------ forward
     def forward(self, x: torch.Tensor, timestep: torch.Tensor, cap_feats: torch.Tensor) -> torch.Tensor:
@@ -358,14 +358,14 @@ class ZImageTransformer(nn.Module):
         _call(self.all_x_embedder[cfg.key], tokens.contiguous(), out=xs[:, :si])
         if si > n_img:
             xs[:, n_img:si] = self.x_pad_token.data.float()
-        self._run_blocks(list(self.noise_refiner), 0, si, cs_img, t_emb)
+        self._run_blocks(list(self.noise_refiner), 0, si, cs_img, t_emb, tag="noise")
 
         cn = ops.norm_modulate(cap.contiguous(), weight=self.cap_embedder[0].weight.data, eps=self.cap_embedder[0].eps,
                                rms=True)
         _call(self.cap_embedder[1], cn, out=xs[:, si:])
         if sc > n_cap:
             xs[:, si + n_cap:] = self.cap_pad_token.data.float()
-        self._run_blocks(list(self.context_refiner), si, si + sc, cs_cap, None)
+        self._run_blocks(list(self.context_refiner), si, si + sc, cs_cap, None, tag="context")
 
         self._run_blocks(list(self.layers), 0, si + sc, cs_all, t_emb, tag="layer")
 

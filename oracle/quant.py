@@ -20,14 +20,30 @@ Two quantizer modes are restated:
   "doc"  the formula in MLX's documentation: scale = (max - min) /
          (2^bits - 1), bias = min.
 Codes: q = clip(rint((w - bias) / scale), 0, 2^bits - 1) with the float32 (unrounded) scale and
-bias, round-half-to-even, packed little-end first into uint32 (element j of a word in bits
-[j*bits, (j+1)*bits)).
+bias, round-half-to-even, packed little-end first: code j of a row occupies bits [j*bits, (j+1)*bits) of the
+row's bit stream, which is then read as uint32 words. For 4 and 8 bits a word holds 8 / 4 whole codes; for 3, 5
+and 6 bits (the other widths of the reference's CLI, src/mflux/cli/defaults/defaults.py:63) MLX packs 8 codes
+into 3 or 5 bytes and 4 codes into 3 bytes, the same bit stream.
 """
 from __future__ import annotations
 
 import numpy as np
 
 EPS = np.float32(1e-7)
+BITS = (3, 4, 5, 6, 8)
+
+
+def pack_codes(q: np.ndarray, bits: int) -> np.ndarray:
+    """Integer codes [N, K] -> uint32 [N, K*bits/32], little-end-first bit stream per row."""
+    n, k = q.shape
+    q = q.astype(np.uint32)
+    if 32 % bits == 0:
+        per = 32 // bits
+        shifts = (np.arange(per, dtype=np.uint32) * np.uint32(bits)).astype(np.uint32)
+        return np.bitwise_or.reduce(q.reshape(n, k // per, per) << shifts, axis=-1).astype(np.uint32)
+    stream = ((q[..., None] >> np.arange(bits, dtype=np.uint32)) & np.uint32(1)).astype(np.uint8)   # [N, K, bits]
+    stream = stream.reshape(n, k * bits // 32, 32).astype(np.uint32)
+    return np.bitwise_or.reduce(stream << np.arange(32, dtype=np.uint32), axis=-1).astype(np.uint32)
 
 
 def _as_f32(a) -> np.ndarray:
@@ -65,8 +81,8 @@ def quantize_affine(w, group_size: int = 64, bits: int = 4, mode: str = "mlx", d
     if w.ndim != 2:
         raise ValueError("w must be [N, K]")
     n, k = w.shape
-    if bits not in (4, 8):
-        raise ValueError("bits must be 4 or 8")
+    if bits not in BITS:
+        raise ValueError(f"bits must be one of {BITS}")
     if k % group_size != 0:
         raise ValueError("K must be a multiple of the group size")
     nb = np.float32((1 << bits) - 1)
@@ -91,19 +107,20 @@ def quantize_affine(w, group_size: int = 64, bits: int = 4, mode: str = "mlx", d
         q = np.rint((g - bias[..., None]) / scale[..., None])
     q = np.where(np.isfinite(q), q, 0.0)  # constant group in "doc" mode: scale == 0 -> code 0
     q = np.clip(q, 0, nb).astype(np.uint32).reshape(n, k)
-    per = 32 // bits
-    q = q.reshape(n, k // per, per)
-    shifts = (np.arange(per, dtype=np.uint32) * np.uint32(bits)).astype(np.uint32)
-    packed = np.bitwise_or.reduce(q << shifts, axis=-1).astype(np.uint32)
-    return packed, round_to_dtype(scale, dtype), round_to_dtype(bias, dtype)
+    return pack_codes(q, bits), round_to_dtype(scale, dtype), round_to_dtype(bias, dtype)
 
 
 def unpack_codes(packed: np.ndarray, bits: int) -> np.ndarray:
     """uint32 [N, K*bits/32] -> integer codes [N, K]."""
-    per = 32 // bits
-    shifts = (np.arange(per, dtype=np.uint32) * np.uint32(bits)).astype(np.uint32)
-    q = (packed[..., None] >> shifts) & np.uint32((1 << bits) - 1)
-    return q.reshape(packed.shape[0], -1)
+    packed = np.asarray(packed, dtype=np.uint32)
+    if 32 % bits == 0:
+        per = 32 // bits
+        shifts = (np.arange(per, dtype=np.uint32) * np.uint32(bits)).astype(np.uint32)
+        q = (packed[..., None] >> shifts) & np.uint32((1 << bits) - 1)
+        return q.reshape(packed.shape[0], -1)
+    n = packed.shape[0]
+    stream = ((packed[..., None] >> np.arange(32, dtype=np.uint32)) & np.uint32(1)).reshape(n, -1, bits)
+    return (stream.astype(np.uint32) << np.arange(bits, dtype=np.uint32)).sum(axis=-1).astype(np.uint32)
 
 
 def dequantize_affine(packed, scales, biases, group_size: int = 64, bits: int = 4) -> np.ndarray:

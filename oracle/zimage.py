@@ -131,14 +131,18 @@ def forward_one(model, image, timestep, cap_feats, collect=None):
     x_emb = torch.where(torch.from_numpy(x_mask)[:, None], model.x_pad_token.detach().float().cpu(), x_emb)
     x_freqs = rope_lookup(tables, x_ids)
     x_emb = x_emb[None]
-    for layer in model.noise_refiner:
+    for i, layer in enumerate(model.noise_refiner):
         x_emb = block(layer, x_emb, x_freqs, t_emb, heads)
+        if collect is not None:
+            collect.setdefault(f"noise{i}", []).append(x_emb[0])
     cap_emb = lin(model.cap_embedder[1], rms(cap_emb, model.cap_embedder[0]))
     cap_emb = torch.where(torch.from_numpy(cap_mask)[:, None], model.cap_pad_token.detach().float().cpu(), cap_emb)
     cap_freqs = rope_lookup(tables, cap_ids)
     cap_emb = cap_emb[None]
-    for layer in model.context_refiner:
+    for i, layer in enumerate(model.context_refiner):
         cap_emb = block(layer, cap_emb, cap_freqs, None, heads)
+        if collect is not None:
+            collect.setdefault(f"context{i}", []).append(cap_emb[0])
     x_len = x_emb.shape[1]
     unified = torch.cat([x_emb, cap_emb], dim=1)
     freqs = torch.cat([x_freqs, cap_freqs], dim=0)
@@ -154,6 +158,7 @@ def forward_one(model, image, timestep, cap_feats, collect=None):
 
 def forward(model, images, timesteps, cap_feats, collect=None):
     """All samples, one at a time as the reference runs them. `collect` (a dict) receives, per main layer, the list
-    of the samples' unified streams [image tokens, then caption tokens] after that layer."""
+    of the samples' unified streams [image tokens, then caption tokens] after that layer ("layer{i}"), and the image
+    / caption streams after every refiner block ("noise{i}", "context{i}")."""
     return torch.stack([forward_one(model, images[i], timesteps[i], cap_feats[i], collect)
                         for i in range(images.shape[0])])

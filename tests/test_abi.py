@@ -37,7 +37,8 @@ def test_argument_validation_needs_no_gpu(lib_built):
     """Host-side validation rejects bad calls before anything touches a device."""
     lib = _lib.load()
     assert lib.mfx_quantize_affine(None, 0, 4, 64, 4, 64, 0, None, None, None, None) == -7
-    assert lib.mfx_quantize_affine(16, 0, 4, 64, 3, 64, 0, 16, 16, 16, None) == -3
+    assert lib.mfx_quantize_affine(16, 0, 4, 64, 7, 64, 0, 16, 16, 16, None) == -3
+    assert lib.mfx_quantize_affine(16, 0, 4, 64, 2, 64, 0, 16, 16, 16, None) == -3
     assert lib.mfx_quantize_affine(16, 0, 4, 96, 4, 64, 0, 16, 16, 16, None) == -1
     assert lib.mfx_quantize_affine(16, 0, 4, 64, 4, 32, 0, 16, 16, 16, None) == -3
     assert lib.mfx_quantize_affine(8, 0, 4, 64, 4, 64, 0, 16, 16, 16, None) == -2
@@ -48,13 +49,18 @@ def test_argument_validation_needs_no_gpu(lib_built):
     a.rows, a.batch, a.K, a.N, a.bits, a.group_size = 128, 1, 96, 64, 4, 64
     assert lib.mfx_qlinear_ex(a, None) == -1  # K % 64
     a.K = 128
-    a.bits = 5
+    a.bits = 7
     assert lib.mfx_qlinear_ex(a, None) == -3
     a.bits = 4
     a.workspace_bytes = 16  # too small for the prepared form of the weight
     assert lib.mfx_qlinear_ex(a, None) == -1
     assert lib.mfx_qlinear_prepared_bytes(12288, 3072, 4, 64) == 12288 * 3072 // 2 + 12288 * 48 * 4
     assert lib.mfx_qlinear_prepared_bytes(12288, 3000, 4, 64) == 0
+    # 3-bit codes are widened to 4 bits, 5- and 6-bit codes to 8 bits in the prepared form
+    assert lib.mfx_qlinear_prepared_bytes(256, 128, 3, 64) == lib.mfx_qlinear_prepared_bytes(256, 128, 4, 64)
+    assert lib.mfx_qlinear_prepared_bytes(256, 128, 5, 64) == lib.mfx_qlinear_prepared_bytes(256, 128, 8, 64)
+    assert lib.mfx_qlinear_prepared_bytes(256, 128, 6, 64) == lib.mfx_qlinear_prepared_bytes(256, 128, 8, 64)
+    assert lib.mfx_qlinear_prepared_bytes(256, 128, 7, 64) == 0
     assert lib.mfx_qlinear_prepared_bytes(10, 64, 4, 64) == 512 + 40  # 320 code bytes padded to 256s + pairs
 
 

@@ -115,7 +115,7 @@ def test_zimage_full_depth_at_reduced_width(lib_built):
     cfg = ZImageConfig(dim=512, n_heads=4, n_layers=30, n_refiner_layers=2, cap_feat_dim=256, ffn_hidden=1408)
     err, curve = _zimage_case(cfg, 8, 32, 64, 32)              # 256 image tokens + 64 caption tokens
     _report("zimage 2+2+30 blocks at hidden 512 W8, 256+64 tokens", output=err, streams=curve)
-    assert len(curve) == 30
+    assert sum(k.startswith("layer") for k in curve) == 30 and len(curve) == 34   # + 2 + 2 refiner blocks
     assert err <= TOL and max(curve.values()) <= TOL, (err, max(curve.values()))
 
 

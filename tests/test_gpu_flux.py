@@ -75,7 +75,7 @@ def test_generate_image_loop_and_resolution_rules(lib_built):
     assert lat1.shape == (1, 16, 64) and torch.isfinite(lat1).all()
     assert torch.equal(lat1, lat2)  # deterministic
     with pytest.raises(ValueError):
-        Flux1(quantize=3, model_config=cfg)
+        Flux1(quantize=7, model_config=cfg)
 
 
 def test_save_and_reload_quantized_model(lib_built, tmp_path):

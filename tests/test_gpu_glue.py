@@ -191,5 +191,6 @@ def test_fmha_bias_argument_validation(lib_built):
         ops.fmha(qkv, 1, key_bias=torch.zeros(2, 63, device="cuda"))
     with pytest.raises(ValueError):
         ops.fmha(qkv, 1, key_bias=torch.zeros(2, 64, device="cuda", dtype=torch.bfloat16))
-    with pytest.raises(ValueError):   # rows of 66 floats: the second sample's bias is not 16-byte aligned
-        ops.fmha(qkv[:, :, :], 1, key_bias=torch.zeros(2, 66, device="cuda")[:, :64])
+    # rows of 66 floats: the second sample's bias would not start on a 16-byte boundary; the wrapper re-pads it
+    out = ops.fmha(qkv, 1, key_bias=torch.zeros(2, 66, device="cuda")[:, :64])
+    assert torch.isfinite(out.float()).all()

@@ -59,6 +59,40 @@ def test_sweep_shapes(lib_built, bits, nk, m):
     assert err <= TOL, err
 
 
+@pytest.mark.parametrize("bits", [3, 5, 6])
+@pytest.mark.parametrize("mnk", [(300, 520, 320), (16, 1032, 192), (1, 264, 256), (4096, 3072, 3072)])
+def test_odd_code_widths(lib_built, bits, mnk):
+    """3-, 5- and 6-bit weights (the other choices of the reference's -q flag, cli/defaults/defaults.py:63): codes
+    packed as MLX packs them (bit stream, codes straddling words), widened when the weight is prepared; both the
+    tensor-core kernel and the small-M kernel against the float32 oracle, rel-L2 <= 1e-2."""
+    m, n, k = mnk
+    w, x, b = _case(m, n, k, bits, 300 + bits + m, torch.bfloat16)
+    pq, _, _, ref = _oracle(w, x, b, bits, "bf16")
+    wq, _, _, y = _run(w, x, b, bits)
+    assert wq.shape == (n, k * bits // 32)
+    np.testing.assert_array_equal(wq.cpu().numpy(), pq)
+    err = quant.rel_l2(y, ref)
+    assert err <= TOL, err
+
+
+def test_odd_width_model_step(lib_built):
+    """A FLUX-shaped step quantized to 6 and to 3 bits (Flux1(quantize=6 | 3)) against the oracle."""
+    from mflux_b200.flux import FluxConfig, Transformer
+    from oracle import flux as oflux
+
+    cfg = FluxConfig(hidden=256, heads=2, num_joint=1, num_single=1, context_dim=128, pooled_dim=64)
+    g = torch.Generator(device="cpu").manual_seed(17)
+    lat = torch.randn(1, 64, cfg.in_channels, generator=g)
+    ctx = torch.randn(1, 24, cfg.context_dim, generator=g).to(torch.bfloat16)
+    pooled = torch.randn(1, cfg.pooled_dim, generator=g).to(torch.bfloat16)
+    ts, gd = torch.full((1,), 400.0), torch.full((1,), 3500.0)
+    for bits in (6, 3):
+        model = Transformer(cfg, bits=bits, device="cuda", seed=bits)
+        out = model(lat.cuda(), ctx.cuda(), pooled.cuda(), ts.cuda(), gd.cuda(), 128, 128)
+        ref = oflux.forward(model, lat.to(torch.bfloat16), ctx, pooled, ts, gd, 128, 128)
+        assert quant.rel_l2(out, ref.numpy()) <= TOL
+
+
 @pytest.mark.parametrize("bits", [4, 8])
 @pytest.mark.parametrize("w_dtype,name", [(torch.float16, "f16"), (torch.float32, "f32")])
 def test_scales_wider_than_bf16_are_rounded_within_tolerance(lib_built, bits, w_dtype, name):

@@ -17,7 +17,7 @@ _NAMES = {torch.float32: "f32", torch.bfloat16: "bf16", torch.float16: "f16"}
 
 
 @pytest.mark.parametrize("mode", ["mlx", "doc"])
-@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("bits", [3, 4, 5, 6, 8])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 def test_quantize_bit_exact(lib_built, mode, bits, dtype):
     from mflux_b200 import ops
@@ -56,7 +56,7 @@ def test_quantize_edge_groups(lib_built):
     w[4] = torch.arange(128) % 16 * 0.5 - 3.75  # exact half-way points for scale 1
     w[5] = -torch.arange(128, dtype=torch.float32)
     for mode in ("mlx", "doc"):
-        for bits in (4, 8):
+        for bits in (3, 4, 5, 6, 8):
             wq, s, b = ops.quantize_affine(w.cuda(), 64, bits, mode)
             pq, ps, pb = quant.quantize_affine(w, 64, bits, mode)
             np.testing.assert_array_equal(wq.cpu().numpy(), pq)
@@ -64,7 +64,7 @@ def test_quantize_edge_groups(lib_built):
             np.testing.assert_array_equal(b.cpu().numpy(), pb)
 
 
-@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("bits", [3, 4, 5, 6, 8])
 @pytest.mark.parametrize("sb_dtype", [torch.float32, torch.bfloat16])
 def test_dequantize_bit_exact_and_round_trip(lib_built, bits, sb_dtype):
     from mflux_b200 import ops
@@ -88,6 +88,6 @@ def test_quantize_rejects_bad_arguments(lib_built):
     with pytest.raises(ValueError):
         ops.quantize_affine(torch.zeros(4, 96, device="cuda"), 64, 4)
     with pytest.raises(ValueError):
-        ops.quantize_affine(torch.zeros(4, 64, device="cuda"), 64, 3)
+        ops.quantize_affine(torch.zeros(4, 64, device="cuda"), 64, 7)
     with pytest.raises(RuntimeError):
         ops.quantize_affine(torch.zeros(4, 64), 64, 4)

@@ -139,7 +139,8 @@ def test_rope_table_matches_reference_construction(lib_built):
 def test_denoise_loop_with_and_without_guidance(lib_built):
     from mflux_b200.zimage import ZImage
 
-    zi = ZImage(quantize=8, model_config=_small_cfg(n_layers=1), seed=2)
+    # guidance needs the base model (supports_guidance); the Turbo configuration forces it to 0
+    zi = ZImage(quantize=8, model_config=_small_cfg(n_layers=1, supports_guidance=True), seed=2)
     g = torch.Generator(device="cuda").manual_seed(0)
     cap = torch.randn(2, 32, 128, device="cuda", generator=g).to(torch.bfloat16)
     neg = torch.randn(2, 32, 128, device="cuda", generator=g).to(torch.bfloat16)
@@ -148,6 +149,10 @@ def test_denoise_loop_with_and_without_guidance(lib_built):
     assert plain.shape == guided.shape == (2, 16, 1, 16, 16)
     assert torch.isfinite(plain).all() and torch.isfinite(guided).all()
     assert not torch.allclose(plain, guided)
+    turbo = ZImage(quantize=8, model_config=_small_cfg(n_layers=1), seed=2)
+    t_plain = turbo.generate_image(1, cap, num_inference_steps=2, height=128, width=128)
+    t_guided = turbo.generate_image(1, cap, neg, num_inference_steps=2, height=128, width=128, guidance=3.0)
+    assert torch.equal(t_plain, t_guided)   # variants/z_image.py:60-62: no guidance support, guidance = 0
     # one guided step equals the hand-combined two evaluations
     lat = torch.randn(2, 16, 1, 16, 16, device="cuda", generator=g)
     t = torch.full((2,), 0.3, device="cuda")

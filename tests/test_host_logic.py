@@ -58,13 +58,13 @@ def test_resolution_rules(stored, requested):
             assert warning is None
 
 
-def test_unsupported_bits_rejected():
-    for b in (3, 5, 6):
+def test_supported_bits_are_the_reference_cli_choices():
+    """src/mflux/cli/defaults/defaults.py:63 offers 3, 4, 5, 6 and 8."""
+    for b in (2, 7, 16):
         with pytest.raises(ValueError):
             resolution.check_supported(b)
-    resolution.check_supported(None)
-    resolution.check_supported(4)
-    resolution.check_supported(8)
+    for b in (None, 3, 4, 5, 6, 8):
+        resolution.check_supported(b)
 
 
 def test_zimage_token_layout_matches_oracle():

@@ -9,7 +9,7 @@ def _w(n, k, seed=0, std=0.02):
     return (np.random.default_rng(seed).standard_normal((n, k)) * std).astype(np.float32)
 
 
-@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("bits", [3, 4, 5, 6, 8])
 @pytest.mark.parametrize("mode", ["mlx", "doc"])
 def test_shapes_and_ranges(bits, mode):
     w = _w(16, 256)
@@ -20,7 +20,7 @@ def test_shapes_and_ranges(bits, mode):
     assert q.min() >= 0 and q.max() <= (1 << bits) - 1
 
 
-@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("bits", [3, 4, 5, 6, 8])
 def test_doc_mode_matches_formula(bits):
     w = _w(8, 128, seed=1)
     packed, s, b = quant.quantize_affine(w, 64, bits, "doc")
@@ -32,7 +32,7 @@ def test_doc_mode_matches_formula(bits):
     assert (q.min(-1) == 0).all() and (q.max(-1) == (1 << bits) - 1).all()
 
 
-@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("bits", [3, 4, 5, 6, 8])
 def test_mlx_mode_zero_is_representable_and_error_bounded(bits):
     w = _w(32, 512, seed=2)
     packed, s, b = quant.quantize_affine(w, 64, bits, "mlx")
@@ -101,4 +101,23 @@ def test_bad_arguments():
     with pytest.raises(ValueError):
         quant.quantize_affine(_w(4, 96), 64, 4)
     with pytest.raises(ValueError):
-        quant.quantize_affine(_w(4, 64), 64, 3)
+        quant.quantize_affine(_w(4, 64), 64, 7)
+
+
+@pytest.mark.parametrize("bits", [3, 5, 6])
+def test_odd_widths_pack_as_mlx_byte_groups(bits):
+    """MLX packs 3- and 5-bit codes eight at a time into 3 / 5 bytes and 6-bit codes four at a time into 3 bytes,
+    each group a little-endian integer with code i at bits [i*bits, (i+1)*bits): the bytes of the packed words must
+    read that way, and the packed row has K*bits/32 words."""
+    rng = np.random.default_rng(bits)
+    q = rng.integers(0, 1 << bits, size=(3, 64)).astype(np.uint32)
+    packed = quant.pack_codes(q, bits)
+    assert packed.shape == (3, 64 * bits // 32)
+    per, nbytes = (8, bits) if bits in (3, 5) else (4, 3)
+    raw = packed.view(np.uint8).reshape(3, -1)
+    for row in range(3):
+        for grp in range(64 // per):
+            v = sum(int(q[row, grp * per + i]) << (bits * i) for i in range(per))
+            want = [(v >> (8 * j)) & 0xFF for j in range(nbytes)]
+            assert list(raw[row, grp * nbytes:(grp + 1) * nbytes]) == want
+    np.testing.assert_array_equal(quant.unpack_codes(packed, bits), q)
