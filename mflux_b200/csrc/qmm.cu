@@ -169,6 +169,11 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
            const __grid_constant__ CUtensorMap tmap_sb, const __grid_constant__ CUtensorMap tmap_t,
            const __grid_constant__ CUtensorMap tmap_lb, const Params p) {
   using L = Smem<BITS, ST, SD>;
+  // With as many TMA stages as dequantized-weight stages the two rings advance in lockstep and one "stage
+  // consumed" barrier serves both: the commit after a stage's MMAs frees its activation tile and its B tile, and
+  // the stage's packed codes were read before its B tile was written, so they are free by then too. That is one
+  // tcgen05.commit and eight dequantizer arrivals less per stage.
+  constexpr bool UNIFIED = (ST == SD);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -184,7 +189,9 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
   auto t_empty = [&](int s) { return bar0 + 8u * (2 * ST + s); };  // local: TMA stage may be refilled
   constexpr int B0 = 3 * ST;
   auto d_full = [&](int s) { return bar0 + 8u * (B0 + s); };             // leader: B halves of both CTAs written
-  auto d_empty = [&](int s) { return bar0 + 8u * (B0 + SD + s); };       // local: B stage consumed
+  auto d_empty = [&](int s) {                                              // local: B stage consumed
+    return UNIFIED ? bar0 + 8u * (2 * ST + s) : bar0 + 8u * (B0 + SD + s);   // (== t_empty when unified)
+  };
   auto acc_full = [&](int s) { return bar0 + 8u * (B0 + 2 * SD + s); };  // local
   auto acc_empty = [&](int s) { return bar0 + 8u * (B0 + 2 * SD + 2 + s); };  // leader
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::OFF_TMEM);
@@ -205,11 +212,12 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     for (int s = 0; s < ST; ++s) {
       mbar_init(w_full(s), 1);
       mbar_init(x_full(s), 1);                  // the leader's expect_tx covers both CTAs' X tiles
-      mbar_init(t_empty(s), 1 + NUM_DQ_WARPS);  // MMA commit (X tiles) + every local dequantizer warp (codes)
+      // MMA commit (X tiles) + every local dequantizer warp (codes); the commit alone when unified
+      mbar_init(t_empty(s), UNIFIED ? 1 : 1 + NUM_DQ_WARPS);
     }
     for (int s = 0; s < SD; ++s) {
       mbar_init(d_full(s), 2 * NUM_DQ_WARPS);   // the dequantizer warps of both CTAs
-      mbar_init(d_empty(s), 1);
+      if (!UNIFIED) mbar_init(d_empty(s), 1);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(acc_full(s), 1);
@@ -328,7 +336,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
               }
             }
             umma_commit_pair(t_empty(st));
-            umma_commit_pair(d_empty(sd));
+            if (!UNIFIED) umma_commit_pair(d_empty(sd));
             if (s == num_all - 1) umma_commit_pair(acc_full(a));
           }
           __syncwarp();
@@ -397,7 +405,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
           __syncwarp();
           if (lane == 0) {
             mbar_arrive_leader(d_full(sd));
-            mbar_arrive(t_empty(st));
+            if (!UNIFIED) mbar_arrive(t_empty(st));
           }
           if (++st == ST) {
             st = 0;
@@ -439,7 +447,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         __syncwarp();
         if (lane == 0) {
           mbar_arrive_leader(d_full(sd));
-          mbar_arrive(t_empty(st));
+          if (!UNIFIED) mbar_arrive(t_empty(st));
         }
         if (++st == ST) {
           st = 0;
