@@ -326,10 +326,10 @@ def qwen_spec(args):
             cfg_groups = [dist.new_group([r, r + tp]) for r in range(tp)]
             pipe = QwenImage(quantize=4, model_config=cfg, device=dev, seed=1234, tp_rank=tp_rank, tp_world=tp,
                              tp_group=tp_groups[branch] if tp > 1 else None, cfg_rank=branch,
-                             cfg_group=cfg_groups[tp_rank], cuda_graph=graph)
+                             cfg_group=cfg_groups[tp_rank], cuda_graph=graph, tp_mode=args.qwen_tp_mode)
         else:
             pipe = QwenImage(quantize=4, model_config=cfg, device=dev, seed=1234, tp_rank=rank, tp_world=world,
-                             cuda_graph=graph)
+                             cuda_graph=graph, tp_mode=args.qwen_tp_mode)
         g = torch.Generator(device="cpu").manual_seed(100)   # every rank sees the same image and prompts
         lat_h = torch.randn(1, si, cfg.in_channels, generator=g).pin_memory()
         emb_h = torch.randn(b, st, cfg.joint_attention_dim, generator=g).to(torch.bfloat16).pin_memory()
@@ -358,7 +358,8 @@ def qwen_spec(args):
         "metric": "qwen_image_w4_dit_steps_per_sec_1328px_cfg2",
         "unit": "steps/s (one step = prompt + negative prompt of one image, 2 x 7145 tokens through 60 blocks)",
         "workload": (f"Qwen-Image-shaped dual-stream MMDiT {cfg.num_layers} blocks, hidden {d}, {cfg.heads}x128 heads, "
-                     f"W4 g64, CFG batch 2, {si} image + {st} text tokens, {par}, "
+                     f"W4 g64, CFG batch 2, {si} image + {st} text tokens, {par}"
+                     f"{'' if args.gpus == 1 else ' (' + args.qwen_tp_mode + ' exchange)'}, "
                      f"{'launches issued one by one' if args.no_cuda_graph else 'step replayed as a CUDA graph'}"),
         "scaling": "strong", "lin": lin, "attn": attn, "per_gpu_batch": b, "build": build,
         "l2_policy": "inputs larger than L2 (10 GB of packed weights, split over the ranks, stream every step)",
@@ -511,6 +512,9 @@ def main():
     ap.add_argument("--qwen-parallel", default="cfg+tp", choices=["cfg+tp", "tp"],
                     help="qwen on N > 1 GPUs: split the two guidance branches over the halves of the ranks and use "
                          "tensor parallelism inside each half (default), or tensor parallelism over all ranks")
+    ap.add_argument("--qwen-tp-mode", default="peer", choices=["peer", "nccl"],
+                    help="qwen tensor parallelism: reduce-scatter / all-gather fused into this library's kernels over "
+                         "peer-mapped memory (default), or NCCL all-reduces beside the matmuls")
     ap.add_argument("--lora-rank", type=int, default=0,
                     help="flux: wrap every attention / feed-forward linear with one LoRA adapter of this rank")
     ap.add_argument("--lora-library", action="store_true",

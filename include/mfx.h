@@ -51,6 +51,9 @@ typedef enum mfx_epilogue {
   MFX_EPI_GELU_TANH = 2,     /* y = gelu(v), tanh form       (mlx.nn.gelu_approx) */
   MFX_EPI_GATE_RESIDUAL = 3, /* y = residual + gate[sample] * v */
   MFX_EPI_SILU = 4,          /* y = v * sigmoid(v) */
+  MFX_EPI_PEER_SCATTER = 6,  /* tensor parallel: the bf16 product (no bias) of a linear split along K is not written
+                                to y but scattered, row by row, into partial-sum slots in the memory of the rank
+                                that owns each row (mfx_qlinear_args.scatter); mfx_tp_fuse sums the slots */
   MFX_EPI_SWIGLU = 5         /* y[:, j] = silu(v[:, 2j]) * v[:, 2j+1]; y is N/2 wide, N % 16 == 0. The caller
                                 interleaves the rows of the gate and up projections (w1 row j -> row 2j, w3 row j
                                 -> row 2j+1), which turns silu(w1 x) * (w3 x) of the reference's FeedForward
@@ -136,6 +139,22 @@ int mfx_qlinear_static_scratch(const void* x, int64_t M, int64_t K, int64_t ldx,
  * residual of joint_transformer_block.py:84-90 / single_transformer_block.py:45,56-57.
  * Weights: either `prepared` (from mfx_qlinear_prepare; then wq/scales/biases may be NULL) or
  * wq + scales + biases + a workspace as in mfx_qlinear. */
+/* Tensor-parallel exchange (no counterpart in the single-device reference; it serves the column- / row-split
+ * QuantizedLinear layers of the Qwen-Image blocks, qwen_transformer_block.py:27-76, when one image is spread over
+ * several GPUs). Every rank owns rows_per_rank consecutive rows of each sample's joint sequence. All pointers in
+ * dst / flags are addresses valid on THIS device: the peers' buffers mapped into this process (peer access or
+ * symmetric memory), entry r belonging to rank r. Peers are written with ordinary stores only. */
+#define MFX_TP_MAX_WORLD 8
+typedef struct mfx_tp_scatter {
+  int world, rank;
+  int64_t rows_per_rank; /* R: rows of a sample's joint sequence owned by one rank */
+  int64_t row_offset;    /* joint-sequence row of this call's first activation row */
+  int64_t D;             /* width of a partial row (= N of the linear) */
+  void* dst[MFX_TP_MAX_WORLD];  /* on rank r: bf16 slots [world, batch, R, D]; this rank writes slot [rank] */
+  int* flags[MFX_TP_MAX_WORLD]; /* on rank r: the counter this rank bumps by one when all its rows are out */
+  int* done_counter;     /* local int, zero between calls (counts finished thread blocks) */
+} mfx_tp_scatter;
+
 typedef struct mfx_qlinear_args {
   const void* x;            /* bf16 */
   int64_t x_row_stride, x_batch_stride;
@@ -170,8 +189,43 @@ typedef struct mfx_qlinear_args {
   const void* lora_b;       /* [N, lora_ld], dense */
   int64_t lora_ld;
   int64_t lora_r;
+  const mfx_tp_scatter* scatter; /* host pointer; required for MFX_EPI_PEER_SCATTER (then y may be NULL) */
 } mfx_qlinear_args;
 int mfx_qlinear_ex(const mfx_qlinear_args* args /* host */, void* stream);
+
+/* The elementwise half of a tensor-parallel block on the rows this rank owns, fused with both collectives:
+ *   wait until rs_flags[r] >= rs_target for every rank r (the partials of the preceding row-split linears),
+ *   x += gate * (sum_r partials[r] + bias)          (qwen_transformer_block.py:56-57,64,69)
+ *   n = LayerNorm(x, eps) * (1 + scale) + shift      (the next sub-layer's modulated pre-norm, :35-47)
+ *   store n (bf16) at its joint row in push_dst[r] for every rank r, then add 1 to *ag_flags[r].
+ * partials == NULL skips the wait and the residual update (first norm of the first block); scale == NULL for both
+ * segments skips norm and push (after the last block). Segment 0 are joint rows < split (text stream), segment 1
+ * the others (image stream): each has its own bias, gate, shift and scale. Rows at or beyond seq are padding. */
+typedef struct mfx_tp_fuse_args {
+  int world, rank;
+  int64_t batch, rows_per_rank, seq_pad /* = world * rows_per_rank */, seq, split, D;
+  float* x;             /* [batch, rows_per_rank, D] float32 residual rows of this rank, updated in place */
+  const void* partials; /* local bf16 [world, batch, rows_per_rank, D], or NULL */
+  const int* rs_flags;  /* local [world] */
+  int rs_target;        /* waited-for value = rs_target + (epoch_base ? epoch_base[0] : 0) */
+  const int* epoch_base; /* local int the caller advances between steps (so that a recorded CUDA graph of a step
+                            can be replayed: the counters only grow), or NULL */
+  const void* bias[2];  /* [D], nullable */
+  int bias_dtype;
+  const void* gate[2];  /* [batch, D] */
+  const void* shift[2];
+  const void* scale[2];
+  int mod_dtype;        /* of gate, shift, scale */
+  int64_t mod_batch_stride;
+  float eps;
+  void* push_dst[MFX_TP_MAX_WORLD]; /* on rank r: bf16 [batch, seq_pad, D] */
+  int* ag_flags[MFX_TP_MAX_WORLD];  /* on rank r: the counter this rank bumps */
+  int* done_counter;    /* local int, zero between calls */
+} mfx_tp_fuse_args;
+int mfx_tp_fuse(const mfx_tp_fuse_args* args /* host */, void* stream);
+/* Enqueues a wait until flags[r] >= target + (epoch_base ? *epoch_base : 0) for r < world (local counters that
+ * peers bump). The wait is bounded: after about a second it gives up and mfx_poll_device_status reports it. */
+int mfx_tp_wait(const int* flags, int world, int target, const int* epoch_base, void* stream);
 
 /* Replaces nn.LayerNorm(affine=False, eps)(x) * (1 + scale) + shift
  * (src/mflux/models/flux/model/flux_transformer/ada_layer_norm_zero.py:20, ada_layer_norm_zero_single.py:17,

@@ -18,10 +18,57 @@ F32, BF16, F16 = 0, 1, 2
 # mfx_qmode
 QMODE_MLX, QMODE_DOC = 0, 1
 # mfx_epilogue
-EPI_NONE, EPI_GELU_ERF, EPI_GELU_TANH, EPI_GATE_RESIDUAL, EPI_SILU, EPI_SWIGLU = 0, 1, 2, 3, 4, 5
+EPI_NONE, EPI_GELU_ERF, EPI_GELU_TANH, EPI_GATE_RESIDUAL, EPI_SILU, EPI_SWIGLU, EPI_PEER_SCATTER = 0, 1, 2, 3, 4, 5, 6
+TP_MAX_WORLD = 8
 
 _VALUE_ERRORS = {-1, -2, -3, -4, -7, -9}
 STATIC_SCRATCH_BYTES = 32 * 1024 * 1024
+
+
+class TpScatter(ctypes.Structure):
+    """struct mfx_tp_scatter (include/mfx.h)."""
+
+    _fields_ = [
+        ("world", c_int),
+        ("rank", c_int),
+        ("rows_per_rank", c_int64),
+        ("row_offset", c_int64),
+        ("D", c_int64),
+        ("dst", c_void_p * TP_MAX_WORLD),
+        ("flags", c_void_p * TP_MAX_WORLD),
+        ("done_counter", c_void_p),
+    ]
+
+
+class TpFuseArgs(ctypes.Structure):
+    """struct mfx_tp_fuse_args (include/mfx.h)."""
+
+    _fields_ = [
+        ("world", c_int),
+        ("rank", c_int),
+        ("batch", c_int64),
+        ("rows_per_rank", c_int64),
+        ("seq_pad", c_int64),
+        ("seq", c_int64),
+        ("split", c_int64),
+        ("D", c_int64),
+        ("x", c_void_p),
+        ("partials", c_void_p),
+        ("rs_flags", c_void_p),
+        ("rs_target", c_int),
+        ("epoch_base", c_void_p),
+        ("bias", c_void_p * 2),
+        ("bias_dtype", c_int),
+        ("gate", c_void_p * 2),
+        ("shift", c_void_p * 2),
+        ("scale", c_void_p * 2),
+        ("mod_dtype", c_int),
+        ("mod_batch_stride", c_int64),
+        ("eps", ctypes.c_float),
+        ("push_dst", c_void_p * TP_MAX_WORLD),
+        ("ag_flags", c_void_p * TP_MAX_WORLD),
+        ("done_counter", c_void_p),
+    ]
 
 
 class QLinearArgs(ctypes.Structure):
@@ -63,6 +110,7 @@ class QLinearArgs(ctypes.Structure):
         ("lora_b", c_void_p),
         ("lora_ld", c_int64),
         ("lora_r", c_int64),
+        ("scatter", ctypes.POINTER(TpScatter)),
     ]
 
 
@@ -169,6 +217,8 @@ SIGNATURES = {
         [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, ctypes.c_float, c_void_p, c_int64,
          c_void_p, c_int64, c_int64, c_void_p],
     ),
+    "mfx_tp_fuse": (c_int, [ctypes.POINTER(TpFuseArgs), c_void_p]),
+    "mfx_tp_wait": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "mfx_vec_sum_act": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int64, c_void_p]),
     "mfx_gate_residual": (
         c_int,

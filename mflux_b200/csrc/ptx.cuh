@@ -155,6 +155,17 @@ __device__ __forceinline__ void umma_f16_ss_pair(uint32_t d_tmem, uint64_t a_des
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Same with the A operand (this CTA's 128 rows) read from tensor memory: 2 x bf16 along K per 32-bit cell, 8 cells
+// per K = 16 step; each CTA's tensor core reads its own tensor memory at `a_tmem`.
+__device__ __forceinline__ void umma_f16_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // The barrier at this offset in BOTH CTAs of the pair gets one arrival once all MMAs issued so far are done.
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
   asm volatile(

@@ -24,9 +24,13 @@
 #include <cuda_fp16.h>
 
 #include <mutex>
+#include <stdlib.h>
+#include <string.h>
 
 #include "host_util.cuh"
 #include "ptx.cuh"
+#include "qmm_common.cuh"
+#include "qmm_t.cuh"
 #include "qmv.cuh"
 
 namespace mfx {
@@ -85,60 +89,6 @@ struct Smem {
   static constexpr int DYN_BYTES = TOTAL + 1024;  // slack for manual 1024-byte alignment
 };
 
-__device__ __forceinline__ float load_scalar(const void* p, int dtype, int64_t i) {
-  if (dtype == MFX_F32) return __ldg(static_cast<const float*>(p) + i);
-  if (dtype == MFX_BF16) return __bfloat162float(__ldg(static_cast<const __nv_bfloat16*>(p) + i));
-  return __half2float(__ldg(static_cast<const __half*>(p) + i));
-}
-
-// d = (a - magic) * s + b on packed 16-bit pairs: the subtraction is exact (small integers),
-// the fma rounds once.
-__device__ __forceinline__ uint32_t sub_fma(uint32_t a, uint32_t magic, uint32_t s, uint32_t b) {
-  uint32_t d;
-  asm("{\n\t.reg .b32 t;\n\t"
-      "sub.rn.bf16x2 t, %1, %2;\n\t"
-      "fma.rn.bf16x2 %0, t, %3, %4;\n\t}"
-      : "=r"(d)
-      : "r"(a), "r"(magic), "r"(s), "r"(b));
-  return d;
-}
-
-// 8 four-bit codes of one prepared uint32 (nibble order e0,e2,e4,e6,e1,e3,e5,e7) -> 8 values in K order:
-// nibble j lands in the low half and nibble 4+j in the high half of one masked word.
-__device__ __forceinline__ uint4 dequant_w4(uint32_t q, uint32_t s2, uint32_t b2) {
-  constexpr uint32_t MAGIC = 0x43004300u;  // bf16 128.0 twice: ulp 1 up to 255
-  uint4 r;
-  r.x = sub_fma((q & 0x000F000Fu) | MAGIC, MAGIC, s2, b2);          // (e0, e1)
-  r.y = sub_fma(((q >> 4) & 0x000F000Fu) | MAGIC, MAGIC, s2, b2);   // (e2, e3)
-  r.z = sub_fma(((q >> 8) & 0x000F000Fu) | MAGIC, MAGIC, s2, b2);   // (e4, e5)
-  r.w = sub_fma(((q >> 12) & 0x000F000Fu) | MAGIC, MAGIC, s2, b2);  // (e6, e7)
-  return r;
-}
-
-// 4 eight-bit codes of one prepared uint32 (byte order e0,e2,e1,e3) -> 4 values in K order, through float32:
-// a byte placed under the exponent of 2^23 is the float 2^23 + code exactly; subtracting 2^23 and one fma with
-// the group's scale and bias (packed f32x2 instructions) give the value, rounded once more when packed to bf16.
-// sc2 / bi2 are (scale, scale) / (bias, bias) as float32 pairs.
-__device__ __forceinline__ uint2 dequant_w8_f32(uint32_t q, uint64_t sc2, uint64_t bi2) {
-  constexpr uint32_t TWO23 = 0x4B000000u;
-  const uint64_t neg = 0xCB000000CB000000ull;  // (-2^23, -2^23)
-  uint64_t v01, v23;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(v01) : "r"(__byte_perm(q, TWO23, 0x7440)), "r"(__byte_perm(q, TWO23, 0x7442)));
-  asm("mov.b64 %0, {%1, %2};" : "=l"(v23) : "r"(__byte_perm(q, TWO23, 0x7441)), "r"(__byte_perm(q, TWO23, 0x7443)));
-  asm("add.rn.f32x2 %0, %0, %1;" : "+l"(v01) : "l"(neg));
-  asm("add.rn.f32x2 %0, %0, %1;" : "+l"(v23) : "l"(neg));
-  asm("fma.rn.f32x2 %0, %0, %1, %2;" : "+l"(v01) : "l"(sc2), "l"(bi2));
-  asm("fma.rn.f32x2 %0, %0, %1, %2;" : "+l"(v23) : "l"(sc2), "l"(bi2));
-  float a, b, c, d;
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v01));
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(c), "=f"(d) : "l"(v23));
-  const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
-  uint2 r;
-  r.x = *reinterpret_cast<const uint32_t*>(&lo);
-  r.y = *reinterpret_cast<const uint32_t*>(&hi);
-  return r;
-}
-
 // Tile order. The weight rows are cut into bands of band_n n-tiles whose packed codes, scales and biases fit in
 // L2 together; inside a band the tiles run m-tile by m-tile with the n-tile index fastest. The pairs that run at
 // the same time then share one or two activation tiles (read from HBM once per band) and sweep a band of weights
@@ -152,15 +102,6 @@ __device__ __forceinline__ void tile_coords(const Params& p, int tile, int& tm, 
   tm = r / width;
   tn = n_first + r - tm * width;
 }
-
-// Out of line on purpose: the epilogue runs beside the main loop of the next tile; a 32-fold unrolled inline
-// erf/tanh body would crowd the small hot loops of the other warps out of the instruction cache.
-__device__ __noinline__ float gelu_erf(float v) { return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f)); }
-__device__ __noinline__ float gelu_tanh(float v) {
-  const float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
-  return 0.5f * v * (1.0f + tanhf(u));
-}
-__device__ __forceinline__ float silu(float v) { return v / (1.0f + __expf(-v)); }
 
 // EXT compiles the low-rank extension stages in; without it the loops below are the plain quantized matmul.
 template <int BITS, uint32_t WF, int ST, int SD, typename OUT, int EPI, int NUM_DQ_WARPS, bool EXT>
@@ -747,16 +688,37 @@ int prepare(const uint32_t* wq, const void* scales, const void* biases, int sb_d
   return MFX_OK;
 }
 
+// The kernel of qmm_t.cu (weights as the tensor-memory operand) serves every call without a low-rank term unless
+// the environment says MFX_QMM_KERNEL=smem (kept for side-by-side timing of the two kernels).
+static bool tmem_operand_kernel() {
+  static const bool on = [] {
+    const char* v = getenv("MFX_QMM_KERNEL");
+    return !(v && strcmp(v, "smem") == 0);
+  }();
+  return on;
+}
+
 int run(const mfx_qlinear_args& a, cudaStream_t st) {
-  if (!a.x || !a.y) return MFX_ERR_NULL;
+  const bool scatter = a.epilogue == MFX_EPI_PEER_SCATTER;
+  if (!a.x || (!a.y && !scatter)) return MFX_ERR_NULL;
   if (!valid_bits(a.bits) || a.group_size != 64) return MFX_ERR_UNSUPPORTED_BITS;
   const int kb = kernel_bits(a.bits);   // width of the prepared codes: 4 (from 3 or 4) or 8 (from 5, 6 or 8)
   if (a.rows <= 0 || a.batch <= 0 || a.N <= 0 || a.K <= 0) return MFX_ERR_SHAPE;
   if (a.K % 64 != 0 || a.N % 8 != 0) return MFX_ERR_SHAPE;
   if (a.rows > (1 << 30) || a.N > (1 << 30) || a.K > (1 << 30) || a.batch > (1 << 20)) return MFX_ERR_TOO_LARGE;
   if (a.bias && !valid_dtype(a.bias_dtype)) return MFX_ERR_DTYPE;
-  if (a.y_dtype != MFX_BF16 && a.y_dtype != MFX_F32) return MFX_ERR_DTYPE;
-  if (a.epilogue < MFX_EPI_NONE || a.epilogue > MFX_EPI_SWIGLU) return MFX_ERR_SHAPE;
+  if (!scatter && a.y_dtype != MFX_BF16 && a.y_dtype != MFX_F32) return MFX_ERR_DTYPE;
+  if (a.epilogue < MFX_EPI_NONE || a.epilogue > MFX_EPI_PEER_SCATTER) return MFX_ERR_SHAPE;
+  if (scatter) {
+    const mfx_tp_scatter* sc = a.scatter;
+    if (!sc || !sc->done_counter) return MFX_ERR_NULL;
+    if (sc->world < 1 || sc->world > MFX_TP_MAX_WORLD || sc->rank < 0 || sc->rank >= sc->world) return MFX_ERR_SHAPE;
+    if (sc->rows_per_rank <= 0 || sc->row_offset < 0 || sc->D != a.N) return MFX_ERR_SHAPE;
+    if (sc->row_offset + a.rows > sc->rows_per_rank * sc->world) return MFX_ERR_SHAPE;
+    for (int r = 0; r < sc->world; ++r)
+      if (!sc->dst[r] || !sc->flags[r]) return MFX_ERR_NULL;
+    if (a.lora_r > 0 || !tmem_operand_kernel()) return MFX_ERR_SHAPE;   // only the tensor-memory kernel scatters
+  }
   if (a.epilogue == MFX_EPI_SWIGLU && a.N % 16 != 0) return MFX_ERR_SHAPE;
   const void* prepared = a.prepared;
   if (!prepared) {
@@ -774,7 +736,7 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
   }
   {
     const size_t es = dtype_size(a.y_dtype);
-    if (!aligned16(a.y) || (a.y_row_stride * es) % 16 != 0 || (a.y_batch_stride * es) % 16 != 0)
+    if (!scatter && (!aligned16(a.y) || (a.y_row_stride * es) % 16 != 0 || (a.y_batch_stride * es) % 16 != 0))
       return MFX_ERR_ALIGN;
     if (!aligned16(a.x) || (a.x_row_stride * 2) % 16 != 0 || (a.x_batch_stride * 2) % 16 != 0) return MFX_ERR_ALIGN;
   }
@@ -794,7 +756,8 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
       return rc;
     prepared = a.workspace;
   }
-  if (!low_rank && qmv::eligible(a)) return qmv::run(a, prepared, codes_bytes_padded(a.N, a.K, a.bits), st);
+  if (!low_rank && !scatter && qmv::eligible(a)) return qmv::run(a, prepared, codes_bytes_padded(a.N, a.K, a.bits), st);
+  if (!low_rank && tmem_operand_kernel()) return qmmt::run(a, prepared, codes_bytes_padded(a.N, a.K, a.bits), st);
   const void* codes = prepared;
   const void* sb_packed = static_cast<const uint8_t*>(prepared) + codes_bytes_padded(a.N, a.K, a.bits);
 

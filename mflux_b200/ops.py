@@ -7,6 +7,7 @@ live on a CUDA device and the library must be built.
 from __future__ import annotations
 
 from ctypes import byref, c_int, c_void_p
+from ctypes import pointer as ctypes_pointer
 
 import torch
 
@@ -154,7 +155,7 @@ def qlinear(x: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, biases: tor
             gate: torch.Tensor | None = None, residual: torch.Tensor | None = None,
             out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
             prepared: torch.Tensor | None = None, lora_t: torch.Tensor | None = None,
-            lora_b: torch.Tensor | None = None, lora_r: int = 0) -> torch.Tensor:
+            lora_b: torch.Tensor | None = None, lora_r: int = 0, scatter=None) -> torch.Tensor:
     """nn.QuantizedLinear.__call__: y[..., N] = x[..., K] . dequant(wq)^T + bias, with optional fused epilogue.
 
     Low-rank term (LoRA adapters over the frozen layer): with `lora_t` [..., ld] (= x @ A, same leading shape as
@@ -167,6 +168,9 @@ def qlinear(x: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, biases: tor
     epilogue "swiglu" returns silu(y[..., 0::2]) * y[..., 1::2], N/2 wide (rows of the gate and up
     projections interleaved by the caller). `prepared` is the cached result of
     prepare_qlinear(wq, scales, biases); without it the weight is prepared into a scratch tensor on every call.
+    `scatter` (a _lib.TpScatter) turns the call into the producer half of a tensor-parallel reduce-scatter: the
+    bf16 product, without bias, goes row by row into the partial-sum slots of the ranks that own the rows; nothing
+    is returned.
     """
     lib = _lib.load()
     _cuda(x, "x")
@@ -185,6 +189,25 @@ def qlinear(x: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, biases: tor
         workspace = torch.empty(lib.mfx_qlinear_prepared_bytes(n, k, bits, group_size), dtype=torch.uint8,
                                 device=x.device)
     n_out = n // 2 if _EPI[epilogue] == EPI_SWIGLU else n
+    if scatter is not None:
+        a = QLinearArgs()
+        a.x, a.x_row_stride, a.x_batch_stride = xv.data_ptr(), x_rs, x_bs
+        a.rows, a.batch, a.K, a.N = rows, batch, k, n
+        a.bits, a.group_size = bits, group_size
+        if prepared is None:
+            raise ValueError("the scatter epilogue needs a prepared weight")
+        a.prepared = prepared.data_ptr()
+        a.epilogue, a.y_dtype = _lib.EPI_PEER_SCATTER, BF16
+        a.scatter = ctypes_pointer(scatter)
+        if TRACE is not None:
+            _trace_begin()
+        _lib.check(lib.mfx_qlinear_ex(byref(a), _stream()), "mfx_qlinear_ex")
+        if TRACE is not None:
+            m = rows * batch
+            _trace_end("qlinear", 2.0 * m * n * k, n * k * bits / 8 + 4.0 * n * (k // group_size) + 2.0 * m * k
+                       + 2.0 * m * n)
+        LAUNCHES[0] += 1
+        return None
     if out is None:
         od = out_dtype or (residual.dtype if residual is not None else torch.bfloat16)
         out = torch.empty((*xv.shape[:-1], n_out), dtype=od, device=x.device)
@@ -545,3 +568,26 @@ def norm_gate_residual(y: torch.Tensor, weight: torch.Tensor, residual: torch.Te
         _trace_end("glue", 0.0, float(rows * batch * d * (yv.element_size() + 8 + (2 if next_out is not None else 0))))
     LAUNCHES[0] += 1
     return residual
+
+
+def tp_fuse(args) -> None:
+    """mfx_tp_fuse on a filled _lib.TpFuseArgs: reduce-scatter consumer + gated residual + modulated LayerNorm +
+    all-gather producer on the rows this rank owns (see include/mfx.h)."""
+    lib = _lib.load()
+    if TRACE is not None:
+        _trace_begin()
+    _lib.check(lib.mfx_tp_fuse(byref(args), _stream()), "mfx_tp_fuse")
+    if TRACE is not None:
+        rows = args.batch * args.rows_per_rank
+        nbytes = rows * args.D * (8 + (2 * args.world if args.partials else 0) + (2 * args.world if args.scale[0] else 0))
+        _trace_end("glue", 0.0, float(nbytes))
+    LAUNCHES[0] += 1
+
+
+def tp_wait(flags: torch.Tensor, world: int, target: int, epoch_base: torch.Tensor | None = None) -> None:
+    """Enqueues a bounded wait until the local counters flags[0:world] (int32, bumped by the peers) reach
+    target (+ the device int epoch_base[0] when given)."""
+    lib = _lib.load()
+    _cuda(flags, "flags")
+    _lib.check(lib.mfx_tp_wait(_ptr(flags), world, int(target), _ptr(epoch_base), _stream()), "mfx_tp_wait")
+    LAUNCHES[0] += 1

@@ -122,12 +122,16 @@ class QwenTimeTextEmbed(nn.Module):
 
 class QwenTransformer(nn.Module):
     def __init__(self, cfg: QwenConfig = QwenConfig(), bits: int | None = 4, device="cuda", std: float = 0.02,
-                 seed: int = 0, mode: str = "mlx", tp_rank: int = 0, tp_world: int = 1, tp_group=None):
+                 seed: int = 0, mode: str = "mlx", tp_rank: int = 0, tp_world: int = 1, tp_group=None,
+                 tp_mode: str = "peer"):
         super().__init__()
         if cfg.heads % tp_world != 0:
             raise ValueError("the number of heads must be divisible by the tensor-parallel size")
+        if tp_mode not in ("peer", "nccl"):
+            raise ValueError("tp_mode is 'peer' (fused exchange over peer-mapped memory) or 'nccl' (all-reduce)")
         self.cfg, self.bits = cfg, bits
-        self.tp_rank, self.tp_world, self.tp_group = tp_rank, tp_world, tp_group
+        self.tp_rank, self.tp_world, self.tp_group, self.tp_mode = tp_rank, tp_world, tp_group, tp_mode
+        self._exchange = {}
         ctx = _Ctx(device, bits, std, seed, mode, tp_rank, tp_world)
         d = cfg.hidden
         self.img_in = ctx.linear(cfg.in_channels, d)
@@ -249,6 +253,9 @@ class QwenTransformer(nn.Module):
         -1e9 in every block's attention, image keys 0. None means all ones, which the reference drops as well
         (:131-132); a caller that knows its mask is all ones should pass None, the masked kernel does more work."""
         cfg = self.cfg
+        if self.tp_world > 1 and self.tp_mode == "peer":
+            return self._forward_peer(hidden_states, encoder_hidden_states, timestep, height, width,
+                                      encoder_hidden_states_mask)
         d, heads = cfg.hidden, cfg.heads // self.tp_world
         b, si, _ = hidden_states.shape
         st = encoder_hidden_states.shape[1]
@@ -301,6 +308,110 @@ class QwenTransformer(nn.Module):
         return _call(self.proj_out, n_img)
 
 
+def _forward_peer(self, hidden_states, encoder_hidden_states, timestep, height, width, encoder_hidden_states_mask):
+    """The tensor-parallel forward with the exchange fused into this library's kernels (see tp.py).
+
+    Every rank keeps the residual stream of the joint-sequence rows it owns only. Per block:
+      all ranks hold n1 (normalised rows of the whole sequence, gathered by peer stores)
+      q/k/v (column split) -> attention over this rank's heads -> attn_to_out / to_add_out (row split): the matmul
+      epilogue scatters every partial row to its owner -> tp_fuse on the owned rows: sum of the partials + bias,
+      gated residual, second modulated LayerNorm, result stored into every rank's copy of the sequence ->
+      mlp_in (column split, GELU) -> mlp_out (row split, scattered) -> tp_fuse with the next block's first norm.
+    Linears, attention and the arithmetic per row are those of the one-GPU path; only the order of the bf16
+    partial sums differs (they are rounded to bf16 per rank before they are added, as in the all-reduce path)."""
+    from .tp import PeerExchange
+
+    cfg = self.cfg
+    d, heads = cfg.hidden, cfg.heads // self.tp_world
+    b, si, _ = hidden_states.shape
+    st = encoder_hidden_states.shape[1]
+    s = st + si
+    dev = hidden_states.device
+    key = (b, st, si, str(dev))
+    ex = self._exchange.get(key)
+    if ex is None:
+        ex = self._exchange[key] = PeerExchange(self.tp_group, self.tp_rank, self.tp_world, b, s, st, d, dev)
+    sp = ex.seq_pad
+    if getattr(self, "_peer_buffers_for", None) != key:
+        tp, r = self.tp_world, cfg.mlp_ratio
+        self.joint = torch.zeros(b, sp, d, dtype=torch.float32, device=dev)       # embeddings before the split
+        self.qkv = torch.zeros(b, sp, 3 * d // tp, dtype=torch.bfloat16, device=dev)
+        self.attn = torch.zeros(b, sp, d // tp, dtype=torch.bfloat16, device=dev)
+        self.ffb = torch.zeros(b, sp, r * d // tp, dtype=torch.bfloat16, device=dev)
+        self._peer_buffers_for = key
+    joint, qkv, attn, ffb, nbuf = self.joint, self.qkv, self.attn, self.ffb, ex.nbuf
+    cos_sin = self.rope_table(height, width, st, dev)
+    key_bias = None
+    if encoder_hidden_states_mask is not None:
+        key_bias = torch.zeros(b, s, dtype=torch.float32, device=dev)
+        key_bias[:, :st] = (1.0 - encoder_hidden_states_mask.to(dev, torch.float32)) * -1e9
+
+    # embeddings (small, replicated), then every rank keeps its own rows
+    _call(self.img_in, hidden_states.to(torch.bfloat16), out=joint[:, st:s])
+    tn = ops.norm_modulate(encoder_hidden_states.to(torch.bfloat16), weight=self.txt_norm.weight.data,
+                           eps=self.txt_norm.eps, rms=True)
+    _call(self.txt_in, tn, out=joint[:, :st])
+    ex.x.copy_(joint[:, ex.lo:ex.lo + ex.rows])
+    temb = self.time_text_embed.timestep_embedder(self.time_proj(timestep).to(torch.bfloat16))
+    sv = ops.vec_sum_act(temb, act="silu", out_dtype=torch.bfloat16)
+
+    def mods(blk):
+        return _call(blk.txt_mod_linear, sv), _call(blk.img_mod_linear, sv)   # [B, 6D] each: (shift, scale, gate) x 2
+
+    def ch(m, j):
+        return m[:, j * d:(j + 1) * d]
+
+    def scattered(layer, x, row_offset):
+        ops.qlinear(x, layer.weight.data, None, None, None, bits=layer.bits, prepared=layer.prepared(),
+                    scatter=ex.scatter(row_offset))
+
+    ex.begin()
+    blocks = list(self.transformer_blocks)
+    mt, mi = mods(blocks[0])
+    ex.fuse(reduce=False, shift=(ch(mt, 0), ch(mi, 0)), scale=(ch(mt, 1), ch(mi, 1)))
+    for i, blk in enumerate(blocks):
+        a = blk.attn
+        ex.wait_gathered()
+        self._fuse(("q", i), [a.to_q, a.to_k, a.to_v])(nbuf[:, st:s], qkv[:, st:s])
+        self._fuse(("a", i), [a.add_q_proj, a.add_k_proj, a.add_v_proj])(nbuf[:, :st], qkv[:, :st])
+        ops.qknorm_rope(qkv[:, :s], heads, a.norm_added_q.weight.data, a.norm_added_k.weight.data,
+                        a.norm_q.weight.data, a.norm_k.weight.data, st, cos_sin, a.norm_q.eps)
+        ops.fmha(qkv[:, :s], heads, out=attn[:, :s], key_bias=key_bias)
+        scattered(a.attn_to_out[0], attn[:, st:s], st)
+        scattered(a.to_add_out, attn[:, :st], 0)
+        ex.fuse(reduce=True, bias=(a.to_add_out.bias, a.attn_to_out[0].bias), gate=(ch(mt, 2), ch(mi, 2)),
+                shift=(ch(mt, 3), ch(mi, 3)), scale=(ch(mt, 4), ch(mi, 4)))
+        ex.wait_gathered()
+        _call(blk.img_ff.mlp_in, nbuf[:, st:s], epilogue="gelu_approx", out=ffb[:, st:s])
+        _call(blk.txt_ff.mlp_in, nbuf[:, :st], epilogue="gelu_approx", out=ffb[:, :st])
+        scattered(blk.img_ff.mlp_out, ffb[:, st:s], st)
+        scattered(blk.txt_ff.mlp_out, ffb[:, :st], 0)
+        gate = (ch(mt, 5), ch(mi, 5))
+        bias = (blk.txt_ff.mlp_out.bias, blk.img_ff.mlp_out.bias)
+        if i + 1 < len(blocks):
+            mt, mi = mods(blocks[i + 1])       # the next block's first norm rides on this exchange
+            ex.fuse(reduce=True, bias=bias, gate=gate, shift=(ch(mt, 0), ch(mi, 0)), scale=(ch(mt, 1), ch(mi, 1)))
+        else:
+            ex.fuse(reduce=True, bias=bias, gate=gate)
+        if self.trace is not None:
+            self.trace[f"block{i}"] = ex.x.clone()    # this rank's rows of the joint stream
+    ex.end()
+
+    # output head on the owned rows, then the ranks' pieces are put together (a few hundred kilobytes)
+    mod = _call(self.norm_out.linear, sv)   # [B, 2D]: scale, shift
+    own = torch.zeros(b, ex.rows, cfg.in_channels, dtype=torch.bfloat16, device=dev)
+    n_live = max(0, ex.hi - ex.lo)
+    if n_live > 0:
+        nrm = ops.norm_modulate(ex.x[:, :n_live], mod[:, d:2 * d], mod[:, 0:d])
+        _call(self.proj_out, nrm, out=own[:, :n_live])
+    parts = torch.empty(self.tp_world, b, ex.rows, cfg.in_channels, dtype=torch.bfloat16, device=dev)
+    dist.all_gather_into_tensor(parts, own, group=self.tp_group)
+    return parts.permute(1, 0, 2, 3).reshape(b, sp, cfg.in_channels)[:, st:s].contiguous()
+
+
+QwenTransformer._forward_peer = _forward_peer
+
+
 class QwenImage:
     """Denoise loop of the reference's QwenImage variant (variants/txt2img/qwen_image.py:99-128,165-174):
     two denoiser evaluations per step (prompt and negative prompt) and the norm-preserving guidance combine.
@@ -312,7 +423,8 @@ class QwenImage:
 
     def __init__(self, quantize: int | None = None, model_config: QwenConfig | None = None, device="cuda",
                  seed: int = 0, stored_quantization: int | None = None, tp_rank: int = 0, tp_world: int = 1,
-                 tp_group=None, cfg_rank: int | None = None, cfg_group=None, cuda_graph: bool = False):
+                 tp_group=None, cfg_rank: int | None = None, cfg_group=None, cuda_graph: bool = False,
+                 tp_mode: str = "peer"):
         bits, warning = resolution.resolve(stored_quantization, quantize)
         if warning:
             print(f"Warning: {warning}")
@@ -322,7 +434,7 @@ class QwenImage:
         self.cfg_rank, self.cfg_group = cfg_rank, cfg_group
         self.cuda_graph, self._captured, self._captured_epoch = cuda_graph, {}, nn.weights_epoch()
         self.transformer = QwenTransformer(self.model_config, bits=bits, device=device, seed=seed, tp_rank=tp_rank,
-                                           tp_world=tp_world, tp_group=tp_group)
+                                           tp_world=tp_world, tp_group=tp_group, tp_mode=tp_mode)
 
     def save_model(self, base_path: str) -> None:
         """ModelSaver.save_model for the component this class owns: `<base_path>/transformer/{i}.safetensors` plus

@@ -1,4 +1,5 @@
 """The C-ABI library builds for sm_100a, loads without a GPU and exports every declared symbol."""
+import ctypes
 import re
 from pathlib import Path
 
@@ -75,8 +76,36 @@ def test_validation_of_the_later_entry_points(lib_built):
     a.x_row_stride, a.y_row_stride, a.y_dtype = 128, 24, _lib.BF16
     a.epilogue = _lib.EPI_SWIGLU
     assert lib.mfx_qlinear_ex(a, None) == -1          # N = 24 is not a multiple of 16
-    a.epilogue = 6
+    a.epilogue = 7
     assert lib.mfx_qlinear_ex(a, None) == -1          # unknown epilogue
+    a.epilogue = _lib.EPI_PEER_SCATTER
+    assert lib.mfx_qlinear_ex(a, None) == -7          # tensor-parallel scatter without its descriptor
+    sc = _lib.TpScatter()
+    sc.world, sc.rank, sc.rows_per_rank, sc.D, sc.done_counter = 2, 0, 64, 24, 1024
+    a.scatter = ctypes.pointer(sc)
+    assert lib.mfx_qlinear_ex(a, None) == -7          # destination tables empty
+    for r in range(2):
+        sc.dst[r], sc.flags[r] = 1024, 1024
+    sc.D = 32
+    assert lib.mfx_qlinear_ex(a, None) == -1          # partial rows as wide as N
+    sc.D, sc.rank = 24, 2
+    assert lib.mfx_qlinear_ex(a, None) == -1          # rank outside the world
+    sc.rank, sc.row_offset = 0, 64
+    assert lib.mfx_qlinear_ex(a, None) == -1          # rows past the end of the joint sequence
+    a.scatter = None
+    f = _lib.TpFuseArgs()
+    assert lib.mfx_tp_fuse(None, None) == -7
+    assert lib.mfx_tp_fuse(f, None) == -1             # empty world
+    f.world, f.rank, f.batch, f.rows_per_rank, f.seq_pad, f.seq, f.split, f.D = 2, 0, 1, 64, 128, 100, 20, 256
+    assert lib.mfx_tp_fuse(f, None) == -7             # no residual rows
+    f.x = f.done_counter = 1024
+    f.mod_dtype = _lib.BF16
+    f.seq = 129
+    assert lib.mfx_tp_fuse(f, None) == -1             # more rows than the padded sequence
+    f.seq, f.partials = 100, 1024
+    assert lib.mfx_tp_fuse(f, None) == -7             # partial sums without gates
+    assert lib.mfx_tp_wait(None, 2, 1, None, None) == -7
+    assert lib.mfx_tp_wait(1024, 9, 1, None, None) == -1    # more ranks than MFX_TP_MAX_WORLD
     # low-rank term of the quantized matmul
     a.epilogue, a.N, a.y_row_stride = _lib.EPI_NONE, 64, 64
     a.lora_r = 8

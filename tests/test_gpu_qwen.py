@@ -122,6 +122,10 @@ def test_tensor_parallel_matches_single_gpu(lib_built, tmp_path):
     assert cfg_err <= 2e-3, cfg_err
     graph_err = float((tmp_path / "graph_err.txt").read_text())
     assert graph_err <= 1e-5, graph_err
+    # exchange fused into the kernels (peer stores): same tolerance, repeatable, masked attention included
+    assert float((tmp_path / "peer_err.txt").read_text()) <= TOL
+    assert (tmp_path / "peer_repeat.txt").read_text() == "True"
+    assert float((tmp_path / "peer_masked_err.txt").read_text()) <= TOL
 
 
 def test_masked_step_matches_oracle(lib_built):

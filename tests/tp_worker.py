@@ -23,14 +23,28 @@ def main():
     lat = torch.randn(2, 6 * 9, 64, generator=g).cuda()
     ctx = torch.randn(2, 40, 128, generator=g).to(torch.bfloat16).cuda()
     sigma = torch.tensor([0.9, 0.3]).cuda()
-    tp = QwenTransformer(cfg, bits=4, device="cuda", seed=5, tp_rank=rank, tp_world=world)
+    tp = QwenTransformer(cfg, bits=4, device="cuda", seed=5, tp_rank=rank, tp_world=world, tp_mode="nccl")
     tp.tp_chunks, tp.tp_chunk_min_rows = 3, 8   # 54 image rows in 3 chunks, 40 text rows in 3: the overlapped path
     y_tp = tp(lat, ctx, sigma, 96, 144).float()
+    # the exchange fused into the matmul epilogue and the norm kernel (peer stores): 94 joint rows, 47 per rank,
+    # so rank 0 owns all text rows and the first image rows; two passes, the second on advanced counters
+    peer = QwenTransformer(cfg, bits=4, device="cuda", seed=5, tp_rank=rank, tp_world=world, tp_mode="peer")
+    y_peer = peer(lat, ctx, sigma, 96, 144).float()
+    y_peer2 = peer(lat, ctx, sigma, 96, 144).float()
+    mask = torch.ones(2, 40, device="cuda")
+    mask[1, 29:] = 0.0
+    y_peer_masked = peer(lat, ctx, sigma, 96, 144, encoder_hidden_states_mask=mask).float()
     torch.cuda.synchronize()
+    from mflux_b200 import ops
+    status = ops.poll_device_status()
     if rank == 0:
         one = QwenTransformer(cfg, bits=4, device="cuda", seed=5)
         y1 = one(lat, ctx, sigma, 96, 144).float()
         (out_dir / "tp_err.txt").write_text(str(rel_l2(y_tp, y1.cpu().numpy())))
+        (out_dir / "peer_err.txt").write_text(str(rel_l2(y_peer, y1.cpu().numpy())))
+        (out_dir / "peer_repeat.txt").write_text(str(int(torch.equal(y_peer, y_peer2)) and status == 0))
+        y1m = one(lat, ctx, sigma, 96, 144, encoder_hidden_states_mask=mask).float()
+        (out_dir / "peer_masked_err.txt").write_text(str(rel_l2(y_peer_masked, y1m.cpu().numpy())))
     # guidance-branch parallelism: rank 0 evaluates the prompt, rank 1 the negative prompt, one all-gather per step
     neg = torch.randn(2, 40, 128, generator=g).to(torch.bfloat16).cuda()
     split = QwenImage(quantize=4, model_config=cfg, seed=5, cfg_rank=rank, cfg_group=dist.group.WORLD)
@@ -42,19 +56,21 @@ def main():
         (out_dir / "cfg_err.txt").write_text(str(rel_l2(z_split, z.cpu().numpy())))
     # the tensor-parallel step (chunked all-reduces included) replayed as a CUDA graph equals the same step issued
     # launch by launch, also for a noise level and latents the graph was not recorded with
-    eager = QwenImage(quantize=4, model_config=cfg, seed=5, tp_rank=rank, tp_world=world)
-    graphed = QwenImage(quantize=4, model_config=cfg, seed=5, tp_rank=rank, tp_world=world, cuda_graph=True)
-    for pipe in (eager, graphed):
-        pipe.transformer.tp_chunks, pipe.transformer.tp_chunk_min_rows = 3, 8
     worst = 0.0
-    for sig, scale in ((0.7, 1.0), (0.2, 0.5), (0.45, 2.0)):
-        z_e = eager.denoise_step(lat * scale, ctx, neg, sig, -0.05, 4.0, 96, 144)
-        z_g = graphed.denoise_step(lat * scale, ctx, neg, sig, -0.05, 4.0, 96, 144)
-        torch.cuda.synchronize()
-        worst = max(worst, rel_l2(z_g, z_e.cpu().numpy()))
+    for tp_mode in ("nccl", "peer"):
+        eager = QwenImage(quantize=4, model_config=cfg, seed=5, tp_rank=rank, tp_world=world, tp_mode=tp_mode)
+        graphed = QwenImage(quantize=4, model_config=cfg, seed=5, tp_rank=rank, tp_world=world, cuda_graph=True,
+                            tp_mode=tp_mode)
+        for pipe in (eager, graphed):
+            pipe.transformer.tp_chunks, pipe.transformer.tp_chunk_min_rows = 3, 8
+        for sig, scale in ((0.7, 1.0), (0.2, 0.5), (0.45, 2.0)):
+            z_e = eager.denoise_step(lat * scale, ctx, neg, sig, -0.05, 4.0, 96, 144)
+            z_g = graphed.denoise_step(lat * scale, ctx, neg, sig, -0.05, 4.0, 96, 144)
+            torch.cuda.synchronize()
+            worst = max(worst, rel_l2(z_g, z_e.cpu().numpy()))
+        graphed.release_graphs()   # a live graph with recorded collectives would keep the communicator from closing
     if rank == 0:
-        (out_dir / "graph_err.txt").write_text(str(worst))
-    graphed.release_graphs()   # a live graph with recorded collectives would keep the communicator from closing
+        (out_dir / "graph_err.txt").write_text(str(worst) if ops.poll_device_status() == 0 else "device status")
     dist.barrier()
     dist.destroy_process_group()
 
