@@ -471,9 +471,9 @@ def run_sweep(args, dev):
                     ops.qlinear(xs[i % copies], wq, None, None, bias, bits=bits, out=ys[i % copies], prepared=preps[i % copies])
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 torch.cuda.synchronize()
-                if m <= 16:
-                    # launches of a few microseconds: replay them from a CUDA graph so that the host's launch
-                    # rate is not what gets timed
+                if m <= 1024:
+                    # launches of a few (tens of) microseconds: replay them from a CUDA graph so that the host's
+                    # launch rate (the Python wrapper and three tensor-map encodings per call) is not what gets timed
                     graph = torch.cuda.CUDAGraph()
                     with torch.cuda.graph(graph):
                         launch_all()

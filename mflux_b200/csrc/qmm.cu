@@ -83,7 +83,7 @@ struct Smem {
   static constexpr int OFF_SB = OFF_WQ + ST * WQ_STAGE;
   static constexpr int OFF_VEC = OFF_SB + ST * SB_STAGE;  // bias[2][256] + gate[2][256] floats
   static constexpr int OFF_BAR = OFF_VEC + 4 * BN * 4;
-  static constexpr int NUM_BARS = 3 * ST + 2 * SD + 4;
+  static constexpr int NUM_BARS = 4 * ST + 2 * SD + 4;
   static constexpr int OFF_TMEM = OFF_BAR + NUM_BARS * 8;
   static constexpr int TOTAL = OFF_TMEM + 16;
   static constexpr int DYN_BYTES = TOTAL + 1024;  // slack for manual 1024-byte alignment
@@ -135,6 +135,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
   };
   auto acc_full = [&](int s) { return bar0 + 8u * (B0 + 2 * SD + s); };  // local
   auto acc_empty = [&](int s) { return bar0 + 8u * (B0 + 2 * SD + 2 + s); };  // leader
+  auto c_empty = [&](int s) { return bar0 + 8u * (B0 + 2 * SD + 4 + s); };    // local: codes of the stage were read
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::OFF_TMEM);
 
   const int warp = threadIdx.x >> 5;
@@ -153,8 +154,8 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     for (int s = 0; s < ST; ++s) {
       mbar_init(w_full(s), 1);
       mbar_init(x_full(s), 1);                  // the leader's expect_tx covers both CTAs' X tiles
-      // MMA commit (X tiles) + every local dequantizer warp (codes); the commit alone when unified
-      mbar_init(t_empty(s), UNIFIED ? 1 : 1 + NUM_DQ_WARPS);
+      mbar_init(t_empty(s), 1);              // MMA commit: the activation tile (and, unified, the B tile) is free
+      mbar_init(c_empty(s), NUM_DQ_WARPS);   // every local dequantizer warp has read the stage's codes
     }
     for (int s = 0; s < SD; ++s) {
       mbar_init(d_full(s), 2 * NUM_DQ_WARPS);   // the dequantizer warps of both CTAs
@@ -180,7 +181,11 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer (lane 0 issues)
+    // ------------------------------------------------------------ TMA producer of the activation tiles
+    // The activation tile of a stage is free only once the stage's MMAs are done, the packed codes as soon as the
+    // dequantizers have read them. Two producers with their own barriers let the codes (warp 2) run ahead of the
+    // activations, so that dequantizing stage s+1, s+2 overlaps the flight time of activation tile s instead of
+    // following it: with both on one barrier the chain TMA -> dequantize -> MMA -> commit bounded a stage.
     int st = 0;
     uint32_t ph = 0;
     bool ok = true;
@@ -189,34 +194,65 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
       tile_coords(p, tile, tm, tn);
       const int b = tm / p.tiles_m_per_sample;
       const int r0 = (tm % p.tiles_m_per_sample) * (2 * BM) + static_cast<int>(rank) * BM;
-      const int n0 = tn * BN + static_cast<int>(rank) * BN_HALF;
       for (int s = 0; s < num_all; ++s) {
-        if (!mbar_wait_sleep(t_empty(st), ph ^ 1u, DEV_TIMEOUT_TMA_EMPTY)) {
+        if (!mbar_wait(t_empty(st), ph ^ 1u, DEV_TIMEOUT_TMA_EMPTY)) {
           ok = false;
           break;
         }
         if (lane == 0) {
           if (rank == 0) mbar_arrive_expect_tx(x_full(st), 2 * L::X_STAGE);
+          if (!EXT || s < num_st) {
+#pragma unroll
+            for (int g = 0; g < GPS; ++g)   // beyond K on a ragged last stage: the loads return zeros
+              tma_load_3d_pair(x_s + st * L::X_STAGE + g * X_TILE_BYTES, &tmap_x, x_full(st), (s * GPS + g) * BK, r0,
+                               b);
+          } else {
+            // extension stage: the activation tile comes from t, whose first EXT_KG columns the tensor cores read
+#pragma unroll
+            for (int g = 0; g < GPS; ++g)
+              tma_load_3d_pair(x_s + st * L::X_STAGE + g * X_TILE_BYTES, &tmap_t, x_full(st),
+                               ((s - num_st) * GPS + g) * EXT_KG, r0, b);
+          }
+        }
+        __syncwarp();
+        if (++st == ST) {
+          st = 0;
+          ph ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 2) {
+    // ------------------------------------------------------------ TMA producer of the packed weights
+    int st = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    for (int tile = pair; tile < p.total_tiles && ok; tile += num_pairs) {
+      int tm, tn;
+      tile_coords(p, tile, tm, tn);
+      const int n0 = tn * BN + static_cast<int>(rank) * BN_HALF;
+      for (int s = 0; s < num_all; ++s) {
+        if (!mbar_wait(c_empty(st), ph ^ 1u, DEV_TIMEOUT_TMA_EMPTY)) {
+          ok = false;
+          break;
+        }
+        if (lane == 0) {
           mbar_arrive_expect_tx(w_full(st), L::WQ_STAGE + L::SB_STAGE);
           if (!EXT || s < num_st) {
 #pragma unroll
             for (int g = 0; g < GPS; ++g) {
-              const int kb = s * GPS + g;  // beyond K on a ragged last stage: the loads return zeros
+              const int kb = s * GPS + g;
               tma_load_2d(wq_s + st * L::WQ_STAGE + g * L::WQ_TILE_BYTES, &tmap_w, w_full(st),
                           kb * (BK * BITS / 32), n0);
               tma_load_2d(sb_s + st * L::SB_STAGE + g * SB_TILE_BYTES, &tmap_sb, w_full(st), n0, kb);
-              tma_load_3d_pair(x_s + st * L::X_STAGE + g * X_TILE_BYTES, &tmap_x, x_full(st), kb * BK, r0, b);
             }
           } else {
-            // Extension stage: the same byte counts on the same barriers. The dense tile lands where the codes
-            // would, the (scale, bias) load reads past the last group (zero fill, unused), and the activation
-            // tile comes from t: its first EXT_KG columns are the ones the tensor cores will read.
+            // Extension stage: the same byte counts on the same barrier. The dense tile lands where the codes
+            // would; the (scale, bias) load reads past the last group (zero fill, unused).
 #pragma unroll
             for (int g = 0; g < GPS; ++g) {
               const int k0 = ((s - num_st) * GPS + g) * EXT_KG;
               tma_load_2d(wq_s + st * L::WQ_STAGE + g * L::WQ_TILE_BYTES, &tmap_lb, w_full(st), k0, n0);
               tma_load_2d(sb_s + st * L::SB_STAGE + g * SB_TILE_BYTES, &tmap_sb, w_full(st), n0, num_kb + g);
-              tma_load_3d_pair(x_s + st * L::X_STAGE + g * X_TILE_BYTES, &tmap_t, x_full(st), k0, r0, b);
             }
           }
         }
@@ -326,7 +362,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
     bool ok = true;
     for (int tile = pair; tile < p.total_tiles && ok; tile += num_pairs) {
       for (int s = 0; s < num_all; ++s) {
-        if (!mbar_wait_sleep(d_empty(sd), ph_d ^ 1u, DEV_TIMEOUT_DQ_EMPTY) ||
+        if (!mbar_wait(d_empty(sd), ph_d ^ 1u, DEV_TIMEOUT_DQ_EMPTY) ||
             !mbar_wait(w_full(st), ph_t, DEV_TIMEOUT_TMA_FULL)) {
           ok = false;
           break;
@@ -346,7 +382,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
           __syncwarp();
           if (lane == 0) {
             mbar_arrive_leader(d_full(sd));
-            if (!UNIFIED) mbar_arrive(t_empty(st));
+            mbar_arrive(c_empty(st));
           }
           if (++st == ST) {
             st = 0;
@@ -388,7 +424,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         __syncwarp();
         if (lane == 0) {
           mbar_arrive_leader(d_full(sd));
-          if (!UNIFIED) mbar_arrive(t_empty(st));
+          mbar_arrive(c_empty(st));
         }
         if (++st == ST) {
           st = 0;
@@ -688,12 +724,14 @@ int prepare(const uint32_t* wq, const void* scales, const void* biases, int sb_d
   return MFX_OK;
 }
 
-// The kernel of qmm_t.cu (weights as the tensor-memory operand) serves every call without a low-rank term unless
-// the environment says MFX_QMM_KERNEL=smem (kept for side-by-side timing of the two kernels).
+// The kernel of qmm_t.cu (weights as the tensor-memory operand) is the slower of the two on every shape measured
+// (about 1050 against 1300 TFLOP/s on the single-linear configuration); it serves the tensor-parallel scatter
+// epilogue, whose stores it can issue as contiguous runs along the output row, and, for side-by-side timing, every
+// call without a low-rank term when the environment says MFX_QMM_KERNEL=tmem.
 static bool tmem_operand_kernel() {
   static const bool on = [] {
     const char* v = getenv("MFX_QMM_KERNEL");
-    return !(v && strcmp(v, "smem") == 0);
+    return v && strcmp(v, "tmem") == 0;
   }();
   return on;
 }
@@ -717,7 +755,7 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
     if (sc->row_offset + a.rows > sc->rows_per_rank * sc->world) return MFX_ERR_SHAPE;
     for (int r = 0; r < sc->world; ++r)
       if (!sc->dst[r] || !sc->flags[r]) return MFX_ERR_NULL;
-    if (a.lora_r > 0 || !tmem_operand_kernel()) return MFX_ERR_SHAPE;   // only the tensor-memory kernel scatters
+    if (a.lora_r > 0) return MFX_ERR_SHAPE;   // the kernel that scatters takes no low-rank term
   }
   if (a.epilogue == MFX_EPI_SWIGLU && a.N % 16 != 0) return MFX_ERR_SHAPE;
   const void* prepared = a.prepared;
@@ -757,7 +795,7 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
     prepared = a.workspace;
   }
   if (!low_rank && !scatter && qmv::eligible(a)) return qmv::run(a, prepared, codes_bytes_padded(a.N, a.K, a.bits), st);
-  if (!low_rank && tmem_operand_kernel()) return qmmt::run(a, prepared, codes_bytes_padded(a.N, a.K, a.bits), st);
+  if (!low_rank && (scatter || tmem_operand_kernel())) return qmmt::run(a, prepared, codes_bytes_padded(a.N, a.K, a.bits), st);
   const void* codes = prepared;
   const void* sb_packed = static_cast<const uint8_t*>(prepared) + codes_bytes_padded(a.N, a.K, a.bits);
 

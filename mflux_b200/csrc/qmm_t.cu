@@ -7,10 +7,16 @@
 //   A operand = dequantized weights, 128 rows per CTA, written by the dequantizer warps straight into tensor
 //               memory (tcgen05.st) and read from there by the tensor cores;
 //   B operand = activations, 96 tokens per CTA (192 per CTA pair), streamed by TMA into shared memory.
-// The kernel in qmm.cu keeps both operands in shared memory and its profile shows the shared-memory data pipe
-// busy more than 90 % of the cycles (per 128-deep stage and CTA: 512 wavefronts of tensor-core operand reads,
-// 320 of dequantized-weight stores, 330 of TMA writes, 150 of code loads, against 1024 cycles of MMA). Here a
-// stage moves 190 wavefronts of operand reads, 265 of TMA writes and 70 of code loads against 768 cycles of MMA.
+// The kernel in qmm.cu keeps both operands in shared memory (per 128-deep stage and CTA: 512 wavefronts of
+// tensor-core operand reads, 320 of dequantized-weight stores, 330 of TMA writes, 150 of code loads, against 1024
+// cycles of MMA); here a stage moves 190 wavefronts of operand reads, 265 of TMA writes and 70 of code loads
+// against 768 cycles of MMA. Measured, this kernel is nevertheless the slower one (about 1050 against 1300 TFLOP/s
+// on M 4096, N 12288, K 3072): tensor memory leaves room for two A slots only beside two accumulators, and with
+// the MMAs and the dequantizer arithmetic switched off the kernel still takes 0.85 us per stage, i.e. it is bound
+// by the latency of the slot hand-off between the dequantizers of both CTAs and the issuing thread (four slots of
+// one group each, with twice the commits, were slower still). It is kept for the epilogue that only its layout
+// serves well: thread = output column, so a warp writes 32 consecutive values of one output row, which makes the
+// tensor-parallel scatter to peer memory (MFX_EPI_PEER_SCATTER) one 64-byte run per store instruction.
 // Per CTA, 512 threads, persistent over tiles of 256 weight rows x 192 tokens per pair:
 //   warp 0      TMA producer: per stage (two quantization groups = 128 k) its 96 tokens of X (counted on the
 //               leader's barrier), the packed codes of its 128 weight rows and their (scale, bias) pairs

@@ -375,7 +375,7 @@ class Flux1:
     restricted to the denoise loop: random-init or caller-loaded transformer, LinearScheduler, Euler steps."""
 
     def __init__(self, quantize: int | None = None, model_config: FluxConfig | None = None, device="cuda",
-                 seed: int = 0, stored_quantization: int | None = None):
+                 seed: int = 0, stored_quantization: int | None = None, cuda_graph: bool = False):
         bits, warning = resolution.resolve(stored_quantization, quantize)
         if warning:
             print(f"Warning: {warning}")
@@ -383,6 +383,34 @@ class Flux1:
         self.bits = bits
         self.model_config = model_config or FluxConfig()
         self.transformer = Transformer(self.model_config, bits=bits, device=device, seed=seed)
+        # cuda_graph: one denoiser evaluation is recorded per (shapes, image size) and replayed; worth it for single
+        # images, where a step is some 600 short launches (the reference gets the same from MLX's lazy graph)
+        self.cuda_graph, self._captured, self._captured_epoch = cuda_graph, {}, nn.weights_epoch()
+
+    def predict_noise(self, latents, prompt_embeds, pooled_prompt_embeds, timestep, guidance, height, width):
+        """One denoiser evaluation; `timestep` and `guidance` are [B] tensors on the device."""
+        if not self.cuda_graph:
+            return self.transformer(latents, prompt_embeds, pooled_prompt_embeds, timestep, guidance, height, width)
+        from .graphs import CapturedStep
+
+        if self._captured and self._captured_epoch != nn.weights_epoch():
+            self.release_graphs()
+        self._captured_epoch = nn.weights_epoch()
+        key = (height, width, guidance is None)
+        step = self._captured.get(key)
+        if step is None:
+            if guidance is None:
+                fn = lambda lat, ctx, pool, ts: self.transformer(lat, ctx, pool, ts, None, height, width)  # noqa: E731
+            else:
+                fn = lambda lat, ctx, pool, ts, gd: self.transformer(lat, ctx, pool, ts, gd, height, width)  # noqa: E731
+            step = self._captured[key] = CapturedStep(fn)
+        args = (latents, prompt_embeds, pooled_prompt_embeds, timestep) + (() if guidance is None else (guidance,))
+        return step(*args)
+
+    def release_graphs(self) -> None:
+        for step in self._captured.values():
+            step.release()
+        self._captured = {}
 
     def save_model(self, base_path: str) -> None:
         """ModelSaver.save_model for the component this class owns: `<base_path>/transformer/{i}.safetensors` plus
@@ -418,6 +446,6 @@ class Flux1:
         gvec = torch.full((b,), guidance * cfg.num_train_steps, device=dev) if cfg.supports_guidance else None
         for t in range(num_inference_steps):
             ts = torch.full((b,), float(sched.sigmas[t]) * cfg.num_train_steps, device=dev)
-            noise = self.transformer(latents, prompt_embeds, pooled_prompt_embeds, ts, gvec, height, width)
+            noise = self.predict_noise(latents, prompt_embeds, pooled_prompt_embeds, ts, gvec, height, width)
             latents = ops.euler_step(latents, noise, sched.dt(t))
         return latents

@@ -382,7 +382,7 @@ class ZImage:
     combine noise + g * (noise - negative) when guidance > 1 and negative features are given."""
 
     def __init__(self, quantize: int | None = None, model_config: ZImageConfig | None = None, device="cuda",
-                 seed: int = 0, stored_quantization: int | None = None):
+                 seed: int = 0, stored_quantization: int | None = None, cuda_graph: bool = False):
         bits, warning = resolution.resolve(stored_quantization, quantize)
         if warning:
             print(f"Warning: {warning}")
@@ -390,6 +390,7 @@ class ZImage:
         self.bits = bits
         self.model_config = model_config or ZImageConfig()
         self.transformer = ZImageTransformer(self.model_config, bits=bits, device=device, seed=seed)
+        self.cuda_graph, self._captured, self._captured_epoch = cuda_graph, None, nn.weights_epoch()
 
     def save_model(self, base_path: str) -> None:
         """ModelSaver.save_model for the component this class owns: `<base_path>/transformer/{i}.safetensors` plus
@@ -422,14 +423,33 @@ class ZImage:
             return sched
         raise NotImplementedError(f"The scheduler {scheduler!r} is not implemented.")
 
+    def _evaluate(self, latents, t, cap_feats):
+        """The transformer call, replayed from a recorded CUDA graph when the model was built with cuda_graph=True
+        (one graph per set of input shapes; a single image is a few hundred short launches per step)."""
+        if not self.cuda_graph:
+            return self.transformer(latents, t, cap_feats)
+        from .graphs import CapturedStep
+
+        if self._captured is not None and self._captured_epoch != nn.weights_epoch():
+            self.release_graphs()
+        self._captured_epoch = nn.weights_epoch()
+        if self._captured is None:
+            self._captured = CapturedStep(lambda lat, tt, cap: self.transformer(lat, tt, cap))
+        return self._captured(latents, t, cap_feats)
+
+    def release_graphs(self) -> None:
+        if self._captured is not None:
+            self._captured.release()
+        self._captured = None
+
     def denoise_step(self, latents, cap_feats, negative_cap_feats, sigma, dt, guidance):
         b = latents.shape[0]
         t = torch.full((b,), 1.0 - sigma, device=latents.device)
         if negative_cap_feats is None:
-            noise = self.transformer(latents, t, cap_feats)
+            noise = self._evaluate(latents, t, cap_feats)
         else:
-            both = self.transformer(torch.cat([latents, latents]), torch.cat([t, t]),
-                                    torch.cat([cap_feats, negative_cap_feats]))
+            both = self._evaluate(torch.cat([latents, latents]), torch.cat([t, t]),
+                                  torch.cat([cap_feats, negative_cap_feats]))
             noise = ops.cfg_combine(both[:b], both[b:], guidance, mode="plain")
         return ops.euler_step(latents, noise, dt)
 

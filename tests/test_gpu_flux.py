@@ -115,3 +115,19 @@ def test_update_after_a_forward_is_seen_by_the_row_fused_projections(lib_built):
     assert not torch.equal(before, want)
     a.update({k: v.detach().clone() for k, v in list(b.named_parameters()) + list(b.named_buffers())})
     assert torch.equal(a(*args), want)
+
+
+def test_cuda_graph_replay_equals_launch_by_launch(lib_built):
+    """Flux1(cuda_graph=True) records one denoiser evaluation per image size and replays it with new latents and
+    timesteps: the loop's result equals the launch-by-launch loop bit for bit."""
+    from mflux_b200.flux import Flux1, FluxConfig
+
+    cfg = FluxConfig(hidden=256, heads=2, num_joint=1, num_single=2, context_dim=128, pooled_dim=64)
+    eager = Flux1(quantize=4, model_config=cfg, seed=3)
+    graphed = Flux1(quantize=4, model_config=cfg, seed=3, cuda_graph=True)
+    _, ctx, pooled = _inputs(cfg, 1, 64, 96, 24, 6)
+    a = eager.generate_image(5, ctx.cuda(), pooled.cuda(), num_inference_steps=3, height=64, width=96)
+    b = graphed.generate_image(5, ctx.cuda(), pooled.cuda(), num_inference_steps=3, height=64, width=96)
+    assert torch.equal(a, b)
+    assert len(graphed._captured) == 1
+    graphed.release_graphs()

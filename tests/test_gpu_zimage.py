@@ -224,3 +224,16 @@ def test_step_with_adapters_on_fused_projections(lib_built):
     # and the adapters matter: the bare model gives something else
     bare = ZImageTransformer(cfg, bits=4, device="cuda", seed=5)
     assert rel_l2(bare(lat.cuda(), t.cuda(), cap.cuda()), ref.numpy()) > 2 * TOL
+
+
+def test_cuda_graph_replay_equals_launch_by_launch(lib_built):
+    from mflux_b200.zimage import ZImage
+
+    eager = ZImage(quantize=8, model_config=_small_cfg(n_layers=2), seed=4)
+    graphed = ZImage(quantize=8, model_config=_small_cfg(n_layers=2), seed=4, cuda_graph=True)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    cap = torch.randn(1, 32, 128, device="cuda", generator=g).to(torch.bfloat16)
+    a = eager.generate_image(2, cap, num_inference_steps=3, height=128, width=128)
+    b = graphed.generate_image(2, cap, num_inference_steps=3, height=128, width=128)
+    assert torch.equal(a, b)
+    graphed.release_graphs()
