@@ -67,6 +67,12 @@ struct Params {
   int64_t res_row_stride, res_batch_stride;
   void* y;
   int64_t y_row_stride, y_batch_stride;
+  // MFX_EPI_PEER_SCATTER: partial rows go to slot [sc_rank] of the rank that owns them (see include/mfx.h)
+  int sc_world, sc_rank;
+  int64_t sc_rows_per_rank, sc_row_offset;
+  __nv_bfloat16* sc_dst[MFX_TP_MAX_WORLD];
+  int* sc_flags[MFX_TP_MAX_WORLD];
+  int* sc_done;
 };
 
 // ST = stages of the TMA ring, SD = stages of the dequantized-weight ring; one stage = GPS groups.
@@ -88,6 +94,8 @@ struct Smem {
   static constexpr int TOTAL = OFF_TMEM + 16;
   static constexpr int DYN_BYTES = TOTAL + 1024;  // slack for manual 1024-byte alignment
 };
+
+__device__ __forceinline__ bool row_ok_for_scatter(int r, int rows) { return r < rows; }
 
 // Tile order. The weight rows are cut into bands of band_n n-tiles whose packed codes, scales and biases fit in
 // L2 together; inside a band the tiles run m-tile by m-tile with the n-tile index fastest. The pairs that run at
@@ -475,6 +483,14 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
       if (EPI == MFX_EPI_GATE_RESIDUAL)
         rrow = static_cast<const OUT*>(p.residual) + b * p.res_batch_stride +
                static_cast<int64_t>(r) * p.res_row_stride + n0;
+      if (EPI == MFX_EPI_PEER_SCATTER && row_ok_for_scatter(r, p.rows)) {
+        // this thread's row of the joint sequence lives on rank `owner`: slot [sc_rank] of its partial-sum buffer
+        const int64_t tj = p.sc_row_offset + r;
+        const int64_t owner = tj / p.sc_rows_per_rank;
+        const int64_t local = tj - owner * p.sc_rows_per_rank;
+        yrow = reinterpret_cast<OUT*>(p.sc_dst[owner]) +
+               ((static_cast<int64_t>(p.sc_rank) * p.batch + b) * p.sc_rows_per_rank + local) * p.N + n0;
+      }
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + a * BN;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -482,6 +498,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
         tmem_ld_32x32(t_addr + c * 32, acc);
         tmem_ld_wait();
         if (row_ok) {
+          uint4 held = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
           for (int g8 = 0; g8 < 4; ++g8) {
             const int col = c * 32 + g8 * 8;
@@ -526,6 +543,21 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                 h[1] = __floats2bfloat162_rn(o[2], o[3]);
                 *reinterpret_cast<uint2*>(yrow + col / 2) = *reinterpret_cast<uint2*>(h);
               }
+            } else if constexpr (EPI == MFX_EPI_PEER_SCATTER) {
+              // two groups of eight columns go out as one 32-byte store: peer memory is reached over NVLink, where
+              // a 32-byte write costs one header for two data flits instead of one for one
+              __nv_bfloat162 h[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+              const uint4 cur = *reinterpret_cast<uint4*>(h);
+              if (g8 & 1) {
+                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(yrow + col - 8),
+                             "r"(held.x), "r"(held.y), "r"(held.z), "r"(held.w), "r"(cur.x), "r"(cur.y), "r"(cur.z),
+                             "r"(cur.w)
+                             : "memory");
+              } else {
+                held = cur;
+              }
             } else if constexpr (sizeof(OUT) == 4) {
               *reinterpret_cast<float4*>(yrow + col) = make_float4(v[0], v[1], v[2], v[3]);
               *reinterpret_cast<float4*>(yrow + col + 4) = make_float4(v[4], v[5], v[6], v[7]);
@@ -541,6 +573,20 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_leader(acc_empty(a));
+    }
+    if (EPI == MFX_EPI_PEER_SCATTER) {
+      // every thread's peer stores are ordered before this CTA's arrival; the last CTA of the grid tells the owners
+      __threadfence_system();
+      named_bar_sync(1, 128);
+      if (threadIdx.x == FIRST_EPI_WARP * 32) {
+        const int done = atomicAdd(p.sc_done, 1);
+        if (done == static_cast<int>(gridDim.x) - 1) {
+          *p.sc_done = 0;
+          __threadfence_system();
+          for (int r = 0; r < p.sc_world; ++r)
+            asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p.sc_flags[r]), "r"(1) : "memory");
+        }
+      }
     }
   }
 
@@ -580,6 +626,11 @@ int launch_ext(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& 
     case MFX_EPI_GATE_RESIDUAL: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_GATE_RESIDUAL, EXT>(tx, tw, tsb, tt, tlb, p, grid, st);
     case MFX_EPI_SILU: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_SILU, EXT>(tx, tw, tsb, tt, tlb, p, grid, st);
     case MFX_EPI_SWIGLU: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_SWIGLU, EXT>(tx, tw, tsb, tt, tlb, p, grid, st);
+    case MFX_EPI_PEER_SCATTER:
+      if constexpr (sizeof(OUT) == 2 && !EXT)
+        return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_PEER_SCATTER, EXT>(tx, tw, tsb, tt, tlb, p, grid, st);
+      else
+        return MFX_ERR_DTYPE;
     default: return launch_epi<BITS, WF, ST, SD, OUT, MFX_EPI_NONE, EXT>(tx, tw, tsb, tt, tlb, p, grid, st);
   }
 }
@@ -755,7 +806,7 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
     if (sc->row_offset + a.rows > sc->rows_per_rank * sc->world) return MFX_ERR_SHAPE;
     for (int r = 0; r < sc->world; ++r)
       if (!sc->dst[r] || !sc->flags[r]) return MFX_ERR_NULL;
-    if (a.lora_r > 0) return MFX_ERR_SHAPE;   // the kernel that scatters takes no low-rank term
+    if (a.lora_r > 0 || a.N % 16 != 0) return MFX_ERR_SHAPE;   // no low-rank term; 32-byte stores of 16 columns
   }
   if (a.epilogue == MFX_EPI_SWIGLU && a.N % 16 != 0) return MFX_ERR_SHAPE;
   const void* prepared = a.prepared;
@@ -795,7 +846,7 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
     prepared = a.workspace;
   }
   if (!low_rank && !scatter && qmv::eligible(a)) return qmv::run(a, prepared, codes_bytes_padded(a.N, a.K, a.bits), st);
-  if (!low_rank && (scatter || tmem_operand_kernel())) return qmmt::run(a, prepared, codes_bytes_padded(a.N, a.K, a.bits), st);
+  if (!low_rank && tmem_operand_kernel()) return qmmt::run(a, prepared, codes_bytes_padded(a.N, a.K, a.bits), st);
   const void* codes = prepared;
   const void* sb_packed = static_cast<const uint8_t*>(prepared) + codes_bytes_padded(a.N, a.K, a.bits);
 
@@ -883,9 +934,23 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
   p.y = a.y;
   p.y_row_stride = a.y_row_stride;
   p.y_batch_stride = a.y_batch_stride;
+  p.sc_world = 0;
+  if (scatter) {
+    const mfx_tp_scatter& sc = *a.scatter;
+    p.sc_world = sc.world;
+    p.sc_rank = sc.rank;
+    p.sc_rows_per_rank = sc.rows_per_rank;
+    p.sc_row_offset = sc.row_offset;
+    for (int r = 0; r < sc.world; ++r) {
+      p.sc_dst[r] = static_cast<__nv_bfloat16*>(sc.dst[r]);
+      p.sc_flags[r] = sc.flags[r];
+    }
+    p.sc_done = sc.done_counter;
+  }
   const int pairs = device_sm_count() / 2;
+  const bool f32_out = a.y_dtype == MFX_F32 && !scatter;
   const int grid = 2 * (p.total_tiles < pairs ? p.total_tiles : pairs);
-  const bool f32 = a.y_dtype == MFX_F32;
+  const bool f32 = f32_out;
   if (kb == 4) {
     return f32 ? launch<4, FMT_BF16, 3, 3, float>(tx, tw, tsb, tt, tlb, p, grid, st)
                : launch<4, FMT_BF16, 3, 3, __nv_bfloat16>(tx, tw, tsb, tt, tlb, p, grid, st);

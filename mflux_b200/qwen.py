@@ -365,15 +365,30 @@ def _forward_peer(self, hidden_states, encoder_hidden_states, timestep, height, 
         ops.qlinear(x, layer.weight.data, None, None, None, bits=layer.bits, prepared=layer.prepared(),
                     scatter=ex.scatter(row_offset))
 
+    own_lo, own_hi = ex.lo, min(s, ex.lo + ex.rows)
+
+    def gathered(jobs):
+        """Column-split matmuls over the gathered activations. `jobs` are (fn(x_rows, out_rows), a, b, x, out) over
+        joint rows [a, b). The rows this rank normalised itself are in place already: their share of every matmul
+        runs first and hides the flight time of the peers' rows; the rest follows the wait for their arrival."""
+        for fn, a_, b_, x, out in jobs:
+            lo_, hi_ = max(a_, own_lo), min(b_, own_hi)
+            if lo_ < hi_:
+                fn(x[:, lo_:hi_], out[:, lo_:hi_])
+        ex.wait_gathered()
+        for fn, a_, b_, x, out in jobs:
+            for lo_, hi_ in ((a_, min(b_, own_lo)), (max(a_, own_hi), b_)):
+                if lo_ < hi_:
+                    fn(x[:, lo_:hi_], out[:, lo_:hi_])
+
     ex.begin()
     blocks = list(self.transformer_blocks)
     mt, mi = mods(blocks[0])
     ex.fuse(reduce=False, shift=(ch(mt, 0), ch(mi, 0)), scale=(ch(mt, 1), ch(mi, 1)))
     for i, blk in enumerate(blocks):
         a = blk.attn
-        ex.wait_gathered()
-        self._fuse(("q", i), [a.to_q, a.to_k, a.to_v])(nbuf[:, st:s], qkv[:, st:s])
-        self._fuse(("a", i), [a.add_q_proj, a.add_k_proj, a.add_v_proj])(nbuf[:, :st], qkv[:, :st])
+        gathered([(self._fuse(("q", i), [a.to_q, a.to_k, a.to_v]), st, s, nbuf, qkv),
+                  (self._fuse(("a", i), [a.add_q_proj, a.add_k_proj, a.add_v_proj]), 0, st, nbuf, qkv)])
         ops.qknorm_rope(qkv[:, :s], heads, a.norm_added_q.weight.data, a.norm_added_k.weight.data,
                         a.norm_q.weight.data, a.norm_k.weight.data, st, cos_sin, a.norm_q.eps)
         ops.fmha(qkv[:, :s], heads, out=attn[:, :s], key_bias=key_bias)
@@ -381,9 +396,8 @@ def _forward_peer(self, hidden_states, encoder_hidden_states, timestep, height, 
         scattered(a.to_add_out, attn[:, :st], 0)
         ex.fuse(reduce=True, bias=(a.to_add_out.bias, a.attn_to_out[0].bias), gate=(ch(mt, 2), ch(mi, 2)),
                 shift=(ch(mt, 3), ch(mi, 3)), scale=(ch(mt, 4), ch(mi, 4)))
-        ex.wait_gathered()
-        _call(blk.img_ff.mlp_in, nbuf[:, st:s], epilogue="gelu_approx", out=ffb[:, st:s])
-        _call(blk.txt_ff.mlp_in, nbuf[:, :st], epilogue="gelu_approx", out=ffb[:, :st])
+        gathered([(lambda x, o, l=blk.img_ff.mlp_in: _call(l, x, epilogue="gelu_approx", out=o), st, s, nbuf, ffb),
+                  (lambda x, o, l=blk.txt_ff.mlp_in: _call(l, x, epilogue="gelu_approx", out=o), 0, st, nbuf, ffb)])
         scattered(blk.img_ff.mlp_out, ffb[:, st:s], st)
         scattered(blk.txt_ff.mlp_out, ffb[:, :st], 0)
         gate = (ch(mt, 5), ch(mi, 5))
