@@ -232,10 +232,21 @@ def flux_spec(args):
 
         def step(i, lat_d, ctx_d, pool_d):
             j = i % len(sched.timesteps)
-            ts = torch.full((batch,), float(sched.sigmas[j]) * cfg.num_train_steps, device=dev)
-            noise = model(lat_d, ctx_d, pool_d, ts, gvec, height, width)
+            nb = lat_d.shape[0]
+            ts = torch.full((nb,), float(sched.sigmas[j]) * cfg.num_train_steps, device=dev)
+            noise = model(lat_d, ctx_d, pool_d, ts, gvec[:nb], height, width)
             return ops.euler_step(lat_d, noise, sched.dt(j))
 
+        def shard(images):
+            """Device inputs of this rank's share of one batch of `images` images split evenly over the ranks
+            (strong scaling: the same model, fewer images per GPU)."""
+            nb = images // world
+            gs = torch.Generator(device="cpu").manual_seed(500 + rank)
+            return [torch.randn(nb, si, cfg.in_channels, generator=gs).to(dev),
+                    torch.randn(nb, st, cfg.context_dim, generator=gs).to(torch.bfloat16).to(dev),
+                    torch.randn(nb, cfg.pooled_dim, generator=gs).to(torch.bfloat16).to(dev)]
+
+        step.shard = shard
         return [lat_h, ctx_h, pool_h], out_h, step
 
     return {
@@ -519,6 +530,9 @@ def main():
                     help="flux: wrap every attention / feed-forward linear with one LoRA adapter of this rank")
     ap.add_argument("--lora-library", action="store_true",
                     help="with --lora-rank: run the adapters as library GEMMs instead of inside the quantized matmul")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="flux: skip the two extra records (the 16-image batch split over the ranks, and the "
+                         "Qwen-Image-shaped tensor-parallel step)")
     ap.add_argument("--no-cuda-graph", action="store_true",
                     help="qwen: issue the step's launches one by one instead of replaying them as a CUDA graph")
     args = ap.parse_args()
@@ -637,6 +651,57 @@ def main():
         trace, ops.TRACE = ops.TRACE, None
     status = ops.poll_device_status()
 
+    def timed(fn, steps, warm):
+        """max-over-ranks device milliseconds per step of fn(i), after `warm` untimed steps."""
+        for i in range(warm):
+            fn(i)
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(steps):
+            fn(i)
+        b.record()
+        barrier()
+        t = torch.tensor([a.elapsed_time(b) / steps], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    extras = {}
+    if args.workload == "flux" and not args.small and not args.no_extra and not args.lora_rank and not args.batch \
+            and 16 % world == 0:
+        # (1) strong scaling of the headline step: the SAME 16 images split over the ranks, no collective
+        shard_in = step.shard(16)
+        ms_strong = timed(lambda i: step(i, *shard_in), 3, 2)
+        extras["strong"] = {"metric": "flux1_w4_dit_16_image_steps_per_sec_1024px_split_over_gpus",
+                            "value": 1e3 / ms_strong, "unit": "steps/s (one step = the same 16 images, 16 / N per GPU)",
+                            "ms_per_step": ms_strong, "n_gpus": world, "per_gpu_batch": 16 // world,
+                            "scaling": "strong"}
+        del shard_in
+        # (2) the part of the path that communicates: the Qwen-Image-shaped 20B step, its two guidance branches on
+        # the two halves of the ranks and tensor parallelism inside each half (one rank: both branches as a batch)
+        if world in (1, 2, 4, 8):
+            import gc
+
+            host_in_main, step_main = host_in, step
+            del dev_in, cur, res
+            step = None
+            gc.collect()
+            torch.cuda.empty_cache()
+            qspec = qwen_spec(args)
+            q_host, _, q_step = qspec["build"](dev, rank, world, 8)
+            q_dev = [t.to(dev) for t in q_host]
+            ms_tp = timed(lambda i: q_step(i, *q_dev), 4, 3)
+            q_status = ops.poll_device_status()
+            extras["tp"] = {"metric": qspec["metric"], "value": 1e3 / ms_tp, "unit": qspec["unit"],
+                            "ms_per_step": ms_tp, "n_gpus": world, "scaling": "strong",
+                            "workload": qspec["workload"], "exchange": args.qwen_tp_mode if world > 2 else None,
+                            "algorithmic_tflop_per_step": (qspec["lin"] + qspec["attn"]) / 1e12,
+                            "device_status": q_status}
+            getattr(q_step, "release", lambda: None)()
+            del q_step, q_dev
+            host_in, step = host_in_main, step_main
+
     times = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -697,6 +762,7 @@ def main():
                               "share_of_step_time": (g_ms / trace_steps) / step_ms if ms > 0 else None},
             "step_tflops": flops / 1e12 * args.steps / (ms / 1e3) / (world if spec["scaling"] == "strong" else 1),
         }
+        line.update(extras)
         if not args.no_cpu_baseline and world == 1:
             tf, desc, cores, threads = cpu_sample()
             line["cpu_baseline"] = {"value": tf * 1e12 / flops, "unit": spec["unit"], "cores": cores,
