@@ -518,8 +518,10 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
             } else if (EPI == MFX_EPI_GATE_RESIDUAL) {
               float rs[8];
               if constexpr (sizeof(OUT) == 4) {
-                const float4 r0 = *reinterpret_cast<const float4*>(rrow + col);
-                const float4 r1 = *reinterpret_cast<const float4*>(rrow + col + 4);
+                // the float32 residual stream is read once and written once per launch and is larger than L2:
+                // streaming loads / stores keep it from evicting the activation tiles the other n-tiles re-read
+                const float4 r0 = __ldcs(reinterpret_cast<const float4*>(rrow + col));
+                const float4 r1 = __ldcs(reinterpret_cast<const float4*>(rrow + col + 4));
                 rs[0] = r0.x; rs[1] = r0.y; rs[2] = r0.z; rs[3] = r0.w;
                 rs[4] = r1.x; rs[5] = r1.y; rs[6] = r1.z; rs[7] = r1.w;
               } else {
@@ -559,8 +561,13 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                 held = cur;
               }
             } else if constexpr (sizeof(OUT) == 4) {
-              *reinterpret_cast<float4*>(yrow + col) = make_float4(v[0], v[1], v[2], v[3]);
-              *reinterpret_cast<float4*>(yrow + col + 4) = make_float4(v[4], v[5], v[6], v[7]);
+              if constexpr (EPI == MFX_EPI_GATE_RESIDUAL) {
+                __stcs(reinterpret_cast<float4*>(yrow + col), make_float4(v[0], v[1], v[2], v[3]));
+                __stcs(reinterpret_cast<float4*>(yrow + col + 4), make_float4(v[4], v[5], v[6], v[7]));
+              } else {
+                *reinterpret_cast<float4*>(yrow + col) = make_float4(v[0], v[1], v[2], v[3]);
+                *reinterpret_cast<float4*>(yrow + col + 4) = make_float4(v[4], v[5], v[6], v[7]);
+              }
             } else {
               __nv_bfloat162 h[4];
 #pragma unroll
