@@ -530,6 +530,8 @@ def main():
                     help="flux: wrap every attention / feed-forward linear with one LoRA adapter of this rank")
     ap.add_argument("--lora-library", action="store_true",
                     help="with --lora-rank: run the adapters as library GEMMs instead of inside the quantized matmul")
+    ap.add_argument("--breakdown", action="store_true",
+                    help="add per-shape kernel times (from the per-launch event pairs) to the JSON line")
     ap.add_argument("--no-extra", action="store_true",
                     help="flux: skip the two extra records (the 16-image batch split over the ranks, and the "
                          "Qwen-Image-shaped tensor-parallel step)")
@@ -763,6 +765,16 @@ def main():
             "step_tflops": flops / 1e12 * args.steps / (ms / 1e3) / (world if spec["scaling"] == "strong" else 1),
         }
         line.update(extras)
+        if args.breakdown:
+            groups = {}
+            for kind, rows_ in trace.items():
+                for t in rows_:
+                    g_ = groups.setdefault((kind, round(t[0]), round(t[1])), [0, 0.0])
+                    g_[0] += 1
+                    g_[1] += t[2].elapsed_time(t[3])
+            line["breakdown"] = sorted(
+                ({"kind": k[0], "flop": k[1], "bytes": k[2], "launches": v[0], "ms_total": round(v[1], 3),
+                  "us_avg": round(1e3 * v[1] / v[0], 1)} for k, v in groups.items()), key=lambda r: -r["ms_total"])
         if not args.no_cpu_baseline and world == 1:
             tf, desc, cores, threads = cpu_sample()
             line["cpu_baseline"] = {"value": tf * 1e12 / flops, "unit": spec["unit"], "cores": cores,

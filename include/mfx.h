@@ -10,7 +10,12 @@
  *  - the return value is 0 (MFX_OK) or a negative mfx_status; nothing throws across this boundary;
  *  - the library allocates no device memory; shapes and alignments are validated on the host
  *    before anything is launched;
- *  - bounded device-side waits report through mfx_poll_device_status() instead of hanging.
+ *  - bounded device-side waits report through mfx_poll_device_status() instead of hanging;
+ *  - threads: every entry point may be called from several host threads, and for several devices of one process
+ *    (the few per-device records the library keeps - kernel attributes, SM count, the address of the static
+ *    scratch - sit under mutexes); calls act on the device that is current in the calling thread. What the library
+ *    does not order is the caller's own memory: two calls that write the same workspace or output, a prepared blob
+ *    that is being rebuilt while another stream reads it, or the one static scratch must be ordered by the caller.
  */
 #ifndef MFX_H_
 #define MFX_H_
@@ -221,8 +226,14 @@ typedef struct mfx_tp_fuse_args {
   void* push_dst[MFX_TP_MAX_WORLD]; /* on rank r: bf16 [batch, seq_pad, D] */
   int* ag_flags[MFX_TP_MAX_WORLD];  /* on rank r: the counter this rank bumps */
   int* done_counter;    /* local int, zero between calls */
+  int push_local_only;  /* 1: store n into push_dst[rank] only and bump no counter: the caller moves the rows to the
+                           peers itself (e.g. with the copy engines, beside the next matmul) and then calls
+                           mfx_tp_signal */
 } mfx_tp_fuse_args;
 int mfx_tp_fuse(const mfx_tp_fuse_args* args /* host */, void* stream);
+/* Adds 1 to *flags[r] for r < world with system-scope release semantics: the arrival signal of rows that were moved
+ * to the peers by stream-ordered copies enqueued before this call on the same stream. `flags` is a host array. */
+int mfx_tp_signal(int* const* flags /* host */, int world, void* stream);
 /* Enqueues a wait until flags[r] >= target + (epoch_base ? *epoch_base : 0) for r < world (local counters that
  * peers bump). The wait is bounded: after about a second it gives up and mfx_poll_device_status reports it. */
 int mfx_tp_wait(const int* flags, int world, int target, const int* epoch_base, void* stream);

@@ -68,6 +68,7 @@ class TpFuseArgs(ctypes.Structure):
         ("push_dst", c_void_p * TP_MAX_WORLD),
         ("ag_flags", c_void_p * TP_MAX_WORLD),
         ("done_counter", c_void_p),
+        ("push_local_only", c_int),
     ]
 
 
@@ -218,6 +219,7 @@ SIGNATURES = {
          c_void_p, c_int64, c_int64, c_void_p],
     ),
     "mfx_tp_fuse": (c_int, [ctypes.POINTER(TpFuseArgs), c_void_p]),
+    "mfx_tp_signal": (c_int, [ctypes.POINTER(c_void_p), c_int, c_void_p]),
     "mfx_tp_wait": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "mfx_vec_sum_act": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int64, c_void_p]),
     "mfx_gate_residual": (

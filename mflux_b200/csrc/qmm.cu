@@ -76,7 +76,8 @@ struct Params {
 };
 
 // ST = stages of the TMA ring, SD = stages of the dequantized-weight ring; one stage = GPS groups.
-template <int BITS, int ST, int SD>
+// STG = bytes of the epilogue's staging buffer (tensor-parallel scatter only).
+template <int BITS, int ST, int SD, int STG = 0>
 struct Smem {
   static constexpr int WQ_TILE_BYTES = BN_HALF * BK * BITS / 8;
   static constexpr int X_STAGE = GPS * X_TILE_BYTES;
@@ -88,14 +89,13 @@ struct Smem {
   static constexpr int OFF_WQ = OFF_WD + SD * WD_STAGE;
   static constexpr int OFF_SB = OFF_WQ + ST * WQ_STAGE;
   static constexpr int OFF_VEC = OFF_SB + ST * SB_STAGE;  // bias[2][256] + gate[2][256] floats
-  static constexpr int OFF_BAR = OFF_VEC + 4 * BN * 4;
+  static constexpr int OFF_STAGE = OFF_VEC + 4 * BN * 4;
+  static constexpr int OFF_BAR = OFF_STAGE + STG;
   static constexpr int NUM_BARS = 4 * ST + 2 * SD + 4;
   static constexpr int OFF_TMEM = OFF_BAR + NUM_BARS * 8;
   static constexpr int TOTAL = OFF_TMEM + 16;
   static constexpr int DYN_BYTES = TOTAL + 1024;  // slack for manual 1024-byte alignment
 };
-
-__device__ __forceinline__ bool row_ok_for_scatter(int r, int rows) { return r < rows; }
 
 // Tile order. The weight rows are cut into bands of band_n n-tiles whose packed codes, scales and biases fit in
 // L2 together; inside a band the tiles run m-tile by m-tile with the n-tile index fastest. The pairs that run at
@@ -117,7 +117,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((FIXED_WARPS + NUM_D
 qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
            const __grid_constant__ CUtensorMap tmap_sb, const __grid_constant__ CUtensorMap tmap_t,
            const __grid_constant__ CUtensorMap tmap_lb, const Params p) {
-  using L = Smem<BITS, ST, SD>;
+  // The scatter epilogue stages 32 rows x SCATTER_ROW bytes per epilogue warp to turn "thread = row" into stores
+  // of whole 128-byte (64-byte for 8-bit codes, where shared memory is tighter) row segments.
+  constexpr int SCATTER_ROW = BITS == 4 ? 128 : 64;
+  using L = Smem<BITS, ST, SD, EPI == MFX_EPI_PEER_SCATTER ? 4 * 32 * SCATTER_ROW : 0>;
   // With as many TMA stages as dequantized-weight stages the two rings advance in lockstep and one "stage
   // consumed" barrier serves both: the commit after a stage's MMAs frees its activation tile and its B tile, and
   // the stage's packed codes were read before its B tile was written, so they are free by then too. That is one
@@ -483,22 +486,68 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
       if (EPI == MFX_EPI_GATE_RESIDUAL)
         rrow = static_cast<const OUT*>(p.residual) + b * p.res_batch_stride +
                static_cast<int64_t>(r) * p.res_row_stride + n0;
-      if (EPI == MFX_EPI_PEER_SCATTER && row_ok_for_scatter(r, p.rows)) {
-        // this thread's row of the joint sequence lives on rank `owner`: slot [sc_rank] of its partial-sum buffer
-        const int64_t tj = p.sc_row_offset + r;
-        const int64_t owner = tj / p.sc_rows_per_rank;
-        const int64_t local = tj - owner * p.sc_rows_per_rank;
-        yrow = reinterpret_cast<OUT*>(p.sc_dst[owner]) +
-               ((static_cast<int64_t>(p.sc_rank) * p.batch + b) * p.sc_rows_per_rank + local) * p.N + n0;
-      }
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + a * BN;
+      if constexpr (EPI == MFX_EPI_PEER_SCATTER) {
+        // Partial rows go to slot [sc_rank] of the rank that owns each row, over NVLink, where only stores of whole
+        // lines run at full rate (measured: 32-byte pieces of 32 different rows per instruction 280 GB/s, whole
+        // lines 655 GB/s). So: thread = row writes its packed bf16 values into a swizzled staging tile, then the
+        // warp stores the tile SCATTER_ROW bytes of a row at a time (lane = 16-byte piece, 32 / PIECES rows per
+        // instruction).
+        constexpr int PIECES = SCATTER_ROW / 16;
+        constexpr int ROWS_PER_ST = 32 / PIECES;
+        constexpr int CHUNKS = SCATTER_ROW / 64;   // 32-column accumulator chunks per staged row
+        uint8_t* stg = smem_gen + L::OFF_STAGE + q * (32 * SCATTER_ROW);
+        const int piece = lane % PIECES, rsub = lane / PIECES;
+        __nv_bfloat16* drow[PIECES];
+#pragma unroll
+        for (int i = 0; i < PIECES; ++i) {
+          const int rr = rsub + ROWS_PER_ST * i;
+          const int rg = r - lane + rr;   // row of the sample this lane stores in pass i
+          drow[i] = nullptr;
+          if (rg < p.rows) {
+            const int64_t tj = p.sc_row_offset + rg;   // row of the joint sequence
+            const int64_t owner = tj / p.sc_rows_per_rank;
+            const int64_t local = tj - owner * p.sc_rows_per_rank;
+            drow[i] = p.sc_dst[owner] +
+                      ((static_cast<int64_t>(p.sc_rank) * p.batch + b) * p.sc_rows_per_rank + local) * p.N + n0;
+          }
+        }
+#pragma unroll 1
+        for (int round = 0; round < BN / (32 * CHUNKS); ++round) {
+          if (n0 + round * 32 * CHUNKS >= p.N) break;
+#pragma unroll
+          for (int h = 0; h < CHUNKS; ++h) {
+            uint32_t acc[32];
+            tmem_ld_32x32(t_addr + (round * CHUNKS + h) * 32, acc);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              __nv_bfloat162 hh[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                hh[e] = __floats2bfloat162_rn(__uint_as_float(acc[8 * j + 2 * e]), __uint_as_float(acc[8 * j + 2 * e + 1]));
+              const int idx = h * 4 + j;
+              *reinterpret_cast<uint4*>(stg + lane * SCATTER_ROW + ((idx ^ (lane & (PIECES - 1))) << 4)) =
+                  *reinterpret_cast<uint4*>(hh);
+            }
+          }
+          __syncwarp();
+          const int col = round * 32 * CHUNKS + piece * 8;
+#pragma unroll
+          for (int i = 0; i < PIECES; ++i) {
+            const int rr = rsub + ROWS_PER_ST * i;
+            const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * SCATTER_ROW + ((piece ^ (rr & (PIECES - 1))) << 4));
+            if (drow[i] != nullptr && n0 + col < p.N) *reinterpret_cast<uint4*>(drow[i] + col) = v;
+          }
+          __syncwarp();
+        }
+      } else
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t acc[32];
         tmem_ld_32x32(t_addr + c * 32, acc);
         tmem_ld_wait();
         if (row_ok) {
-          uint4 held = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
           for (int g8 = 0; g8 < 4; ++g8) {
             const int col = c * 32 + g8 * 8;
@@ -544,21 +593,6 @@ qmm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ C
                 h[0] = __floats2bfloat162_rn(o[0], o[1]);
                 h[1] = __floats2bfloat162_rn(o[2], o[3]);
                 *reinterpret_cast<uint2*>(yrow + col / 2) = *reinterpret_cast<uint2*>(h);
-              }
-            } else if constexpr (EPI == MFX_EPI_PEER_SCATTER) {
-              // two groups of eight columns go out as one 32-byte store: peer memory is reached over NVLink, where
-              // a 32-byte write costs one header for two data flits instead of one for one
-              __nv_bfloat162 h[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-              const uint4 cur = *reinterpret_cast<uint4*>(h);
-              if (g8 & 1) {
-                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(yrow + col - 8),
-                             "r"(held.x), "r"(held.y), "r"(held.z), "r"(held.w), "r"(cur.x), "r"(cur.y), "r"(cur.z),
-                             "r"(cur.w)
-                             : "memory");
-              } else {
-                held = cur;
               }
             } else if constexpr (sizeof(OUT) == 4) {
               if constexpr (EPI == MFX_EPI_GATE_RESIDUAL) {
@@ -611,7 +645,7 @@ MFX_DEFINE_STATUS_READER(read_status)
 template <int BITS, uint32_t WF, int ST, int SD, typename OUT, int EPI, bool EXT>
 int launch_epi(const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tsb, const CUtensorMap& tt,
                const CUtensorMap& tlb, const Params& p, int grid, cudaStream_t st) {
-  using L = Smem<BITS, ST, SD>;
+  using L = Smem<BITS, ST, SD, EPI == MFX_EPI_PEER_SCATTER ? 4 * 32 * (BITS == 4 ? 128 : 64) : 0>;
   // eight dequantizer warps keep up with the tensor pipe for both widths (8-bit codes go through packed float32
   // arithmetic, five instructions per pair) and draw less power than sixteen
   constexpr int NDQ = 8;
@@ -959,6 +993,8 @@ int run(const mfx_qlinear_args& a, cudaStream_t st) {
   const int grid = 2 * (p.total_tiles < pairs ? p.total_tiles : pairs);
   const bool f32 = f32_out;
   if (kb == 4) {
+    // the scatter epilogue's staging tile takes the room of the third dequantized-weight stage
+    if (scatter) return launch<4, FMT_BF16, 3, 2, __nv_bfloat16>(tx, tw, tsb, tt, tlb, p, grid, st);
     return f32 ? launch<4, FMT_BF16, 3, 3, float>(tx, tw, tsb, tt, tlb, p, grid, st)
                : launch<4, FMT_BF16, 3, 3, __nv_bfloat16>(tx, tw, tsb, tt, tlb, p, grid, st);
   }

@@ -26,7 +26,7 @@ namespace tp {
 
 constexpr int THREADS = 128;
 constexpr int MAX_D = 4096;
-constexpr int E = 4;
+constexpr int E = 8;   // elements per thread and vector: 16-byte bf16 stores to the peers
 constexpr int MAXV = MAX_D / E / THREADS;
 
 enum : int { DEV_TIMEOUT_TP = 110 };
@@ -55,18 +55,20 @@ __device__ __forceinline__ float ld_scalar(const void* p, int dtype, int64_t i) 
   if (dtype == MFX_BF16) return __bfloat162float(__ldg(static_cast<const __nv_bfloat16*>(p) + i));
   return __half2float(__ldg(static_cast<const __half*>(p) + i));
 }
-__device__ __forceinline__ void ld4(const void* p, int dtype, int64_t off, float (&o)[4]) {
+__device__ __forceinline__ void ldv(const void* p, int dtype, int64_t off, float (&o)[E]) {
   if (dtype == MFX_BF16) {
-    const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(p) + off);
+    const uint4 raw = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p) + off);
     const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&raw);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) o[i] = __bfloat162float(h[i]);
+    for (int i = 0; i < E; ++i) o[i] = __bfloat162float(h[i]);
   } else if (dtype == MFX_F32) {
     const float4 a = *reinterpret_cast<const float4*>(static_cast<const float*>(p) + off);
+    const float4 b = *(reinterpret_cast<const float4*>(static_cast<const float*>(p) + off) + 1);
     o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w;
+    o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
   } else {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) o[i] = ld_scalar(p, dtype, off + i);
+    for (int i = 0; i < E; ++i) o[i] = ld_scalar(p, dtype, off + i);
   }
 }
 __device__ __forceinline__ float block_sum(float v, float* red) {
@@ -108,25 +110,26 @@ __global__ void __launch_bounds__(THREADS) tp_fuse_kernel(const mfx_tp_fuse_args
     for (int k = 0; k < MAXV; ++k) {
       const int c = tid + THREADS * k;
       if (c < nvec) {
-        const float4 xv = *reinterpret_cast<const float4*>(x + static_cast<int64_t>(c) * E);
-        v[k][0] = xv.x; v[k][1] = xv.y; v[k][2] = xv.z; v[k][3] = xv.w;
+        ldv(x, MFX_F32, static_cast<int64_t>(c) * E, v[k]);
         if (p.partials != nullptr) {
-          float acc[E] = {0.f, 0.f, 0.f, 0.f};
+          float acc[E] = {};
           for (int src = 0; src < p.world; ++src) {   // fixed order: the sum does not depend on arrival order
             const __nv_bfloat16* part = static_cast<const __nv_bfloat16*>(p.partials) +
                                         ((static_cast<int64_t>(src) * p.batch + b) * R + i) * p.D;
             // written by a peer over NVLink: read around L1
-            const uint2 raw = __ldcg(reinterpret_cast<const uint2*>(part + static_cast<int64_t>(c) * E));
+            const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(part + static_cast<int64_t>(c) * E));
             const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&raw);
 #pragma unroll
             for (int j = 0; j < E; ++j) acc[j] += __bfloat162float(h[j]);
           }
-          float bias[E] = {0.f, 0.f, 0.f, 0.f}, gate[E];
-          if (p.bias[seg]) ld4(p.bias[seg], p.bias_dtype, static_cast<int64_t>(c) * E, bias);
-          ld4(p.gate[seg], p.mod_dtype, b * p.mod_batch_stride + static_cast<int64_t>(c) * E, gate);
+          float bias[E] = {}, gate[E];
+          if (p.bias[seg]) ldv(p.bias[seg], p.bias_dtype, static_cast<int64_t>(c) * E, bias);
+          ldv(p.gate[seg], p.mod_dtype, b * p.mod_batch_stride + static_cast<int64_t>(c) * E, gate);
 #pragma unroll
           for (int j = 0; j < E; ++j) v[k][j] += gate[j] * (acc[j] + bias[j]);
-          *reinterpret_cast<float4*>(x + static_cast<int64_t>(c) * E) = make_float4(v[k][0], v[k][1], v[k][2], v[k][3]);
+          float4* xo = reinterpret_cast<float4*>(x + static_cast<int64_t>(c) * E);
+          xo[0] = make_float4(v[k][0], v[k][1], v[k][2], v[k][3]);
+          xo[1] = make_float4(v[k][4], v[k][5], v[k][6], v[k][7]);
         }
 #pragma unroll
         for (int j = 0; j < E; ++j) sum += v[k][j];
@@ -154,23 +157,28 @@ __global__ void __launch_bounds__(THREADS) tp_fuse_kernel(const mfx_tp_fuse_args
         if (c < nvec) {
           float sc[E], sh[E];
           const int64_t moff = b * p.mod_batch_stride + static_cast<int64_t>(c) * E;
-          ld4(p.scale[seg], p.mod_dtype, moff, sc);
-          ld4(p.shift[seg], p.mod_dtype, moff, sh);
-          __nv_bfloat162 h[2];
-          h[0] = __floats2bfloat162_rn((v[k][0] - mean) * rstd * (1.0f + sc[0]) + sh[0],
-                                       (v[k][1] - mean) * rstd * (1.0f + sc[1]) + sh[1]);
-          h[1] = __floats2bfloat162_rn((v[k][2] - mean) * rstd * (1.0f + sc[2]) + sh[2],
-                                       (v[k][3] - mean) * rstd * (1.0f + sc[3]) + sh[3]);
-          const uint2 out = *reinterpret_cast<uint2*>(h);
-          for (int dst = 0; dst < p.world; ++dst)
-            *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.push_dst[dst]) + row_off +
+          ldv(p.scale[seg], p.mod_dtype, moff, sc);
+          ldv(p.shift[seg], p.mod_dtype, moff, sh);
+          __nv_bfloat162 h[E / 2];
+#pragma unroll
+          for (int j = 0; j < E / 2; ++j)
+            h[j] = __floats2bfloat162_rn((v[k][2 * j] - mean) * rstd * (1.0f + sc[2 * j]) + sh[2 * j],
+                                         (v[k][2 * j + 1] - mean) * rstd * (1.0f + sc[2 * j + 1]) + sh[2 * j + 1]);
+          const uint4 out = *reinterpret_cast<uint4*>(h);
+          if (p.push_local_only) {
+            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.push_dst[p.rank]) + row_off +
                                       static_cast<int64_t>(c) * E) = out;
+          } else {
+            for (int dst = 0; dst < p.world; ++dst)
+              *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.push_dst[dst]) + row_off +
+                                        static_cast<int64_t>(c) * E) = out;
+          }
         }
       }
     }
   }
 
-  if (p.scale[0] == nullptr && p.scale[1] == nullptr) return;   // nothing was pushed, nobody waits for this call
+  if (p.push_local_only || (p.scale[0] == nullptr && p.scale[1] == nullptr)) return;   // nobody waits for this call
   // completion: every thread's peer stores are ordered before the block's arrival; the last block tells the peers
   __threadfence_system();
   __syncthreads();
@@ -187,6 +195,16 @@ __global__ void __launch_bounds__(THREADS) tp_fuse_kernel(const mfx_tp_fuse_args
 __global__ void tp_wait_kernel(const int* flags, int world, int target, const int* epoch_base) {
   if (epoch_base) target += __ldg(epoch_base);
   if (static_cast<int>(threadIdx.x) < world) wait_counter(flags + threadIdx.x, target);
+}
+
+struct SignalArgs {
+  int* flags[MFX_TP_MAX_WORLD];
+};
+__global__ void tp_signal_kernel(const SignalArgs a, int world) {
+  if (static_cast<int>(threadIdx.x) < world) {
+    __threadfence_system();
+    red_release_sys_add(a.flags[threadIdx.x], 1);
+  }
 }
 
 MFX_DEFINE_STATUS_READER(read_status)
@@ -206,7 +224,7 @@ int mfx_tp_fuse(const mfx_tp_fuse_args* a, void* stream) {
   if (a->batch * a->rows_per_rank > (1ll << 30)) return MFX_ERR_TOO_LARGE;
   if (!a->x || !a->done_counter) return MFX_ERR_NULL;
   if (!aligned16(a->x) || (a->partials && !aligned16(a->partials))) return MFX_ERR_ALIGN;
-  if (!valid_dtype(a->mod_dtype) || (a->mod_batch_stride * static_cast<int64_t>(dtype_size(a->mod_dtype))) % 8 != 0)
+  if (!valid_dtype(a->mod_dtype) || (a->mod_batch_stride * static_cast<int64_t>(dtype_size(a->mod_dtype))) % 16 != 0)
     return MFX_ERR_DTYPE;
   const bool norm = a->scale[0] != nullptr || a->scale[1] != nullptr;
   for (int s = 0; s < 2; ++s) {
@@ -221,6 +239,21 @@ int mfx_tp_fuse(const mfx_tp_fuse_args* a, void* stream) {
   if (int rc = check_arch()) return rc;
   const unsigned blocks = static_cast<unsigned>(a->batch * a->rows_per_rank);
   tp::tp_fuse_kernel<<<blocks, tp::THREADS, 0, static_cast<cudaStream_t>(stream)>>>(*a);
+  MFX_CUDA_TRY(cudaGetLastError());
+  return MFX_OK;
+}
+
+int mfx_tp_signal(int* const* flags, int world, void* stream) {
+  using namespace mfx;
+  if (!flags) return MFX_ERR_NULL;
+  if (world < 1 || world > MFX_TP_MAX_WORLD) return MFX_ERR_SHAPE;
+  tp::SignalArgs a;
+  for (int r = 0; r < world; ++r) {
+    if (!flags[r]) return MFX_ERR_NULL;
+    a.flags[r] = flags[r];
+  }
+  if (int rc = check_arch()) return rc;
+  tp::tp_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(a, world);
   MFX_CUDA_TRY(cudaGetLastError());
   return MFX_OK;
 }

@@ -584,6 +584,15 @@ def tp_fuse(args) -> None:
     LAUNCHES[0] += 1
 
 
+def tp_signal(flag_ptrs, world: int) -> None:
+    """Adds 1 to the int32 counters at the `world` device addresses in `flag_ptrs` (one per rank, peer-mapped) on
+    the current stream: the arrival signal after stream-ordered copies to the peers."""
+    lib = _lib.load()
+    arr = (c_void_p * world)(*[int(v) for v in flag_ptrs[:world]])
+    _lib.check(lib.mfx_tp_signal(arr, world, _stream()), "mfx_tp_signal")
+    LAUNCHES[0] += 1
+
+
 def tp_wait(flags: torch.Tensor, world: int, target: int, epoch_base: torch.Tensor | None = None) -> None:
     """Enqueues a bounded wait until the local counters flags[0:world] (int32, bumped by the peers) reach
     target (+ the device int epoch_base[0] when given)."""

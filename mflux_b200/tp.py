@@ -28,7 +28,8 @@ _DT = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.float16: _lib.F
 
 
 class PeerExchange:
-    def __init__(self, group, rank: int, world: int, batch: int, seq: int, split: int, dim: int, device):
+    def __init__(self, group, rank: int, world: int, batch: int, seq: int, split: int, dim: int, device,
+                 copy_engine_gather: bool = True):
         import torch.distributed._symmetric_memory as symm
 
         if world > _lib.TP_MAX_WORLD:
@@ -54,6 +55,14 @@ class PeerExchange:
         self.epoch_base = torch.zeros(2, dtype=torch.int32, device=device)   # [0] part arrivals, [1] nbuf arrivals
         self.x = torch.zeros(batch, self.rows, dim, dtype=torch.float32, device=device)   # owned residual rows
         self.rs_count = self.ag_count = 0       # arrivals issued so far in the current forward pass
+        # All-gather by the copy engines: tp_fuse stores the normalised rows locally only; this rank's rows then go
+        # to every peer as stream-ordered device-to-device copies on a side stream (NVLink, no SMs), followed by
+        # the arrival signal, while the main stream already runs the matmuls over the rank's own rows.
+        self.copy_engine_gather = copy_engine_gather
+        self.copy_stream = torch.cuda.Stream(device=device)
+        self.peer_nbuf = [self.handle.get_buffer(r, (batch, self.seq_pad, dim), torch.bfloat16, 0)
+                          for r in range(world)]
+        self.ag_flag_ptrs = [self.bases[r] + self._off_flags + 4 * (world + rank) for r in range(world)]
         torch.cuda.synchronize(device)
         self.handle.barrier()                    # every rank's buffer is zeroed before anyone writes into it
 
@@ -71,6 +80,8 @@ class PeerExchange:
 
     def end(self) -> None:
         """Advances the device-side epoch bases by what this pass added (stream-ordered, so capturable)."""
+        if self.copy_engine_gather:
+            self.join()
         self.epoch_base += self._delta()
 
     def _delta(self):
@@ -128,11 +139,30 @@ class PeerExchange:
         if pushes:
             for r in range(self.world):
                 a.push_dst[r] = self.bases[r]
-                a.ag_flags[r] = self.bases[r] + self._off_flags + 4 * (self.world + self.rank)
+                a.ag_flags[r] = self.ag_flag_ptrs[r]
+            a.push_local_only = int(self.copy_engine_gather)
         a.done_counter = self.local.data_ptr() + 4
         ops.tp_fuse(a)
         if pushes:
             self.ag_count += 1
+            if self.copy_engine_gather:
+                self._copy_rows_to_peers()
+
+    def _copy_rows_to_peers(self) -> None:
+        main = torch.cuda.current_stream()
+        self.copy_stream.wait_stream(main)
+        lo, hi = self.lo, min(self.seq, self.lo + self.rows)
+        with torch.cuda.stream(self.copy_stream):
+            if hi > lo:
+                for r in range(self.world):
+                    if r != self.rank:
+                        for b in range(self.batch):   # one contiguous block per sample: a plain device-to-device copy
+                            self.peer_nbuf[r][b, lo:hi].copy_(self.nbuf[b, lo:hi], non_blocking=True)
+            ops.tp_signal(self.ag_flag_ptrs, self.world)
+
+    def join(self) -> None:
+        """The main stream waits for the side stream's copies (end of a pass; needed before a capture ends)."""
+        torch.cuda.current_stream().wait_stream(self.copy_stream)
 
     def wait_gathered(self) -> None:
         """Stream-ordered wait until every rank's rows of the latest all-gather sit in the local nbuf."""
