@@ -22,6 +22,8 @@
 // All waits are bounded.
 #include <cuda_bf16.h>
 
+#include <cstdlib>
+
 #include "host_util.cuh"
 #include "ptx.cuh"
 
@@ -150,13 +152,14 @@ __device__ __forceinline__ void exp2_poly2(uint64_t x2, float& p0, float& p1) {
 constexpr uint32_t POLY_PAIRS = 0x8888u;
 
 // p = 2^(s * scale - m) for 32 scores, bf16 pairs into pk, float sums into lsum2.
+template <uint32_t POLY = POLY_PAIRS>
 __device__ __forceinline__ void exp_chunk(const uint32_t (&s)[32], uint64_t scale2, uint64_t negm2, uint64_t& lsum2,
                                           uint32_t (&pk)[16]) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
     const uint64_t x2 = fma2(pack2(__uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1])), scale2, negm2);
     float p0, p1;
-    if ((POLY_PAIRS >> i) & 1u) {
+    if ((POLY >> i) & 1u) {
       exp2_poly2(x2, p0, p1);
     } else {
       float x0, x1;
@@ -219,7 +222,7 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    if (elect_one()) {
       mbar_arrive_expect_tx(q_full, Q_BYTES);
       tma_load_4d(q_s, &tmap_q, q_full, 0, h, q0, b);
       tma_load_4d(q_s + Q_HALF, &tmap_q, q_full, 64, h, q0, b);
@@ -231,7 +234,7 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       const uint32_t ph = static_cast<uint32_t>((j >> 1) & 1);
       // the stage is free once S of the tile that used it (j - 2) is complete: that is what s_full signals
       if (j >= 2 && !mbar_wait(s_full + 8 * st, ph ^ 1u, DEV_TIMEOUT_ATTN)) break;
-      if (lane == 0) {
+      if (elect_one()) {
         mbar_arrive_expect_tx(k_full + 8 * st, KV_BYTES);
         tma_load_4d(k_s + st * KV_BYTES, &tmap_k, k_full + 8 * st, 0, h, j * BKV, b);
         tma_load_4d(k_s + st * KV_BYTES + KV_HALF, &tmap_k, k_full + 8 * st, 64, h, j * BKV, b);
@@ -243,7 +246,7 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       const int st = j & 1;
       const uint32_t ph = static_cast<uint32_t>((j >> 1) & 1);
       if (!mbar_wait(v_empty + 8 * st, ph ^ 1u, DEV_TIMEOUT_ATTN)) break;
-      if (lane == 0) {
+      if (elect_one()) {
         mbar_arrive_expect_tx(v_full + 8 * st, KV_BYTES);
         tma_load_4d(v_s + st * KV_BYTES, &tmap_v, v_full + 8 * st, 0, h, j * BKV, b);
         tma_load_4d(v_s + st * KV_BYTES + KV_HALF, &tmap_v, v_full + 8 * st, 64, h, j * BKV, b);
@@ -263,7 +266,7 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       if (!mbar_wait(k_full + 8 * st, ph, DEV_TIMEOUT_ATTN)) break;
       if (t >= 2 && !mbar_wait(v_empty + 8 * st, ph ^ 1u, DEV_TIMEOUT_ATTN)) break;
       tc_fence_after();
-      if (lane == 0) {
+      if (elect_one()) {
 #pragma unroll
         for (int i = 0; i < HD / 16; ++i) {
           // half of d, then 32 B per 16 d inside the 128-byte rows
@@ -284,7 +287,7 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       if (!mbar_wait(p_full + 8 * st, ph, DEV_TIMEOUT_ATTN) || !mbar_wait(v_full + 8 * st, ph, DEV_TIMEOUT_ATTN))
         break;
       tc_fence_after();
-      if (lane == 0) {
+      if (elect_one()) {
 #pragma unroll
         for (int i = 0; i < BKV / 16; ++i) {
           // A: 16 keys of P = 8 TMEM columns (the 32 keys of softmax part p at columns 32 p .. 32 p + 15 of the
@@ -460,6 +463,361 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------------------
+// Ping-pong variant: one CTA per SM works on two 128-query tiles of the same (sample, head) against the same
+// stream of 128-key tiles. Tensor memory holds S0 | S1 | O0 | O1 (4 x 128 columns). The products are issued in the
+// order P0(j) V(j), S0(j+1) = Q0 K(j+1)^T, P1(j) V(j), S1(j+1): while the softmax of one query tile runs, the
+// tensor pipe works for the other, and because the pipe executes one thread's products in order, S_t(j+1) may
+// overwrite the columns P_t(j) occupied without a wait. 576 threads:
+//   warps 0-15 softmax: warp = 8 * tile + 4 * half + quarter. Two threads per query row, one per 64-key half of
+//              the tile: scores of the half in registers, row maximum swapped with the partner through shared
+//              memory, stale running maximum, exponentials split between the special-function unit and an
+//              FMA-pipe cubic, P as bf16 pairs over the first 32 columns of the thread's own S half, the rare
+//              rescale of O and the final O / rowsum -> global (each thread 64 columns of d). Four softmax warps
+//              per scheduler: one warp alone issues an instruction every third clock.
+//   warp 16    TMA producer: both Q tiles and K(0) once, then the pairs {V(j), K(j+1)} through two 64 KiB slots
+//              (one barrier wait per pair on the issuing side; K(0) borrows the K half of slot 1)
+//   warp 17    allocates the 512 columns and issues every product
+namespace pp {
+
+constexpr int BK = 128;                       // keys per tile
+constexpr int NUM_SM_WARPS = 16;
+constexpr int PRODUCER_WARP = NUM_SM_WARPS, ISSUER_WARP = NUM_SM_WARPS + 1;
+constexpr int NT = (ISSUER_WARP + 1) * 32;
+constexpr int SLOTS = 2;                      // ring slots of 64 KiB: V(j) and K(j+1) travel together
+#ifndef MFX_PP_POLY
+#define MFX_PP_POLY 0x8888u
+#endif
+constexpr uint32_t PP_POLY = MFX_PP_POLY;   // pairs of a 32-key chunk whose exponential runs on the FMA pipe
+constexpr int TILE_BYTES = 128 * HD * 2;      // 32 KiB, two 16 KiB halves of d, for a Q tile and for a K or V tile
+constexpr int TILE_HALF = TILE_BYTES / 2;
+constexpr uint32_t COL_S0 = 0, COL_O0 = 256;  // + 128 for the second query tile
+constexpr int OFF_Q2 = 0;
+constexpr int OFF_KV = OFF_Q2 + 2 * TILE_BYTES;
+constexpr int OFF_BAR2 = OFF_KV + SLOTS * 2 * TILE_BYTES;
+constexpr int NUM_BARS2 = 1 + 2 * SLOTS + 7;
+constexpr int OFF_TMEM2 = OFF_BAR2 + NUM_BARS2 * 8;
+constexpr int OFF_XCH2 = (OFF_TMEM2 + 16 + 15) / 16 * 16;   // float [2 parities][2 tiles][4 quarters][2 halves][32 rows]
+constexpr int XCH2_FLOATS = 2 * 4 * 2 * 32;
+constexpr int DYN_BYTES2 = OFF_XCH2 + 2 * XCH2_FLOATS * 4 + 1024;
+static_assert(DYN_BYTES2 <= 227 * 1024, "shared memory of the ping-pong kernel");
+
+// scores -> s * scale * log2(e) + bias * log2(e) for one 32-key chunk starting at key k0 (keys < `valid` exist)
+__device__ __forceinline__ void add_bias_chunk(uint32_t (&s)[32], const float* bp, int valid, float scale_log2) {
+  constexpr float LOG2E = 1.4426950408889634f;
+  if (valid >= 32) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float4 bv = __ldg(reinterpret_cast<const float4*>(bp) + i);
+      s[4 * i + 0] = __float_as_uint(fmaf(__uint_as_float(s[4 * i + 0]), scale_log2, bv.x * LOG2E));
+      s[4 * i + 1] = __float_as_uint(fmaf(__uint_as_float(s[4 * i + 1]), scale_log2, bv.y * LOG2E));
+      s[4 * i + 2] = __float_as_uint(fmaf(__uint_as_float(s[4 * i + 2]), scale_log2, bv.z * LOG2E));
+      s[4 * i + 3] = __float_as_uint(fmaf(__uint_as_float(s[4 * i + 3]), scale_log2, bv.w * LOG2E));
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float bv = i < valid ? __ldg(bp + i) : 0.f;
+      s[i] = __float_as_uint(fmaf(__uint_as_float(s[i]), scale_log2, bv * LOG2E));
+    }
+  }
+}
+
+// keys past the end of the sequence get a score of -inf (weight 0)
+__device__ __forceinline__ void mask_chunk(uint32_t (&s)[32], int valid) {
+#pragma unroll
+  for (int i = 0; i < 32; ++i)
+    if (i >= valid) s[i] = __float_as_uint(-INFINITY);
+}
+
+template <bool HAS_BIAS>
+__global__ void __launch_bounds__(NT, 1)
+fmha_pingpong_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                     const __grid_constant__ CUtensorMap tmap_v, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t q_s = smem_base + OFF_Q2, kv_s = smem_base + OFF_KV;
+  const uint32_t bar0 = smem_base + OFF_BAR2;
+  const uint32_t q_full = bar0, kv_full = bar0 + 8, kv_empty = kv_full + 8 * SLOTS, s_full = kv_empty + 8 * SLOTS,
+                 p_first = s_full + 16, p_full = p_first + 16, o_full = p_full + 16;   // s_full, p_first, p_full: per query tile
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + OFF_TMEM2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q0 = blockIdx.x * (2 * BQ);
+  const int h = blockIdx.y;
+  const int b = blockIdx.z;
+  const int n_tiles = (p.seq + BK - 1) / BK;
+  const bool two = q0 + BQ < p.seq;   // the last block of a sequence may hold one query tile only
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+#pragma unroll
+    for (int i = 0; i < SLOTS; ++i) {
+      mbar_init(kv_full + 8 * i, 1);
+      mbar_init(kv_empty + 8 * i, 1);
+    }
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(s_full + 8 * t, 1);
+      mbar_init(p_first + 8 * t, 8);
+      mbar_init(p_full + 8 * t, 8);
+    }
+    mbar_init(o_full, 1);
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == ISSUER_WARP) {
+    tmem_alloc(smem_base + OFF_TMEM2, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == PRODUCER_WARP) {
+    // ------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      mbar_arrive_expect_tx(q_full, (two ? 2 : 1) * TILE_BYTES);
+      for (int t = 0; t < (two ? 2 : 1); ++t) {
+        tma_load_4d(q_s + t * TILE_BYTES, &tmap_q, q_full, 0, h, q0 + t * BQ, b);
+        tma_load_4d(q_s + t * TILE_BYTES + TILE_HALF, &tmap_q, q_full, 64, h, q0 + t * BQ, b);
+      }
+    }
+    __syncwarp();
+    // K(0) into the K half of slot 1, then pair j = {V(j), K(j+1)} into slot j & 1. Slot 1 therefore completes
+    // one phase more than slot 0 at the same pair index.
+    if (elect_one()) {
+      mbar_arrive_expect_tx(kv_full + 8, TILE_BYTES);
+      tma_load_4d(kv_s + 3 * TILE_BYTES, &tmap_k, kv_full + 8, 0, h, 0, b);
+      tma_load_4d(kv_s + 3 * TILE_BYTES + TILE_HALF, &tmap_k, kv_full + 8, 64, h, 0, b);
+    }
+    __syncwarp();
+    for (int j = 0; j < n_tiles; ++j) {
+      const int slot = j & 1;
+      const int use = (j >> 1) + slot;          // how often the slot was filled before
+      if (use >= 1 && !mbar_wait(kv_empty + 8 * slot, static_cast<uint32_t>((use - 1) & 1), DEV_TIMEOUT_ATTN)) break;
+      if (elect_one()) {
+        const bool more = j + 1 < n_tiles;
+        const uint32_t dst = kv_s + slot * 2 * TILE_BYTES;
+        mbar_arrive_expect_tx(kv_full + 8 * slot, (more ? 2 : 1) * TILE_BYTES);
+        tma_load_4d(dst, &tmap_v, kv_full + 8 * slot, 0, h, j * BK, b);
+        tma_load_4d(dst + TILE_HALF, &tmap_v, kv_full + 8 * slot, 64, h, j * BK, b);
+        if (more) {
+          tma_load_4d(dst + TILE_BYTES, &tmap_k, kv_full + 8 * slot, 0, h, (j + 1) * BK, b);
+          tma_load_4d(dst + TILE_BYTES + TILE_HALF, &tmap_k, kv_full + 8 * slot, 64, h, (j + 1) * BK, b);
+        }
+      }
+      __syncwarp();
+    }
+  } else if (warp == ISSUER_WARP) {
+    // ------------------------------------------------------------ issuer of every product
+    // Order P0(j) V(j), S0(j+1), P1(j) V(j), S1(j+1). The commit after S_t(j+1) also covers P_t(j) V(j): a softmax
+    // warp that sees S_t(j+1) may rescale O_t. P V starts once the first 32 keys of both halves of P are stored.
+    // The whole warp runs the loop and its waits; elect_one() picks the issuing thread per block of products.
+    // (A region guarded by `lane == 0` is divergent code to the compiler: operands are then built in vector
+    // registers and moved to uniform registers one product at a time, and that instruction chain starves behind
+    // the softmax warps of the same scheduler: 90-110 clocks per product instead of 64.)
+    constexpr uint32_t IDESC_S = make_idesc(FMT_BF16, FMT_BF16, BQ, BK);        // K-major x K-major
+    constexpr uint32_t IDESC_O = make_idesc_b_mn(FMT_BF16, FMT_BF16, BQ, HD);   // P (TMEM) x V (MN-major)
+    // S_t = Q_t K^T (called by the elected thread)
+    auto issue_s = [&](int t, uint32_t kaddr) {
+#pragma unroll
+      for (int i = 0; i < HD / 16; ++i) {
+        const uint32_t off = (i >> 2) * TILE_HALF + (i & 3) * 32;   // half of d, then 32 B per 16 d
+        umma_f16_ss(tmem_base + COL_S0 + 128 * t, smem_desc_sw128(q_s + t * TILE_BYTES + off),
+                    smem_desc_sw128(kaddr + off), IDESC_S, i != 0 ? 1u : 0u);
+      }
+      umma_commit(s_full + 8 * t);
+    };
+    // One part of P_t(j) V(j) (called by the elected thread). A = 16 keys of P = 8 columns of bf16 pairs (each
+    // 64-key half of P lies over the first 32 columns of its own half of S); B = 16 key rows of V, 2048 B per 16
+    // keys, d halves TILE_HALF apart. Part 0 = the first 32 keys of either half (what every softmax thread stores
+    // first).
+    auto issue_pv_part = [&](int t, int part, uint32_t vaddr, bool first_tile) {
+#pragma unroll
+      for (int ii = 0; ii < BK / 32; ++ii) {
+        const int i = (ii >> 1) * 4 + part * 2 + (ii & 1);   // 16-key groups 0,1,4,5 or 2,3,6,7
+        umma_f16_ts(tmem_base + COL_O0 + 128 * t, tmem_base + COL_S0 + 128 * t + 64 * (i >> 2) + 8 * (i & 3),
+                    smem_desc_sw128_mn(vaddr + i * 2048, TILE_HALF), IDESC_O,
+                    (first_tile && part == 0 && ii == 0) ? 0u : 1u);
+      }
+    };
+    bool ok = mbar_wait(q_full, 0, DEV_TIMEOUT_ATTN) && mbar_wait(kv_full + 8, 0, DEV_TIMEOUT_ATTN);
+    if (ok) {
+      tc_fence_after();
+      if (elect_one()) {
+        issue_s(0, kv_s + 3 * TILE_BYTES);
+        if (two) issue_s(1, kv_s + 3 * TILE_BYTES);
+        umma_commit(kv_empty + 8);
+      }
+      __syncwarp();
+    }
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const uint32_t ph = static_cast<uint32_t>(j & 1);
+      const bool more = j + 1 < n_tiles;
+      const int slot = j & 1;
+      // every scalar step here costs the issuing warp 25-170 clocks while the pipe holds ~300 clocks of queued
+      // products: one barrier per operand pair, one elected region per wait
+      if (!mbar_wait_ready(kv_full + 8 * slot, static_cast<uint32_t>(((j >> 1) + slot) & 1), DEV_TIMEOUT_ATTN)) break;
+      const uint32_t vaddr = kv_s + slot * 2 * TILE_BYTES, kaddr = vaddr + TILE_BYTES;
+      if (!mbar_wait_ready(p_first, ph, DEV_TIMEOUT_ATTN)) break;
+      tc_fence_after();
+      if (elect_one()) issue_pv_part(0, 0, vaddr, j == 0);
+      __syncwarp();   // the other lanes must not poll the next barrier in between the elected lane's products
+      if (!mbar_wait(p_full, ph, DEV_TIMEOUT_ATTN)) break;
+      tc_fence_after();
+      if (elect_one()) {
+        issue_pv_part(0, 1, vaddr, false);
+        if (more) issue_s(0, kaddr);
+        if (!two) umma_commit(more ? kv_empty + 8 * slot : o_full);
+      }
+      __syncwarp();
+      if (two) {
+        if (!mbar_wait_ready(p_first + 8, ph, DEV_TIMEOUT_ATTN)) break;
+        tc_fence_after();
+        if (elect_one()) issue_pv_part(1, 0, vaddr, j == 0);
+        __syncwarp();
+        if (!mbar_wait(p_full + 8, ph, DEV_TIMEOUT_ATTN)) break;
+        tc_fence_after();
+        if (elect_one()) {
+          issue_pv_part(1, 1, vaddr, false);
+          if (more) issue_s(1, kaddr);
+          umma_commit(more ? kv_empty + 8 * slot : o_full);
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp < 8 || two) {
+    // ------------------------------------------------------------ softmax + output (two threads per query row)
+    const int t = warp >> 3;          // query tile
+    const int hf = (warp >> 2) & 1;   // which 64 of the tile's 128 keys (and which 64 columns of d at the end)
+    const int qd = warp & 3;          // TMEM lane quarter this warp may access
+    const int row = qd * 32 + lane;
+    const uint32_t t_row = tmem_base + (static_cast<uint32_t>(qd * 32) << 16);
+    const uint32_t t_s = t_row + COL_S0 + 128 * t + 64 * hf;   // own S columns; own P goes over the first 32
+    const uint32_t t_o = t_row + COL_O0 + 128 * t + 64 * hf;   // own O columns
+    const uint32_t my_s_full = s_full + 8 * t, my_p_first = p_first + 8 * t, my_p_full = p_full + 8 * t;
+    float* xch = reinterpret_cast<float*>(smem_gen + OFF_XCH2);
+    const int xch_mine = ((t * 4 + qd) * 2 + hf) * 32 + lane, xch_other = ((t * 4 + qd) * 2 + (hf ^ 1)) * 32 + lane;
+    const uint32_t pair_bar = 1 + t * 4 + qd;   // named barrier of the two warps that share these rows
+    const float sc = HAS_BIAS ? 1.0f : p.scale_log2;
+    float m_ref = -INFINITY, l_sum = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      if (!mbar_wait(my_s_full, static_cast<uint32_t>(j & 1), DEV_TIMEOUT_ATTN)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint32_t sa[32], sb[32];
+      tmem_ld_32x32(t_s, sa);
+      tmem_ld_32x32(t_s + 32, sb);
+      tmem_ld_fence(sa);
+      tmem_ld_fence(sb);
+      const int keys_here = p.seq - j * BK - 64 * hf;   // >= 64 except on the last tile of a ragged sequence
+      if constexpr (HAS_BIAS) {
+        const float* bp = p.key_bias + b * p.bias_batch_stride + j * BK + 64 * hf;
+        add_bias_chunk(sa, bp, keys_here, p.scale_log2);
+        add_bias_chunk(sb, bp + 32, keys_here - 32, p.scale_log2);
+      }
+      if (keys_here < 64) {
+        mask_chunk(sa, keys_here);
+        mask_chunk(sb, keys_here - 32);
+      }
+      const float m_mine = fmaxf(max_chunk(sa, -INFINITY), max_chunk(sb, -INFINITY));
+      // the partner warp holds the other 64 keys of the same rows: swap maxima (two buffers by tile parity; the
+      // barrier per tile keeps the two warps at most one tile apart)
+      float* x = xch + (j & 1) * XCH2_FLOATS;
+      x[xch_mine] = m_mine;
+      named_bar_sync(pair_bar, 64);
+      const float m_tile = fmaxf(m_mine, x[xch_other]) * sc;
+      // grow the reference maximum only when it would change the exponent range by more than 2^8; both warps of
+      // a row see the same maxima and take the same branch, each rescaling its own half of O
+      const bool grow = m_tile > m_ref + 8.0f;
+      if (__any_sync(0xffffffffu, grow)) {
+        const float m_new = fmaxf(m_ref, m_tile);
+        const float alpha = (m_ref == -INFINITY) ? 0.f : ex2(m_ref - m_new);
+        l_sum *= alpha;
+        if (j > 0) {
+          // P(j-1) V(j-1) has finished: the commit that announced S(j) was issued after it by the same thread
+#pragma unroll 1
+          for (int c = 0; c < 64 / 16; ++c) {
+            uint32_t o[16];
+            tmem_ld_32x16(t_o + c * 16, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x16(t_o + c * 16, o);
+          }
+          tmem_st_wait();
+        }
+        m_ref = m_new;
+      }
+      const uint64_t scale2 = pack2(sc, sc), negm2 = pack2(-m_ref, -m_ref);
+      uint64_t la = pack2(0.f, 0.f), lb = pack2(0.f, 0.f);
+      uint32_t pk[16];
+      exp_chunk<PP_POLY>(sa, scale2, negm2, la, pk);
+      tmem_st_32x16(t_s, pk);
+      // P V can start on the first 32 keys of both halves
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(my_p_first);
+      exp_chunk<PP_POLY>(sb, scale2, negm2, lb, pk);
+      tmem_st_32x16(t_s + 16, pk);
+      float l0, l1;
+      unpack2(add2(la, lb), l0, l1);
+      l_sum += l0 + l1;
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(my_p_full);
+    }
+    if (ok && mbar_wait(o_full, 0, DEV_TIMEOUT_ATTN)) {
+      tc_fence_after();
+      // total row sum = this thread's half + the partner's
+      float* x = xch + (n_tiles & 1) * XCH2_FLOATS;
+      x[xch_mine] = l_sum;
+      named_bar_sync(pair_bar, 64);
+      const float inv = 1.0f / (l_sum + x[xch_other]);
+      const int q = q0 + t * BQ + row;
+      __nv_bfloat16* dst = p.out + b * p.out_batch_stride + static_cast<int64_t>(q) * p.out_row_stride + h * HD +
+                           64 * hf;
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        uint32_t o[32];
+        tmem_ld_32x32(t_o + c * 32, o);
+        tmem_ld_wait();
+        if (q < p.seq) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            __nv_bfloat162 hh[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              hh[i] = __floats2bfloat162_rn(__uint_as_float(o[g * 8 + 2 * i]) * inv,
+                                            __uint_as_float(o[g * 8 + 2 * i + 1]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = *reinterpret_cast<uint4*>(hh);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == ISSUER_WARP) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace pp
+
 MFX_DEFINE_STATUS_READER(read_status)
 
 }  // namespace fmha
@@ -467,6 +825,22 @@ MFX_DEFINE_STATUS_READER(read_status)
 
 namespace mfx {
 namespace fmha {
+
+// Which kernel serves a call. The ping-pong kernel (two query tiles per CTA, one CTA per SM) is the faster main
+// loop (1245-1270 against 1150-1170 TFLOP/s at 16 x 24 heads x 4608 tokens), but its work items are twice as
+// large: it is chosen from 1024 keys on, and only if the last wave of CTAs leaves at most a tenth of the SMs'
+// time unused (2 x 24 heads x 7145 tokens is 9.08 waves of 148: the two-CTAs-per-SM kernel wins there).
+// MFX_FMHA_KERNEL=pingpong | pair overrides the choice.
+static bool use_pingpong(int64_t seq, int64_t batch, int heads) {
+  const char* e = getenv("MFX_FMHA_KERNEL");
+  if (e && e[0] == 'p' && e[1] == 'i') return true;
+  if (e && e[0] == 'p' && e[1] == 'a') return false;
+  if (seq < 1024) return false;
+  const int64_t ctas = (seq + 2 * BQ - 1) / (2 * BQ) * heads * batch;
+  const int64_t sms = device_sm_count();
+  const int64_t waves = (ctas + sms - 1) / sms;
+  return ctas * 10 >= waves * sms * 9;
+}
 
 int run(const void* q, const void* k, const void* v, int64_t qkv_row_stride, int64_t qkv_batch_stride, int64_t seq,
         int64_t batch, int heads, float scale, const float* key_bias, int64_t bias_batch_stride, void* out,
@@ -489,7 +863,8 @@ int run(const void* q, const void* k, const void* v, int64_t qkv_row_stride, int
   const uint64_t bstride = batch > 1 ? static_cast<uint64_t>(qkv_batch_stride) * 2
                                      : static_cast<uint64_t>(qkv_row_stride) * 2 * seq;
   const uint64_t strides[3] = {HD * 2, static_cast<uint64_t>(qkv_row_stride) * 2, bstride};
-  const uint32_t box_q[4] = {64, 1, BQ, 1}, box_kv[4] = {64, 1, BKV, 1};
+  const bool pingpong = use_pingpong(seq, batch, heads);
+  const uint32_t box_q[4] = {64, 1, BQ, 1}, box_kv[4] = {64, 1, static_cast<uint32_t>(pingpong ? pp::BK : BKV), 1};
   const void* ptrs[3] = {q, k, v};
   CUtensorMap* maps[3] = {&tq, &tk, &tv};
   for (int i = 0; i < 3; ++i)
@@ -506,6 +881,25 @@ int run(const void* q, const void* k, const void* v, int64_t qkv_row_stride, int
   p.out = static_cast<__nv_bfloat16*>(out);
   p.out_row_stride = out_row_stride;
   p.out_batch_stride = out_batch_stride;
+  if (pingpong) {
+    dim3 grid(static_cast<unsigned>((seq + 2 * BQ - 1) / (2 * BQ)), static_cast<unsigned>(heads),
+              static_cast<unsigned>(batch));
+    if (key_bias) {
+      static SmemConfigured configured;
+      if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(pp::fmha_pingpong_kernel<true>),
+                                       pp::DYN_BYTES2, configured))
+        return rc;
+      pp::fmha_pingpong_kernel<true><<<grid, pp::NT, pp::DYN_BYTES2, stream>>>(tq, tk, tv, p);
+    } else {
+      static SmemConfigured configured;
+      if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(pp::fmha_pingpong_kernel<false>),
+                                       pp::DYN_BYTES2, configured))
+        return rc;
+      pp::fmha_pingpong_kernel<false><<<grid, pp::NT, pp::DYN_BYTES2, stream>>>(tq, tk, tv, p);
+    }
+    MFX_CUDA_TRY(cudaGetLastError());
+    return MFX_OK;
+  }
   dim3 grid(static_cast<unsigned>((seq + BQ - 1) / BQ), static_cast<unsigned>(heads), static_cast<unsigned>(batch));
   if (key_bias) {
     static SmemConfigured configured;

@@ -106,6 +106,10 @@ def test_validation_of_the_later_entry_points(lib_built):
     assert lib.mfx_tp_fuse(f, None) == -7             # partial sums without gates
     assert lib.mfx_tp_wait(None, 2, 1, None, None) == -7
     assert lib.mfx_tp_wait(1024, 9, 1, None, None) == -1    # more ranks than MFX_TP_MAX_WORLD
+    assert lib.mfx_tp_signal(None, 2, None) == -7
+    ptrs = (ctypes.c_void_p * 2)(1024, None)
+    assert lib.mfx_tp_signal(ptrs, 9, None) == -1           # more ranks than MFX_TP_MAX_WORLD
+    assert lib.mfx_tp_signal(ptrs, 2, None) == -7           # a rank without a counter
     # low-rank term of the quantized matmul
     a.epilogue, a.N, a.y_row_stride = _lib.EPI_NONE, 64, 64
     a.lora_r = 8

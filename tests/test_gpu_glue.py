@@ -80,10 +80,14 @@ def test_qknorm_rope(lib_built):
 
 
 @pytest.mark.parametrize("shape", [(1, 128, 1), (2, 256, 2), (1, 384, 3), (2, 200, 2), (1, 1000, 1), (1, 17, 1), (2, 97, 2),
-                                   (1, 161, 1)])
-def test_fmha(lib_built, shape):
+                                   (1, 161, 1), (1, 1300, 2)])
+@pytest.mark.parametrize("kernel", ["pair", "pingpong"])
+def test_fmha(lib_built, shape, kernel, monkeypatch):
+    """Both attention kernels on every shape: `pair` (one 128-query tile per CTA, two CTAs per SM) and `pingpong`
+    (two query tiles per CTA); the library picks by sequence length and grid size when the variable is unset."""
     from mflux_b200 import ops
 
+    monkeypatch.setenv("MFX_FMHA_KERNEL", kernel)
     b, s, heads = shape
     g = _g(s)
     qkv = torch.randn(b, s, 3 * heads * 128, generator=g).to(torch.bfloat16)
@@ -97,10 +101,12 @@ def test_fmha(lib_built, shape):
     assert err <= TOL, err
 
 
-def test_fmha_peaked_scores_and_strided_output(lib_built):
+@pytest.mark.parametrize("kernel", ["pair", "pingpong"])
+def test_fmha_peaked_scores_and_strided_output(lib_built, kernel, monkeypatch):
     """Large score ranges exercise the running-max rescale; output written into a wider buffer."""
     from mflux_b200 import ops
 
+    monkeypatch.setenv("MFX_FMHA_KERNEL", kernel)
     b, s, heads = 1, 512, 2
     g = _g(99)
     qkv = torch.randn(b, s, 3 * heads * 128, generator=g)
@@ -151,13 +157,15 @@ def test_gate_residual_dense_and_row_range(lib_built, y_dtype):
 
 
 @pytest.mark.parametrize("shape", [(2, 256, 2, 40), (1, 200, 1, 70), (2, 1000, 1, 130), (1, 97, 2, 5)])
-def test_fmha_key_padding_bias(lib_built, shape):
+@pytest.mark.parametrize("kernel", ["pair", "pingpong"])
+def test_fmha_key_padding_bias(lib_built, shape, kernel, monkeypatch):
     """Additive per-key bias as AttentionUtils.convert_key_padding_mask_to_additive_mask builds it
     (attention_utils.py:55-72): the first `pad` keys of sample 0 (text keys come first) carry -1e9, which may
     cover whole 64-key tiles at the start of the sequence; sample 1 keeps every key. rel-L2 <= 1e-2 against the
     float32 oracle, the tolerance north_star states for layer outputs."""
     from mflux_b200 import ops
 
+    monkeypatch.setenv("MFX_FMHA_KERNEL", kernel)
     b, s, heads, pad = shape
     g = _g(s + pad)
     qkv = torch.randn(b, s, 3 * heads * 128, generator=g).to(torch.bfloat16)
@@ -194,3 +202,25 @@ def test_fmha_bias_argument_validation(lib_built):
     # rows of 66 floats: the second sample's bias would not start on a 16-byte boundary; the wrapper re-pads it
     out = ops.fmha(qkv, 1, key_bias=torch.zeros(2, 66, device="cuda")[:, :64])
     assert torch.isfinite(out.float()).all()
+
+
+def test_fmha_default_kernel_choice_matches_both(lib_built, monkeypatch):
+    """With the variable unset the library chooses by shape (here a grid that fills whole waves of CTAs, so the
+    two-query-tile kernel); either way the result is the oracle's."""
+    from mflux_b200 import ops
+
+    monkeypatch.delenv("MFX_FMHA_KERNEL", raising=False)
+    b, s, heads = 37, 1024, 4   # 4 x 4 x 37 = 592 CTAs of two query tiles = exactly 4 waves of 148
+    g = _g(5)
+    qkv = torch.randn(b, s, 3 * heads * 128, generator=g).to(torch.bfloat16).cuda()
+    out = ops.fmha(qkv, heads)
+    torch.cuda.synchronize()
+    assert ops.poll_device_status() == 0
+    hd = heads * 128
+    sample = qkv[3:4].cpu()
+    q, k, v = (blocks.heads_first(sample[..., i * hd:(i + 1) * hd], heads) for i in range(3))
+    ref = blocks.heads_last(blocks.sdpa(q, k, v))
+    assert rel_l2(out[3:4], ref.numpy()) <= TOL
+    for kernel in ("pair", "pingpong"):
+        monkeypatch.setenv("MFX_FMHA_KERNEL", kernel)
+        assert rel_l2(ops.fmha(qkv, heads), out.float().cpu().numpy()) <= 3e-3
