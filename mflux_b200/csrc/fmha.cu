@@ -624,13 +624,17 @@ fmha_pingpong_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     // the softmax warps of the same scheduler: 90-110 clocks per product instead of 64.)
     constexpr uint32_t IDESC_S = make_idesc(FMT_BF16, FMT_BF16, BQ, BK);        // K-major x K-major
     constexpr uint32_t IDESC_O = make_idesc_b_mn(FMT_BF16, FMT_BF16, BQ, HD);   // P (TMEM) x V (MN-major)
+    // Descriptors of the tiles' first bytes; a step inside a tile adds its byte offset >> 4 to the start-address
+    // field (no carry out of it: every tile lies inside the 256 KiB the field spans), one add per operand instead
+    // of rebuilding the descriptor for every product.
+    const uint64_t q_desc0 = smem_desc_sw128(q_s), q_desc1 = smem_desc_sw128(q_s + TILE_BYTES);
     // S_t = Q_t K^T (called by the elected thread)
-    auto issue_s = [&](int t, uint32_t kaddr) {
+    auto issue_s = [&](int t, uint64_t k_desc) {
+      const uint64_t q_desc = t ? q_desc1 : q_desc0;
 #pragma unroll
       for (int i = 0; i < HD / 16; ++i) {
-        const uint32_t off = (i >> 2) * TILE_HALF + (i & 3) * 32;   // half of d, then 32 B per 16 d
-        umma_f16_ss(tmem_base + COL_S0 + 128 * t, smem_desc_sw128(q_s + t * TILE_BYTES + off),
-                    smem_desc_sw128(kaddr + off), IDESC_S, i != 0 ? 1u : 0u);
+        const uint32_t off = ((i >> 2) * TILE_HALF + (i & 3) * 32) >> 4;   // half of d, then 32 B per 16 d
+        umma_f16_ss(tmem_base + COL_S0 + 128 * t, q_desc + off, k_desc + off, IDESC_S, i != 0 ? 1u : 0u);
       }
       umma_commit(s_full + 8 * t);
     };
@@ -638,21 +642,20 @@ fmha_pingpong_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     // 64-key half of P lies over the first 32 columns of its own half of S); B = 16 key rows of V, 2048 B per 16
     // keys, d halves TILE_HALF apart. Part 0 = the first 32 keys of either half (what every softmax thread stores
     // first).
-    auto issue_pv_part = [&](int t, int part, uint32_t vaddr, bool first_tile) {
+    auto issue_pv_part = [&](int t, int part, uint64_t v_desc, bool first_tile) {
 #pragma unroll
       for (int ii = 0; ii < BK / 32; ++ii) {
         const int i = (ii >> 1) * 4 + part * 2 + (ii & 1);   // 16-key groups 0,1,4,5 or 2,3,6,7
         umma_f16_ts(tmem_base + COL_O0 + 128 * t, tmem_base + COL_S0 + 128 * t + 64 * (i >> 2) + 8 * (i & 3),
-                    smem_desc_sw128_mn(vaddr + i * 2048, TILE_HALF), IDESC_O,
-                    (first_tile && part == 0 && ii == 0) ? 0u : 1u);
+                    v_desc + (i * 2048 >> 4), IDESC_O, (first_tile && part == 0 && ii == 0) ? 0u : 1u);
       }
     };
     bool ok = mbar_wait(q_full, 0, DEV_TIMEOUT_ATTN) && mbar_wait(kv_full + 8, 0, DEV_TIMEOUT_ATTN);
     if (ok) {
       tc_fence_after();
       if (elect_one()) {
-        issue_s(0, kv_s + 3 * TILE_BYTES);
-        if (two) issue_s(1, kv_s + 3 * TILE_BYTES);
+        issue_s(0, smem_desc_sw128(kv_s + 3 * TILE_BYTES));
+        if (two) issue_s(1, smem_desc_sw128(kv_s + 3 * TILE_BYTES));
         umma_commit(kv_empty + 8);
       }
       __syncwarp();
@@ -664,7 +667,8 @@ fmha_pingpong_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       // every scalar step here costs the issuing warp 25-170 clocks while the pipe holds ~300 clocks of queued
       // products: one barrier per operand pair, one elected region per wait
       if (!mbar_wait_ready(kv_full + 8 * slot, static_cast<uint32_t>(((j >> 1) + slot) & 1), DEV_TIMEOUT_ATTN)) break;
-      const uint32_t vaddr = kv_s + slot * 2 * TILE_BYTES, kaddr = vaddr + TILE_BYTES;
+      const uint64_t vaddr = smem_desc_sw128_mn(kv_s + slot * 2 * TILE_BYTES, TILE_HALF);
+      const uint64_t kaddr = smem_desc_sw128(kv_s + slot * 2 * TILE_BYTES + TILE_BYTES);
       if (!mbar_wait_ready(p_first, ph, DEV_TIMEOUT_ATTN)) break;
       tc_fence_after();
       if (elect_one()) issue_pv_part(0, 0, vaddr, j == 0);
@@ -828,8 +832,8 @@ namespace fmha {
 
 // Which kernel serves a call. The ping-pong kernel (two query tiles per CTA, one CTA per SM) is the faster main
 // loop (1245-1270 against 1150-1170 TFLOP/s at 16 x 24 heads x 4608 tokens), but its work items are twice as
-// large: it is chosen from 1024 keys on, and only if the last wave of CTAs leaves at most a tenth of the SMs'
-// time unused (2 x 24 heads x 7145 tokens is 9.08 waves of 148: the two-CTAs-per-SM kernel wins there).
+// large: it is chosen from 1024 keys on, and only if the last wave of CTAs leaves at most 7 % of the SMs' time
+// unused (2 x 24 heads x 7145 tokens is 9.08 waves of 148 = 91 %: 1091 against 1158 TFLOP/s, the other kernel wins).
 // MFX_FMHA_KERNEL=pingpong | pair overrides the choice.
 static bool use_pingpong(int64_t seq, int64_t batch, int heads) {
   const char* e = getenv("MFX_FMHA_KERNEL");
@@ -839,7 +843,7 @@ static bool use_pingpong(int64_t seq, int64_t batch, int heads) {
   const int64_t ctas = (seq + 2 * BQ - 1) / (2 * BQ) * heads * batch;
   const int64_t sms = device_sm_count();
   const int64_t waves = (ctas + sms - 1) / sms;
-  return ctas * 10 >= waves * sms * 9;
+  return ctas * 100 >= waves * sms * 93;
 }
 
 int run(const void* q, const void* k, const void* v, int64_t qkv_row_stride, int64_t qkv_batch_stride, int64_t seq,
