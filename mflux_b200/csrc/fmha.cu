@@ -267,12 +267,14 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
       if (t >= 2 && !mbar_wait(v_empty + 8 * st, ph ^ 1u, DEV_TIMEOUT_ATTN)) break;
       tc_fence_after();
       if (elect_one()) {
+        // descriptors of the tiles' first bytes; a step adds its byte offset >> 4 to the start-address field
+        const uint64_t q_desc = smem_desc_sw128(q_s), k_desc = smem_desc_sw128(k_s + st * KV_BYTES);
 #pragma unroll
         for (int i = 0; i < HD / 16; ++i) {
           // half of d, then 32 B per 16 d inside the 128-byte rows
           const uint32_t qoff = (i >> 2) * Q_HALF + (i & 3) * 32, koff = (i >> 2) * KV_HALF + (i & 3) * 32;
-          umma_f16_ss(tmem_base + COL_S + BKV * st, smem_desc_sw128(q_s + qoff),
-                      smem_desc_sw128(k_s + st * KV_BYTES + koff), IDESC_S, i != 0 ? 1u : 0u);
+          umma_f16_ss(tmem_base + COL_S + BKV * st, q_desc + (qoff >> 4), k_desc + (koff >> 4), IDESC_S,
+                      i != 0 ? 1u : 0u);
         }
         umma_commit(s_full + 8 * st);
       }
@@ -288,12 +290,13 @@ fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ 
         break;
       tc_fence_after();
       if (elect_one()) {
+        const uint64_t v_desc = smem_desc_sw128_mn(v_s + st * KV_BYTES, KV_HALF);
 #pragma unroll
         for (int i = 0; i < BKV / 16; ++i) {
           // A: 16 keys of P = 8 TMEM columns (the 32 keys of softmax part p at columns 32 p .. 32 p + 15 of the
           // buffer); B: 16 key rows of V = 2048 B further, d halves KV_HALF apart
           umma_f16_ts(tmem_base + COL_O, tmem_base + COL_S + BKV * st + (i >> 1) * 32 + 8 * (i & 1),
-                      smem_desc_sw128_mn(v_s + st * KV_BYTES + i * 2048, KV_HALF), IDESC_O, (j | i) != 0 ? 1u : 0u);
+                      v_desc + (i * 2048 >> 4), IDESC_O, (j | i) != 0 ? 1u : 0u);
         }
         umma_commit(v_empty + 8 * st);
         if (j == n_tiles - 1) umma_commit(o_full);
