@@ -107,10 +107,11 @@ class QwenTransformerBlock(nn.Module):
     def __init__(self, ctx, cfg):
         super().__init__()
         d = cfg.hidden
-        self.img_mod_linear = ctx.linear(d, 6 * d)
+        # tensor parallel: every rank holds 1/tp of the modulation linears' output rows (QwenTransformer._modulations)
+        self.img_mod_linear = ctx.linear(d, 6 * d, split="col")
         self.attn = QwenAttention(ctx, d)
         self.img_ff = QwenFeedForward(ctx, d, cfg.mlp_ratio)
-        self.txt_mod_linear = ctx.linear(d, 6 * d)
+        self.txt_mod_linear = ctx.linear(d, 6 * d, split="col")
         self.txt_ff = QwenFeedForward(ctx, d, cfg.mlp_ratio)
 
 
@@ -132,6 +133,7 @@ class QwenTransformer(nn.Module):
         self.cfg, self.bits = cfg, bits
         self.tp_rank, self.tp_world, self.tp_group, self.tp_mode = tp_rank, tp_world, tp_group, tp_mode
         self._exchange = {}
+        self._text_stream = {}
         ctx = _Ctx(device, bits, std, seed, mode, tp_rank, tp_world)
         d = cfg.hidden
         self.img_in = ctx.linear(cfg.in_channels, d)
@@ -281,10 +283,14 @@ class QwenTransformer(nn.Module):
         temb = self.time_text_embed.timestep_embedder(self.time_proj(timestep).to(torch.bfloat16))
         sv = ops.vec_sum_act(temb, act="silu", out_dtype=torch.bfloat16)
 
+        all_mods = self._modulations(sv) if self.tp_world > 1 else None
         for i, blk in enumerate(self.transformer_blocks):
             a = blk.attn
-            mi = _call(blk.img_mod_linear, sv)   # [B, 6D]: (shift, scale, gate) x 2
-            mt = _call(blk.txt_mod_linear, sv)
+            if all_mods is None:
+                mi = _call(blk.img_mod_linear, sv)   # [B, 6D]: (shift, scale, gate) x 2
+                mt = _call(blk.txt_mod_linear, sv)
+            else:
+                mt, mi = all_mods[2 * i], all_mods[2 * i + 1]
             ops.norm_modulate(x_img, mi[:, 0:d], mi[:, d:2 * d], out=n_img)
             ops.norm_modulate(x_txt, mt[:, 0:d], mt[:, d:2 * d], out=n_txt)
             self._fuse(("q", i), [a.to_q, a.to_k, a.to_v])(n_img, qkv[:, st:])
@@ -355,55 +361,89 @@ def _forward_peer(self, hidden_states, encoder_hidden_states, timestep, height, 
     temb = self.time_text_embed.timestep_embedder(self.time_proj(timestep).to(torch.bfloat16))
     sv = ops.vec_sum_act(temb, act="silu", out_dtype=torch.bfloat16)
 
-    def mods(blk):
-        return _call(blk.txt_mod_linear, sv), _call(blk.img_mod_linear, sv)   # [B, 6D] each: (shift, scale, gate) x 2
+    all_mods = self._modulations(sv)
+
+    def mods(i):
+        return all_mods[2 * i], all_mods[2 * i + 1]   # [B, 6D] each: (shift, scale, gate) x 2 of the text / image stream
 
     def ch(m, j):
         return m[:, j * d:(j + 1) * d]
 
-    def scattered(layer, x, row_offset):
+    # The text stream's linears (256 rows: a dozen tiles for 74 CTA pairs, 35-50 us each whatever their size) run on
+    # a second stream beside the image stream's: their CTAs start on the SMs the image matmul's last wave leaves
+    # idle. The main stream joins the second one before anything reads their output, in particular before tp_fuse,
+    # which waits for the arrival counts this rank's own text scatter contributes to.
+    main = torch.cuda.current_stream(dev)
+    side = self._text_stream.get(str(dev))
+    if side is None:
+        side = self._text_stream[str(dev)] = torch.cuda.Stream(device=dev)
+
+    def fork():
+        """The second stream continues from what the main stream has queued so far. Called BEFORE the image
+        matmul is launched, so that the text matmul launched after it does not wait for its end."""
+        side.wait_stream(main)
+
+    def on_side(fn):
+        with torch.cuda.stream(side):
+            fn()
+
+    def scattered(layer, x, row_offset, lane=0):
         ops.qlinear(x, layer.weight.data, None, None, None, bits=layer.bits, prepared=layer.prepared(),
-                    scatter=ex.scatter(row_offset))
+                    scatter=ex.scatter(row_offset, lane))
 
     own_lo, own_hi = ex.lo, min(s, ex.lo + ex.rows)
 
     def gathered(jobs):
-        """Column-split matmuls over the gathered activations. `jobs` are (fn(x_rows, out_rows), a, b, x, out) over
-        joint rows [a, b). The rows this rank normalised itself are in place already: their share of every matmul
-        runs first and hides the flight time of the peers' rows; the rest follows the wait for their arrival."""
-        for fn, a_, b_, x, out in jobs:
-            lo_, hi_ = max(a_, own_lo), min(b_, own_hi)
-            if lo_ < hi_:
-                fn(x[:, lo_:hi_], out[:, lo_:hi_])
+        """Column-split matmuls over the gathered activations. `jobs` are (fn(x_rows, out_rows), a, b, x, out, text)
+        over joint rows [a, b); text-stream jobs go to the second stream. The rows this rank normalised itself are
+        in place already: their share of every matmul runs first and hides the flight time of the peers' rows; the
+        rest follows the wait for their arrival."""
+        def run(pieces):
+            fork()
+            for text_pass in (False, True):     # image matmuls first: the text tiles fill the SMs they leave
+                for fn, x, out, lo_, hi_, text in pieces:
+                    if text == text_pass:
+                        if text:
+                            on_side(lambda: fn(x[:, lo_:hi_], out[:, lo_:hi_]))
+                        else:
+                            fn(x[:, lo_:hi_], out[:, lo_:hi_])
+
+        own = [(fn, x, out, max(a_, own_lo), min(b_, own_hi), text) for fn, a_, b_, x, out, text in jobs
+               if max(a_, own_lo) < min(b_, own_hi)]
+        run(own)
         ex.wait_gathered()
-        for fn, a_, b_, x, out in jobs:
-            for lo_, hi_ in ((a_, min(b_, own_lo)), (max(a_, own_hi), b_)):
-                if lo_ < hi_:
-                    fn(x[:, lo_:hi_], out[:, lo_:hi_])
+        rest = [(fn, x, out, lo_, hi_, text) for fn, a_, b_, x, out, text in jobs
+                for lo_, hi_ in ((a_, min(b_, own_lo)), (max(a_, own_hi), b_)) if lo_ < hi_]
+        run(rest)
+        main.wait_stream(side)
 
     ex.begin()
     blocks = list(self.transformer_blocks)
-    mt, mi = mods(blocks[0])
+    mt, mi = mods(0)
     ex.fuse(reduce=False, shift=(ch(mt, 0), ch(mi, 0)), scale=(ch(mt, 1), ch(mi, 1)))
     for i, blk in enumerate(blocks):
         a = blk.attn
-        gathered([(self._fuse(("q", i), [a.to_q, a.to_k, a.to_v]), st, s, nbuf, qkv),
-                  (self._fuse(("a", i), [a.add_q_proj, a.add_k_proj, a.add_v_proj]), 0, st, nbuf, qkv)])
+        gathered([(self._fuse(("q", i), [a.to_q, a.to_k, a.to_v]), st, s, nbuf, qkv, False),
+                  (self._fuse(("a", i), [a.add_q_proj, a.add_k_proj, a.add_v_proj]), 0, st, nbuf, qkv, True)])
         ops.qknorm_rope(qkv[:, :s], heads, a.norm_added_q.weight.data, a.norm_added_k.weight.data,
                         a.norm_q.weight.data, a.norm_k.weight.data, st, cos_sin, a.norm_q.eps)
         ops.fmha(qkv[:, :s], heads, out=attn[:, :s], key_bias=key_bias)
+        fork()
         scattered(a.attn_to_out[0], attn[:, st:s], st)
-        scattered(a.to_add_out, attn[:, :st], 0)
+        on_side(lambda: scattered(a.to_add_out, attn[:, :st], 0, 1))
+        main.wait_stream(side)
         ex.fuse(reduce=True, bias=(a.to_add_out.bias, a.attn_to_out[0].bias), gate=(ch(mt, 2), ch(mi, 2)),
                 shift=(ch(mt, 3), ch(mi, 3)), scale=(ch(mt, 4), ch(mi, 4)))
-        gathered([(lambda x, o, l=blk.img_ff.mlp_in: _call(l, x, epilogue="gelu_approx", out=o), st, s, nbuf, ffb),
-                  (lambda x, o, l=blk.txt_ff.mlp_in: _call(l, x, epilogue="gelu_approx", out=o), 0, st, nbuf, ffb)])
+        gathered([(lambda x, o, l=blk.img_ff.mlp_in: _call(l, x, epilogue="gelu_approx", out=o), st, s, nbuf, ffb, False),
+                  (lambda x, o, l=blk.txt_ff.mlp_in: _call(l, x, epilogue="gelu_approx", out=o), 0, st, nbuf, ffb, True)])
+        fork()
         scattered(blk.img_ff.mlp_out, ffb[:, st:s], st)
-        scattered(blk.txt_ff.mlp_out, ffb[:, :st], 0)
+        on_side(lambda: scattered(blk.txt_ff.mlp_out, ffb[:, :st], 0, 1))
+        main.wait_stream(side)
         gate = (ch(mt, 5), ch(mi, 5))
         bias = (blk.txt_ff.mlp_out.bias, blk.img_ff.mlp_out.bias)
         if i + 1 < len(blocks):
-            mt, mi = mods(blocks[i + 1])       # the next block's first norm rides on this exchange
+            mt, mi = mods(i + 1)       # the next block's first norm rides on this exchange
             ex.fuse(reduce=True, bias=bias, gate=gate, shift=(ch(mt, 0), ch(mi, 0)), scale=(ch(mt, 1), ch(mi, 1)))
         else:
             ex.fuse(reduce=True, bias=bias, gate=gate)
@@ -423,7 +463,26 @@ def _forward_peer(self, hidden_states, encoder_hidden_states, timestep, height, 
     return parts.permute(1, 0, 2, 3).reshape(b, sp, cfg.in_channels)[:, st:s].contiguous()
 
 
+def _modulations(self, sv):
+    """Modulation vectors of every block on a tensor-parallel group: [2 * blocks, B, 6D], text stream at 2i, image
+    stream at 2i + 1. The 2 x 60 AdaLN linears (qwen_transformer_block.py:27-34) all read the same conditioning
+    vector and stream 28 MB of weights each; replicated, they were 9 % of the 8-GPU step. Every rank computes its
+    1/tp of each linear's output rows before the first block, one all-gather of a few megabytes puts the rows
+    together."""
+    blocks = list(self.transformer_blocks)
+    tp, b = self.tp_world, sv.shape[0]
+    n = 6 * self.cfg.hidden // tp
+    part = torch.empty(2 * len(blocks), b, n, dtype=torch.bfloat16, device=sv.device)
+    for i, blk in enumerate(blocks):
+        _call(blk.txt_mod_linear, sv, out=part[2 * i])
+        _call(blk.img_mod_linear, sv, out=part[2 * i + 1])
+    gathered = torch.empty(tp, 2 * len(blocks), b, n, dtype=torch.bfloat16, device=sv.device)
+    dist.all_gather_into_tensor(gathered, part, group=self.tp_group)
+    return gathered.permute(1, 2, 0, 3).reshape(2 * len(blocks), b, tp * n)
+
+
 QwenTransformer._forward_peer = _forward_peer
+QwenTransformer._modulations = _modulations
 
 
 class QwenImage:

@@ -51,7 +51,8 @@ class PeerExchange:
         self.part = self.buf[self._off_part:self._off_part + n_part].view(torch.bfloat16).view(
             world, batch, self.rows, dim)
         self.flags = self.buf[self._off_flags:self._off_flags + 8 * world].view(torch.int32)
-        self.local = torch.zeros(4, dtype=torch.int32, device=device)   # [0] scatter, [1] fuse completion counts
+        self.local = torch.zeros(4, dtype=torch.int32, device=device)   # completion counts: [0] scatter, [1] fuse,
+        # [2] scatter launches of a second stream (two scatters in flight at once must not share a count)
         self.epoch_base = torch.zeros(2, dtype=torch.int32, device=device)   # [0] part arrivals, [1] nbuf arrivals
         self.x = torch.zeros(batch, self.rows, dim, dtype=torch.float32, device=device)   # owned residual rows
         self.rs_count = self.ag_count = 0       # arrivals issued so far in the current forward pass
@@ -92,14 +93,15 @@ class PeerExchange:
             cache[key] = torch.tensor(key, dtype=torch.int32, device=self.epoch_base.device)
         return cache[key]
 
-    def scatter(self, row_offset: int) -> "_lib.TpScatter":
-        """Descriptor for a row-split linear whose activation rows start at joint row `row_offset`."""
+    def scatter(self, row_offset: int, lane: int = 0) -> "_lib.TpScatter":
+        """Descriptor for a row-split linear whose activation rows start at joint row `row_offset`. Launches that
+        may run at the same time (different streams) take different `lane`s (0 or 1): each counts its own CTAs."""
         sc = _lib.TpScatter()
         sc.world, sc.rank, sc.rows_per_rank, sc.row_offset, sc.D = self.world, self.rank, self.rows, row_offset, self.dim
         for r in range(self.world):
             sc.dst[r] = self.bases[r] + self._off_part
             sc.flags[r] = self.bases[r] + self._off_flags + 4 * self.rank
-        sc.done_counter = self.local.data_ptr()
+        sc.done_counter = self.local.data_ptr() + (8 if lane else 0)
         self.rs_count += 1
         return sc
 
