@@ -284,6 +284,28 @@ class QwenTransformer(nn.Module):
         sv = ops.vec_sum_act(temb, act="silu", out_dtype=torch.bfloat16)
 
         all_mods = self._modulations(sv) if self.tp_world > 1 else None
+        # One rank: the text stream's linears (a few hundred rows: a dozen tiles for 74 CTA pairs) run on a second
+        # stream beside the image stream's and start on the SMs the image matmul's last wave leaves idle. The
+        # all-reduce path keeps everything on one stream (its chunked collectives have their own).
+        main = torch.cuda.current_stream(dev)
+        side = None
+        if self.tp_world == 1:
+            side = self._text_stream.get(str(dev))
+            if side is None:
+                side = self._text_stream[str(dev)] = torch.cuda.Stream(device=dev)
+
+        def pair(img_fn, txt_fn):
+            """image-stream launch on the main stream, text-stream launch beside it"""
+            if side is None:
+                img_fn()
+                txt_fn()
+                return
+            side.wait_stream(main)
+            img_fn()
+            with torch.cuda.stream(side):
+                txt_fn()
+            main.wait_stream(side)
+
         for i, blk in enumerate(self.transformer_blocks):
             a = blk.attn
             if all_mods is None:
@@ -293,19 +315,19 @@ class QwenTransformer(nn.Module):
                 mt, mi = all_mods[2 * i], all_mods[2 * i + 1]
             ops.norm_modulate(x_img, mi[:, 0:d], mi[:, d:2 * d], out=n_img)
             ops.norm_modulate(x_txt, mt[:, 0:d], mt[:, d:2 * d], out=n_txt)
-            self._fuse(("q", i), [a.to_q, a.to_k, a.to_v])(n_img, qkv[:, st:])
-            self._fuse(("a", i), [a.add_q_proj, a.add_k_proj, a.add_v_proj])(n_txt, qkv[:, :st])
+            pair(lambda: self._fuse(("q", i), [a.to_q, a.to_k, a.to_v])(n_img, qkv[:, st:]),
+                 lambda: self._fuse(("a", i), [a.add_q_proj, a.add_k_proj, a.add_v_proj])(n_txt, qkv[:, :st]))
             ops.qknorm_rope(qkv, heads, a.norm_added_q.weight.data, a.norm_added_k.weight.data, a.norm_q.weight.data,
                             a.norm_k.weight.data, st, cos_sin, a.norm_q.eps)
             ops.fmha(qkv, heads, out=attn, key_bias=key_bias)
-            self._row_parallel(a.attn_to_out[0], attn[:, st:], mi[:, 2 * d:3 * d], x_img)
-            self._row_parallel(a.to_add_out, attn[:, :st], mt[:, 2 * d:3 * d], x_txt)
+            pair(lambda: self._row_parallel(a.attn_to_out[0], attn[:, st:], mi[:, 2 * d:3 * d], x_img),
+                 lambda: self._row_parallel(a.to_add_out, attn[:, :st], mt[:, 2 * d:3 * d], x_txt))
             ops.norm_modulate(x_img, mi[:, 3 * d:4 * d], mi[:, 4 * d:5 * d], out=n_img)
             ops.norm_modulate(x_txt, mt[:, 3 * d:4 * d], mt[:, 4 * d:5 * d], out=n_txt)
-            _call(blk.img_ff.mlp_in, n_img, epilogue="gelu_approx", out=ffb[:, st:])
-            self._row_parallel(blk.img_ff.mlp_out, ffb[:, st:], mi[:, 5 * d:6 * d], x_img)
-            _call(blk.txt_ff.mlp_in, n_txt, epilogue="gelu_approx", out=ffb[:, :st])
-            self._row_parallel(blk.txt_ff.mlp_out, ffb[:, :st], mt[:, 5 * d:6 * d], x_txt)
+            pair(lambda: _call(blk.img_ff.mlp_in, n_img, epilogue="gelu_approx", out=ffb[:, st:]),
+                 lambda: _call(blk.txt_ff.mlp_in, n_txt, epilogue="gelu_approx", out=ffb[:, :st]))
+            pair(lambda: self._row_parallel(blk.img_ff.mlp_out, ffb[:, st:], mi[:, 5 * d:6 * d], x_img),
+                 lambda: self._row_parallel(blk.txt_ff.mlp_out, ffb[:, :st], mt[:, 5 * d:6 * d], x_txt))
             if self.trace is not None:
                 self.trace[f"block{i}"] = (x_txt.clone(), x_img.clone())
 
