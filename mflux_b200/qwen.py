@@ -340,11 +340,13 @@ def _forward_peer(self, hidden_states, encoder_hidden_states, timestep, height, 
     """The tensor-parallel forward with the exchange fused into this library's kernels (see tp.py).
 
     Every rank keeps the residual stream of the joint-sequence rows it owns only. Per block:
-      all ranks hold n1 (normalised rows of the whole sequence, gathered by peer stores)
-      q/k/v (column split) -> attention over this rank's heads -> attn_to_out / to_add_out (row split): the matmul
-      epilogue scatters every partial row to its owner -> tp_fuse on the owned rows: sum of the partials + bias,
-      gated residual, second modulated LayerNorm, result stored into every rank's copy of the sequence ->
-      mlp_in (column split, GELU) -> mlp_out (row split, scattered) -> tp_fuse with the next block's first norm.
+      all ranks hold n1 (normalised rows of the whole sequence: every rank's own rows, copied to its peers by the
+      copy engines) -> q/k/v (column split) -> attention over this rank's heads -> attn_to_out / to_add_out (row
+      split): the matmul epilogue scatters every partial row to its owner -> tp_fuse on the owned rows: sum of the
+      partials + bias, gated residual, second modulated LayerNorm into this rank's copy of the sequence, from where
+      the copy engines carry the rows to the peers -> mlp_in (column split, GELU) -> mlp_out (row split, scattered)
+      -> tp_fuse with the next block's first norm. The text stream's linears run on a second stream beside the image
+      stream's; all modulation vectors are computed before the first block (_modulations).
     Linears, attention and the arithmetic per row are those of the one-GPU path; only the order of the bf16
     partial sums differs (they are rounded to bf16 per rank before they are added, as in the all-reduce path)."""
     from .tp import PeerExchange
