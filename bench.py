@@ -751,7 +751,7 @@ def main():
                          "share_of_step_time": (q_ms / trace_steps) / step_ms if ms > 0 else None, "traffic": traffic,
                          "traffic_unit": "DRAM bytes per launch, mean over the step's launches (ncu record under "
                                          "profiles/, null when the kernel source changed since the capture)"},
-            "roofline_attention": {"bound": "tensor", "kernel": "fmha_kernel (flash attention, head dim 128)",
+            "roofline_attention": {"bound": "tensor", "kernel": "attn::sdpa_pingpong_kernel / attn::sdpa_pair_kernel (flash attention, head dim 128)",
                                    "achieved": a_achieved, "peak": peak, "unit": "TFLOP/s",
                                    "frac": a_achieved / peak if peak else None, "peak_kind": peak_kind,
                                    "burst_peak": burst, "frac_of_burst": a_achieved / burst if burst else None,

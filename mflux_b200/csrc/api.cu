@@ -8,7 +8,7 @@ int read_status(int* out, cudaStream_t stream);
 namespace qmmt {
 int read_status(int* out, cudaStream_t stream);
 }
-namespace fmha {
+namespace attn {
 int read_status(int* out, cudaStream_t stream);
 }
 namespace tp {
@@ -22,7 +22,7 @@ int mfx_poll_device_status(int* status_out, void* stream) {
   if (!status_out) return MFX_ERR_NULL;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int v = 0, v2 = 0, v3 = 0, v4 = 0;
-  if (mfx::qmm::read_status(&v, st) != 0 || mfx::fmha::read_status(&v2, st) != 0 ||
+  if (mfx::qmm::read_status(&v, st) != 0 || mfx::attn::read_status(&v2, st) != 0 ||
       mfx::qmmt::read_status(&v3, st) != 0 || mfx::tp::read_status(&v4, st) != 0) {
     mfx::set_cuda_error_text("reading the device status word failed");
     return MFX_ERR_CUDA;

@@ -28,7 +28,7 @@
 #include "ptx.cuh"
 
 namespace mfx {
-namespace fmha {
+namespace attn {
 
 constexpr int BQ = 128;
 constexpr int PARTS = 2;                     // softmax warps per 32-row quarter, each owning 32 key columns.
@@ -177,7 +177,7 @@ __device__ __forceinline__ void exp_chunk(const uint32_t (&s)[32], uint64_t scal
 // variant without it is the plain kernel, instruction for instruction.
 template <bool HAS_BIAS>
 __global__ void __launch_bounds__(NUM_THREADS, CTAS_PER_SM)
-fmha_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+sdpa_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
             const __grid_constant__ CUtensorMap tmap_v, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -536,7 +536,7 @@ __device__ __forceinline__ void mask_chunk(uint32_t (&s)[32], int valid) {
 
 template <bool HAS_BIAS>
 __global__ void __launch_bounds__(NT, 1)
-fmha_pingpong_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+sdpa_pingpong_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                      const __grid_constant__ CUtensorMap tmap_v, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -827,11 +827,11 @@ fmha_pingpong_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 
 MFX_DEFINE_STATUS_READER(read_status)
 
-}  // namespace fmha
+}  // namespace attn
 }  // namespace mfx
 
 namespace mfx {
-namespace fmha {
+namespace attn {
 
 // Which kernel serves a call. The ping-pong kernel (two query tiles per CTA, one CTA per SM) is the faster main
 // loop (1245-1270 against 1150-1170 TFLOP/s at 16 x 24 heads x 4608 tokens), but its work items are twice as
@@ -893,16 +893,16 @@ int run(const void* q, const void* k, const void* v, int64_t qkv_row_stride, int
               static_cast<unsigned>(batch));
     if (key_bias) {
       static SmemConfigured configured;
-      if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(pp::fmha_pingpong_kernel<true>),
+      if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(pp::sdpa_pingpong_kernel<true>),
                                        pp::DYN_BYTES2, configured))
         return rc;
-      pp::fmha_pingpong_kernel<true><<<grid, pp::NT, pp::DYN_BYTES2, stream>>>(tq, tk, tv, p);
+      pp::sdpa_pingpong_kernel<true><<<grid, pp::NT, pp::DYN_BYTES2, stream>>>(tq, tk, tv, p);
     } else {
       static SmemConfigured configured;
-      if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(pp::fmha_pingpong_kernel<false>),
+      if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(pp::sdpa_pingpong_kernel<false>),
                                        pp::DYN_BYTES2, configured))
         return rc;
-      pp::fmha_pingpong_kernel<false><<<grid, pp::NT, pp::DYN_BYTES2, stream>>>(tq, tk, tv, p);
+      pp::sdpa_pingpong_kernel<false><<<grid, pp::NT, pp::DYN_BYTES2, stream>>>(tq, tk, tv, p);
     }
     MFX_CUDA_TRY(cudaGetLastError());
     return MFX_OK;
@@ -910,20 +910,20 @@ int run(const void* q, const void* k, const void* v, int64_t qkv_row_stride, int
   dim3 grid(static_cast<unsigned>((seq + BQ - 1) / BQ), static_cast<unsigned>(heads), static_cast<unsigned>(batch));
   if (key_bias) {
     static SmemConfigured configured;
-    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(fmha_kernel<true>), DYN_BYTES, configured))
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(sdpa_pair_kernel<true>), DYN_BYTES, configured))
       return rc;
-    fmha_kernel<true><<<grid, NUM_THREADS, DYN_BYTES, stream>>>(tq, tk, tv, p);
+    sdpa_pair_kernel<true><<<grid, NUM_THREADS, DYN_BYTES, stream>>>(tq, tk, tv, p);
   } else {
     static SmemConfigured configured;
-    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(fmha_kernel<false>), DYN_BYTES, configured))
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(sdpa_pair_kernel<false>), DYN_BYTES, configured))
       return rc;
-    fmha_kernel<false><<<grid, NUM_THREADS, DYN_BYTES, stream>>>(tq, tk, tv, p);
+    sdpa_pair_kernel<false><<<grid, NUM_THREADS, DYN_BYTES, stream>>>(tq, tk, tv, p);
   }
   MFX_CUDA_TRY(cudaGetLastError());
   return MFX_OK;
 }
 
-}  // namespace fmha
+}  // namespace attn
 }  // namespace mfx
 
 extern "C" {
@@ -931,7 +931,7 @@ extern "C" {
 int mfx_fmha(const void* q, const void* k, const void* v, int64_t qkv_row_stride, int64_t qkv_batch_stride,
              int64_t seq, int64_t batch, int heads, float scale, void* out, int64_t out_row_stride,
              int64_t out_batch_stride, void* stream) {
-  return mfx::fmha::run(q, k, v, qkv_row_stride, qkv_batch_stride, seq, batch, heads, scale, nullptr, 0, out,
+  return mfx::attn::run(q, k, v, qkv_row_stride, qkv_batch_stride, seq, batch, heads, scale, nullptr, 0, out,
                         out_row_stride, out_batch_stride, static_cast<cudaStream_t>(stream));
 }
 
@@ -940,7 +940,7 @@ int mfx_fmha_bias(const void* q, const void* k, const void* v, int64_t qkv_row_s
                   int64_t bias_batch_stride, void* out, int64_t out_row_stride, int64_t out_batch_stride,
                   void* stream) {
   if (!key_bias) return MFX_ERR_NULL;
-  return mfx::fmha::run(q, k, v, qkv_row_stride, qkv_batch_stride, seq, batch, heads, scale, key_bias,
+  return mfx::attn::run(q, k, v, qkv_row_stride, qkv_batch_stride, seq, batch, heads, scale, key_bias,
                         bias_batch_stride, out, out_row_stride, out_batch_stride, static_cast<cudaStream_t>(stream));
 }
 
