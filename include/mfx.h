@@ -292,6 +292,33 @@ int mfx_fmha_bias(const void* q, const void* k, const void* v, int64_t qkv_row_s
                   int64_t bias_batch_stride, void* out, int64_t out_row_stride, int64_t out_batch_stride,
                   void* stream);
 
+/* The same attention with its general shape: a key / value sequence of its own length and fewer key / value heads
+ * than query heads. Replaces scaled_dot_product_attention as called
+ *  - with keys and values that carry cached reference tokens behind the current ones, so seq_kv > seq_q
+ *    (Flux2KVCache.append_reference, src/mflux/models/flux2/model/flux2_transformer/flux2_kv_cache.py:51-61, used by
+ *    flux2_transformer/attention.py:69-72 and parallel_self_attention.py:46-49);
+ *  - after mx.repeat(k / v, heads // kvheads, axis=1), i.e. grouped-query attention
+ *    (src/mflux/models/krea2/model/krea2_transformer/attention.py:33-38): query head h reads key / value head
+ *    h / (heads / kv_heads), nothing is repeated in memory.
+ * q is bf16 [batch, seq_q, heads, 128], k and v bf16 [batch, seq_kv, kv_heads, 128] (row / batch strides in
+ * elements, k and v share theirs), key_bias optional f32 [batch, seq_kv] as for mfx_fmha_bias, out bf16
+ * [batch, seq_q, heads * 128]. heads must be a multiple of kv_heads. */
+typedef struct mfx_fmha_args {
+  const void* q;
+  const void* k;
+  const void* v;
+  int64_t q_row_stride, q_batch_stride;
+  int64_t kv_row_stride, kv_batch_stride;
+  int64_t seq_q, seq_kv, batch;
+  int heads, kv_heads;
+  float scale;
+  const float* key_bias;       /* NULL: no bias */
+  int64_t bias_batch_stride;
+  void* out;
+  int64_t out_row_stride, out_batch_stride;
+} mfx_fmha_args;
+int mfx_fmha_ex(const mfx_fmha_args* args /* host */, void* stream);
+
 /* out = act(a + b + c) elementwise (b, c nullable; act 0 = identity, 1 = SiLU, 2 = tanh): the conditioning-vector
  * arithmetic of time_text_embed.py:25-31, the nn.silu in front of every AdaLN linear and the mx.tanh on the
  * Z-Image gates (z_image_transformer/transformer_block.py:26-27). */

@@ -72,6 +72,31 @@ class TpFuseArgs(ctypes.Structure):
     ]
 
 
+class FmhaArgs(ctypes.Structure):
+    """struct mfx_fmha_args (include/mfx.h)."""
+
+    _fields_ = [
+        ("q", c_void_p),
+        ("k", c_void_p),
+        ("v", c_void_p),
+        ("q_row_stride", c_int64),
+        ("q_batch_stride", c_int64),
+        ("kv_row_stride", c_int64),
+        ("kv_batch_stride", c_int64),
+        ("seq_q", c_int64),
+        ("seq_kv", c_int64),
+        ("batch", c_int64),
+        ("heads", c_int),
+        ("kv_heads", c_int),
+        ("scale", ctypes.c_float),
+        ("key_bias", c_void_p),
+        ("bias_batch_stride", c_int64),
+        ("out", c_void_p),
+        ("out_row_stride", c_int64),
+        ("out_batch_stride", c_int64),
+    ]
+
+
 class QLinearArgs(ctypes.Structure):
     """struct mfx_qlinear_args (include/mfx.h)."""
 
@@ -213,6 +238,7 @@ SIGNATURES = {
         [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, ctypes.c_float, c_void_p, c_int64,
          c_int64, c_void_p],
     ),
+    "mfx_fmha_ex": (c_int, [ctypes.POINTER(FmhaArgs), c_void_p]),
     "mfx_fmha_bias": (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, ctypes.c_float, c_void_p, c_int64,

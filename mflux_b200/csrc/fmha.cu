@@ -63,7 +63,9 @@ constexpr int XCH_BYTES = 2 * XCH_FLOATS * 4;     // two buffers by tile parity
 constexpr int DYN_BYTES = OFF_XCH + XCH_BYTES + 1024;
 
 struct Params {
-  int seq, batch, heads;
+  int seq, batch, heads;   // seq = number of queries
+  int seq_kv;              // number of keys / values (>= 1; equals seq for self-attention)
+  int kv_rep;              // query heads per key/value head (1 unless grouped-query attention)
   float scale_log2;  // scale * log2(e)
   const float* key_bias;        // optional additive bias per (sample, key), added to the scaled scores
   int64_t bias_batch_stride;
@@ -193,7 +195,8 @@ sdpa_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
   const int q0 = blockIdx.x * BQ;
   const int h = blockIdx.y;
   const int b = blockIdx.z;
-  const int n_tiles = (p.seq + BKV - 1) / BKV;
+  const int n_tiles = (p.seq_kv + BKV - 1) / BKV;
+  const int hk = h / p.kv_rep;   // key/value head of this query head
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -236,8 +239,8 @@ sdpa_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       if (j >= 2 && !mbar_wait(s_full + 8 * st, ph ^ 1u, DEV_TIMEOUT_ATTN)) break;
       if (elect_one()) {
         mbar_arrive_expect_tx(k_full + 8 * st, KV_BYTES);
-        tma_load_4d(k_s + st * KV_BYTES, &tmap_k, k_full + 8 * st, 0, h, j * BKV, b);
-        tma_load_4d(k_s + st * KV_BYTES + KV_HALF, &tmap_k, k_full + 8 * st, 64, h, j * BKV, b);
+        tma_load_4d(k_s + st * KV_BYTES, &tmap_k, k_full + 8 * st, 0, hk, j * BKV, b);
+        tma_load_4d(k_s + st * KV_BYTES + KV_HALF, &tmap_k, k_full + 8 * st, 64, hk, j * BKV, b);
       }
       __syncwarp();
     }
@@ -248,8 +251,8 @@ sdpa_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       if (!mbar_wait(v_empty + 8 * st, ph ^ 1u, DEV_TIMEOUT_ATTN)) break;
       if (elect_one()) {
         mbar_arrive_expect_tx(v_full + 8 * st, KV_BYTES);
-        tma_load_4d(v_s + st * KV_BYTES, &tmap_v, v_full + 8 * st, 0, h, j * BKV, b);
-        tma_load_4d(v_s + st * KV_BYTES + KV_HALF, &tmap_v, v_full + 8 * st, 64, h, j * BKV, b);
+        tma_load_4d(v_s + st * KV_BYTES, &tmap_v, v_full + 8 * st, 0, hk, j * BKV, b);
+        tma_load_4d(v_s + st * KV_BYTES + KV_HALF, &tmap_v, v_full + 8 * st, 64, hk, j * BKV, b);
       }
       __syncwarp();
     }
@@ -323,7 +326,7 @@ sdpa_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       }
       tc_fence_after();
       const uint32_t t_s = t_row + COL_S + BKV * st + 32 * pt;   // own S columns; own P goes over the first 16
-      const int keys_here = min(BKV, p.seq - j * BKV) - pt * 32;  // valid keys among this warp's 32 columns
+      const int keys_here = min(BKV, p.seq_kv - j * BKV) - pt * 32;  // valid keys among this warp's 32 columns
       const bool tail = keys_here < 32;  // only the last tile of a ragged sequence needs key masking
       uint32_t sA[32];
       tmem_ld_32x32(t_s, sA);
@@ -551,7 +554,8 @@ sdpa_pingpong_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   const int q0 = blockIdx.x * (2 * BQ);
   const int h = blockIdx.y;
   const int b = blockIdx.z;
-  const int n_tiles = (p.seq + BK - 1) / BK;
+  const int n_tiles = (p.seq_kv + BK - 1) / BK;
+  const int hk = h / p.kv_rep;   // key/value head of this query head
   const bool two = q0 + BQ < p.seq;   // the last block of a sequence may hold one query tile only
 
   if (threadIdx.x == 0) {
@@ -596,8 +600,8 @@ sdpa_pingpong_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     // one phase more than slot 0 at the same pair index.
     if (elect_one()) {
       mbar_arrive_expect_tx(kv_full + 8, TILE_BYTES);
-      tma_load_4d(kv_s + 3 * TILE_BYTES, &tmap_k, kv_full + 8, 0, h, 0, b);
-      tma_load_4d(kv_s + 3 * TILE_BYTES + TILE_HALF, &tmap_k, kv_full + 8, 64, h, 0, b);
+      tma_load_4d(kv_s + 3 * TILE_BYTES, &tmap_k, kv_full + 8, 0, hk, 0, b);
+      tma_load_4d(kv_s + 3 * TILE_BYTES + TILE_HALF, &tmap_k, kv_full + 8, 64, hk, 0, b);
     }
     __syncwarp();
     for (int j = 0; j < n_tiles; ++j) {
@@ -608,11 +612,11 @@ sdpa_pingpong_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         const bool more = j + 1 < n_tiles;
         const uint32_t dst = kv_s + slot * 2 * TILE_BYTES;
         mbar_arrive_expect_tx(kv_full + 8 * slot, (more ? 2 : 1) * TILE_BYTES);
-        tma_load_4d(dst, &tmap_v, kv_full + 8 * slot, 0, h, j * BK, b);
-        tma_load_4d(dst + TILE_HALF, &tmap_v, kv_full + 8 * slot, 64, h, j * BK, b);
+        tma_load_4d(dst, &tmap_v, kv_full + 8 * slot, 0, hk, j * BK, b);
+        tma_load_4d(dst + TILE_HALF, &tmap_v, kv_full + 8 * slot, 64, hk, j * BK, b);
         if (more) {
-          tma_load_4d(dst + TILE_BYTES, &tmap_k, kv_full + 8 * slot, 0, h, (j + 1) * BK, b);
-          tma_load_4d(dst + TILE_BYTES + TILE_HALF, &tmap_k, kv_full + 8 * slot, 64, h, (j + 1) * BK, b);
+          tma_load_4d(dst + TILE_BYTES, &tmap_k, kv_full + 8 * slot, 0, hk, (j + 1) * BK, b);
+          tma_load_4d(dst + TILE_BYTES + TILE_HALF, &tmap_k, kv_full + 8 * slot, 64, hk, (j + 1) * BK, b);
         }
       }
       __syncwarp();
@@ -726,7 +730,7 @@ sdpa_pingpong_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       tmem_ld_32x32(t_s + 32, sb);
       tmem_ld_fence(sa);
       tmem_ld_fence(sb);
-      const int keys_here = p.seq - j * BK - 64 * hf;   // >= 64 except on the last tile of a ragged sequence
+      const int keys_here = p.seq_kv - j * BK - 64 * hf;   // >= 64 except on the last tile of a ragged sequence
       if constexpr (HAS_BIAS) {
         const float* bp = p.key_bias + b * p.bias_batch_stride + j * BK + 64 * hf;
         add_bias_chunk(sa, bp, keys_here, p.scale_log2);
@@ -838,48 +842,76 @@ namespace attn {
 // large: it is chosen from 1024 keys on, and only if the last wave of CTAs leaves at most 7 % of the SMs' time
 // unused (2 x 24 heads x 7145 tokens is 9.08 waves of 148 = 91 %: 1091 against 1158 TFLOP/s, the other kernel wins).
 // MFX_FMHA_KERNEL=pingpong | pair overrides the choice.
-static bool use_pingpong(int64_t seq, int64_t batch, int heads) {
+static bool use_pingpong(int64_t seq, int64_t seq_kv, int64_t batch, int heads) {
   const char* e = getenv("MFX_FMHA_KERNEL");
   if (e && e[0] == 'p' && e[1] == 'i') return true;
   if (e && e[0] == 'p' && e[1] == 'a') return false;
-  if (seq < 1024) return false;
+  if (seq_kv < 1024) return false;
   const int64_t ctas = (seq + 2 * BQ - 1) / (2 * BQ) * heads * batch;
   const int64_t sms = device_sm_count();
   const int64_t waves = (ctas + sms - 1) / sms;
   return ctas * 100 >= waves * sms * 93;
 }
 
-int run(const void* q, const void* k, const void* v, int64_t qkv_row_stride, int64_t qkv_batch_stride, int64_t seq,
-        int64_t batch, int heads, float scale, const float* key_bias, int64_t bias_batch_stride, void* out,
-        int64_t out_row_stride, int64_t out_batch_stride, cudaStream_t stream) {
+// Arguments of one attention call (the C entry points fill it).
+struct Call {
+  const void *q, *k, *v;
+  int64_t q_row_stride, q_batch_stride, kv_row_stride, kv_batch_stride;   // elements
+  int64_t seq, seq_kv, batch;
+  int heads, kv_heads;
+  float scale;
+  const float* key_bias;
+  int64_t bias_batch_stride;
+  void* out;
+  int64_t out_row_stride, out_batch_stride;
+};
+
+int run(const Call& c, cudaStream_t stream) {
+  const void *q = c.q, *k = c.k, *v = c.v;
+  void* out = c.out;
+  const int64_t seq = c.seq, seq_kv = c.seq_kv, batch = c.batch;
+  const int heads = c.heads;
+  const float* key_bias = c.key_bias;
+  const int64_t bias_batch_stride = c.bias_batch_stride, out_row_stride = c.out_row_stride,
+                out_batch_stride = c.out_batch_stride;
   if (!q || !k || !v || !out) return MFX_ERR_NULL;
-  if (seq <= 0 || batch <= 0 || heads <= 0) return MFX_ERR_SHAPE;
-  if (seq > (1 << 24) || batch > 65535 || heads > 65535) return MFX_ERR_TOO_LARGE;
-  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || (qkv_row_stride * 2) % 16 != 0 ||
-      (qkv_batch_stride * 2) % 16 != 0 || (out_row_stride * 2) % 16 != 0 || (out_batch_stride * 2) % 16 != 0)
+  if (seq <= 0 || seq_kv <= 0 || batch <= 0 || heads <= 0 || c.kv_heads <= 0 || heads % c.kv_heads != 0)
+    return MFX_ERR_SHAPE;
+  if (seq > (1 << 24) || seq_kv > (1 << 24) || batch > 65535 || heads > 65535) return MFX_ERR_TOO_LARGE;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out) || (c.q_row_stride * 2) % 16 != 0 ||
+      (c.q_batch_stride * 2) % 16 != 0 || (c.kv_row_stride * 2) % 16 != 0 || (c.kv_batch_stride * 2) % 16 != 0 ||
+      (out_row_stride * 2) % 16 != 0 || (out_batch_stride * 2) % 16 != 0)
     return MFX_ERR_ALIGN;
   if (key_bias) {
     // the kernel reads the bias of 32 consecutive keys as eight 16-byte vectors
     if (!aligned16(key_bias) || (batch > 1 && (bias_batch_stride * 4) % 16 != 0)) return MFX_ERR_ALIGN;
-    if (batch > 1 && bias_batch_stride < seq) return MFX_ERR_SHAPE;
+    if (batch > 1 && bias_batch_stride < seq_kv) return MFX_ERR_SHAPE;
   }
   if (int rc = check_arch()) return rc;
   CUtensorMap tq, tk, tv;
-  const uint64_t dims[4] = {HD, static_cast<uint64_t>(heads), static_cast<uint64_t>(seq),
-                            static_cast<uint64_t>(batch)};
-  const uint64_t bstride = batch > 1 ? static_cast<uint64_t>(qkv_batch_stride) * 2
-                                     : static_cast<uint64_t>(qkv_row_stride) * 2 * seq;
-  const uint64_t strides[3] = {HD * 2, static_cast<uint64_t>(qkv_row_stride) * 2, bstride};
-  const bool pingpong = use_pingpong(seq, batch, heads);
+  const uint64_t dims_q[4] = {HD, static_cast<uint64_t>(heads), static_cast<uint64_t>(seq),
+                              static_cast<uint64_t>(batch)};
+  const uint64_t dims_kv[4] = {HD, static_cast<uint64_t>(c.kv_heads), static_cast<uint64_t>(seq_kv),
+                               static_cast<uint64_t>(batch)};
+  const uint64_t strides_q[3] = {HD * 2, static_cast<uint64_t>(c.q_row_stride) * 2,
+                                 batch > 1 ? static_cast<uint64_t>(c.q_batch_stride) * 2
+                                           : static_cast<uint64_t>(c.q_row_stride) * 2 * seq};
+  const uint64_t strides_kv[3] = {HD * 2, static_cast<uint64_t>(c.kv_row_stride) * 2,
+                                  batch > 1 ? static_cast<uint64_t>(c.kv_batch_stride) * 2
+                                            : static_cast<uint64_t>(c.kv_row_stride) * 2 * seq_kv};
+  const bool pingpong = use_pingpong(seq, seq_kv, batch, heads);
   const uint32_t box_q[4] = {64, 1, BQ, 1}, box_kv[4] = {64, 1, static_cast<uint32_t>(pingpong ? pp::BK : BKV), 1};
   const void* ptrs[3] = {q, k, v};
   CUtensorMap* maps[3] = {&tq, &tk, &tv};
   for (int i = 0; i < 3; ++i)
-    if (int rc = encode_tmap(maps[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, ptrs[i], dims, strides,
-                             i == 0 ? box_q : box_kv, CU_TENSOR_MAP_SWIZZLE_128B))
+    if (int rc = encode_tmap(maps[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, ptrs[i], i == 0 ? dims_q : dims_kv,
+                             i == 0 ? strides_q : strides_kv, i == 0 ? box_q : box_kv, CU_TENSOR_MAP_SWIZZLE_128B))
       return rc;
+  const float scale = c.scale;
   Params p;
   p.seq = static_cast<int>(seq);
+  p.seq_kv = static_cast<int>(seq_kv);
+  p.kv_rep = heads / c.kv_heads;
   p.batch = static_cast<int>(batch);
   p.heads = heads;
   p.scale_log2 = scale * 1.4426950408889634f;
@@ -931,8 +963,9 @@ extern "C" {
 int mfx_fmha(const void* q, const void* k, const void* v, int64_t qkv_row_stride, int64_t qkv_batch_stride,
              int64_t seq, int64_t batch, int heads, float scale, void* out, int64_t out_row_stride,
              int64_t out_batch_stride, void* stream) {
-  return mfx::attn::run(q, k, v, qkv_row_stride, qkv_batch_stride, seq, batch, heads, scale, nullptr, 0, out,
-                        out_row_stride, out_batch_stride, static_cast<cudaStream_t>(stream));
+  const mfx::attn::Call c{q, k, v, qkv_row_stride, qkv_batch_stride, qkv_row_stride, qkv_batch_stride, seq, seq, batch,
+                          heads, heads, scale, nullptr, 0, out, out_row_stride, out_batch_stride};
+  return mfx::attn::run(c, static_cast<cudaStream_t>(stream));
 }
 
 int mfx_fmha_bias(const void* q, const void* k, const void* v, int64_t qkv_row_stride, int64_t qkv_batch_stride,
@@ -940,8 +973,17 @@ int mfx_fmha_bias(const void* q, const void* k, const void* v, int64_t qkv_row_s
                   int64_t bias_batch_stride, void* out, int64_t out_row_stride, int64_t out_batch_stride,
                   void* stream) {
   if (!key_bias) return MFX_ERR_NULL;
-  return mfx::attn::run(q, k, v, qkv_row_stride, qkv_batch_stride, seq, batch, heads, scale, key_bias,
-                        bias_batch_stride, out, out_row_stride, out_batch_stride, static_cast<cudaStream_t>(stream));
+  const mfx::attn::Call c{q, k, v, qkv_row_stride, qkv_batch_stride, qkv_row_stride, qkv_batch_stride, seq, seq, batch,
+                          heads, heads, scale, key_bias, bias_batch_stride, out, out_row_stride, out_batch_stride};
+  return mfx::attn::run(c, static_cast<cudaStream_t>(stream));
+}
+
+int mfx_fmha_ex(const mfx_fmha_args* a, void* stream) {
+  if (!a) return MFX_ERR_NULL;
+  const mfx::attn::Call c{a->q, a->k, a->v, a->q_row_stride, a->q_batch_stride, a->kv_row_stride, a->kv_batch_stride,
+                          a->seq_q, a->seq_kv, a->batch, a->heads, a->kv_heads, a->scale, a->key_bias,
+                          a->bias_batch_stride, a->out, a->out_row_stride, a->out_batch_stride};
+  return mfx::attn::run(c, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -400,6 +400,60 @@ def fmha(qkv: torch.Tensor, heads: int, scale: float | None = None, out: torch.T
     return out
 
 
+def fmha_ex(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads: int, kv_heads: int | None = None,
+            scale: float | None = None, key_bias: torch.Tensor | None = None,
+            out: torch.Tensor | None = None) -> torch.Tensor:
+    """softmax(Q K^T * scale [+ key_bias]) V for head dim 128 with keys / values of their own length and head count.
+
+    q is a bf16 [batch, seq_q, heads*128] view, k and v bf16 [batch, seq_kv, kv_heads*128] views with equal
+    strides (dense last dim; e.g. slices of one fused projection buffer, or buffers that hold cached tokens behind
+    the current ones). Query head h attends to key / value head h // (heads // kv_heads): grouped-query attention
+    without repeating K / V (krea2_transformer/attention.py:33-38); seq_kv > seq_q is the cached-reference case of
+    flux2_kv_cache.py:51-61. `key_bias` is an optional float32 [batch, seq_kv]. Returns bf16
+    [batch, seq_q, heads*128]."""
+    lib = _lib.load()
+    kv_heads = heads if kv_heads is None else kv_heads
+    for t, name in ((q, "q"), (k, "k"), (v, "v")):
+        _cuda(t, name)
+        if t.dtype != torch.bfloat16 or t.dim() != 3 or t.stride(-1) != 1:
+            raise ValueError(f"{name} must be a bf16 [batch, seq, heads*128] view with a dense last dim")
+    batch, seq_q, wq = q.shape
+    if wq != heads * 128 or k.shape[-1] != kv_heads * 128 or k.shape != v.shape or k.shape[0] != batch:
+        raise ValueError("q must be [batch, seq_q, heads*128], k and v [batch, seq_kv, kv_heads*128]")
+    if heads % kv_heads != 0:
+        raise ValueError("heads must be a multiple of kv_heads")
+    if k.stride() != v.stride():
+        raise ValueError("k and v must share their strides")
+    seq_kv = k.shape[1]
+    if out is None:
+        out = torch.empty((batch, seq_q, heads * 128), dtype=torch.bfloat16, device=q.device)
+    if out.dtype != torch.bfloat16 or tuple(out.shape) != (batch, seq_q, heads * 128) or out.stride(-1) != 1:
+        raise ValueError("out must be a bf16 [batch, seq_q, heads*128] view with a dense last dim")
+    a = _lib.FmhaArgs()
+    a.q, a.k, a.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+    a.q_row_stride, a.q_batch_stride = q.stride(1), q.stride(0)
+    a.kv_row_stride, a.kv_batch_stride = k.stride(1), k.stride(0)
+    a.seq_q, a.seq_kv, a.batch, a.heads, a.kv_heads = seq_q, seq_kv, batch, heads, kv_heads
+    a.scale = float(scale if scale is not None else 128 ** -0.5)
+    if key_bias is not None:
+        _cuda(key_bias, "key_bias")
+        if key_bias.dtype != torch.float32 or tuple(key_bias.shape) != (batch, seq_kv) or key_bias.stride(1) != 1:
+            raise ValueError("key_bias must be a float32 [batch, seq_kv] tensor with a dense last dim")
+        if batch > 1 and key_bias.stride(0) % 4 != 0:
+            padded = torch.zeros(batch, (seq_kv + 3) // 4 * 4, dtype=torch.float32, device=key_bias.device)
+            padded[:, :seq_kv] = key_bias
+            key_bias = padded[:, :seq_kv]
+        a.key_bias, a.bias_batch_stride = key_bias.data_ptr(), key_bias.stride(0)
+    a.out, a.out_row_stride, a.out_batch_stride = out.data_ptr(), out.stride(1), out.stride(0)
+    if TRACE is not None:
+        _trace_begin()
+    _lib.check(lib.mfx_fmha_ex(byref(a), _stream()), "mfx_fmha_ex")
+    if TRACE is not None:
+        _trace_end("fmha", 4.0 * batch * heads * seq_q * seq_kv * 128, 0.0)
+    LAUNCHES[0] += 1
+    return out
+
+
 def vec_sum_act(a: torch.Tensor, b: torch.Tensor | None = None, c: torch.Tensor | None = None, act: str | None = None,
                 out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
     """act(a + b + c) elementwise; act is None, "silu" or "tanh"."""

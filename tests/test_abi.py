@@ -150,4 +150,15 @@ def test_validation_of_the_later_entry_points(lib_built):
     assert lib.mfx_cfg_combine(1024, 1024, _lib.BF16, 3.0, 0, 1024, 4, 2048, None) == -1  # more channels than a warp holds
     assert lib.mfx_fmha(1024, 1024, 1024, 384, 0, 0, 1, 1, 1.0, 1024, 128, 0, None) == -1
     assert lib.mfx_fmha(1024, 1024, 1028, 384, 0, 16, 1, 1, 1.0, 1024, 128, 0, None) == -2
+    assert lib.mfx_fmha_ex(None, None) == -7
+    f = _lib.FmhaArgs()
+    f.q = f.k = f.v = f.out = 1024
+    f.q_row_stride = f.kv_row_stride = f.out_row_stride = 512
+    f.seq_q, f.seq_kv, f.batch, f.heads, f.kv_heads, f.scale = 64, 96, 1, 4, 3, 1.0
+    assert lib.mfx_fmha_ex(f, None) == -1             # 4 query heads over 3 key/value heads
+    f.kv_heads = 2
+    f.seq_kv = 0
+    assert lib.mfx_fmha_ex(f, None) == -1             # no keys
+    f.seq_kv, f.kv_row_stride = 96, 260
+    assert lib.mfx_fmha_ex(f, None) == -2             # key rows not 16-byte aligned
     assert lib.mfx_vec_sum_act(1024, None, None, _lib.BF16, 3, 1024, _lib.BF16, 8, None) == -1

@@ -224,3 +224,34 @@ def test_fmha_default_kernel_choice_matches_both(lib_built, monkeypatch):
     for kernel in ("pair", "pingpong"):
         monkeypatch.setenv("MFX_FMHA_KERNEL", kernel)
         assert rel_l2(ops.fmha(qkv, heads), out.float().cpu().numpy()) <= 3e-3
+
+
+@pytest.mark.parametrize("kernel", ["pair", "pingpong"])
+@pytest.mark.parametrize("shape", [(2, 200, 200, 8, 2), (1, 300, 429, 4, 4), (2, 130, 1200, 6, 3), (1, 97, 33, 2, 1)])
+def test_fmha_grouped_heads_and_longer_keys(lib_built, shape, kernel, monkeypatch):
+    """mfx_fmha_ex: fewer key/value heads than query heads (the reference repeats K and V,
+    krea2_transformer/attention.py:33-38) and key/value sequences longer or shorter than the query sequence (cached
+    reference tokens appended to K and V, flux2_kv_cache.py:51-61), with and without a key bias. rel-L2 <= 1e-2
+    against the float32 oracle."""
+    from mflux_b200 import ops
+
+    monkeypatch.setenv("MFX_FMHA_KERNEL", kernel)
+    b, sq, skv, heads, kvh = shape
+    g = _g(sq + skv)
+    q = torch.randn(b, sq, heads * 128, generator=g).to(torch.bfloat16)
+    kv = torch.randn(b, skv, 2 * kvh * 128, generator=g).to(torch.bfloat16)   # k | v of one fused projection
+    kv_d = kv.cuda()
+    k_d, v_d = kv_d[..., :kvh * 128], kv_d[..., kvh * 128:]
+    bias = torch.zeros(b, skv)
+    bias[0, 1::5] = -1e9
+    rep = heads // kvh
+    qh = blocks.heads_first(q, heads)
+    kh = blocks.heads_first(kv[..., :kvh * 128], kvh).repeat_interleave(rep, dim=1)
+    vh = blocks.heads_first(kv[..., kvh * 128:], kvh).repeat_interleave(rep, dim=1)
+    for mask in (None, bias):
+        out = ops.fmha_ex(q.cuda(), k_d, v_d, heads, kvh, key_bias=None if mask is None else mask.cuda())
+        torch.cuda.synchronize()
+        assert ops.poll_device_status() == 0
+        ref = blocks.heads_last(blocks.sdpa(qh, kh, vh, mask=mask))
+        err = rel_l2(out, ref.numpy())
+        assert err <= TOL, (err, mask is None)
