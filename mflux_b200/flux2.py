@@ -13,7 +13,8 @@ modulation for all single blocks, LayerNorm without affine, q/k RMSNorm, rotary 
     single projection bit for bit;
   * `to_out` reads that buffer, so the reference's concatenate (parallel_self_attention.py:75) never happens, and
     applies the gated residual as its epilogue.
-The reference's KV cache for reference-image tokens (flux2_kv_cache.py) is outside this slice.
+The reference's KV cache for reference-image tokens (flux2_kv_cache.py) is `Flux2KVCache` below: nothing is
+concatenated for it, the attention kernels take keys / values longer than the queries (`ops.fmha_ex`).
 """
 from __future__ import annotations
 
@@ -45,6 +46,55 @@ class Flux2SingleTransformerBlock(nn.Module):
     def __init__(self, ctx, dim: int, heads: int, mlp_ratio: float = 3.0):
         super().__init__()
         self.attn = Flux2ParallelSelfAttention(ctx, dim, heads, mlp_ratio)
+
+
+class Flux2KVCache:
+    """Keys and values of the reference-image tokens, per layer (flux2_kv_cache.py:13-61 with the reference's method
+    and attribute names). One pass runs with the reference tokens at the end of the sequence ([text, target,
+    reference]) in mode "extract" and keeps their keys and values (after q/k norm and RoPE) for every layer; later
+    passes over [text, target] alone run in mode "cached" and attend to those keys and values as well."""
+
+    def __init__(self, num_double_layers: int, num_single_layers: int) -> None:
+        self._double = [None] * num_double_layers
+        self._single = [None] * num_single_layers
+        self.mode = None
+        self.num_ref_tokens = 0
+
+    def configure(self, *, mode: str, num_ref_tokens: int) -> None:
+        if mode not in ("extract", "cached"):
+            raise ValueError("mode is 'extract' or 'cached'")
+        self.mode, self.num_ref_tokens = mode, int(num_ref_tokens)
+
+    @property
+    def has_reference_tokens(self) -> bool:
+        return self.num_ref_tokens > 0
+
+    @property
+    def is_extracting(self) -> bool:
+        return self.mode == "extract" and self.has_reference_tokens
+
+    @property
+    def is_cached(self) -> bool:
+        return self.mode == "cached"
+
+    def _slots(self, stream: str):
+        if stream == "double":
+            return self._double
+        if stream == "single":
+            return self._single
+        raise ValueError(f"Unknown stream {stream!r}")
+
+    def store_reference(self, stream: str, layer_idx: int, key: torch.Tensor, value: torch.Tensor) -> None:
+        """key / value: [B, S, heads*128] views; the trailing num_ref_tokens rows are kept (copied)."""
+        if self.is_extracting:
+            r = self.num_ref_tokens
+            self._slots(stream)[layer_idx] = (key[:, -r:].clone(), value[:, -r:].clone())
+
+    def load(self, stream: str, layer_idx: int):
+        slot = self._slots(stream)[layer_idx]
+        if slot is None:
+            raise RuntimeError(f"KV cache slot for {stream} layer {layer_idx} is empty")
+        return slot
 
 
 class _SplitProjection:
@@ -105,17 +155,23 @@ class Flux2SingleStream(nn.Module):
             outs.append(torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1))
         return torch.cat(outs, dim=1).contiguous()
 
-    def forward(self, hidden_states: torch.Tensor, temb: torch.Tensor, cos_sin: torch.Tensor) -> torch.Tensor:
+    def forward(self, hidden_states: torch.Tensor, temb: torch.Tensor, cos_sin: torch.Tensor,
+                kv_cache: Flux2KVCache | None = None) -> torch.Tensor:
         """hidden_states [B, S, D] (float32 residual stream, updated in place and returned), temb [B, D],
-        cos_sin [S, 64, 2] on the device."""
+        cos_sin [S, 64, 2] on the device. With a `kv_cache` in mode "extract" the last num_ref_tokens rows are
+        reference-image tokens: their keys and values are kept per layer, they attend to themselves only and the
+        other rows to everything (Flux2KVCache.compute_extract_attention, flux2_kv_cache.py:63-99); in mode
+        "cached" the kept keys and values follow the sequence's own (append_reference, :51-61)."""
         b, s, d = hidden_states.shape
         dev = hidden_states.device
         a0 = self.single_transformer_blocks[0].attn
         inner, mlp = a0.inner_dim, a0.mlp_hidden_dim
-        key = (b, s, str(dev))
+        extra = kv_cache.num_ref_tokens if kv_cache is not None and kv_cache.is_cached else 0
+        key = (b, s, extra, str(dev))
         if self._buffers_for != key:
             self.nbuf = torch.empty(b, s, d, dtype=torch.bfloat16, device=dev)
-            self.qkv = torch.empty(b, s, 3 * inner, dtype=torch.bfloat16, device=dev)
+            # q | k | v of the sequence; in cached mode `extra` more rows whose k and v columns take the kept tokens
+            self.qkv = torch.empty(b, s + extra, 3 * inner, dtype=torch.bfloat16, device=dev)
             self.cat = torch.empty(b, s, inner + mlp, dtype=torch.bfloat16, device=dev)   # [attention | mlp]
             self._buffers_for = key
         xs = hidden_states if hidden_states.dtype == torch.float32 else hidden_states.float()
@@ -136,10 +192,25 @@ class Flux2SingleStream(nn.Module):
                         x1, x2 = y[..., 3 * inner:3 * inner + mlp], y[..., 3 * inner + mlp:]
                         mlp_out.copy_(torch.nn.functional.silu(x1.float()) * x2.float())
                 fused[i] = proj
-            proj(self.nbuf, self.qkv, self.cat[..., inner:])
-            ops.qknorm_rope(self.qkv, self.heads, a.norm_q.weight.data, a.norm_k.weight.data, a.norm_q.weight.data,
+            qkv = self.qkv[:, :s]
+            proj(self.nbuf, qkv, self.cat[..., inner:])
+            ops.qknorm_rope(qkv, self.heads, a.norm_q.weight.data, a.norm_k.weight.data, a.norm_q.weight.data,
                             a.norm_k.weight.data, 0, cos_sin, a.norm_q.eps)
-            ops.fmha(self.qkv, self.heads, out=self.cat[..., :inner])
+            q_all, k_all, v_all = qkv[..., :inner], qkv[..., inner:2 * inner], qkv[..., 2 * inner:]
+            if kv_cache is not None and kv_cache.is_extracting:
+                r = kv_cache.num_ref_tokens
+                kv_cache.store_reference("single", i, k_all, v_all)
+                ops.fmha_ex(q_all[:, :s - r], k_all, v_all, self.heads, out=self.cat[:, :s - r, :inner])
+                ops.fmha_ex(q_all[:, s - r:], k_all[:, s - r:], v_all[:, s - r:], self.heads,
+                            out=self.cat[:, s - r:, :inner])
+            elif extra:
+                ref_k, ref_v = kv_cache.load("single", i)
+                self.qkv[:, s:, inner:2 * inner].copy_(ref_k)
+                self.qkv[:, s:, 2 * inner:].copy_(ref_v)
+                ops.fmha_ex(q_all, self.qkv[..., inner:2 * inner], self.qkv[..., 2 * inner:], self.heads,
+                            out=self.cat[..., :inner])
+            else:
+                ops.fmha(qkv, self.heads, out=self.cat[..., :inner])
             if isinstance(a.to_out, nn.QuantizedLinear):
                 a.to_out(self.cat, epilogue="gate_residual", gate=gate, residual=xs, out=xs)
             else:

@@ -26,8 +26,11 @@ def rope_table(ids, axes_dim=(32, 32, 32, 32), theta=2000.0):
     return torch.cat(outs, dim=1)
 
 
-def forward(model, hidden_states, temb, cos_sin, collect=None):
-    """Joint hidden states [B, S, D] after all single blocks, float32."""
+def forward(model, hidden_states, temb, cos_sin, collect=None, kv_cache=None):
+    """Joint hidden states [B, S, D] after all single blocks, float32. `kv_cache` is a dict {"mode", "num_ref",
+    "store": {layer: (k, v)}} restating Flux2KVCache (flux2_kv_cache.py): "extract" keeps the keys / values of the
+    trailing num_ref tokens per layer, lets those tokens attend to themselves only and the others to everything
+    (:63-99); "cached" appends the kept keys / values to the sequence's own (:51-61)."""
     x = hidden_states.float().cpu()
     d, heads = model.dim, model.heads
     mod = lin(model.single_stream_modulation.linear, silu(temb.float().cpu()))
@@ -42,7 +45,17 @@ def forward(model, hidden_states, temb, cos_sin, collect=None):
         q = blocks.rms_norm(q, a.norm_q.weight.detach().float().cpu(), a.norm_q.eps)
         k = blocks.rms_norm(k, a.norm_k.weight.detach().float().cpu(), a.norm_k.eps)
         q, k = blocks.apply_rope(q, cs[None, None]), blocks.apply_rope(k, cs[None, None])
-        o = blocks.heads_last(blocks.sdpa(q, k, v))
+        if kv_cache is not None and kv_cache["mode"] == "extract" and kv_cache["num_ref"] > 0:
+            r = kv_cache["num_ref"]
+            kv_cache["store"][i] = (k[:, :, -r:], v[:, :, -r:])
+            o = torch.cat([blocks.sdpa(q[:, :, :-r], k, v), blocks.sdpa(q[:, :, -r:], k[:, :, -r:], v[:, :, -r:])],
+                          dim=2)
+            o = blocks.heads_last(o)
+        elif kv_cache is not None and kv_cache["mode"] == "cached":
+            rk, rv = kv_cache["store"][i]
+            o = blocks.heads_last(blocks.sdpa(q, torch.cat([k, rk], dim=2), torch.cat([v, rv], dim=2)))
+        else:
+            o = blocks.heads_last(blocks.sdpa(q, k, v))
         x1, x2 = proj[..., 3 * inner:3 * inner + mlp], proj[..., 3 * inner + mlp:]
         out = lin(a.to_out, torch.cat([o, silu(x1) * x2], dim=-1))
         x = x + gate * out
