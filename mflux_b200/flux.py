@@ -239,6 +239,7 @@ class Transformer(nn.Module):
         self.norm_out = AdaNorm(ctx, d, 2, bias=False)
         self.proj_out = ctx.linear(d, cfg.in_channels)
         self._fused = {}
+        self._text_stream = {}
         self._buffers_for = None
         self._rope = {}
         self.trace = None   # a dict here receives a copy of the residual stream after every block (parity tests)
@@ -326,29 +327,62 @@ class Transformer(nn.Module):
         _call(self.context_embedder, prompt_embeds.to(torch.bfloat16), out=x_txt)
         sv = self.conditioning(timestep, pooled_prompt_embeds, guidance)
 
+        # With few text rows (a handful of 256 x 256 tiles for 74 CTA pairs) the text stream's kernels run on a second
+        # CUDA stream beside the image stream's: between the two points where the streams meet (attention, block
+        # end) they share no data, and the text launches start on the SMs the image kernels leave idle. With many
+        # rows (the 16-image batch) both streams fill the GPU by themselves and stay on one CUDA stream.
+        main = torch.cuda.current_stream(dev)
+        side = None
+        if b * st <= 2048 and dev.type == "cuda":
+            side = self._text_stream.get(str(dev))
+            if side is None:
+                side = self._text_stream[str(dev)] = torch.cuda.Stream(device=dev)
+
+        def pair(img_fn, txt_fn):
+            if side is None:
+                img_fn()
+                txt_fn()
+                return
+            side.wait_stream(main)
+            img_fn()
+            with torch.cuda.stream(side):
+                txt_fn()
+            main.wait_stream(side)
+
         for i, blk in enumerate(self.transformer_blocks):
             a = blk.attn
             mod_i = _call(blk.norm1.linear, sv)            # [B, 6D]: shift, scale, gate (msa) | shift, scale, gate (mlp)
             mod_t = _call(blk.norm1_context.linear, sv)
-            ops.norm_modulate(x_img, mod_i[:, 0:d], mod_i[:, d:2 * d], out=n_img)
-            ops.norm_modulate(x_txt, mod_t[:, 0:d], mod_t[:, d:2 * d], out=n_txt)
-            self._fuse(("jq", i), [a.to_q, a.to_k, a.to_v])(n_img, qkv[:, st:])
-            self._fuse(("ja", i), [a.add_q_proj, a.add_k_proj, a.add_v_proj])(n_txt, qkv[:, :st])
+
+            def img_in():
+                ops.norm_modulate(x_img, mod_i[:, 0:d], mod_i[:, d:2 * d], out=n_img)
+                self._fuse(("jq", i), [a.to_q, a.to_k, a.to_v])(n_img, qkv[:, st:])
+
+            def txt_in():
+                ops.norm_modulate(x_txt, mod_t[:, 0:d], mod_t[:, d:2 * d], out=n_txt)
+                self._fuse(("ja", i), [a.add_q_proj, a.add_k_proj, a.add_v_proj])(n_txt, qkv[:, :st])
+
+            def img_out():
+                _call(a.to_out[0], attn[:, st:], epilogue="gate_residual", gate=mod_i[:, 2 * d:3 * d], residual=x_img,
+                      out=x_img)
+                ops.norm_modulate(x_img, mod_i[:, 3 * d:4 * d], mod_i[:, 4 * d:5 * d], out=n_img)
+                _call(blk.ff.linear1, n_img, epilogue="gelu", out=ffb[:, st:])
+                _call(blk.ff.linear2, ffb[:, st:], epilogue="gate_residual", gate=mod_i[:, 5 * d:6 * d],
+                      residual=x_img, out=x_img)
+
+            def txt_out():
+                _call(a.to_add_out, attn[:, :st], epilogue="gate_residual", gate=mod_t[:, 2 * d:3 * d], residual=x_txt,
+                      out=x_txt)
+                ops.norm_modulate(x_txt, mod_t[:, 3 * d:4 * d], mod_t[:, 4 * d:5 * d], out=n_txt)
+                _call(blk.ff_context.linear1, n_txt, epilogue="gelu_approx", out=ffb[:, :st])
+                _call(blk.ff_context.linear2, ffb[:, :st], epilogue="gate_residual", gate=mod_t[:, 5 * d:6 * d],
+                      residual=x_txt, out=x_txt)
+
+            pair(img_in, txt_in)
             ops.qknorm_rope(qkv, heads, a.norm_added_q.weight.data, a.norm_added_k.weight.data, a.norm_q.weight.data,
                             a.norm_k.weight.data, st, cos_sin, a.norm_q.eps)
             ops.fmha(qkv, heads, out=attn)
-            _call(a.to_out[0], attn[:, st:], epilogue="gate_residual", gate=mod_i[:, 2 * d:3 * d], residual=x_img,
-                  out=x_img)
-            _call(a.to_add_out, attn[:, :st], epilogue="gate_residual", gate=mod_t[:, 2 * d:3 * d], residual=x_txt,
-                  out=x_txt)
-            ops.norm_modulate(x_img, mod_i[:, 3 * d:4 * d], mod_i[:, 4 * d:5 * d], out=n_img)
-            ops.norm_modulate(x_txt, mod_t[:, 3 * d:4 * d], mod_t[:, 4 * d:5 * d], out=n_txt)
-            _call(blk.ff.linear1, n_img, epilogue="gelu", out=ffb[:, st:])
-            _call(blk.ff.linear2, ffb[:, st:], epilogue="gate_residual", gate=mod_i[:, 5 * d:6 * d], residual=x_img,
-                  out=x_img)
-            _call(blk.ff_context.linear1, n_txt, epilogue="gelu_approx", out=ffb[:, :st])
-            _call(blk.ff_context.linear2, ffb[:, :st], epilogue="gate_residual", gate=mod_t[:, 5 * d:6 * d],
-                  residual=x_txt, out=x_txt)
+            pair(img_out, txt_out)
             if self.trace is not None:
                 self.trace[f"joint{i}"] = xs.clone()
 
