@@ -276,9 +276,10 @@ __global__ void __launch_bounds__(NORM_THREADS) norm_gate_residual_kernel(const 
 }
 
 struct RopeParams {
-  __nv_bfloat16* qkv;  // [batch, seq, 3 * heads * 128]: q | k | v
+  __nv_bfloat16* qkv;  // [batch, seq, (heads + 2 * kv_heads) * 128]: q | k | v
   int64_t row_stride, batch_stride;
   int seq, batch, heads;
+  int kv_heads;             // heads of K (and V): equal to heads unless grouped-query attention
   int split;                // rows < split use the *_a norm weights (text stream), the rest *_b
   const void* qw_a;         // RMSNorm weights [128]
   const void* kw_a;
@@ -307,10 +308,11 @@ __global__ void __launch_bounds__(256) qknorm_rope_kernel(const RopeParams p) {
   const int which = lane >> 4, l = lane & 15;
   __nv_bfloat16* base = p.qkv + b * p.batch_stride + static_cast<int64_t>(s) * p.row_stride +
                         (which * p.heads + h0) * 128 + l * 8;
+  const int my_heads = which == 0 ? p.heads : p.kv_heads;   // the K half-warp idles on heads K does not have
   uint4 raw[ROPE_HEADS];
 #pragma unroll
   for (int i = 0; i < ROPE_HEADS; ++i)
-    if (h0 + i < p.heads) raw[i] = *reinterpret_cast<const uint4*>(base + i * 128);
+    raw[i] = h0 + i < my_heads ? *reinterpret_cast<const uint4*>(base + i * 128) : make_uint4(0, 0, 0, 0);
   const float4* csp = reinterpret_cast<const float4*>(p.cos_sin + (static_cast<int64_t>(s) * 64 + 4 * l) * 2);
   const float4 cs0 = __ldg(csp), cs1 = __ldg(csp + 1);
   const void* w = which == 0 ? (s < p.split ? p.qw_a : p.qw_b) : (s < p.split ? p.kw_a : p.kw_b);
@@ -340,8 +342,31 @@ __global__ void __launch_bounds__(256) qknorm_rope_kernel(const RopeParams p) {
     o[5] = cs1.y * x[4] + cs1.x * x[5];
     o[6] = cs1.z * x[6] - cs1.w * x[7];
     o[7] = cs1.w * x[6] + cs1.z * x[7];
-    store8_bf16(base + i * 128, o);
+    if (h0 + i < my_heads) store8_bf16(base + i * 128, o);
   }
+}
+
+// y[r, :] *= sigmoid(g[r, :]) on bf16 rows of D elements (8 per thread), rows addressed by (sample, row) strides.
+__global__ void __launch_bounds__(256) sigmoid_mul_kernel(__nv_bfloat16* y, int64_t y_row_stride, int64_t y_batch_stride,
+                                                          const __nv_bfloat16* g, int64_t g_row_stride,
+                                                          int64_t g_batch_stride, int rows, int batch, int D) {
+  const int vec_per_row = D / 8;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t total = static_cast<int64_t>(batch) * rows * vec_per_row;
+  if (idx >= total) return;
+  const int c = static_cast<int>(idx % vec_per_row) * 8;
+  const int64_t tok = idx / vec_per_row;
+  const int r = static_cast<int>(tok % rows);
+  const int b = static_cast<int>(tok / rows);
+  __nv_bfloat16* yp = y + b * y_batch_stride + static_cast<int64_t>(r) * y_row_stride + c;
+  const uint4 yv = *reinterpret_cast<const uint4*>(yp);
+  const uint4 gv = *reinterpret_cast<const uint4*>(g + b * g_batch_stride + static_cast<int64_t>(r) * g_row_stride + c);
+  const __nv_bfloat16* yh = reinterpret_cast<const __nv_bfloat16*>(&yv);
+  const __nv_bfloat16* gh = reinterpret_cast<const __nv_bfloat16*>(&gv);
+  float o[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o[j] = __bfloat162float(yh[j]) / (1.0f + __expf(-__bfloat162float(gh[j])));
+  store8_bf16(yp, o);
 }
 
 // out[i] = f(a[i] (+ b[i]) (+ c[i])), f = identity, SiLU or tanh; out dtype bf16 or f32.
@@ -485,15 +510,40 @@ int mfx_norm_modulate(const mfx_norm_args* a, void* stream) {
 int mfx_qknorm_rope(void* qkv, int64_t row_stride, int64_t batch_stride, int64_t seq, int64_t batch, int heads,
                     int64_t split, const void* qw_a, const void* kw_a, const void* qw_b, const void* kw_b,
                     int w_dtype, const float* cos_sin, float eps, void* stream) {
+  return mfx_qknorm_rope_gqa(qkv, row_stride, batch_stride, seq, batch, heads, heads, split, qw_a, kw_a, qw_b, kw_b,
+                             w_dtype, cos_sin, eps, stream);
+}
+
+int mfx_sigmoid_mul(void* y, int64_t y_row_stride, int64_t y_batch_stride, const void* gate, int64_t g_row_stride,
+                    int64_t g_batch_stride, int64_t rows, int64_t batch, int64_t D, void* stream) {
+  using namespace mfx;
+  if (!y || !gate) return MFX_ERR_NULL;
+  if (rows <= 0 || batch <= 0 || D <= 0 || D % 8 != 0) return MFX_ERR_SHAPE;
+  if (!aligned16(y) || !aligned16(gate) || y_row_stride % 8 != 0 || y_batch_stride % 8 != 0 || g_row_stride % 8 != 0 ||
+      g_batch_stride % 8 != 0)
+    return MFX_ERR_ALIGN;
+  if (rows > (1ll << 30) || batch > 65535) return MFX_ERR_TOO_LARGE;
+  if (int rc = check_arch()) return rc;
+  const int64_t total = rows * batch * (D / 8);
+  glue::sigmoid_mul_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(y), y_row_stride, y_batch_stride, static_cast<const __nv_bfloat16*>(gate),
+      g_row_stride, g_batch_stride, static_cast<int>(rows), static_cast<int>(batch), static_cast<int>(D));
+  MFX_CUDA_TRY(cudaGetLastError());
+  return MFX_OK;
+}
+
+int mfx_qknorm_rope_gqa(void* qkv, int64_t row_stride, int64_t batch_stride, int64_t seq, int64_t batch, int heads,
+                        int kv_heads, int64_t split, const void* qw_a, const void* kw_a, const void* qw_b,
+                        const void* kw_b, int w_dtype, const float* cos_sin, float eps, void* stream) {
   using namespace mfx;
   using namespace mfx::glue;
   if (!qkv || !qw_a || !kw_a || !qw_b || !kw_b || !cos_sin) return MFX_ERR_NULL;
-  if (seq <= 0 || batch <= 0 || heads <= 0 || split < 0) return MFX_ERR_SHAPE;
+  if (seq <= 0 || batch <= 0 || heads <= 0 || kv_heads <= 0 || kv_heads > heads || split < 0) return MFX_ERR_SHAPE;
   if (!valid_dtype(w_dtype)) return MFX_ERR_DTYPE;
   if (!aligned16(qkv) || row_stride % 8 != 0 || batch_stride % 8 != 0 || !aligned16(cos_sin) ||
       (w_dtype != MFX_F16 && (!aligned16(qw_a) || !aligned16(kw_a) || !aligned16(qw_b) || !aligned16(kw_b))))
     return MFX_ERR_ALIGN;
-  if (row_stride < 3ll * heads * 128) return MFX_ERR_SHAPE;
+  if (row_stride < (heads + 2ll * kv_heads) * 128) return MFX_ERR_SHAPE;
   if (int rc = check_arch()) return rc;
   RopeParams p;
   p.qkv = static_cast<__nv_bfloat16*>(qkv);
@@ -502,6 +552,7 @@ int mfx_qknorm_rope(void* qkv, int64_t row_stride, int64_t batch_stride, int64_t
   p.seq = static_cast<int>(seq);
   p.batch = static_cast<int>(batch);
   p.heads = heads;
+  p.kv_heads = kv_heads;
   p.split = static_cast<int>(split);
   p.qw_a = qw_a;
   p.kw_a = kw_a;

@@ -321,19 +321,21 @@ def norm_modulate(x: torch.Tensor, shift: torch.Tensor | None = None, scale: tor
 
 def qknorm_rope(qkv: torch.Tensor, heads: int, q_weight_a: torch.Tensor, k_weight_a: torch.Tensor,
                 q_weight_b: torch.Tensor, k_weight_b: torch.Tensor, split: int, cos_sin: torch.Tensor,
-                eps: float = 1e-5) -> torch.Tensor:
-    """In place on qkv [batch, seq, 3*heads*128] (bf16): per-head RMSNorm(128) of Q and K, then RoPE.
+                eps: float = 1e-5, kv_heads: int | None = None) -> torch.Tensor:
+    """In place on qkv [batch, seq, (heads + 2*kv_heads)*128] (bf16, q | k | v per token): per-head RMSNorm(128)
+    of Q and K, then RoPE. kv_heads defaults to heads.
 
     Rows s < split use the `_a` weights (text stream), the others the `_b` weights. cos_sin is f32
     [seq, 64, 2] holding (cos, sin) of every rotated (even, odd) pair.
     """
+    kv_heads = heads if kv_heads is None else kv_heads
     lib = _lib.load()
     _cuda(qkv, "qkv")
     if qkv.dtype != torch.bfloat16 or qkv.dim() != 3 or qkv.stride(-1) != 1:
         raise ValueError("qkv must be a bf16 [batch, seq, 3*heads*128] view with a dense last dim")
     batch, seq, width = qkv.shape
-    if width != 3 * heads * 128:
-        raise ValueError("last dim must be 3 * heads * 128")
+    if width != (heads + 2 * kv_heads) * 128:
+        raise ValueError("last dim must be (heads + 2 * kv_heads) * 128")
     ws = [w.contiguous() for w in (q_weight_a, k_weight_a, q_weight_b, k_weight_b)]
     if len({w.dtype for w in ws}) != 1 or any(w.numel() != 128 for w in ws):
         raise ValueError("norm weights must be four [128] tensors of one dtype")
@@ -342,9 +344,10 @@ def qknorm_rope(qkv: torch.Tensor, heads: int, q_weight_a: torch.Tensor, k_weigh
         raise ValueError("cos_sin must be f32 [seq, 64, 2]")
     if TRACE is not None:
         _trace_begin()
-    rc = lib.mfx_qknorm_rope(_ptr(qkv), qkv.stride(1), qkv.stride(0), seq, batch, heads, split, _ptr(ws[0]),
-                             _ptr(ws[1]), _ptr(ws[2]), _ptr(ws[3]), _dt(ws[0]), _ptr(cos_sin), eps, _stream())
-    _lib.check(rc, "mfx_qknorm_rope")
+    rc = lib.mfx_qknorm_rope_gqa(_ptr(qkv), qkv.stride(1), qkv.stride(0), seq, batch, heads, kv_heads, split,
+                                 _ptr(ws[0]), _ptr(ws[1]), _ptr(ws[2]), _ptr(ws[3]), _dt(ws[0]), _ptr(cos_sin), eps,
+                                 _stream())
+    _lib.check(rc, "mfx_qknorm_rope_gqa")
     if TRACE is not None:   # q and k sections read and written once
         _trace_end("glue", 0.0, float(2 * 2 * batch * seq * heads * 128 * 2))
     LAUNCHES[0] += 1
@@ -398,6 +401,22 @@ def fmha(qkv: torch.Tensor, heads: int, scale: float | None = None, out: torch.T
         _trace_end("fmha", 4.0 * batch * heads * seq * seq * 128, 0.0)
     LAUNCHES[0] += 1
     return out
+
+
+def sigmoid_mul(y: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """y *= sigmoid(gate) in place on bf16 [batch, rows, D] views (dense last dim, D a multiple of 8)."""
+    lib = _lib.load()
+    _cuda(y, "y")
+    _cuda(gate, "gate")
+    if y.dtype != torch.bfloat16 or gate.dtype != torch.bfloat16 or y.dim() != 3 or y.shape != gate.shape or \
+            y.stride(-1) != 1 or gate.stride(-1) != 1:
+        raise ValueError("y and gate must be bf16 [batch, rows, D] views of one shape with dense last dims")
+    batch, rows, d = y.shape
+    rc = lib.mfx_sigmoid_mul(_ptr(y), y.stride(1), y.stride(0), _ptr(gate), gate.stride(1), gate.stride(0), rows, batch,
+                             d, _stream())
+    _lib.check(rc, "mfx_sigmoid_mul")
+    LAUNCHES[0] += 1
+    return y
 
 
 def fmha_ex(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads: int, kv_heads: int | None = None,
