@@ -271,18 +271,25 @@ int mfx_qknorm_rope(void* qkv, int64_t row_stride, int64_t batch_stride, int64_t
                     int64_t split, const void* qw_a, const void* kw_a, const void* qw_b, const void* kw_b,
                     int w_dtype, const float* cos_sin, float eps, void* stream);
 
-/* The same with fewer key heads than query heads: the buffer holds q (heads) | k (kv_heads) | v (kv_heads) per
- * token. Replaces Krea2QKNorm + Krea2RopeEmbedder.apply_rope on the projections of Krea2Attention
- * (src/mflux/models/krea2/model/krea2_transformer/attention.py:25-35, common.py:19-28, rope_embedder.py:31-37: the
- * same rotation of (even, odd) pairs; the caller passes the norm weights as scale + 1, common.py:13-14). */
+/* The same with fewer key heads than query heads and a choice of rotary layout: the buffer holds q (heads) |
+ * k (kv_heads) | v (kv_heads) per token. Replaces Krea2QKNorm + Krea2RopeEmbedder.apply_rope on the projections of
+ * Krea2Attention (src/mflux/models/krea2/model/krea2_transformer/attention.py:25-35, common.py:19-28,
+ * rope_embedder.py:31-37: the same rotation of (even, odd) pairs, rope_mode 0; the caller passes the norm weights as
+ * scale + 1, common.py:13-14), and norm_q / norm_k + apply_rotary_emb of ErnieAttention
+ * (src/mflux/models/ernie_image/model/ernie_transformer/attention.py:42-46, rope_embedder.py:31-37), rope_mode 1:
+ * x * cos + (-x[64:], x[:64]) * sin, where element j of either half reads angle j / 2 of cos_sin[s] (the embedder
+ * stores every angle twice, rope_embedder.py:24-28). */
 int mfx_qknorm_rope_gqa(void* qkv, int64_t row_stride, int64_t batch_stride, int64_t seq, int64_t batch, int heads,
-                        int kv_heads, int64_t split, const void* qw_a, const void* kw_a, const void* qw_b,
-                        const void* kw_b, int w_dtype, const float* cos_sin, float eps, void* stream);
+                        int kv_heads, int rope_mode, int64_t split, const void* qw_a, const void* kw_a,
+                        const void* qw_b, const void* kw_b, int w_dtype, const float* cos_sin, float eps,
+                        void* stream);
 
-/* y[b, r, :] *= sigmoid(gate[b, r, :]) on bf16 rows of D elements (D a multiple of 8, strides in elements): the
- * output gate of Krea2Attention, `out * mx.sigmoid(gate)` in front of `wo` (krea2_transformer/attention.py:41). */
-int mfx_sigmoid_mul(void* y, int64_t y_row_stride, int64_t y_batch_stride, const void* gate, int64_t g_row_stride,
-                    int64_t g_batch_stride, int64_t rows, int64_t batch, int64_t D, void* stream);
+/* y[b, r, :] *= act(gate[b, r, :]) on bf16 rows of D elements (D a multiple of 8, strides in elements). act 0 =
+ * sigmoid: the output gate of Krea2Attention, `out * mx.sigmoid(gate)` in front of `wo`
+ * (krea2_transformer/attention.py:41); act 1 = GELU (erf): `up_proj(x) * nn.gelu(gate_proj(x))` of ErnieFeedForward
+ * (src/mflux/models/ernie_image/model/ernie_transformer/feed_forward.py:12-13). */
+int mfx_act_mul(void* y, int64_t y_row_stride, int64_t y_batch_stride, const void* gate, int64_t g_row_stride,
+                int64_t g_batch_stride, int64_t rows, int64_t batch, int64_t D, int act, void* stream);
 
 /* Replaces mx.fast.scaled_dot_product_attention(q, k, v, scale) without mask
  * (attention_utils.py:48-52) for head dimension 128: softmax(Q K^T * scale) V per (sample, head).

@@ -235,11 +235,11 @@ SIGNATURES = {
     ),
     "mfx_qknorm_rope_gqa": (
         c_int,
-        [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
-         c_int, c_void_p, ctypes.c_float, c_void_p],
+        [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p,
+         c_void_p, c_int, c_void_p, ctypes.c_float, c_void_p],
     ),
-    "mfx_sigmoid_mul": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
-                                c_void_p]),
+    "mfx_act_mul": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_int,
+                            c_void_p]),
     "mfx_fmha": (
         c_int,
         [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, ctypes.c_float, c_void_p, c_int64,

@@ -280,6 +280,7 @@ struct RopeParams {
   int64_t row_stride, batch_stride;
   int seq, batch, heads;
   int kv_heads;             // heads of K (and V): equal to heads unless grouped-query attention
+  int rope_mode;            // 0: rotate (even, odd) pairs; 1: pairs (j, j + 64), element j uses angle j / 2
   int split;                // rows < split use the *_a norm weights (text stream), the rest *_b
   const void* qw_a;         // RMSNorm weights [128]
   const void* kw_a;
@@ -334,22 +335,35 @@ __global__ void __launch_bounds__(256) qknorm_rope_kernel(const RopeParams p) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) x[j] = x[j] * r * wt[j];
     float o[8];
-    o[0] = cs0.x * x[0] - cs0.y * x[1];
-    o[1] = cs0.y * x[0] + cs0.x * x[1];
-    o[2] = cs0.z * x[2] - cs0.w * x[3];
-    o[3] = cs0.w * x[2] + cs0.z * x[3];
-    o[4] = cs1.x * x[4] - cs1.y * x[5];
-    o[5] = cs1.y * x[4] + cs1.x * x[5];
-    o[6] = cs1.z * x[6] - cs1.w * x[7];
-    o[7] = cs1.w * x[6] + cs1.z * x[7];
+    if (p.rope_mode == 0) {
+      o[0] = cs0.x * x[0] - cs0.y * x[1];
+      o[1] = cs0.y * x[0] + cs0.x * x[1];
+      o[2] = cs0.z * x[2] - cs0.w * x[3];
+      o[3] = cs0.w * x[2] + cs0.z * x[3];
+      o[4] = cs1.x * x[4] - cs1.y * x[5];
+      o[5] = cs1.y * x[4] + cs1.x * x[5];
+      o[6] = cs1.z * x[6] - cs1.w * x[7];
+      o[7] = cs1.w * x[6] + cs1.z * x[7];
+    } else {
+      // x * cos + rotate_half(x) * sin with rotate_half(x) = (-x[64:], x[:64]); the partner element sits 8 lanes
+      // away, and element j of either half reads the angle j / 2 (angles 4l .. 4l + 3 for this lane's 8 elements)
+      const float sgn = l < 8 ? -1.0f : 1.0f;
+      const float cc[4] = {cs0.x, cs0.z, cs1.x, cs1.z}, sn[4] = {cs0.y, cs0.w, cs1.y, cs1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float partner = __shfl_xor_sync(0xffffffffu, x[j], 8);
+        o[j] = x[j] * cc[j >> 1] + sgn * partner * sn[j >> 1];
+      }
+    }
     if (h0 + i < my_heads) store8_bf16(base + i * 128, o);
   }
 }
 
-// y[r, :] *= sigmoid(g[r, :]) on bf16 rows of D elements (8 per thread), rows addressed by (sample, row) strides.
-__global__ void __launch_bounds__(256) sigmoid_mul_kernel(__nv_bfloat16* y, int64_t y_row_stride, int64_t y_batch_stride,
+// y[r, :] *= act(g[r, :]) on bf16 rows of D elements (8 per thread), rows addressed by (sample, row) strides;
+// act 0 = sigmoid, 1 = GELU (erf).
+__global__ void __launch_bounds__(256) act_mul_kernel(__nv_bfloat16* y, int64_t y_row_stride, int64_t y_batch_stride,
                                                           const __nv_bfloat16* g, int64_t g_row_stride,
-                                                          int64_t g_batch_stride, int rows, int batch, int D) {
+                                                          int64_t g_batch_stride, int rows, int batch, int D, int act) {
   const int vec_per_row = D / 8;
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   const int64_t total = static_cast<int64_t>(batch) * rows * vec_per_row;
@@ -365,7 +379,11 @@ __global__ void __launch_bounds__(256) sigmoid_mul_kernel(__nv_bfloat16* y, int6
   const __nv_bfloat16* gh = reinterpret_cast<const __nv_bfloat16*>(&gv);
   float o[8];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) o[j] = __bfloat162float(yh[j]) / (1.0f + __expf(-__bfloat162float(gh[j])));
+  for (int j = 0; j < 8; ++j) {
+    const float gv_ = __bfloat162float(gh[j]);
+    const float f = act == 0 ? 1.0f / (1.0f + __expf(-gv_)) : 0.5f * gv_ * (1.0f + erff(gv_ * 0.70710678118654752f));
+    o[j] = __bfloat162float(yh[j]) * f;
+  }
   store8_bf16(yp, o);
 }
 
@@ -510,35 +528,37 @@ int mfx_norm_modulate(const mfx_norm_args* a, void* stream) {
 int mfx_qknorm_rope(void* qkv, int64_t row_stride, int64_t batch_stride, int64_t seq, int64_t batch, int heads,
                     int64_t split, const void* qw_a, const void* kw_a, const void* qw_b, const void* kw_b,
                     int w_dtype, const float* cos_sin, float eps, void* stream) {
-  return mfx_qknorm_rope_gqa(qkv, row_stride, batch_stride, seq, batch, heads, heads, split, qw_a, kw_a, qw_b, kw_b,
+  return mfx_qknorm_rope_gqa(qkv, row_stride, batch_stride, seq, batch, heads, heads, 0, split, qw_a, kw_a, qw_b, kw_b,
                              w_dtype, cos_sin, eps, stream);
 }
 
-int mfx_sigmoid_mul(void* y, int64_t y_row_stride, int64_t y_batch_stride, const void* gate, int64_t g_row_stride,
-                    int64_t g_batch_stride, int64_t rows, int64_t batch, int64_t D, void* stream) {
+int mfx_act_mul(void* y, int64_t y_row_stride, int64_t y_batch_stride, const void* gate, int64_t g_row_stride,
+                int64_t g_batch_stride, int64_t rows, int64_t batch, int64_t D, int act, void* stream) {
   using namespace mfx;
   if (!y || !gate) return MFX_ERR_NULL;
-  if (rows <= 0 || batch <= 0 || D <= 0 || D % 8 != 0) return MFX_ERR_SHAPE;
+  if (rows <= 0 || batch <= 0 || D <= 0 || D % 8 != 0 || act < 0 || act > 1) return MFX_ERR_SHAPE;
   if (!aligned16(y) || !aligned16(gate) || y_row_stride % 8 != 0 || y_batch_stride % 8 != 0 || g_row_stride % 8 != 0 ||
       g_batch_stride % 8 != 0)
     return MFX_ERR_ALIGN;
   if (rows > (1ll << 30) || batch > 65535) return MFX_ERR_TOO_LARGE;
   if (int rc = check_arch()) return rc;
   const int64_t total = rows * batch * (D / 8);
-  glue::sigmoid_mul_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  glue::act_mul_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<__nv_bfloat16*>(y), y_row_stride, y_batch_stride, static_cast<const __nv_bfloat16*>(gate),
-      g_row_stride, g_batch_stride, static_cast<int>(rows), static_cast<int>(batch), static_cast<int>(D));
+      g_row_stride, g_batch_stride, static_cast<int>(rows), static_cast<int>(batch), static_cast<int>(D), act);
   MFX_CUDA_TRY(cudaGetLastError());
   return MFX_OK;
 }
 
 int mfx_qknorm_rope_gqa(void* qkv, int64_t row_stride, int64_t batch_stride, int64_t seq, int64_t batch, int heads,
-                        int kv_heads, int64_t split, const void* qw_a, const void* kw_a, const void* qw_b,
+                        int kv_heads, int rope_mode, int64_t split, const void* qw_a, const void* kw_a, const void* qw_b,
                         const void* kw_b, int w_dtype, const float* cos_sin, float eps, void* stream) {
   using namespace mfx;
   using namespace mfx::glue;
   if (!qkv || !qw_a || !kw_a || !qw_b || !kw_b || !cos_sin) return MFX_ERR_NULL;
-  if (seq <= 0 || batch <= 0 || heads <= 0 || kv_heads <= 0 || kv_heads > heads || split < 0) return MFX_ERR_SHAPE;
+  if (seq <= 0 || batch <= 0 || heads <= 0 || kv_heads <= 0 || kv_heads > heads || split < 0 || rope_mode < 0 ||
+      rope_mode > 1)
+    return MFX_ERR_SHAPE;
   if (!valid_dtype(w_dtype)) return MFX_ERR_DTYPE;
   if (!aligned16(qkv) || row_stride % 8 != 0 || batch_stride % 8 != 0 || !aligned16(cos_sin) ||
       (w_dtype != MFX_F16 && (!aligned16(qw_a) || !aligned16(kw_a) || !aligned16(qw_b) || !aligned16(kw_b))))
@@ -553,6 +573,7 @@ int mfx_qknorm_rope_gqa(void* qkv, int64_t row_stride, int64_t batch_stride, int
   p.batch = static_cast<int>(batch);
   p.heads = heads;
   p.kv_heads = kv_heads;
+  p.rope_mode = rope_mode;
   p.split = static_cast<int>(split);
   p.qw_a = qw_a;
   p.kw_a = kw_a;

@@ -11,7 +11,7 @@ What runs where:
   * q/k RMSNorm + RoPE: `qknorm_rope` with fewer key heads than query heads, in place;
   * attention: `fmha_ex`, query head h reading key/value head h // (heads // kvheads): the reference's
     mx.repeat of K and V (attention.py:36-39) never happens;
-  * `out * sigmoid(gate)`: `sigmoid_mul` in place;
+  * `out * sigmoid(gate)`: `act_mul` in place;
   * wo and mlp.down: quantized matmuls with the gated residual as their epilogue (x + gate * y);
   * mlp.gate | mlp.up: one quantized matmul with the SwiGLU epilogue.
 """
@@ -151,7 +151,7 @@ class Krea2SingleStream(nn.Module):
             qw, kw = a.qknorm.qnorm.weight(), a.qknorm.knorm.weight()
             ops.qknorm_rope(qkv, h, qw, kw, qw, kw, 0, cos_sin, a.qknorm.qnorm.eps, kv_heads=hk)
             ops.fmha_ex(qkv[..., :wq], qkv[..., wq:wq + wkv], qkv[..., wq + wkv:], h, hk, out=self.abuf)
-            ops.sigmoid_mul(self.abuf, self.proj[..., wq + 2 * wkv:])
+            ops.act_mul(self.abuf, self.proj[..., wq + 2 * wkv:], "sigmoid")
             _call(a.wo, self.abuf, epilogue="gate_residual", gate=pregate, residual=xs, out=xs)
             ops.norm_modulate(xs, postshift, postscale, weight=blk.postnorm.weight(), eps=blk.postnorm.eps, rms=True,
                               out=self.nbuf)

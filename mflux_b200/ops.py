@@ -321,14 +321,18 @@ def norm_modulate(x: torch.Tensor, shift: torch.Tensor | None = None, scale: tor
 
 def qknorm_rope(qkv: torch.Tensor, heads: int, q_weight_a: torch.Tensor, k_weight_a: torch.Tensor,
                 q_weight_b: torch.Tensor, k_weight_b: torch.Tensor, split: int, cos_sin: torch.Tensor,
-                eps: float = 1e-5, kv_heads: int | None = None) -> torch.Tensor:
+                eps: float = 1e-5, kv_heads: int | None = None, rope_mode: str = "pairs") -> torch.Tensor:
     """In place on qkv [batch, seq, (heads + 2*kv_heads)*128] (bf16, q | k | v per token): per-head RMSNorm(128)
     of Q and K, then RoPE. kv_heads defaults to heads.
 
     Rows s < split use the `_a` weights (text stream), the others the `_b` weights. cos_sin is f32
-    [seq, 64, 2] holding (cos, sin) of every rotated (even, odd) pair.
+    [seq, 64, 2] holding (cos, sin) of 64 angles per token: rope_mode "pairs" rotates the (even, odd) pair i by
+    angle i; "halves" computes x * cos + (-x[64:], x[:64]) * sin with element j of either half reading angle j // 2
+    (ernie_transformer/rope_embedder.py:24-37).
     """
     kv_heads = heads if kv_heads is None else kv_heads
+    if rope_mode not in ("pairs", "halves"):
+        raise ValueError("rope_mode is 'pairs' or 'halves'")
     lib = _lib.load()
     _cuda(qkv, "qkv")
     if qkv.dtype != torch.bfloat16 or qkv.dim() != 3 or qkv.stride(-1) != 1:
@@ -344,7 +348,8 @@ def qknorm_rope(qkv: torch.Tensor, heads: int, q_weight_a: torch.Tensor, k_weigh
         raise ValueError("cos_sin must be f32 [seq, 64, 2]")
     if TRACE is not None:
         _trace_begin()
-    rc = lib.mfx_qknorm_rope_gqa(_ptr(qkv), qkv.stride(1), qkv.stride(0), seq, batch, heads, kv_heads, split,
+    rc = lib.mfx_qknorm_rope_gqa(_ptr(qkv), qkv.stride(1), qkv.stride(0), seq, batch, heads, kv_heads,
+                                 1 if rope_mode == "halves" else 0, split,
                                  _ptr(ws[0]), _ptr(ws[1]), _ptr(ws[2]), _ptr(ws[3]), _dt(ws[0]), _ptr(cos_sin), eps,
                                  _stream())
     _lib.check(rc, "mfx_qknorm_rope_gqa")
@@ -403,8 +408,11 @@ def fmha(qkv: torch.Tensor, heads: int, scale: float | None = None, out: torch.T
     return out
 
 
-def sigmoid_mul(y: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
-    """y *= sigmoid(gate) in place on bf16 [batch, rows, D] views (dense last dim, D a multiple of 8)."""
+def act_mul(y: torch.Tensor, gate: torch.Tensor, act: str = "sigmoid") -> torch.Tensor:
+    """y *= act(gate) in place on bf16 [batch, rows, D] views (dense last dim, D a multiple of 8); act is "sigmoid"
+    or "gelu" (erf)."""
+    if act not in ("sigmoid", "gelu"):
+        raise ValueError("act is 'sigmoid' or 'gelu'")
     lib = _lib.load()
     _cuda(y, "y")
     _cuda(gate, "gate")
@@ -412,9 +420,9 @@ def sigmoid_mul(y: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
             y.stride(-1) != 1 or gate.stride(-1) != 1:
         raise ValueError("y and gate must be bf16 [batch, rows, D] views of one shape with dense last dims")
     batch, rows, d = y.shape
-    rc = lib.mfx_sigmoid_mul(_ptr(y), y.stride(1), y.stride(0), _ptr(gate), gate.stride(1), gate.stride(0), rows, batch,
-                             d, _stream())
-    _lib.check(rc, "mfx_sigmoid_mul")
+    rc = lib.mfx_act_mul(_ptr(y), y.stride(1), y.stride(0), _ptr(gate), gate.stride(1), gate.stride(0), rows, batch, d,
+                         0 if act == "sigmoid" else 1, _stream())
+    _lib.check(rc, "mfx_act_mul")
     LAUNCHES[0] += 1
     return y
 

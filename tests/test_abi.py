@@ -150,11 +150,13 @@ def test_validation_of_the_later_entry_points(lib_built):
     assert lib.mfx_cfg_combine(1024, 1024, _lib.BF16, 3.0, 0, 1024, 4, 2048, None) == -1  # more channels than a warp holds
     assert lib.mfx_fmha(1024, 1024, 1024, 384, 0, 0, 1, 1, 1.0, 1024, 128, 0, None) == -1
     assert lib.mfx_fmha(1024, 1024, 1028, 384, 0, 16, 1, 1, 1.0, 1024, 128, 0, None) == -2
-    assert lib.mfx_qknorm_rope_gqa(1024, 1024, 0, 4, 1, 4, 8, 0, 1024, 1024, 1024, 1024, _lib.F32, 1024, 1e-5, None) == -1
-    assert lib.mfx_qknorm_rope_gqa(1024, 512, 0, 4, 1, 4, 2, 0, 1024, 1024, 1024, 1024, _lib.F32, 1024, 1e-5, None) == -1
-    assert lib.mfx_sigmoid_mul(1024, 256, 0, 1024, 256, 0, 4, 1, 100, None) == -1     # D not a multiple of 8
-    assert lib.mfx_sigmoid_mul(1024, 250, 0, 1024, 256, 0, 4, 1, 128, None) == -2
-    assert lib.mfx_sigmoid_mul(None, 256, 0, 1024, 256, 0, 4, 1, 128, None) == -7
+    assert lib.mfx_qknorm_rope_gqa(1024, 1024, 0, 4, 1, 4, 8, 0, 0, 1024, 1024, 1024, 1024, _lib.F32, 1024, 1e-5, None) == -1
+    assert lib.mfx_qknorm_rope_gqa(1024, 512, 0, 4, 1, 4, 2, 0, 0, 1024, 1024, 1024, 1024, _lib.F32, 1024, 1e-5, None) == -1
+    assert lib.mfx_act_mul(1024, 256, 0, 1024, 256, 0, 4, 1, 100, 0, None) == -1     # D not a multiple of 8
+    assert lib.mfx_act_mul(1024, 250, 0, 1024, 256, 0, 4, 1, 128, 0, None) == -2
+    assert lib.mfx_act_mul(None, 256, 0, 1024, 256, 0, 4, 1, 128, 0, None) == -7
+    assert lib.mfx_act_mul(1024, 256, 0, 1024, 256, 0, 4, 1, 128, 2, None) == -1    # unknown activation
+    assert lib.mfx_qknorm_rope_gqa(1024, 1024, 0, 4, 1, 4, 2, 2, 0, 1024, 1024, 1024, 1024, _lib.F32, 1024, 1e-5, None) == -1
     assert lib.mfx_fmha_ex(None, None) == -7
     f = _lib.FmhaArgs()
     f.q = f.k = f.v = f.out = 1024

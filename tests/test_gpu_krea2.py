@@ -43,7 +43,7 @@ def test_krea2_blocks_match_oracle(lib_built, bits, heads, kvheads):
         assert rel_l2(model.trace[k], v.numpy()) <= TOL, k
 
 
-def test_qknorm_rope_with_fewer_key_heads_and_sigmoid_mul(lib_built):
+def test_qknorm_rope_with_fewer_key_heads_and_act_mul(lib_built):
     """The two glue kernels the block adds: q/k RMSNorm + RoPE on a q (4 heads) | k (2) | v (2) buffer, V and the
     columns behind it untouched; y *= sigmoid(gate) on strided views."""
     from mflux_b200 import ops
@@ -68,5 +68,5 @@ def test_qknorm_rope_with_fewer_key_heads_and_sigmoid_mul(lib_built):
     y = torch.randn(b, s, 256, generator=g).to(torch.bfloat16)
     gate = torch.randn(b, s, 512, generator=g).to(torch.bfloat16)
     yd = y.cuda()
-    ops.sigmoid_mul(yd, gate.cuda()[..., 256:])
+    ops.act_mul(yd, gate.cuda()[..., 256:], "sigmoid")
     assert rel_l2(yd, (y.float() * torch.sigmoid(gate[..., 256:].float())).numpy()) <= 5e-3
