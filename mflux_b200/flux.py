@@ -333,7 +333,7 @@ class Transformer(nn.Module):
         # rows (the 16-image batch) both streams fill the GPU by themselves and stay on one CUDA stream.
         main = torch.cuda.current_stream(dev)
         side = None
-        if b * st <= 2048 and dev.type == "cuda":
+        if b * st <= 2048 and dev.type == "cuda" and ops.TRACE is None:   # per-launch timing: one stream
             side = self._text_stream.get(str(dev))
             if side is None:
                 side = self._text_stream[str(dev)] = torch.cuda.Stream(device=dev)

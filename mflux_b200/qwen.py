@@ -289,7 +289,7 @@ class QwenTransformer(nn.Module):
         # all-reduce path keeps everything on one stream (its chunked collectives have their own).
         main = torch.cuda.current_stream(dev)
         side = None
-        if self.tp_world == 1:
+        if self.tp_world == 1 and ops.TRACE is None:   # per-launch timing wants the launches one after the other
             side = self._text_stream.get(str(dev))
             if side is None:
                 side = self._text_stream[str(dev)] = torch.cuda.Stream(device=dev)
@@ -402,14 +402,24 @@ def _forward_peer(self, hidden_states, encoder_hidden_states, timestep, height, 
     if side is None:
         side = self._text_stream[str(dev)] = torch.cuda.Stream(device=dev)
 
+    two_streams = ops.TRACE is None   # per-launch timing wants the launches one after the other
+
     def fork():
         """The second stream continues from what the main stream has queued so far. Called BEFORE the image
         matmul is launched, so that the text matmul launched after it does not wait for its end."""
-        side.wait_stream(main)
+        if two_streams:
+            side.wait_stream(main)
 
     def on_side(fn):
+        if not two_streams:
+            fn()
+            return
         with torch.cuda.stream(side):
             fn()
+
+    def join():
+        if two_streams:
+            main.wait_stream(side)
 
     def scattered(layer, x, row_offset, lane=0):
         ops.qlinear(x, layer.weight.data, None, None, None, bits=layer.bits, prepared=layer.prepared(),
@@ -439,7 +449,7 @@ def _forward_peer(self, hidden_states, encoder_hidden_states, timestep, height, 
         rest = [(fn, x, out, lo_, hi_, text) for fn, a_, b_, x, out, text in jobs
                 for lo_, hi_ in ((a_, min(b_, own_lo)), (max(a_, own_hi), b_)) if lo_ < hi_]
         run(rest)
-        main.wait_stream(side)
+        join()
 
     ex.begin()
     blocks = list(self.transformer_blocks)
@@ -455,7 +465,7 @@ def _forward_peer(self, hidden_states, encoder_hidden_states, timestep, height, 
         fork()
         scattered(a.attn_to_out[0], attn[:, st:s], st)
         on_side(lambda: scattered(a.to_add_out, attn[:, :st], 0, 1))
-        main.wait_stream(side)
+        join()
         ex.fuse(reduce=True, bias=(a.to_add_out.bias, a.attn_to_out[0].bias), gate=(ch(mt, 2), ch(mi, 2)),
                 shift=(ch(mt, 3), ch(mi, 3)), scale=(ch(mt, 4), ch(mi, 4)))
         gathered([(lambda x, o, l=blk.img_ff.mlp_in: _call(l, x, epilogue="gelu_approx", out=o), st, s, nbuf, ffb, False),
@@ -463,7 +473,7 @@ def _forward_peer(self, hidden_states, encoder_hidden_states, timestep, height, 
         fork()
         scattered(blk.img_ff.mlp_out, ffb[:, st:s], st)
         on_side(lambda: scattered(blk.txt_ff.mlp_out, ffb[:, :st], 0, 1))
-        main.wait_stream(side)
+        join()
         gate = (ch(mt, 5), ch(mi, 5))
         bias = (blk.txt_ff.mlp_out.bias, blk.img_ff.mlp_out.bias)
         if i + 1 < len(blocks):
