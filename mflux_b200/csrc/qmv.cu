@@ -212,14 +212,15 @@ int run(const mfx_qlinear_args& a, const void* prepared, size_t codes_bytes, cud
   p.y = a.y;
   p.y_dtype = a.y_dtype;
   p.y_row_stride = a.y_row_stride;
-  // 32 rows per block while that still gives every SM two blocks, else 8 rows per block
-  const bool wide = (a.N + 31) / 32 >= 2 * device_sm_count();
-  const unsigned blocks = static_cast<unsigned>(wide ? (a.N + 31) / 32 : (a.N + 7) / 8);
+  // 16 rows per block while that still gives every SM two blocks, else 8 rows per block (32 rows per block take 100
+  // registers and leave two blocks per SM: 10-25 % slower on 9216 to 18432 rows)
+  const bool wide = (a.N + 15) / 16 >= 2 * device_sm_count();
+  const unsigned blocks = static_cast<unsigned>(wide ? (a.N + 15) / 16 : (a.N + 7) / 8);
   if (kernel_bits(a.bits) == 4) {
-    if (wide) qmv_kernel<4, 4><<<blocks, THREADS, 0, st>>>(p);
+    if (wide) qmv_kernel<4, 2><<<blocks, THREADS, 0, st>>>(p);
     else qmv_kernel<4, 1><<<blocks, THREADS, 0, st>>>(p);
   } else {
-    if (wide) qmv_kernel<8, 4><<<blocks, THREADS, 0, st>>>(p);
+    if (wide) qmv_kernel<8, 2><<<blocks, THREADS, 0, st>>>(p);
     else qmv_kernel<8, 1><<<blocks, THREADS, 0, st>>>(p);
   }
   MFX_CUDA_TRY(cudaGetLastError());
