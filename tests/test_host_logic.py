@@ -346,3 +346,69 @@ def test_weight_updates_invalidate_derived_caches():
     nn.fused_cache(o)["k"] = "blob"
     nn.quantize(torch.nn.Sequential(), class_predicate=lambda p, mod: False)
     assert nn.fused_cache(o) == {}
+
+
+def test_flux2_kv_cache_modes_and_slots():
+    """Flux2KVCache (flux2_kv_cache.py:13-61): only an extracting cache with reference tokens stores; the stored
+    rows are the trailing num_ref_tokens of the layer's keys / values; an empty slot raises when it is read."""
+    import pytest
+    import torch
+
+    from mflux_b200.flux2 import Flux2KVCache
+
+    cache = Flux2KVCache(num_double_layers=2, num_single_layers=3)
+    assert not cache.has_reference_tokens and not cache.is_extracting and not cache.is_cached
+    k, v = torch.arange(2 * 10 * 4.0).reshape(2, 10, 4), -torch.arange(2 * 10 * 4.0).reshape(2, 10, 4)
+    cache.store_reference("single", 1, k, v)           # not configured: nothing is kept
+    with pytest.raises(RuntimeError):
+        cache.load("single", 1)
+    cache.configure(mode="extract", num_ref_tokens=0)   # extracting needs reference tokens
+    assert not cache.is_extracting
+    cache.configure(mode="extract", num_ref_tokens=3)
+    assert cache.is_extracting and not cache.is_cached
+    cache.store_reference("single", 1, k, v)
+    cache.store_reference("double", 0, k, v)
+    rk, rv = cache.load("single", 1)
+    assert torch.equal(rk, k[:, -3:]) and torch.equal(rv, v[:, -3:])
+    k += 1.0                                            # the cache holds copies
+    assert torch.equal(rk, (k - 1.0)[:, -3:])
+    cache.configure(mode="cached", num_ref_tokens=3)
+    assert cache.is_cached and not cache.is_extracting
+    cache.store_reference("single", 2, k, v)            # cached mode does not store
+    with pytest.raises(RuntimeError):
+        cache.load("single", 2)
+    with pytest.raises(ValueError):
+        cache.load("triple", 0)
+    with pytest.raises(ValueError):
+        cache.configure(mode="other", num_ref_tokens=1)
+
+
+def test_oracle_rotary_layouts_agree_on_what_they_share():
+    """The two rotary layouts of the q/k norm + RoPE kernel, restated: rotating (even, odd) pairs (FLUX, Krea-2) and
+    x * cos + rotate_half(x) * sin with every angle stored twice (ERNIE). Both preserve the norm of a pair they
+    rotate by one angle; the ERNIE layout pairs element j with j + 64 and reads angle j // 2 for either."""
+    import torch
+
+    from oracle import blocks
+    from oracle import ernie as oe
+
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(1, 5, 2, 128, generator=g)
+    ids = torch.stack([torch.arange(5.0), torch.arange(5.0) * 2, torch.arange(5.0) % 3], dim=1)
+    cos, sin = oe.rope_cos_sin(ids)
+    assert cos.shape == (5, 128) and torch.equal(cos[:, 0::2], cos[:, 1::2])     # every angle twice
+    y = oe.apply_rotary_emb(x, cos, sin)
+    j = 10
+    want_lo = x[..., j] * cos[:, j][None, :, None] - x[..., j + 64] * sin[:, j][None, :, None]
+    want_hi = x[..., j + 64] * cos[:, j + 64][None, :, None] + x[..., j] * sin[:, j + 64][None, :, None]
+    torch.testing.assert_close(y[..., j], want_lo)
+    torch.testing.assert_close(y[..., j + 64], want_hi)
+    # position 0 has angle 0 everywhere: both layouts leave the row unchanged there
+    torch.testing.assert_close(y[:, 0], x[:, 0])
+    cs = torch.stack([cos[:, 0::2], sin[:, 0::2]], dim=-1)
+    z = blocks.apply_rope(x.permute(0, 2, 1, 3), cs[None, None])
+    torch.testing.assert_close(z[:, :, 0], x.permute(0, 2, 1, 3)[:, :, 0])
+    # the pair layout is a true rotation: it keeps the norm of every (even, odd) pair (up to the bf16 rounding of the table)
+    n_in = (x.permute(0, 2, 1, 3)[..., 0::2] ** 2 + x.permute(0, 2, 1, 3)[..., 1::2] ** 2)
+    n_out = (z[..., 0::2] ** 2 + z[..., 1::2] ** 2)
+    torch.testing.assert_close(n_out, n_in, rtol=2e-2, atol=1e-3)
