@@ -554,6 +554,10 @@ def main():
 
     import math
 
+    # The few NCCL collectives of a step (one all-gather per pass) do not need the in-switch reduction, and every
+    # number of the tensor-parallel path was measured with it off; a caller's own setting wins.
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+
     import torch
     import torch.distributed as dist
 
