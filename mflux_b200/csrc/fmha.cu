@@ -1,9 +1,14 @@
 // Non-causal flash attention for head dimension 128 on tcgen05 (sm_100a).
 //
 // Replaces mx.fast.scaled_dot_product_attention(q, k, v, scale) as called by the reference's
-// AttentionUtils.compute_attention (src/mflux/models/flux/model/flux_transformer/common/attention_utils.py:48-52).
+// AttentionUtils.compute_attention (src/mflux/models/flux/model/flux_transformer/common/attention_utils.py:48-52),
+// optionally with a per-key additive bias, keys / values of their own length and fewer key / value heads than
+// query heads (the entry points at the end of the file say which reference call each shape replaces).
 //
-// One CTA = one (sample, head, 128-query tile); two CTAs share an SM. Keys go in tiles of 64 and the score tile
+// Two kernels, chosen per call by use_pingpong(): sdpa_pair_kernel (this comment) and sdpa_pingpong_kernel (namespace
+// pp below: two query tiles per CTA, one CTA per SM, for long sequences on grids that fill their last wave).
+//
+// sdpa_pair_kernel: one CTA = one (sample, head, 128-query tile); two CTAs share an SM. Keys go in tiles of 64 and the score tile
 // S is double-buffered in tensor memory, so S of tile j+1 is computed while the softmax of tile j runs and the
 // softmax warps never wait for a matmul in steady state. 384 threads:
 //   warp 0     TMA producer: Q once, then K tiles of 64 keys into two stages (128-byte swizzle, two 64-wide
